@@ -1,0 +1,78 @@
+// Shared helpers for the engine's CUDA kernels (sm_100a).
+//
+// Every launcher is an `extern "C"` function that takes raw device pointers,
+// sizes and a stream, and returns 0 on success, a positive cudaError_t when the
+// launch failed, or a negative TIB_E_* code when it refuses its arguments.
+// A refused size is an error, never a wrong result.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TIB_API extern "C" __attribute__((visibility("default")))
+
+// Element types of activations, weights and cache pages.
+enum TibDtype : int { TIB_F32 = 0, TIB_BF16 = 1 };
+
+// Argument errors (negative so they cannot collide with cudaError_t).
+enum TibError : int {
+  TIB_OK = 0,
+  TIB_E_DTYPE = -1,      // unknown dtype code
+  TIB_E_SIZE = -2,       // a size the kernel does not take
+  TIB_E_ALIGN = -3,      // a pointer or stride that is not aligned as required
+  TIB_E_SMEM = -4,       // needs more shared memory than an SM offers
+  TIB_E_ARG = -5,        // null pointer or inconsistent arguments
+};
+
+#define TIB_LAUNCH_CHECK()                         \
+  do {                                             \
+    cudaError_t e__ = cudaGetLastError();          \
+    if (e__ != cudaSuccess) return (int)e__;       \
+  } while (0)
+
+namespace tib {
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` holds at least 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+}  // namespace tib

@@ -1,0 +1,216 @@
+// Embedding lookup, RMSNorm (plain and fused with the residual add), SwiGLU and casts.
+//
+// The residual stream is held in 32-bit whatever the activation type: the
+// embedding writes it, every fused add+norm updates it in place, and the
+// normalised rows leave in the activation type T (float or bf16).
+//
+// Formulas (file:line in the reference project):
+//   RMSNorm      y = x * rsqrt(mean(x^2) + eps) * w, all in fp32
+//                src/torchinferno/kernels/triton_ops.py:2044-2048
+//   add + norm   h = x + residual (fp32), n = rmsnorm(h)
+//                src/torchinferno/kernels/triton_ops.py:2088-2096
+//   SwiGLU       gate / (1 + exp(-gate)) * up, gate in fp32
+//                src/torchinferno/kernels/triton_ops.py:29-32
+#include "common.cuh"
+
+namespace tib {
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ out, int hidden, int vocab) {
+  const int row = blockIdx.x;
+  const int id = ids[row];
+  float* dst = out + (size_t)row * hidden;
+  if (id < 0 || id >= vocab) {  // an id outside the table must show, not alias a row
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = __int_as_float(0x7fc00000);
+    return;
+  }
+  const T* src = table + (size_t)id * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]);
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One block per output row.  delta == nullptr: plain norm of residual[row].
+// rows != nullptr: output row i reads source row rows[i] and the residual is
+// left untouched (used to norm only the rows whose logits are wanted).
+template <typename T>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restrict__ residual,
+                                   const int* __restrict__ rows, const float* __restrict__ weight,
+                                   T* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int orow = blockIdx.x;
+  const int srow = rows ? rows[orow] : orow;
+  float* res = residual + (size_t)srow * hidden;
+  const T* dl = delta ? delta + (size_t)srow * hidden : nullptr;
+  const bool write_back = (delta != nullptr) && (rows == nullptr);
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float h = res[c];
+    if (dl) h += to_f32(dl[c]);
+    if (write_back) res[c] = h;
+    ss += h * h;
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = rsqrtf(total / (float)hidden + eps);
+  T* dst = out + (size_t)orow * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float h = res[c];
+    if (dl && !write_back) h += to_f32(dl[c]);
+    dst[c] = from_f32<T>(h * inv * weight[c]);
+  }
+}
+
+// Plain RMSNorm of rows held in type T (for parts that norm something other
+// than the residual stream, e.g. per-head norms).
+template <typename T>
+__global__ void rmsnorm_t_kernel(const T* __restrict__ x, const float* __restrict__ weight,
+                                 T* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[33];
+  const T* src = x + (size_t)blockIdx.x * hidden;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float h = to_f32(src[c]);
+    ss += h * h;
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = rsqrtf(total / (float)hidden + eps);
+  T* dst = out + (size_t)blockIdx.x * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+    dst[c] = from_f32<T>(to_f32(src[c]) * inv * weight[c]);
+}
+
+// ------------------------------------------------------------------- SwiGLU
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter,
+                              int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / inter;
+    const int col = (int)(i - row * inter);
+    const T* src = gate_up + row * 2 * (int64_t)inter;
+    const float g = to_f32(src[col]);
+    const float u = to_f32(src[inter + col]);
+    out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+template <typename A, typename B>
+__global__ void cast_kernel(const A* __restrict__ in, B* __restrict__ out, int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<B>(to_f32(in[i]));
+}
+
+__global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ index,
+                                   const int* __restrict__ value, int n, int64_t dst_size) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const int64_t at = index[i];
+    if (at >= 0 && at < dst_size) dst[at] = value[i];
+  }
+}
+
+static inline int norm_threads(int hidden) {
+  int t = ((hidden + 3) / 4 + 31) / 32 * 32;  // about four elements a thread
+  if (t < 32) t = 32;
+  if (t > 1024) t = 1024;
+  return t;
+}
+
+}  // namespace tib
+
+using namespace tib;
+
+TIB_API int tib_embedding(const int* ids, const void* table, float* out, int n_tokens, int hidden,
+                          int vocab, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return TIB_OK;
+  if (!ids || !table || !out || n_tokens < 0 || hidden < 1 || vocab < 1) return TIB_E_ARG;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == TIB_F32)
+    embedding_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+  else if (dtype == TIB_BF16)
+    embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+  else
+    return TIB_E_DTYPE;
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}
+
+// delta may be null (plain norm of the residual); rows may be null (all rows in order).
+TIB_API int tib_add_rmsnorm(const void* delta, float* residual, const int* rows, const float* weight,
+                            void* out, int n_out, int hidden, float eps, int dtype,
+                            cudaStream_t stream) {
+  if (n_out == 0) return TIB_OK;
+  if (!residual || !weight || !out || n_out < 0 || hidden < 1) return TIB_E_ARG;
+  const int threads = norm_threads(hidden);
+  if (dtype == TIB_F32)
+    add_rmsnorm_kernel<float><<<n_out, threads, 0, stream>>>((const float*)delta, residual, rows, weight, (float*)out, hidden, eps);
+  else if (dtype == TIB_BF16)
+    add_rmsnorm_kernel<__nv_bfloat16><<<n_out, threads, 0, stream>>>((const __nv_bfloat16*)delta, residual, rows, weight, (__nv_bfloat16*)out, hidden, eps);
+  else
+    return TIB_E_DTYPE;
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}
+
+TIB_API int tib_rmsnorm(const void* x, const float* weight, void* out, int n_rows, int hidden,
+                        float eps, int dtype, cudaStream_t stream) {
+  if (n_rows == 0) return TIB_OK;
+  if (!x || !weight || !out || n_rows < 0 || hidden < 1) return TIB_E_ARG;
+  const int threads = norm_threads(hidden);
+  if (dtype == TIB_F32)
+    rmsnorm_t_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)x, weight, (float*)out, hidden, eps);
+  else if (dtype == TIB_BF16)
+    rmsnorm_t_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>((const __nv_bfloat16*)x, weight, (__nv_bfloat16*)out, hidden, eps);
+  else
+    return TIB_E_DTYPE;
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}
+
+TIB_API int tib_swiglu(const void* gate_up, void* out, int n_rows, int inter, int dtype,
+                       cudaStream_t stream) {
+  const int64_t total = (int64_t)n_rows * inter;
+  if (total == 0) return TIB_OK;
+  if (!gate_up || !out || n_rows < 0 || inter < 1) return TIB_E_ARG;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == TIB_F32)
+    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+  else if (dtype == TIB_BF16)
+    swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+  else
+    return TIB_E_DTYPE;
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}
+
+// Cast between float and bf16: in_dtype -> out_dtype.
+TIB_API int tib_cast(const void* in, void* out, int64_t total, int in_dtype, int out_dtype,
+                     cudaStream_t stream) {
+  if (total == 0) return TIB_OK;
+  if (!in || !out || total < 0) return TIB_E_ARG;
+  const int threads = 256;
+  const int64_t want = (total + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  if (in_dtype == TIB_BF16 && out_dtype == TIB_F32)
+    cast_kernel<__nv_bfloat16, float><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)in, (float*)out, total);
+  else if (in_dtype == TIB_F32 && out_dtype == TIB_BF16)
+    cast_kernel<float, __nv_bfloat16><<<blocks, threads, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, total);
+  else
+    return TIB_E_DTYPE;
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}
+
+// dst[index[i]] = value[i] for i < n; indices outside [0, dst_size) are skipped.
+// Used to apply queued block-table changes in one launch.
+TIB_API int tib_scatter_i32(int* dst, const int* index, const int* value, int n, int64_t dst_size,
+                            cudaStream_t stream) {
+  if (n == 0) return TIB_OK;
+  if (!dst || !index || !value || n < 0) return TIB_E_ARG;
+  scatter_i32_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(dst, index, value, n, dst_size);
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}

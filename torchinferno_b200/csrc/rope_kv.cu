@@ -1,0 +1,130 @@
+// Rotary position encoding of q and k, fused with the write of k and v into
+// the paged cache.
+//
+// Formula (src/torchinferno/models/llama3/pipeline.py:555-568): angle =
+// float(position) * inv_freq[i]; rotate-half pairs (i, i + rot/2):
+//   lo' = lo * cos - hi * sin,   hi' = hi * cos + lo * sin.
+// Angles, cos and sin are 32-bit.  The frequency table is an input, so any
+// scaling law is a different table, not a different kernel.  `interleaved`
+// pairs (2i, 2i+1) instead; `rot_dim` < head_dim leaves the tail unrotated.
+//
+// Cache layout of one layer: [pages][2 (k, v)][kv_heads][page_size][head_dim];
+// a token at `position` of the request in `slot` goes to page
+// block_table[slot][position / page_size] at offset position % page_size
+// (slot arithmetic as in src/torchinferno/runtime/paged.py:463-477).
+#include "common.cuh"
+
+namespace tib {
+
+template <typename T>
+__global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                   T* __restrict__ pool, const int* __restrict__ positions,
+                                   const int* __restrict__ token_slot,
+                                   const int* __restrict__ block_table, int table_stride,
+                                   const float* __restrict__ inv_freq, int heads, int kv_heads,
+                                   int head_dim, int rot_dim, int interleaved, int page_size,
+                                   int64_t page_stride, int num_pages, int write_kv,
+                                   int* __restrict__ error_word) {
+  extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
+  const int tok = blockIdx.x;
+  const int pos = positions[tok];
+  const int half = rot_dim >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float ang = (float)pos * inv_freq[i];
+    cs[i] = cosf(ang);
+    cs[half + i] = sinf(ang);
+  }
+  __syncthreads();
+
+  const int q_width = heads * head_dim, kv_width = kv_heads * head_dim;
+  const T* row = qkv + (size_t)tok * (q_width + 2 * kv_width);
+
+  // q: rotate into q_out
+  const int pairs_per_head = head_dim >> 1;  // work items per head: rotated pairs + pass-through pairs
+  for (int w = threadIdx.x; w < heads * pairs_per_head; w += blockDim.x) {
+    const int hh = w / pairs_per_head, i = w - hh * pairs_per_head;
+    const T* src = row + hh * head_dim;
+    T* dst = q_out + (size_t)tok * q_width + hh * head_dim;
+    if (i < half) {
+      const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+      const float lo = to_f32(src[a]), hi = to_f32(src[b]);
+      const float c = cs[i], s = cs[half + i];
+      dst[a] = from_f32<T>(lo * c - hi * s);
+      dst[b] = from_f32<T>(hi * c + lo * s);
+    } else {
+      const int a = rot_dim + 2 * (i - half);
+      dst[a] = src[a];
+      dst[a + 1] = src[a + 1];
+    }
+  }
+  if (!write_kv) return;
+
+  const int slot = token_slot[tok];
+  const int page = block_table[(size_t)slot * table_stride + pos / page_size];
+  if (page < 0 || page >= num_pages) {
+    if (error_word && threadIdx.x == 0) atomicExch(error_word, 1 + tok);
+    return;
+  }
+  const int off = pos % page_size;
+  T* kpage = pool + (size_t)page * page_stride;
+  T* vpage = kpage + (size_t)kv_heads * page_size * head_dim;
+  const T* ksrc = row + q_width;
+  const T* vsrc = ksrc + kv_width;
+  for (int w = threadIdx.x; w < kv_heads * pairs_per_head; w += blockDim.x) {
+    const int hh = w / pairs_per_head, i = w - hh * pairs_per_head;
+    const T* src = ksrc + hh * head_dim;
+    T* dst = kpage + ((size_t)hh * page_size + off) * head_dim;
+    if (i < half) {
+      const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+      const float lo = to_f32(src[a]), hi = to_f32(src[b]);
+      const float c = cs[i], s = cs[half + i];
+      dst[a] = from_f32<T>(lo * c - hi * s);
+      dst[b] = from_f32<T>(hi * c + lo * s);
+    } else {
+      const int a = rot_dim + 2 * (i - half);
+      dst[a] = src[a];
+      dst[a + 1] = src[a + 1];
+    }
+  }
+  for (int w = threadIdx.x; w < kv_width; w += blockDim.x) {
+    const int hh = w / head_dim, dd = w - hh * head_dim;
+    vpage[((size_t)hh * page_size + off) * head_dim + dd] = vsrc[w];
+  }
+}
+
+}  // namespace tib
+
+using namespace tib;
+
+// qkv: [n_tokens, (heads + 2*kv_heads) * head_dim]; q_out: [n_tokens, heads * head_dim];
+// pool: this layer's pages; block_table: [slots, table_stride] page ids.
+TIB_API int tib_rope_append(const void* qkv, void* q_out, void* pool, const int* positions,
+                            const int* token_slot, const int* block_table, int table_stride,
+                            const float* inv_freq, int n_tokens, int heads, int kv_heads,
+                            int head_dim, int rot_dim, int interleaved, int page_size,
+                            int64_t page_stride, int num_pages, int write_kv, int* error_word,
+                            int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return TIB_OK;
+  if (!qkv || !q_out || !positions || n_tokens < 0) return TIB_E_ARG;
+  if (rot_dim > 0 && !inv_freq) return TIB_E_ARG;
+  if (write_kv && (!pool || !token_slot || !block_table || page_size < 1)) return TIB_E_ARG;
+  if (heads < 1 || kv_heads < 0 || head_dim < 2 || (head_dim & 1)) return TIB_E_SIZE;
+  if (rot_dim < 0 || rot_dim > head_dim || (rot_dim & 1)) return TIB_E_SIZE;
+  const int threads = 256;
+  const size_t smem = (size_t)rot_dim * sizeof(float);
+  if (smem > 48 * 1024) return TIB_E_SMEM;
+  if (dtype == TIB_F32)
+    rope_append_kernel<float><<<n_tokens, threads, smem, stream>>>(
+        (const float*)qkv, (float*)q_out, (float*)pool, positions, token_slot, block_table,
+        table_stride, inv_freq, heads, kv_heads, head_dim, rot_dim, interleaved, page_size,
+        page_stride, num_pages, write_kv, error_word);
+  else if (dtype == TIB_BF16)
+    rope_append_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(
+        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, positions,
+        token_slot, block_table, table_stride, inv_freq, heads, kv_heads, head_dim, rot_dim,
+        interleaved, page_size, page_stride, num_pages, write_kv, error_word);
+  else
+    return TIB_E_DTYPE;
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}

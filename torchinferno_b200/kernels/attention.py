@@ -1,0 +1,22 @@
+"""Choice of the attention kernel for a step.
+
+All kernels here read the ragged batch the same way: entry e owns the token
+rows q_start[e] .. q_start[e+1]-1, its first query token stands at position
+kv_start[e] of the request, and its pages are row slots[e] of the block table.
+A kernel that does not take a shape is passed over; the CUDA-core kernel takes
+every shape, and is the only one used in 32-bit.
+"""
+from __future__ import annotations
+
+import torch
+
+from torchinferno_b200.kernels import ops
+
+
+def paged_attention(q: torch.Tensor, out: torch.Tensor, ctx, heads: int, kv_heads: int, head_dim: int,
+                    scale: float, window: int | None) -> torch.Tensor:
+    batch, kv = ctx.batch, ctx.kv
+    return ops.paged_attention_simt(
+        q, kv.pool, out, batch.q_start, batch.kv_start, batch.slots, kv.block_table,
+        batch.n_entries, batch.max_q_len, heads, kv_heads, head_dim, scale,
+        window=int(window or 0), error_word=ctx.error_word)

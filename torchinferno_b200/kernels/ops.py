@@ -1,0 +1,260 @@
+"""Python faces of the CUDA kernels.
+
+Each function checks device, dtype, contiguity and shapes, then calls the C
+entry point on torch's current stream.  A refusal by a kernel (a size it does
+not take) raises :class:`KernelError`; nothing falls back to another path.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+import torch
+
+from torchinferno_b200.kernels.library import load_library
+
+F32, BF16 = 0, 1
+
+_ERRORS = {
+    -1: "unknown dtype code",
+    -2: "a size this kernel does not take",
+    -3: "a pointer or stride that is not aligned as required",
+    -4: "needs more shared memory than an SM offers",
+    -5: "null pointer or inconsistent arguments",
+    -6: "the device-side wait limit was reached (kernel gave up)",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_counter = {"launches": 0}
+
+
+def launch_count() -> int:
+    """How many kernels of this library were launched by this process so far."""
+    return _counter["launches"]
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {dtype} is not supported by the kernels (float32 or bfloat16)")
+
+
+def _check(name: str, status: int) -> None:
+    _counter["launches"] += 1
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{name}: refused: {_ERRORS.get(status, status)}")
+    raise KernelError(f"{name}: CUDA error {status} at launch")
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype: torch.dtype | None = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_signatures_set = False
+
+
+def lib() -> ctypes.CDLL:
+    global _signatures_set
+    library = load_library()
+    if not _signatures_set:
+        for fn in ("tib_embedding", "tib_add_rmsnorm", "tib_rmsnorm", "tib_swiglu", "tib_cast",
+                   "tib_scatter_i32", "tib_rope_append", "tib_paged_attention_simt", "tib_gemm_f32", "tib_sample"):
+            getattr(library, fn).restype = c_int
+        _signatures_set = True
+    return library
+
+
+# ---------------------------------------------------------------------------
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = float(table[ids[t]]): the residual stream starts in 32-bit."""
+    _need(ids, "ids", torch.int32), _need(table, "table"), _need(out, "out", torch.float32)
+    n, (vocab, hidden) = ids.numel(), table.shape
+    if out.shape != (n, hidden):
+        raise KernelError(f"embedding: out is {tuple(out.shape)}, wanted {(n, hidden)}")
+    _check("embedding", lib().tib_embedding(_ptr(ids), _ptr(table), _ptr(out), c_int(n), c_int(hidden),
+                                            c_int(vocab), c_int(_code(table.dtype)), _stream()))
+    return out
+
+
+def add_rmsnorm(delta: torch.Tensor | None, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
+    """residual += delta (fp32, in place, when rows is None); out = rmsnorm(residual) * weight.
+
+    With ``rows`` only those source rows are read, the residual is left as it
+    is and ``out`` has one row per index.
+    """
+    _need(residual, "residual", torch.float32), _need(weight, "weight", torch.float32), _need(out, "out")
+    hidden = residual.shape[-1]
+    if delta is not None:
+        _need(delta, "delta", out.dtype)
+        if delta.shape != residual.shape:
+            raise KernelError("add_rmsnorm: delta and residual differ in shape")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    n_out = residual.shape[0] if rows is None else rows.numel()
+    if out.shape != (n_out, hidden) or weight.numel() != hidden:
+        raise KernelError(f"add_rmsnorm: out {tuple(out.shape)} / weight {tuple(weight.shape)} do not fit {(n_out, hidden)}")
+    _check("add_rmsnorm", lib().tib_add_rmsnorm(_ptr(delta), _ptr(residual), _ptr(rows), _ptr(weight), _ptr(out),
+                                                c_int(n_out), c_int(hidden), c_float(eps),
+                                                c_int(_code(out.dtype)), _stream()))
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """RMSNorm over the last dimension of rows held in the activation type."""
+    _need(x, "x"), _need(weight, "weight", torch.float32), _need(out, "out", x.dtype)
+    hidden = x.shape[-1]
+    n_rows = x.numel() // hidden if hidden else 0
+    if out.shape != x.shape or weight.numel() != hidden:
+        raise KernelError("rmsnorm: shapes do not fit")
+    _check("rmsnorm", lib().tib_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), c_int(n_rows), c_int(hidden),
+                                        c_float(eps), c_int(_code(x.dtype)), _stream()))
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:], silu and product in fp32."""
+    _need(gate_up, "gate_up"), _need(out, "out", gate_up.dtype)
+    n, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (n, two_i // 2):
+        raise KernelError("swiglu: shapes do not fit")
+    _check("swiglu", lib().tib_swiglu(_ptr(gate_up), _ptr(out), c_int(n), c_int(two_i // 2),
+                                      c_int(_code(gate_up.dtype)), _stream()))
+    return out
+
+
+def cast(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(x, "x"), _need(out, "out")
+    if x.numel() != out.numel():
+        raise KernelError("cast: sizes differ")
+    _check("cast", lib().tib_cast(_ptr(x), _ptr(out), c_int64(x.numel()), c_int(_code(x.dtype)),
+                                  c_int(_code(out.dtype)), _stream()))
+    return out
+
+
+def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, pool: torch.Tensor | None, positions: torch.Tensor,
+                token_slot: torch.Tensor | None, block_table: torch.Tensor | None, inv_freq: torch.Tensor,
+                heads: int, kv_heads: int, head_dim: int, *, rot_dim: int | None = None,
+                interleaved: bool = False, write_kv: bool = True,
+                error_word: torch.Tensor | None = None) -> torch.Tensor:
+    """Rotate q into ``q_out``; rotate k and copy v into the layer's pages.
+
+    ``qkv``: [tokens, (heads + 2 kv_heads) * head_dim]; ``pool``: the layer's pages
+    [pages, 2, kv_heads, page_size, head_dim]; ``block_table``: [slots, max_pages] int32.
+    """
+    _need(qkv, "qkv"), _need(q_out, "q_out", qkv.dtype), _need(positions, "positions", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32)
+    n = qkv.shape[0]
+    rot = head_dim if rot_dim is None else rot_dim
+    if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim or q_out.numel() != n * heads * head_dim:
+        raise KernelError("rope_append: qkv / q_out widths do not fit the head counts")
+    if inv_freq.numel() != rot // 2 or positions.numel() != n:
+        raise KernelError("rope_append: inv_freq or positions have the wrong length")
+    page_size = page_stride = num_pages = table_stride = 0
+    if write_kv:
+        if pool is None or token_slot is None or block_table is None:
+            raise KernelError("rope_append: pool, token_slot and block_table are needed to write the cache")
+        _need(pool, "pool", qkv.dtype), _need(token_slot, "token_slot", torch.int32)
+        _need(block_table, "block_table", torch.int32)
+        if pool.dim() != 5 or pool.shape[1] != 2 or pool.shape[2] != kv_heads or pool.shape[4] != head_dim:
+            raise KernelError(f"rope_append: pool shape {tuple(pool.shape)} does not fit")
+        num_pages, page_size = pool.shape[0], pool.shape[3]
+        page_stride = pool.stride(0)
+        table_stride = block_table.stride(0)
+    _check("rope_append", lib().tib_rope_append(
+        _ptr(qkv), _ptr(q_out), _ptr(pool), _ptr(positions), _ptr(token_slot), _ptr(block_table),
+        c_int(table_stride), _ptr(inv_freq), c_int(n), c_int(heads), c_int(kv_heads), c_int(head_dim),
+        c_int(rot), c_int(int(interleaved)), c_int(page_size), c_int64(page_stride), c_int(num_pages),
+        c_int(int(write_kv)), _ptr(error_word), c_int(_code(qkv.dtype)), _stream()))
+    return q_out
+
+
+def paged_attention_simt(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor,
+                         kv_start: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor,
+                         n_entries: int, max_q_len: int, heads: int, kv_heads: int, head_dim: int,
+                         scale: float, window: int = 0, error_word: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of a ragged batch over the paged cache, on CUDA cores."""
+    _need(q, "q"), _need(pool, "pool", q.dtype), _need(out, "out", q.dtype)
+    for name, t in (("q_start", q_start), ("kv_start", kv_start), ("slots", slots), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if pool.dim() != 5 or pool.shape[1] != 2 or pool.shape[2] != kv_heads or pool.shape[4] != head_dim:
+        raise KernelError(f"paged_attention: pool shape {tuple(pool.shape)} does not fit")
+    if q.numel() != out.numel() or q.numel() % (heads * head_dim):
+        raise KernelError("paged_attention: q / out do not fit the head counts")
+    if q_start.numel() < n_entries + 1 or kv_start.numel() < n_entries or slots.numel() < n_entries:
+        raise KernelError("paged_attention: entry arrays are shorter than n_entries")
+    _check("paged_attention_simt", lib().tib_paged_attention_simt(
+        _ptr(q), _ptr(pool), _ptr(out), _ptr(q_start), _ptr(kv_start), _ptr(slots), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(n_entries), c_int(max_q_len), c_int(heads), c_int(kv_heads),
+        c_int(head_dim), c_int(pool.shape[3]), c_int64(pool.stride(0)), c_int(pool.shape[0]), c_int(window),
+        c_float(scale), _ptr(error_word), c_int(_code(q.dtype)), _stream()))
+    return out
+
+
+def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] (fp32) = x[M, K] . w[N, K]^T with fp32 FMAs in fixed k order."""
+    _need(out, "out", torch.float32)
+    for name, t in (("x", x), ("w", w)):
+        if not t.is_cuda or t.stride(-1) != 1 or t.dim() != 2:
+            raise KernelError(f"gemm_f32: {name} must be a 2-D CUDA tensor with unit inner stride")
+    (m, k), (n, k2) = x.shape, w.shape
+    if k != k2 or out.shape != (m, n):
+        raise KernelError(f"gemm_f32: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    _check("gemm_f32", lib().tib_gemm_f32(_ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k),
+                                          c_int64(x.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)),
+                                          c_int(_code(x.dtype)), c_int(_code(w.dtype)), _stream()))
+    return out
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor | None = None,
+           seeds: torch.Tensor | None = None, positions: torch.Tensor | None = None) -> torch.Tensor:
+    """Token ids from fp32 logits: greedy where temperature <= 0, else seeded Gumbel-max."""
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be a 2-D fp32 CUDA tensor with unit inner stride")
+    _need(out, "out", torch.int32)
+    n, vocab = logits.shape
+    if temperature is not None:
+        _need(temperature, "temperature", torch.float32)
+    if seeds is not None:
+        _need(seeds, "seeds", torch.int64)
+    if positions is not None:
+        _need(positions, "positions", torch.int32)
+    for t in (temperature, seeds, positions):
+        if t is not None and t.numel() < n:
+            raise KernelError("sample: a per-row array is shorter than the number of rows")
+    if out.numel() < n:
+        raise KernelError("sample: out is too short")
+    _check("sample", lib().tib_sample(_ptr(logits), c_int64(logits.stride(0)), _ptr(temperature), _ptr(seeds),
+                                      _ptr(positions), _ptr(out), c_int(n), c_int(vocab), _stream()))
+    return out
+
+
+def scatter_i32(dst: torch.Tensor, index: torch.Tensor, value: torch.Tensor) -> torch.Tensor:
+    """dst.view(-1)[index[i]] = value[i]; applies queued block-table changes."""
+    _need(dst, "dst", torch.int32), _need(index, "index", torch.int32), _need(value, "value", torch.int32)
+    if index.numel() != value.numel():
+        raise KernelError("scatter_i32: index and value differ in length")
+    _check("scatter_i32", lib().tib_scatter_i32(_ptr(dst), _ptr(index), _ptr(value), c_int(index.numel()),
+                                                c_int64(dst.numel()), _stream()))
+    return dst

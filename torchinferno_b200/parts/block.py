@@ -1,0 +1,45 @@
+"""The arrangement of parts in one layer.
+
+Pre-norm block (src/torchinferno/models/llama3/pipeline.py:190-198):
+    h = h + mixer(norm1(h));  h = h + feed_forward(norm2(h))
+The adds are left pending on the residual stream so the next norm (of this
+block, of the next block or the final one) does them in its own pass
+(src/torchinferno/models/llama3/tensor_parallel.py:7430-7435).
+"""
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from torchinferno_b200.parts.base import (Block, LayerContext, Part, PartSpec, ResidualStream,
+                                          build_part, register_part)
+
+
+def _spec(value: PartSpec | Mapping) -> PartSpec:
+    return value if isinstance(value, PartSpec) else PartSpec(**value)
+
+
+class PreNormBlock(Block):
+    def __init__(self, *, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
+                 feed_forward_norm: PartSpec, dtype: torch.dtype, device: torch.device) -> None:
+        super().__init__(dtype=dtype, device=device)
+        self.specs = {"mixer": _spec(mixer), "feed_forward": _spec(feed_forward),
+                      "mixer_norm": _spec(mixer_norm), "feed_forward_norm": _spec(feed_forward_norm)}
+        self.mixer = build_part("mixer", self.specs["mixer"], dtype=dtype, device=device)
+        self.feed_forward = build_part("feed_forward", self.specs["feed_forward"], dtype=dtype, device=device)
+        self.mixer_norm = build_part("norm", self.specs["mixer_norm"], dtype=dtype, device=device)
+        self.feed_forward_norm = build_part("norm", self.specs["feed_forward_norm"], dtype=dtype, device=device)
+
+    def named_parts(self) -> list[tuple[str, Part]]:
+        return [(self.specs["mixer_norm"].prefix, self.mixer_norm),
+                (self.specs["mixer"].prefix, self.mixer),
+                (self.specs["feed_forward_norm"].prefix, self.feed_forward_norm),
+                (self.specs["feed_forward"].prefix, self.feed_forward)]
+
+    def forward(self, stream: ResidualStream, ctx: LayerContext) -> None:
+        stream.add(self.mixer.forward(stream.normed(self.mixer_norm), ctx))
+        stream.add(self.feed_forward.forward(stream.normed(self.feed_forward_norm), ctx))
+
+
+register_part("block", "prenorm", PreNormBlock)
