@@ -1,0 +1,161 @@
+"""The cache manager on the CPU: no page lost, held twice or freed twice, under random orders."""
+import random
+
+import pytest
+import torch
+
+from torchinferno_b200.cache.manager import CacheError, CacheManager, OutOfPages, PageAllocator
+from torchinferno_b200.parts.base import CacheSpec, StateSpec
+
+
+def manager(num_pages=8, page_size=4, specs=None, states=None, max_requests=4, max_request_tokens=64, tensors=False):
+    specs = specs or [CacheSpec(2, 16)] * 2
+    return CacheManager(specs, states or [None] * len(specs), page_size=page_size, num_pages=num_pages,
+                        max_requests=max_requests, max_request_tokens=max_request_tokens, dtype=torch.float32,
+                        device="cpu", allocate_tensors=tensors)
+
+
+def test_allocator_lowest_first_lifo_reuse_and_double_free():
+    a = PageAllocator(4)
+    assert [a.alloc() for _ in range(4)] == [0, 1, 2, 3]
+    with pytest.raises(OutOfPages):
+        a.alloc()
+    a.release(2), a.release(0)
+    assert a.alloc() == 0 and a.alloc() == 2          # last freed is reused first
+    a.release(1)
+    with pytest.raises(CacheError, match="twice"):
+        a.release(1)
+    with pytest.raises(CacheError):
+        a.release(9)
+    a.retain(3)
+    a.release(3)
+    assert a.num_free == 1 and a.refcount(3) == 1     # still held by the other holder
+    a.release(3)
+    assert a.num_free == 2
+
+
+def test_pages_come_as_tokens_arrive_and_go_back_at_the_end():
+    m = manager()
+    assert m.open("a") == 0 and m.extend("a", 5) == 0
+    assert m.block_table("a") == [0, 1] and m.length("a") == 5 and m.free_pages() == [6]
+    assert m.extend("a", 3) == 5 and m.block_table("a") == [0, 1]          # fills the second page
+    assert m.extend("a", 1) == 8 and m.block_table("a") == [0, 1, 2]
+    m.open("b"), m.extend("b", 4)
+    assert m.block_table("b") == [3]
+    m.audit()
+    m.close("a")
+    assert m.free_pages() == [7] and "a" not in m
+    m.open("c"), m.extend("c", 9)
+    assert m.block_table("c") == [2, 1, 0]                                   # pages of "a" are used again
+    m.audit()
+    with pytest.raises(CacheError):
+        m.close("a")
+    with pytest.raises(CacheError):
+        m.extend("zzz", 1)
+    with pytest.raises(CacheError, match="already open"):
+        m.open("b")
+
+
+def test_out_of_pages_changes_nothing():
+    m = manager(num_pages=3)
+    m.open("a"), m.extend("a", 8)
+    m.open("b")
+    assert not m.can_extend("b", 5) and m.can_extend("b", 4)
+    with pytest.raises(OutOfPages):
+        m.extend("b", 5)
+    assert m.length("b") == 0 and m.block_table("b") == [] and m.free_pages() == [1]
+    m.extend("b", 4)
+    m.audit()
+
+
+def test_groups_have_pools_of_their_own_and_windows_release_early():
+    specs = [CacheSpec(2, 16), CacheSpec(2, 16, window=6), CacheSpec(2, 16), CacheSpec(1, 32, window=6)]
+    m = manager(num_pages=6, specs=specs, max_request_tokens=24)
+    assert len(m.groups) == 3 and m.groups[0].cache_layers == [0, 2] and m.groups[1].cache_layers == [1]
+    assert m.group_of_layer(3) == 2
+    m.open("a")
+    m.extend("a", 12)
+    assert m.free_pages() == [3, 3, 3]
+    # next query stands at 12 and reads keys >= 7: the first page (keys 0..3) has passed the window
+    assert m.release_behind_window("a") == 2
+    assert m.block_table("a", 0) == [0, 1, 2] and m.block_table("a", 1) == [-1, 1, 2] and m.free_pages() == [3, 4, 4]
+    m.extend("a", 8)
+    m.release_behind_window("a")
+    assert m.block_table("a", 1)[:3] == [-1, -1, -1] and m.block_table("a", 0) == [0, 1, 2, 3, 4]
+    m.audit()
+    m.close("a")
+    assert m.free_pages() == [6, 6, 6]
+    m.audit()
+
+
+def test_table_updates_are_queued_once():
+    m = manager()
+    m.open("a"), m.extend("a", 6)
+    (index, value), = m.drain_table_updates()
+    stride = m.max_pages_per_request
+    assert index == [0 * stride + 0, 0 * stride + 1] and value == [0, 1]
+    assert m.drain_table_updates() == [([], [])]
+    m.close("a")
+    (index, value), = m.drain_table_updates()
+    assert value == [-1, -1]
+
+
+def test_state_slots_are_zeroed_and_reused():
+    m = manager(states=[StateSpec((3,)), None], tensors=True)
+    slot = m.open("a")
+    m.state(0)[slot] += 5
+    m.close("a")
+    assert m.open("b") == slot and torch.all(m.state(0)[slot] == 0) and m.state(1) is None
+    for name in "cde":
+        m.open(name)
+    with pytest.raises(CacheError, match="slots"):
+        m.open("f")
+    m.audit()
+
+
+def test_request_limit():
+    m = manager(max_request_tokens=10)
+    m.open("a")
+    with pytest.raises(CacheError, match="limit"):
+        m.extend("a", 11)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_never_lose_or_double_a_page(seed):
+    rng = random.Random(seed)
+    specs = [CacheSpec(2, 16), CacheSpec(2, 16, window=rng.choice([3, 5, 9]))]
+    m = manager(num_pages=rng.choice([5, 9, 16]), page_size=rng.choice([1, 3, 4]), specs=specs,
+                max_requests=5, max_request_tokens=40)
+    live, counter = [], 0
+    for _ in range(600):
+        action = rng.random()
+        if action < 0.25 and m.free_slots():
+            counter += 1
+            m.open(counter)
+            live.append(counter)
+        elif action < 0.75 and live:
+            rid = rng.choice(live)
+            n = rng.randint(1, 7)
+            before = (m.length(rid), m.free_pages(), m.block_table(rid, 0), m.block_table(rid, 1))
+            if m.length(rid) + n > 40:
+                continue
+            try:
+                start = m.extend(rid, n)
+                assert start == before[0] and m.length(rid) == start + n
+                m.release_behind_window(rid)
+            except OutOfPages:
+                assert before == (m.length(rid), m.free_pages(), m.block_table(rid, 0), m.block_table(rid, 1))
+        elif live:
+            rid = live.pop(rng.randrange(len(live)))
+            m.close(rid)
+        m.audit()
+        for rid in live:                      # every readable key has a page
+            for g, spec in enumerate(s for s in specs):
+                table = m.block_table(rid, g)
+                lo = max(0, m.length(rid) - spec.window + 1) if spec.window else 0
+                for pos in range(lo, m.length(rid)):
+                    assert table[pos // m.page_size] >= 0
+    for rid in live:
+        m.close(rid)
+    m.audit()
+    assert m.free_pages() == [m.num_pages] * 2

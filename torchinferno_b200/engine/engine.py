@@ -1,0 +1,218 @@
+"""The Python entry point: ``InferenceEngine`` over scheduler, step function and sampler.
+
+Interface as in the reference (src/torchinferno/engine/engine.py:35-54, 91-151):
+``InferenceEngine.from_config(EngineConfig)``, ``generate(request)``,
+``generate_stream(request)``, ``cancel(request_id)``, ``close()``, context
+manager.  ``generate_many`` runs several requests together through the
+continuous-batching scheduler.  Tokens go in and come out as host integers;
+text prompts need a tokenizer (``EngineConfig.tokenizer`` or the model folder's
+``tokenizer.json``, through the optional ``tokenizers`` package as in
+src/torchinferno/tokenization.py:7-61).
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Hashable, Iterable, Iterator, Sequence
+
+import torch
+
+from torchinferno_b200.config.engine_config import EngineConfig
+from torchinferno_b200.engine.batch import StepEntry
+from torchinferno_b200.engine.factory import load_model, make_runner
+from torchinferno_b200.engine.scheduler import Scheduler, SchedulerRequest, StepPlan, TokenEvent
+from torchinferno_b200.engine.types import GenerateOutput, GenerateRequest, SamplingConfig, TokenOutput, Usage
+from torchinferno_b200.sampling.sampler import Sampler, SamplingParams
+
+
+class InferenceEngine:
+    def __init__(self, model, config: EngineConfig, tokenizer=None) -> None:
+        self.model = model
+        self.config = config
+        self.tokenizer = tokenizer
+        limit = model.spec.max_positions if config.max_model_len is None else min(config.max_model_len, model.spec.max_positions)
+        if config.num_pages is not None:
+            num_pages = config.num_pages
+        else:
+            tokens = config.kv_cache_tokens or config.max_batch_size * limit
+            num_pages = -(-tokens // config.page_size) + config.max_batch_size
+        self.runner = make_runner(model, page_size=config.page_size, num_pages=num_pages,
+                                  max_requests=config.max_batch_size, max_request_tokens=limit, check_errors=False)
+        self.runner.use_cuda_graphs = config.use_cuda_graphs
+        self.scheduler = Scheduler(self.runner.cache, max_batch_size=config.max_batch_size,
+                                   max_step_tokens=config.max_num_batched_tokens,
+                                   prefill_chunk_size=config.prefill_chunk_size)
+        self.sampler = Sampler(model.device)
+        self._requests: dict[Hashable, GenerateRequest] = {}
+        self._cancelled: set[Hashable] = set()
+        self._closed = False
+        self.stats = {"steps": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+
+    # -------------------------------------------------------- construction
+    @classmethod
+    def from_config(cls, config: EngineConfig) -> "InferenceEngine":
+        if config.model_kind not in ("auto", "llama3", "llama"):
+            raise ValueError(f"model_kind={config.model_kind!r} is not known; use 'auto'")
+        model = load_model(config.model, dtype=config.dtype, device=config.device or "cuda:0")
+        return cls(model, config, _load_tokenizer(config))
+
+    def __enter__(self) -> "InferenceEngine":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
+    def close(self) -> None:
+        if self._closed:
+            return
+        for request_id in list(self._requests):
+            self.cancel(request_id)
+        self._closed = True
+
+    # ------------------------------------------------------------ requests
+    def _prompt_ids(self, request: GenerateRequest) -> list[int]:
+        if request.prompt_token_ids is not None:
+            return list(request.prompt_token_ids)
+        if self.tokenizer is None:
+            raise ValueError("a text prompt needs a tokenizer; give prompt_token_ids or EngineConfig.tokenizer")
+        if request.prompt is not None:
+            return list(self.tokenizer.encode(request.prompt).ids)
+        text = "".join(f"{m.get('role', 'user')}: {m.get('content', '')}\n" for m in request.messages)
+        return list(self.tokenizer.encode(text).ids)
+
+    def _decode(self, ids: Sequence[int]) -> str:
+        return "" if self.tokenizer is None or not ids else self.tokenizer.decode(list(ids))
+
+    def submit(self, request: GenerateRequest) -> None:
+        if self._closed:
+            raise RuntimeError("the engine is closed")
+        prompt = self._prompt_ids(request)
+        sampling = request.sampling
+        self.scheduler.submit(SchedulerRequest(
+            request.request_id, prompt, sampling.max_tokens, sampling.temperature,
+            sampling.seed if sampling.seed else self.config.seed, sampling.stop_token_ids))
+        self._requests[request.request_id] = request
+
+    def cancel(self, request_id: Hashable) -> bool:
+        """Stop a request; its pages are given back (src/torchinferno/engine/engine.py:87-89)."""
+        if request_id not in self._requests:
+            return False
+        self._cancelled.add(request_id)
+        self.scheduler.cancel(request_id)
+        self._requests.pop(request_id, None)
+        return True
+
+    # ---------------------------------------------------------------- step
+    def step(self) -> list[TokenEvent]:
+        """Plan one step, run it, draw tokens, and return what happened."""
+        plan = self.scheduler.plan()
+        if not plan.entries:
+            return []
+        sampled = self._run(plan)
+        return self.scheduler.commit(plan, sampled)
+
+    def _run(self, plan: StepPlan) -> dict[Hashable, int]:
+        entries = [StepEntry(e.request_id, e.tokens, (len(e.tokens) - 1,) if e.samples else ()) for e in plan.entries]
+        with torch.inference_mode():
+            logits = self.runner.step(entries)
+            drawing = [e for e in plan.entries if e.samples]
+            if not drawing:
+                self.stats["steps"] += 1
+                self.stats["h2d_bytes"] += self.runner.last_batch.h2d_bytes
+                return {}
+            params, positions = [], []
+            for e in drawing:
+                request = self.scheduler._by_id[e.request_id]
+                params.append(SamplingParams(request.temperature, request.seed))
+                positions.append(e.start + len(e.tokens))  # position of the token being drawn
+            tokens = self.sampler.sample(logits, params, positions)
+            host = tokens.cpu()
+        self.stats["steps"] += 1
+        self.stats["h2d_bytes"] += self.runner.last_batch.h2d_bytes
+        self.stats["d2h_bytes"] += host.numel() * host.element_size()
+        return {e.request_id: int(t) for e, t in zip(drawing, host.tolist())}
+
+    # ------------------------------------------------------------ generate
+    def generate_stream(self, request: GenerateRequest) -> Iterator[TokenOutput]:
+        """Yield one ``TokenOutput`` per token, then a final one with ``finished`` and ``usage``."""
+        self.submit(request)
+        prompt_tokens = len(self.scheduler._by_id[request.request_id].prompt)
+        emitted: list[int] = []
+        reason = None
+        while reason is None:
+            if request.request_id in self._cancelled:
+                reason = "cancelled"
+                break
+            for event in self.step():
+                if event.request_id != request.request_id:
+                    continue
+                if event.token is not None:
+                    emitted.append(event.token)
+                    yield TokenOutput(request.request_id, event.token, self._decode([event.token]), len(emitted) - 1)
+                if event.finished:
+                    reason = event.finish_reason
+            if reason is None and not self.scheduler.has_work():
+                reason = "cancelled" if request.request_id in self._cancelled else "length"
+        self._requests.pop(request.request_id, None)
+        self._cancelled.discard(request.request_id)
+        yield TokenOutput(request.request_id, None, "", len(emitted), True, reason, Usage(prompt_tokens, len(emitted)))
+
+    def generate(self, request: GenerateRequest) -> GenerateOutput:
+        tokens: list[int] = []
+        final = None
+        for out in self.generate_stream(request):
+            if out.finished:
+                final = out
+            elif out.token_id is not None:
+                tokens.append(out.token_id)
+        return GenerateOutput(request.request_id, tuple(tokens), self._decode(tokens), final.finish_reason, final.usage)
+
+    def generate_many(self, requests: Iterable[GenerateRequest]) -> list[GenerateOutput]:
+        """Run requests together (continuous batching); results in the order given."""
+        requests = list(requests)
+        for request in requests:
+            self.submit(request)
+        prompts = {r.request_id: len(self.scheduler._by_id[r.request_id].prompt) for r in requests}
+        tokens: dict[Hashable, list[int]] = {r.request_id: [] for r in requests}
+        reasons: dict[Hashable, str] = {}
+        while len(reasons) < len(requests) and self.scheduler.has_work():
+            for event in self.step():
+                if event.request_id not in tokens:
+                    continue
+                if event.token is not None:
+                    tokens[event.request_id].append(event.token)
+                if event.finished:
+                    reasons[event.request_id] = event.finish_reason
+        outputs = []
+        for r in requests:
+            self._requests.pop(r.request_id, None)
+            ids = tokens[r.request_id]
+            outputs.append(GenerateOutput(r.request_id, tuple(ids), self._decode(ids),
+                                          reasons.get(r.request_id, "cancelled"), Usage(prompts[r.request_id], len(ids))))
+        return outputs
+
+
+def _load_tokenizer(config: EngineConfig):
+    path = config.tokenizer
+    if path is None:
+        candidate = Path(config.model) / "tokenizer.json"
+        if not candidate.is_file():
+            return None
+        path = str(candidate)
+    elif Path(path).is_dir():
+        path = str(Path(path) / "tokenizer.json")
+    try:
+        from tokenizers import Tokenizer
+    except ImportError as exc:
+        raise RuntimeError("text prompts need the optional 'tokenizers' package") from exc
+    return Tokenizer.from_file(path)
+
+
+def generate(model_dir: str, prompt_token_ids: Sequence[int], *, max_new_tokens: int = 16, temperature: float = 0.0,
+             seed: int = 0, dtype: str = "auto", stop_token_ids: Sequence[int] = (), **engine_options) -> list[int]:
+    """One call from a model folder and prompt ids to new token ids (the shape of the reference's
+    ``model.generate(input_ids, max_new_tokens=, temperature=)``: src/torchinferno/models/llama3/pipeline.py:404-433)."""
+    config = EngineConfig(model=str(model_dir), dtype=dtype, **engine_options)
+    with InferenceEngine.from_config(config) as engine:
+        out = engine.generate(GenerateRequest("generate-0", prompt_token_ids=list(prompt_token_ids),
+                                              sampling=SamplingConfig(max_new_tokens, temperature, tuple(stop_token_ids), seed)))
+    return list(out.token_ids)

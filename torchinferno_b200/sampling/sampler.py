@@ -1,0 +1,61 @@
+"""Next-token choice: greedy and temperature sampling, per request.
+
+The reference samples with ``argmax`` when ``temperature <= 0`` and otherwise
+draws from ``softmax(logits.float() / temperature)`` with ``torch.multinomial``
+(src/torchinferno/runtime/sampling.py:7-11); its tensor-parallel model draws the
+same distribution in Gumbel-max form
+(src/torchinferno/models/llama3/tensor_parallel.py:9946-9996).  Per-request
+temperatures override the engine default (src/torchinferno/runtime/serving.py:413).
+top_p other than 1, top-k and penalties are not offered there
+(src/torchinferno/server/openai_protocol.py:34-38) nor here.
+
+Here the Gumbel-max form runs in one kernel with counter-based noise keyed by
+(request seed, position of the token being drawn, vocabulary index): a request's
+tokens do not depend on what else is in the batch, nor on how its prompt was cut.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Sequence
+
+import torch
+
+from torchinferno_b200.kernels import ops
+
+
+@dataclass(frozen=True)
+class SamplingParams:
+    temperature: float = 0.0
+    seed: int = 0
+
+    def __post_init__(self) -> None:
+        if self.temperature < 0:
+            raise ValueError("temperature must be non-negative")
+
+
+class Sampler:
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], positions: Sequence[int]) -> torch.Tensor:
+        """Token ids (int32, on the device) for fp32 ``logits`` [n, vocab].
+
+        ``positions[i]`` is the position in its sequence of the token being drawn for row i.
+        """
+        n = logits.shape[0]
+        if len(params) != n or len(positions) != n:
+            raise ValueError("one SamplingParams and one position per logits row are needed")
+        out = torch.empty(n, dtype=torch.int32, device=self.device)
+        if n == 0:
+            return out
+        if all(p.temperature <= 0 for p in params):
+            return ops.sample(logits, out)
+        temperature = torch.tensor([p.temperature for p in params], dtype=torch.float32).to(self.device)
+        seeds = torch.tensor([_as_int64(p.seed) for p in params], dtype=torch.int64).to(self.device)
+        pos = torch.tensor(list(positions), dtype=torch.int32).to(self.device)
+        return ops.sample(logits, out, temperature, seeds, pos)
+
+
+def _as_int64(seed: int) -> int:
+    seed &= 0xFFFFFFFFFFFFFFFF
+    return seed - (1 << 64) if seed >= (1 << 63) else seed
