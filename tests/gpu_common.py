@@ -1,0 +1,59 @@
+"""Shared by the GPU tests: tolerances (set once), plain-reference logits, request sets."""
+from __future__ import annotations
+
+import functools
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+
+# The 32-bit path against the float64 plain implementation.
+F32_ATOL, F32_RTOL = 2e-5, 1e-4
+# bfloat16 against the same: largest error relative to the largest logit of the sequence
+# (the measure of scripts/cmp_paged_dense_logits.py in the reference project, which expects
+# about 1 % in bf16 on a deep model).
+BF16_REL = 0.015
+
+
+def need_gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+
+
+def requests_for(config, seed, lengths):
+    g = torch.Generator().manual_seed(1234 + seed)
+    return {f"r{i}": torch.randint(0, config["vocab_size"], (n,), generator=g).tolist() for i, n in enumerate(lengths)}
+
+
+_plain_cache: dict = {}
+
+
+def plain_logits(folder, tokens):
+    key = (str(folder), tuple(tokens))
+    if key not in _plain_cache:
+        if str(folder) not in _plain_cache:
+            _plain_cache[str(folder)] = plain_llama.read_model_folder(folder)
+        config, weights = _plain_cache[str(folder)]
+        _plain_cache[key] = plain_llama.forward(config, weights, tokens).numpy()
+    return _plain_cache[key]
+
+
+def check_rows(rows, folder, requests, dtype):
+    """Every (request, position) row against the plain implementation."""
+    assert rows, "nothing was compared"
+    worst = 0.0
+    for (name, pos), got_list in rows.items():
+        ref = plain_logits(folder, requests[name])
+        for got in got_list:
+            got = np.asarray(got, dtype=np.float64)
+            assert np.isfinite(got).all(), f"{name}@{pos}: non-finite logits"
+            err = np.abs(got - ref[pos]).max()
+            if dtype == "float32":
+                bound = F32_ATOL + F32_RTOL * np.abs(ref[pos]).max()
+            else:
+                bound = BF16_REL * np.abs(ref).max()
+            worst = max(worst, err / bound)
+            assert err <= bound, f"{name}@{pos} ({dtype}): max error {err:.3e} exceeds {bound:.3e}"
+    return worst

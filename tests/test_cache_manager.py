@@ -159,3 +159,14 @@ def test_random_orders_never_lose_or_double_a_page(seed):
         m.close(rid)
     m.audit()
     assert m.free_pages() == [m.num_pages] * 2
+
+
+def test_a_slot_reused_between_two_steps_queues_each_table_entry_once():
+    m = manager()
+    m.open("a"), m.extend("a", 6)
+    m.drain_table_updates()
+    m.close("a")
+    m.open("b"), m.extend("b", 3)                     # same slot, first entry set again
+    (index, value), = m.drain_table_updates()
+    assert sorted(index) == [0, 1] and len(set(index)) == len(index)
+    assert dict(zip(index, value)) == {0: m.block_table("b")[0], 1: -1}

@@ -1,0 +1,195 @@
+"""Generation through the Python entry point and the command line, long decoding, and the first tokens
+of a sequence, against the plain implementation."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+from conftest import TINY
+from gpu_common import BF16_REL, check_rows, need_gpu, plain_logits, requests_for
+from replay_util import InProcessReplayer, gather, peak_tokens, trace_tail_decode
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def engine_for(folder, dtype, **options):
+    from torchinferno_b200.config.engine_config import EngineConfig
+    from torchinferno_b200.engine.engine import InferenceEngine
+    return InferenceEngine.from_config(EngineConfig(model=str(folder), dtype=dtype, **options))
+
+
+def requests(prompts, max_tokens, temperature=0.0, seeds=None, stop=()):
+    from torchinferno_b200.engine.types import GenerateRequest, SamplingConfig
+    return [GenerateRequest(f"g{i}", prompt_token_ids=p, sampling=SamplingConfig(
+        max_tokens, temperature, stop, 0 if seeds is None else seeds[i])) for i, p in enumerate(prompts)]
+
+
+def test_greedy_generation_equals_the_plain_implementation_fp32(model_folders):
+    """Tiny A: prompts of 7, 13 and 1 tokens, pages of 4, eight greedy tokens each, all together."""
+    need_gpu()
+    config, seed = TINY["A"]
+    prompts = list(requests_for(config, seed, [7, 13, 1]).values())
+    cfg, weights = plain_llama.read_model_folder(model_folders["A"])
+    want = [plain_llama.generate_greedy(cfg, weights, p, 8) for p in prompts]
+    with engine_for(model_folders["A"], "float32", page_size=4, max_batch_size=4) as engine:
+        outs = engine.generate_many(requests(prompts, 8))
+        assert [list(o.token_ids) for o in outs] == want
+        assert all(o.finish_reason == "length" and o.usage.completion_tokens == 8 for o in outs)
+        assert [o.usage.prompt_tokens for o in outs] == [7, 13, 1]
+        # one at a time through generate(), and streamed
+        single = engine.generate(requests(prompts[:1], 8)[0])
+        assert list(single.token_ids) == want[0]
+        streamed = list(engine.generate_stream(requests(prompts[1:2], 8)[0]))
+        assert [t.token_id for t in streamed[:-1]] == want[1] and streamed[-1].finished and streamed[-1].finish_reason == "length"
+        assert [t.index for t in streamed[:-1]] == list(range(8))
+        # a stop token ends the request and is emitted
+        stopped = engine.generate(requests(prompts[:1], 8, stop=(want[0][3],))[0])
+        assert list(stopped.token_ids) == want[0][:want[0].index(want[0][3]) + 1] and stopped.finish_reason == "stop"
+        assert engine.runner.cache.free_pages() == [engine.runner.cache.num_pages]
+
+
+def test_seeded_temperature_generation_fp32(model_folders):
+    """Tiny B: five prompts (1, 5, 17, 40, 96 tokens), pages of 16, portions of 32, twelve tokens at
+    temperature 0.8.  Each token must be the Gumbel-max choice of the plain logits for the engine's own
+    prefix with the request's seed, and must not depend on batching."""
+    need_gpu()
+    config, seed = TINY["B"]
+    prompts = list(requests_for(config, seed, [1, 5, 17, 40, 96]).values())
+    cfg, weights = plain_llama.read_model_folder(model_folders["B"])
+    seeds = [11, 12, 13, 14, 15]
+    with engine_for(model_folders["B"], "float32", page_size=16, prefill_chunk_size=32, max_num_batched_tokens=64) as engine:
+        together = engine.generate_many(requests(prompts, 12, 0.8, seeds))
+        alone = [engine.generate(r) for r in requests(prompts, 12, 0.8, seeds)]
+    assert [o.token_ids for o in together] == [o.token_ids for o in alone]
+    for prompt, out, s in zip(prompts, together, seeds):
+        ids = list(prompt) + list(out.token_ids)
+        logits = plain_llama.forward(cfg, weights, ids[:-1]).numpy()
+        for i, tok in enumerate(out.token_ids):
+            pos = len(prompt) + i
+            scores = plain_llama.gumbel_scores(logits[pos - 1], 0.8, s, pos)
+            assert scores[tok] >= scores.max() - 1e-4, (pos, tok, int(scores.argmax()))
+    assert len({o.token_ids for o in together}) == 5
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_greedy_generation_bf16_follows_the_plain_logits(model_folders, name):
+    """In bfloat16 a near-tie may go the other way, so each generated token is checked against the plain
+    logits of the engine's own prefix: it must be within the bf16 tolerance of the best."""
+    need_gpu()
+    config, seed = TINY[name]
+    prompts = list(requests_for(config, seed, [7, 13, 1, 60]).values())
+    cfg, weights = plain_llama.read_model_folder(model_folders[name])
+    with engine_for(model_folders[name], "bfloat16", page_size=16) as engine:
+        outs = engine.generate_many(requests(prompts, 10))
+    for prompt, out in zip(prompts, outs):
+        ids = list(prompt) + list(out.token_ids)
+        logits = plain_llama.forward(cfg, weights, ids[:-1]).numpy()
+        for i, tok in enumerate(out.token_ids):
+            row = logits[len(prompt) + i - 1]
+            assert row[tok] >= row.max() - 2 * BF16_REL * np.abs(logits).max()
+
+
+def test_preemption_on_a_small_pool_does_not_change_the_tokens(model_folders):
+    need_gpu()
+    config, seed = TINY["B"]
+    prompts = list(requests_for(config, seed + 1, [30, 45, 20, 33, 50, 12]).values())
+    with engine_for(model_folders["B"], "float32", page_size=16, max_batch_size=8) as engine:
+        roomy = engine.generate_many(requests(prompts, 40, 0.7, list(range(6))))
+    with engine_for(model_folders["B"], "float32", page_size=16, max_batch_size=8, num_pages=11) as engine:
+        tight = engine.generate_many(requests(prompts, 40, 0.7, list(range(6))))
+        assert engine.scheduler.stats["preemptions"] > 0
+        engine.runner.cache.audit()
+        assert engine.runner.cache.free_pages() == [11]
+    assert [o.token_ids for o in tight] == [o.token_ids for o in roomy]
+
+
+def test_cancel_gives_pages_back(model_folders):
+    need_gpu()
+    with engine_for(model_folders["A"], "float32", page_size=4) as engine:
+        stream = engine.generate_stream(requests([[1, 2, 3, 4, 5]], 50)[0])
+        first = [next(stream) for _ in range(3)]
+        assert all(not t.finished for t in first)
+        assert engine.cancel("g0")
+        rest = list(stream)
+        assert rest[-1].finished and rest[-1].finish_reason == "cancelled"
+        assert engine.runner.cache.free_pages() == [engine.runner.cache.num_pages]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(model_folders, dtype):
+    """One request decoded token by token for hundreds of steps, over many pages."""
+    need_gpu()
+    config, seed = TINY["C"]
+    reqs = requests_for(config, seed + 3, [620])
+    steps, index = trace_tail_decode(reqs, tail=500)
+    replayer = InProcessReplayer(model_folders["C"], dtype, max_tokens=peak_tokens(steps))
+    check_rows(gather(replayer.run(steps), index), model_folders["C"], reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_first_tokens_of_a_sequence(model_folders, dtype):
+    """Positions 0, 1, 2 one by one: the first token has nothing before it, the pages are new."""
+    need_gpu()
+    from torchinferno_b200.engine.batch import StepEntry
+    for name in ("A", "B"):
+        config, seed = TINY[name]
+        reqs = requests_for(config, seed + 5, [4, 4])
+        replayer = InProcessReplayer(model_folders[name], dtype, max_tokens=128)
+        rows = {}
+        with torch.inference_mode():
+            for pos in range(4):
+                out = replayer.runner.step([StepEntry(k, [v[pos]], [0]) for k, v in reqs.items()]).cpu().numpy()
+                for i, k in enumerate(reqs):
+                    rows[(k, pos)] = [out[i]]
+        check_rows(rows, model_folders[name], reqs, dtype)
+
+
+def test_step_refuses_bad_input_and_reports_no_room(model_folders):
+    need_gpu()
+    from torchinferno_b200.cache.manager import OutOfPages
+    from torchinferno_b200.engine.batch import StepEntry
+    from torchinferno_b200.engine.runner import StepError
+    replayer = InProcessReplayer(model_folders["A"], "float32", max_tokens=64)
+    runner = replayer.runner
+    with torch.inference_mode():
+        with pytest.raises(StepError, match="vocabulary"):
+            runner.step([StepEntry("a", [256], [0])])
+        with pytest.raises(StepError, match="twice"):
+            runner.step([StepEntry("a", [1], [0]), StepEntry("a", [2], [0])])
+        with pytest.raises(StepError, match="wants logits"):
+            runner.step([StepEntry("a", [1, 2], [2])])
+        with pytest.raises(StepError, match="no tokens"):
+            runner.step([StepEntry("a", [], [])])
+        runner.step([StepEntry("a", [1] * 40, [])])
+        with pytest.raises(OutOfPages):
+            runner.step([StepEntry("b", [1] * 20, []), StepEntry("a", [1] * 10, [])])
+        assert runner.cache.length("a") == 40 and "b" not in runner.cache      # nothing changed
+        runner.cache.audit()
+        with pytest.raises(StepError, match="limit"):
+            runner.step([StepEntry("c", [1] * 129, [])])
+
+
+def test_command_line(model_folders, tmp_path):
+    need_gpu()
+    folder = model_folders["A"]
+    cfg, weights = plain_llama.read_model_folder(folder)
+    cli = [sys.executable, str(ROOT / "bin" / "torchinferno-b200")]
+    out = subprocess.run(cli + ["generate", str(folder), "--input-ids", "5", "17", "3", "--new-tokens", "6", "--dtype", "float32",
+                                "--page-size", "4"], capture_output=True, text=True, check=True).stdout
+    line = next(l for l in out.splitlines() if l.startswith("output_ids="))
+    assert json.loads(line.split("=", 1)[1]) == [5, 17, 3] + plain_llama.generate_greedy(cfg, weights, [5, 17, 3], 6)
+    captured = tmp_path / "logits.json"
+    subprocess.run(cli + ["capture-logits", str(folder), str(captured), "--input-ids", "9", "8", "7", "--dtype", "float32"], check=True,
+                   capture_output=True)
+    got = json.loads(captured.read_text())["logits"]
+    assert np.allclose(got, plain_llama.forward(cfg, weights, [9, 8, 7])[-1].numpy(), atol=2e-5)
+    ok = subprocess.run(cli + ["validate-logits", str(folder), str(captured), "--dtype", "float32"], capture_output=True, text=True)
+    assert ok.returncode == 0 and "ok" in ok.stdout
+    smoke = subprocess.run(cli + ["serve-smoke", "--dtype", "bfloat16"], capture_output=True, text=True, check=True).stdout
+    assert smoke.count("finish_reason=length") == 3

@@ -1,0 +1,346 @@
+"""Each CUDA kernel alone against a plain PyTorch reference (float64 on the CPU), at sizes other
+than the engine's tiny models: widths that are no power of two, head sizes in steps of 16, odd
+group sizes, page sizes from 1 up, windows, ragged batches."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+from gpu_common import need_gpu
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-6, rtol=2e-6) if dtype == torch.float32 else dict(atol=1e-2, rtol=1.6e-2)
+
+
+def dev(t, dtype=None):
+    return t.to("cuda", dtype) if dtype else t.to("cuda")
+
+
+def as_ref(t):
+    return t.detach().cpu().double()
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+# ------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [100, 4096, 5000])
+def test_embedding(dtype, hidden):
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    table = rnd(37, hidden, dtype=dtype)
+    ids = torch.tensor([3, 36, 0, 3, 40, -1], dtype=torch.int32)
+    out = torch.empty(6, hidden, device="cuda")
+    ops.embedding(dev(ids), dev(table), out)
+    assert torch.equal(out[:4].cpu(), table[ids[:4].long()].float())
+    assert torch.isnan(out[4:]).all()                      # ids outside the table must show
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows, hidden, eps", [(5, 100, 1e-5), (3, 4096, 1e-6), (2, 5000, 3e-6), (1, 24, 1e-2)])
+def test_add_rmsnorm(dtype, rows, hidden, eps):
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    res0, delta, w = rnd(rows, hidden, scale=3), rnd(rows, hidden, dtype=dtype, seed=1), 1 + 0.2 * rnd(hidden, seed=2)
+    # plain norm of the residual
+    res = dev(res0.clone())
+    out = torch.empty(rows, hidden, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(None, res, dev(w), eps, out)
+    want = plain_llama.rms_norm(res0.double(), w.double(), eps)
+    assert torch.allclose(as_ref(out), want, **tol(dtype)) and torch.equal(res.cpu(), res0)
+    # fused add: the residual is updated in 32-bit, the normed rows leave in dtype
+    ops.add_rmsnorm(dev(delta), res, dev(w), eps, out)
+    summed = res0 + delta.float()
+    assert torch.equal(res.cpu(), summed)
+    assert torch.allclose(as_ref(out), plain_llama.rms_norm(summed.double(), w.double(), eps), **tol(dtype))
+    # rows: only the picked rows, residual untouched
+    pick = torch.tensor([rows - 1, 0, rows - 1], dtype=torch.int32)
+    out3 = torch.empty(3, hidden, dtype=dtype, device="cuda")
+    before = res.clone()
+    ops.add_rmsnorm(dev(delta), res, dev(w), eps, out3, rows=dev(pick))
+    want3 = plain_llama.rms_norm((summed + delta.float()).double(), w.double(), eps)[pick.long()]
+    assert torch.allclose(as_ref(out3), want3, **tol(dtype)) and torch.equal(res, before)
+    # rows of the activation type
+    x = rnd(rows, hidden, dtype=dtype, seed=5)
+    ops.rmsnorm(dev(x), dev(w), eps, out)
+    assert torch.allclose(as_ref(out), plain_llama.rms_norm(x.double(), w.double(), eps), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows, inter", [(7, 200), (1, 14336), (33, 17)])
+def test_swiglu(dtype, rows, inter):
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    gu = rnd(rows, 2 * inter, dtype=dtype, scale=3)
+    out = torch.empty(rows, inter, dtype=dtype, device="cuda")
+    ops.swiglu(dev(gu), out)
+    g, u = gu.double()[:, :inter], gu.double()[:, inter:]
+    assert torch.allclose(as_ref(out), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+
+
+def test_cast_and_scatter():
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    x = rnd(1000, 3)
+    y = ops.cast(dev(x), torch.empty(1000, 3, dtype=torch.bfloat16, device="cuda"))
+    assert torch.equal(y.cpu(), x.to(torch.bfloat16))
+    assert torch.equal(ops.cast(y, torch.empty(1000, 3, device="cuda")).cpu(), x.to(torch.bfloat16).float())
+    table = torch.full((4, 5), -1, dtype=torch.int32, device="cuda")
+    ops.scatter_i32(table, dev(torch.tensor([7, 0, 19, 99], dtype=torch.int32)), dev(torch.tensor([70, 1, 190, 5], dtype=torch.int32)))
+    want = torch.full((20,), -1, dtype=torch.int32)
+    want[7], want[0], want[19] = 70, 1, 190
+    assert torch.equal(table.cpu().view(-1), want)
+
+
+# ------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("m, n, k", [(1, 64, 64), (37, 129, 100), (130, 67, 257), (5, 1000, 4096)])
+@pytest.mark.parametrize("wdtype", DTYPES)
+def test_gemm_f32_is_true_fp32_and_row_independent(m, n, k, wdtype):
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    x, w = rnd(m, k, scale=2), rnd(n, k, dtype=wdtype, seed=3)
+    out = ops.gemm_f32(dev(x), dev(w), torch.empty(m, n, device="cuda"))
+    want = x.double() @ w.double().T
+    # fp32 accumulation over k terms: error far below what a tf32 or bf16 product would leave
+    assert (as_ref(out) - want).abs().max() <= 4e-7 * math.sqrt(k) * (x.abs().max() * w.float().abs().max()).item() * math.sqrt(k)
+    one = ops.gemm_f32(dev(x[m // 2: m // 2 + 1].contiguous()), dev(w), torch.empty(1, n, device="cuda"))
+    assert torch.equal(one[0], out[m // 2])               # a row does not depend on the rows beside it
+
+
+# -------------------------------------------------------------- RoPE + KV
+def paged_layout(n_requests, lengths, page_size, kv_heads, d, dtype, spare_pages=3, seed=0):
+    """A pool with NaN everywhere, shuffled page ids, and block tables for the given lengths."""
+    g = torch.Generator().manual_seed(seed)
+    pages_per = [-(-n // page_size) for n in lengths]
+    total = sum(pages_per) + spare_pages
+    order = torch.randperm(total, generator=g).tolist()
+    width = max(pages_per) + 1
+    table = torch.full((n_requests + 2, width), -1, dtype=torch.int32)
+    slots = torch.randperm(n_requests + 2, generator=g)[:n_requests].tolist()
+    for r, slot in enumerate(slots):
+        for p in range(pages_per[r]):
+            table[slot, p] = order.pop()
+    pool = torch.full((total, 2, kv_heads, page_size, d), float("nan"), dtype=dtype)
+    return pool, table, slots
+
+
+def fill_pages(pool, table, slot, k, v, start=0):
+    """k, v: [kv_heads, T, d] written at positions start.. of the request in ``slot``."""
+    p = pool.shape[3]
+    for t in range(k.shape[1]):
+        pos = start + t
+        page = int(table[slot, pos // p])
+        pool[page, 0, :, pos % p] = k[:, t]
+        pool[page, 1, :, pos % p] = v[:, t]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv_heads, d, rot, inter, page", [
+    (4, 2, 16, None, False, 4), (5, 1, 48, None, False, 3), (3, 3, 80, 32, False, 16), (8, 2, 128, None, True, 16),
+    (2, 1, 64, 0, False, 5)])
+def test_rope_append(dtype, heads, kv_heads, d, rot, inter, page):
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    from torchinferno_b200.parts.rope import rotary_frequencies
+    rot_dim = d if rot is None else rot
+    starts, lens = [0, 37, 5], [6, 1, 9]                 # three entries: a prompt start, a decode, a portion
+    pool, table, slots = paged_layout(3, [s + n for s, n in zip(starts, lens)], page, kv_heads, d, dtype)
+    positions = torch.tensor([s + i for s, n in zip(starts, lens) for i in range(n)], dtype=torch.int32)
+    token_slot = torch.tensor([slots[e] for e, n in enumerate(lens) for _ in range(n)], dtype=torch.int32)
+    n = int(positions.numel())
+    qkv = rnd(n, (heads + 2 * kv_heads) * d, dtype=dtype)
+    scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+               "original_max_position_embeddings": 16}
+    inv_freq = rotary_frequencies(rot_dim, 10000.0, scaling) if rot_dim else torch.zeros(0)
+    pool_d, q_out = dev(pool), torch.empty(n, heads * d, dtype=dtype, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.rope_append(dev(qkv), q_out, pool_d, dev(positions), dev(token_slot), dev(table), dev(inv_freq),
+                    heads, kv_heads, d, rot_dim=rot_dim, interleaved=inter, error_word=err)
+    assert int(err) == 0
+
+    def rotate(x):                                      # x [T, H, d] float64
+        if rot_dim == 0:
+            return x
+        ang = (positions.float()[:, None] * inv_freq[None, :]).double()      # fp32 product, as the kernel
+        c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        out = x.clone()
+        if inter:
+            lo, hi = x[..., 0:rot_dim:2], x[..., 1:rot_dim:2]
+            out[..., 0:rot_dim:2], out[..., 1:rot_dim:2] = lo * c - hi * s, hi * c + lo * s
+        else:
+            h = rot_dim // 2
+            lo, hi = x[..., :h], x[..., h:rot_dim]
+            out[..., :h], out[..., h:rot_dim] = lo * c - hi * s, hi * c + lo * s
+        return out
+
+    q, k, v = qkv.double().split([heads * d, kv_heads * d, kv_heads * d], dim=1)
+    assert torch.allclose(as_ref(q_out).view(n, heads, d), rotate(q.view(n, heads, d)), **tol(dtype))
+    want_k, got = rotate(k.reshape(n, kv_heads, d)), pool_d.cpu()
+    written = torch.zeros(pool.shape[0], page, dtype=torch.bool)
+    for t in range(n):
+        pos, slot = int(positions[t]), int(token_slot[t])
+        pg = int(table[slot, pos // page])
+        written[pg, pos % page] = True
+        assert torch.allclose(got[pg, 0, :, pos % page].double(), want_k[t], **tol(dtype))
+        assert torch.equal(got[pg, 1, :, pos % page], v.reshape(n, kv_heads, d)[t].to(dtype))
+    untouched = got.permute(0, 3, 1, 2, 4)[~written]
+    assert torch.isnan(untouched).all()                 # nothing else in the pool was written
+    # a page id outside the pool is reported, not written
+    bad = table.clone()
+    bad[slots[1], 37 // page] = pool.shape[0] + 5
+    ops.rope_append(dev(qkv), q_out, pool_d, dev(positions), dev(token_slot), dev(bad), dev(inv_freq),
+                    heads, kv_heads, d, rot_dim=rot_dim, interleaved=inter, error_word=err)
+    assert int(err) != 0
+
+
+# -------------------------------------------------------------- attention
+def attention_case(dtype, heads, kv_heads, d, page, entries, window=0, seed=0, standout=None):
+    """entries: list of (kv_start, q_len).  Returns kernel output and the float64 reference."""
+    from torchinferno_b200.kernels import ops
+    lengths = [s + n for s, n in entries]
+    pool, table, slots = paged_layout(len(entries), lengths, page, kv_heads, d, dtype, seed=seed)
+    q_rows, refs, q_start = [], [], [0]
+    group = heads // kv_heads
+    for e, (start, n) in enumerate(entries):
+        total = start + n
+        k, v = rnd(kv_heads, total, d, dtype=dtype, seed=seed + e), rnd(kv_heads, total, d, dtype=dtype, seed=seed + 50 + e)
+        q = rnd(heads, n, d, dtype=dtype, seed=seed + 100 + e)
+        if standout is not None and standout < total:
+            # every query shares a component along u, and one far key points along u: its score
+            # (about 12) stands out from the others (about N(0, 1)) for every query that may see it
+            u = torch.ones(d) / math.sqrt(d)
+            q = (q.float() * 0.2 + 8.0 * u).to(dtype)
+            k[:, standout] = (12.0 * math.sqrt(d) / 8.0 * u).to(dtype)
+            v[:, standout] = (v[:, standout].float() + 7).to(dtype)
+        fill_pages(pool, table, slots[e], k, v)
+        q_rows.append(q.transpose(0, 1).reshape(n, heads * d))
+        full_q = torch.zeros(heads, total, d, dtype=torch.float64)
+        full_q[:, start:] = q.double()
+        ref = plain_llama.causal_attention(full_q, k.double(), v.double(), group, window=window or None)[:, start:]
+        refs.append(ref.transpose(0, 1).reshape(n, heads * d))
+        q_start.append(q_start[-1] + n)
+    q_all = torch.cat(q_rows)
+    out = torch.empty_like(q_all, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    i32 = lambda xs: dev(torch.tensor(xs, dtype=torch.int32))
+    ops.paged_attention_simt(dev(q_all), dev(pool), out, i32(q_start), i32([s for s, _ in entries]), i32(slots),
+                             dev(table), len(entries), max(n for _, n in entries), heads, kv_heads, d,
+                             1.0 / math.sqrt(d), window=window, error_word=err)
+    assert int(err) == 0
+    return out.cpu(), torch.cat(refs)
+
+
+ATTN_SHAPES = [  # heads, kv_heads, d, page
+    (4, 2, 16, 4), (6, 3, 32, 16), (5, 1, 48, 3), (7, 7, 80, 1), (8, 2, 128, 16), (32, 1, 64, 64), (2, 1, 256, 16),
+    (14, 2, 96, 5)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv_heads, d, page", ATTN_SHAPES)
+def test_paged_attention_ragged_batch(dtype, heads, kv_heads, d, page):
+    need_gpu()
+    entries = [(0, 70), (130, 1), (31, 2), (0, 1), (63, 33)]       # whole prompt, decode, tiny portion, first token, portion over block edges
+    out, ref = attention_case(dtype, heads, kv_heads, d, page, entries)
+    assert torch.isfinite(out).all()                              # NaN in unwritten slots must not leak
+    assert torch.allclose(out.double(), ref, **(dict(atol=3e-6, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)))
+
+
+@pytest.mark.parametrize("window", [1, 5, 32, 33, 100])
+def test_paged_attention_window_edges(window):
+    need_gpu()
+    entries = [(0, 90), (200, 1), (95, 7)]
+    out, ref = attention_case(torch.float32, 4, 2, 32, 16, entries, window=window, seed=3)
+    assert torch.allclose(out.double(), ref, atol=3e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("standout", [0, 3, 511, 512, 700])
+def test_paged_attention_finds_one_far_key_among_hundreds(dtype, standout):
+    need_gpu()
+    entries = [(900, 1), (640, 70)]
+    out, ref = attention_case(dtype, 8, 2, 64, 16, entries, seed=5, standout=standout)
+    assert ref.abs().max() > 3                                    # the far key really dominates the reference
+    assert torch.allclose(out.double(), ref, **(dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=6e-2, rtol=2e-2)))
+
+
+def test_paged_attention_rows_do_not_depend_on_the_batch():
+    need_gpu()
+    alone, _ = attention_case(torch.float32, 6, 3, 32, 16, [(40, 9)], seed=9)
+    # same request (same seed → same q, k, v for entry 0) with others beside it
+    mixed, _ = attention_case(torch.float32, 6, 3, 32, 16, [(40, 9), (0, 50), (77, 1)], seed=9)
+    assert torch.equal(alone, mixed[:9])
+
+
+def test_attention_refuses_what_it_cannot_do():
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    i32 = lambda xs: dev(torch.tensor(xs, dtype=torch.int32))
+
+    def call(heads, kv_heads, d):
+        q = torch.zeros(4, heads * d, device="cuda")
+        pool = torch.zeros(2, 2, kv_heads, 16, d, device="cuda")
+        ops.paged_attention_simt(q, pool, torch.empty_like(q), i32([0, 4]), i32([0]), i32([0]), i32([[0, 1]]), 1, 4,
+                                 heads, kv_heads, d, 1.0)
+
+    call(4, 2, 256)
+    with pytest.raises(ops.KernelError, match="size"):
+        call(4, 2, 272)                                             # head size above 256
+    with pytest.raises(ops.KernelError, match="size"):
+        call(5, 2, 32)                                              # heads not a multiple of kv heads
+    with pytest.raises(ops.KernelError, match="CUDA tensor"):
+        ops.swiglu(torch.zeros(2, 4), torch.zeros(2, 2))            # no CPU path
+
+
+# --------------------------------------------------------------- sampling
+def test_greedy_takes_the_lowest_index_among_maxima_and_nan_wins():
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    logits = rnd(5, 3001)
+    logits[0, 77] = logits[0, 2900] = 9.0
+    logits[1, 3000] = 50.0
+    logits[2, 1500] = float("nan")
+    logits[3] = -float("inf")
+    out = ops.sample(dev(logits), torch.empty(5, dtype=torch.int32, device="cuda")).cpu()
+    assert out.tolist()[:4] == [77, 3000, 1500, 0] and out[4] == int(torch.argmax(logits[4]))
+
+
+@pytest.mark.parametrize("vocab", [17, 1000, 128256])
+def test_temperature_sampling_is_the_seeded_gumbel_max(vocab):
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    logits = rnd(4, vocab, scale=2)
+    temps, seeds, pos = [0.8, 1.5, 0.0, 0.3], [1, 2 ** 40 + 5, 3, -9], [0, 17, 5, 100000]
+    i64 = torch.tensor(seeds, dtype=torch.int64)
+    out = ops.sample(dev(logits), torch.empty(4, dtype=torch.int32, device="cuda"), dev(torch.tensor(temps)),
+                     dev(i64), dev(torch.tensor(pos, dtype=torch.int32))).cpu().tolist()
+    for r in range(4):
+        if temps[r] == 0:
+            assert out[r] == int(torch.argmax(logits[r]))
+            continue
+        scores = plain_llama.gumbel_scores(logits[r].numpy(), temps[r], seeds[r], pos[r])
+        assert scores[out[r]] >= scores.max() - 1e-4        # the argmax, up to float rounding of near-ties
+    # what else is in the batch does not matter
+    alone = ops.sample(dev(logits[1:2].contiguous()), torch.empty(1, dtype=torch.int32, device="cuda"),
+                       dev(torch.tensor(temps[1:2])), dev(i64[1:2].contiguous()), dev(torch.tensor(pos[1:2], dtype=torch.int32))).cpu()
+    assert int(alone) == out[1]
+
+
+def test_temperature_sampling_draws_from_the_softmax():
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5]]).repeat(20000, 1)
+    temp = 0.7
+    out = ops.sample(dev(logits), torch.empty(20000, dtype=torch.int32, device="cuda"), dev(torch.full((20000,), temp)),
+                     dev(torch.arange(20000, dtype=torch.int64)), dev(torch.zeros(20000, dtype=torch.int32))).cpu()
+    freq = torch.bincount(out.long(), minlength=5).double() / 20000
+    want = torch.softmax(logits[0].double() / temp, dim=0)
+    assert (freq - want).abs().max() < 0.012

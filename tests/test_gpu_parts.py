@@ -1,0 +1,295 @@
+"""Each part alone against the plain implementation, a schedule that names a layer twice and lets a
+call read another call's cache, and a toy mixer with state of its own that is registered, built and
+stepped without a change to the framework's files."""
+import dataclasses
+import json
+import math
+
+import pytest
+import torch
+
+import plain_llama
+from conftest import TINY_B, TINY_C
+from gpu_common import BF16_REL, F32_ATOL, F32_RTOL, need_gpu
+
+pytestmark = pytest.mark.gpu
+CUDA = torch.device("cuda")
+
+
+def _batch(entries):
+    """entries: (request id, slot, kv_start, q_len) -> StepBatch without tokens."""
+    from torchinferno_b200.engine.batch import EntryPlacement, build_batch
+    places, row = [], 0
+    for rid, slot, start, n in entries:
+        places.append(EntryPlacement(rid, slot, row, n, start))
+        row += n
+    batch, _ = build_batch(places, [[0] * p.q_len for p in places], [[] for _ in places], [], CUDA)
+    return batch
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    need_gpu()
+    from torchinferno_b200.parts.base import PartSpec, ResidualStream, build_part
+    norm = build_part("norm", PartSpec("rmsnorm", {"width": 120, "eps": 3e-6}), dtype=dtype, device=CUDA)
+    assert [(w.name, w.shape, w.init, w.role) for w in norm.weight_specs()] == [("weight", (120,), "ones", "vector")]
+    w = 1 + 0.3 * torch.randn(120)
+    norm.bind({"weight": w.to(torch.bfloat16).cuda()})
+    w = w.to(torch.bfloat16).double()
+    res = torch.randn(9, 120) * 2
+    stream = ResidualStream(res.clone().cuda(), dtype)
+    tol = dict(atol=2e-6, rtol=2e-6) if dtype == torch.float32 else dict(atol=2e-2, rtol=1e-2)
+    assert torch.allclose(stream.normed(norm).cpu().double(), plain_llama.rms_norm(res.double(), w, 3e-6), **tol)
+    delta = torch.randn(9, 120).to(dtype)
+    stream.add(delta.cuda())
+    with pytest.raises(RuntimeError):
+        stream.add(delta.cuda())
+    got = stream.normed(norm)
+    assert stream.pending is None and torch.equal(stream.residual.cpu(), res + delta.float())
+    assert torch.allclose(got.cpu().double(), plain_llama.rms_norm((res + delta.float()).double(), w, 3e-6), **tol)
+
+
+def test_rotary_part_tables_match_the_plain_law():
+    need_gpu()
+    from torchinferno_b200.parts.base import PartSpec, build_part
+    for cfg in (TINY_B, TINY_C, {**TINY_B, "rope_scaling": None}):
+        d = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
+        rope = build_part("position", PartSpec("rotary", {"head_dim": d, "theta": cfg["rope_theta"], "scaling": cfg["rope_scaling"]}),
+                          dtype=torch.float32, device=CUDA)
+        assert torch.equal(rope.inv_freq.cpu(), plain_llama.inverse_frequencies(cfg))
+    with pytest.raises(ValueError):
+        build_part("position", PartSpec("rotary", {"head_dim": 32, "theta": 1e4, "scaling": {"rope_type": "yarn"}}), dtype=torch.float32, device=CUDA)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part(dtype):
+    need_gpu()
+    from torchinferno_b200.parts.base import LayerContext, PartSpec, build_part
+    ffn = build_part("feed_forward", PartSpec("swiglu", {"hidden_size": 72, "intermediate_size": 200}), dtype=dtype, device=CUDA)
+    assert {w.name: w.shape for w in ffn.weight_specs()} == {"gate_proj.weight": (200, 72), "up_proj.weight": (200, 72), "down_proj.weight": (72, 200)}
+    ws = {"gate_proj.weight": torch.randn(200, 72) * 0.2, "up_proj.weight": torch.randn(200, 72) * 0.2, "down_proj.weight": torch.randn(72, 200) * 0.2}
+    ws = {k: v.to(torch.bfloat16) for k, v in ws.items()}
+    ffn.bind({k: v.to(dtype).cuda() for k, v in ws.items()})
+    x = torch.randn(11, 72).to(dtype)
+    got = ffn.forward(x.cuda(), LayerContext(batch=None))
+    want = plain_llama.swiglu_mlp(x.double(), *(ws[k].double() for k in ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=5e-2, rtol=3e-2)
+    assert torch.allclose(got.cpu().double(), want, **tol)
+
+
+def _attention_weights(hidden, heads, kv, d, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda *s: (torch.randn(*s, generator=g) * 0.3).to(torch.bfloat16)
+    return {"q_proj.weight": mk(heads * d, hidden), "k_proj.weight": mk(kv * d, hidden), "v_proj.weight": mk(kv * d, hidden),
+            "o_proj.weight": mk(hidden, heads * d)}
+
+
+def _plain_attention(x, ws, heads, kv, d, cfg, window=None):
+    T = x.shape[0]
+    inv = plain_llama.inverse_frequencies(cfg)
+    pos = torch.arange(T)
+    q = plain_llama.rotary((x @ ws["q_proj.weight"].double().T).view(T, heads, d).transpose(0, 1), pos, inv)
+    k = plain_llama.rotary((x @ ws["k_proj.weight"].double().T).view(T, kv, d).transpose(0, 1), pos, inv)
+    v = (x @ ws["v_proj.weight"].double().T).view(T, kv, d).transpose(0, 1)
+    a = plain_llama.causal_attention(q, k, v, heads // kv, window=window).transpose(0, 1).reshape(T, heads * d)
+    return a @ ws["o_proj.weight"].double().T
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 9])
+def test_attention_part_in_portions_over_its_own_cache(dtype, window):
+    need_gpu()
+    from torchinferno_b200.cache.manager import CacheManager
+    from torchinferno_b200.kernels import ops
+    from torchinferno_b200.parts.base import KVBinding, LayerContext, PartSpec, build_part
+    hidden, heads, kv, d = 120, 5, 1, 48
+    cfg = {**TINY_C}
+    position = PartSpec("rotary", {"head_dim": d, "theta": cfg["rope_theta"], "scaling": cfg["rope_scaling"]})
+    mixer = build_part("mixer", PartSpec("gqa_attention", {"hidden_size": hidden, "heads": heads, "kv_heads": kv, "head_dim": d,
+                                                            "position": position, "window": window}), dtype=dtype, device=CUDA)
+    assert mixer.cache_spec().window == window and mixer.state_spec() is None
+    ws = _attention_weights(hidden, heads, kv, d)
+    mixer.bind({k: v.to(dtype).cuda() for k, v in ws.items()})
+    cache = CacheManager([mixer.cache_spec()], [None], page_size=4, num_pages=40, max_requests=3, max_request_tokens=80,
+                         dtype=dtype, device=CUDA)
+    cache.groups[0].pool.fill_(float("nan"))
+    x = (torch.randn(70, hidden) * 0.5).to(dtype)
+    want = _plain_attention(x.double(), ws, heads, kv, d, cfg, window)
+    cache.open("warm"), cache.extend("warm", 3)        # another request holds the first pages and slot
+    outs, pos = [], 0
+    for n in (1, 2, 30, 5, 1, 31):
+        cache.open("r") if pos == 0 else None
+        start = cache.extend("r", n)
+        for group, (idx, val) in zip(cache.groups, cache.drain_table_updates()):
+            if idx:
+                ops.scatter_i32(group.table_device, torch.tensor(idx, dtype=torch.int32).cuda(), torch.tensor(val, dtype=torch.int32).cuda())
+        b = cache.kv_binding(0)
+        ctx = LayerContext(batch=_batch([("r", cache.slot("r"), start, n)]), kv=KVBinding(b.pool, b.block_table, b.page_size, b.window),
+                           error_word=cache.error_word)
+        outs.append(mixer.forward(x[pos:pos + n].cuda().contiguous(), ctx))
+        cache.release_behind_window("r")
+        pos += n
+    assert int(cache.error_word) == 0
+    if window:
+        assert -1 in cache.block_table("r")               # pages behind the window went back
+    got = torch.cat(outs).cpu().double()
+    if dtype == torch.float32:
+        assert torch.allclose(got, want, atol=2e-5, rtol=1e-4)
+    else:
+        assert (got - want).abs().max() <= BF16_REL * want.abs().max()
+
+
+def test_a_layer_run_twice_and_a_call_that_reads_another_calls_cache(model_folders):
+    need_gpu()
+    from torchinferno_b200.config.model_config import LlamaConfig
+    from torchinferno_b200.engine.batch import StepEntry
+    from torchinferno_b200.engine.factory import make_runner
+    from torchinferno_b200.models.llama import build_llama
+    from torchinferno_b200.models.model import CausalLM
+    from torchinferno_b200.models.spec import LayerCall
+    from torchinferno_b200.weights.loader import load_weights
+    folder = model_folders["B"]
+    config, weights = plain_llama.read_model_folder(folder)
+    spec = build_llama(LlamaConfig.from_dict(config))
+    # layer 0, layer 1, layer 0 again (cache of its own), then layer 2 reading what layer 1 stored
+    schedule = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2), LayerCall(2, 1, writes_cache=False))
+    model = CausalLM(dataclasses.replace(spec, schedule=schedule), dtype=torch.float32, device=CUDA)
+    load_weights(model, folder)
+    runner = make_runner(model, page_size=16, max_tokens=256, max_requests=2)
+    tokens = torch.randint(0, config["vocab_size"], (90,), generator=torch.Generator().manual_seed(5)).tolist()
+
+    # plain: the same order, with the shared cache spelled out
+    def layer(x, i, kv_from=None):
+        heads, kv = config["num_attention_heads"], config["num_key_value_heads"]
+        d, eps, T = config["hidden_size"] // heads, config["rms_norm_eps"], x.shape[0]
+        p, inv, pos = f"model.layers.{i}.", plain_llama.inverse_frequencies(config), torch.arange(T)
+        n = plain_llama.rms_norm(x, weights[p + "input_layernorm.weight"], eps)
+        q = plain_llama.rotary((n @ weights[p + "self_attn.q_proj.weight"].T).view(T, heads, d).transpose(0, 1), pos, inv)
+        if kv_from is None:
+            k = plain_llama.rotary((n @ weights[p + "self_attn.k_proj.weight"].T).view(T, kv, d).transpose(0, 1), pos, inv)
+            v = (n @ weights[p + "self_attn.v_proj.weight"].T).view(T, kv, d).transpose(0, 1)
+        else:
+            k, v = kv_from
+        a = plain_llama.causal_attention(q, k, v, heads // kv).transpose(0, 1).reshape(T, heads * d)
+        x = x + a @ weights[p + "self_attn.o_proj.weight"].T
+        n = plain_llama.rms_norm(x, weights[p + "post_attention_layernorm.weight"], eps)
+        x = x + plain_llama.swiglu_mlp(n, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"], weights[p + "mlp.down_proj.weight"])
+        return x, (k, v)
+
+    x = weights["model.embed_tokens.weight"][torch.tensor(tokens)]
+    x, _ = layer(x, 0)
+    x, kv1 = layer(x, 1)
+    x, _ = layer(x, 0)
+    x, _ = layer(x, 2, kv_from=kv1)
+    want = plain_llama.rms_norm(x, weights["model.norm.weight"], config["rms_norm_eps"]) @ weights["model.embed_tokens.weight"].T
+    with torch.inference_mode():
+        got = torch.cat([runner.step([StepEntry("a", tokens[:50], list(range(50)))]),
+                         runner.step([StepEntry("a", tokens[50:52], [0, 1])]),
+                         runner.step([StepEntry("a", tokens[52:], list(range(38)))])]).cpu().double()
+    assert torch.allclose(got, want, atol=F32_ATOL, rtol=F32_RTOL), (got - want).abs().max()
+
+
+# ------------------------------------------------------------------ toy mixer with state
+def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped(tmp_path):
+    """A mixer defined here: y_t = W . mean(x_0 .. x_t).  It keeps no keys; its state (the running sum
+    and the count) is of fixed size per request and lives in the cache manager's state slots.  It is
+    registered as a part, named by a new architecture's model description beside an attention layer,
+    given random weights by the framework's own writer, loaded, and stepped in portions."""
+    need_gpu()
+    from torchinferno_b200.config.registry import ArchitectureEntry, register_architecture, unregister_architecture
+    from torchinferno_b200.engine.batch import StepEntry
+    from torchinferno_b200.engine.factory import load_model, make_runner
+    from torchinferno_b200.models.spec import BlockSpec, LayerCall, ModelSpec
+    from torchinferno_b200.parts.base import Mixer, PartSpec, StateSpec, WeightSpec, register_part, unregister_part
+    from torchinferno_b200.weights.random_init import write_random_model
+
+    class RunningMeanMixer(Mixer):
+        def __init__(self, *, width, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.width = width
+
+        def weight_specs(self):
+            return [WeightSpec("mix.weight", (self.width, self.width), std=0.2)]
+
+        def bind(self, weights):
+            self.weight = weights["mix.weight"].float()
+
+        def state_spec(self):
+            return StateSpec((self.width + 1,), torch.float32)      # running sum and count
+
+        def forward(self, x, ctx):
+            out = torch.empty_like(x)
+            for e in ctx.batch.entries:                              # a request's tokens in order
+                rows = slice(e.q_start, e.q_start + e.q_len)
+                state = ctx.state[e.slot]
+                sums = state[:-1] + torch.cumsum(x[rows].float(), dim=0)
+                counts = state[-1] + torch.arange(1, e.q_len + 1, device=x.device)
+                out[rows] = ((sums / counts[:, None]) @ self.weight.T).to(x.dtype)
+                state[:-1], state[-1] = sums[-1], counts[-1]
+            return out
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyConfig:
+        vocab_size: int
+        width: int
+        inter: int
+
+        @classmethod
+        def from_dict(cls, data):
+            return cls(data["vocab_size"], data["width"], data["inter"])
+
+    def build_toy(cfg):
+        norm = PartSpec("rmsnorm", {"width": cfg.width, "eps": 1e-5})
+        ffn = PartSpec("swiglu", {"hidden_size": cfg.width, "intermediate_size": cfg.inter}, prefix="ffn.")
+        toy = PartSpec("prenorm", {"mixer": PartSpec("running_mean", {"width": cfg.width}, prefix="toy."), "feed_forward": ffn,
+                                   "mixer_norm": dataclasses.replace(norm, prefix="n1."), "feed_forward_norm": dataclasses.replace(norm, prefix="n2.")})
+        attn = PartSpec("prenorm", {"mixer": PartSpec("gqa_attention", {
+            "hidden_size": cfg.width, "heads": 2, "kv_heads": 1, "head_dim": 16, "position": PartSpec("none", {"head_dim": 16})}, prefix="attn."),
+            "feed_forward": ffn, "mixer_norm": dataclasses.replace(norm, prefix="n1."), "feed_forward_norm": dataclasses.replace(norm, prefix="n2.")})
+        return ModelSpec(architecture="ToyForCausalLM", hidden_size=cfg.width, vocab_size=cfg.vocab_size, max_positions=512,
+                         embedding_name="emb.weight", layers=(BlockSpec(toy, "l0."), BlockSpec(attn, "l1.")),
+                         schedule=(LayerCall(0, None), LayerCall(1, 0), LayerCall(0, None)),
+                         final_norm=dataclasses.replace(norm, prefix="final."), head_name="head.weight")
+
+    register_part("mixer", "running_mean", RunningMeanMixer)
+    register_architecture(ArchitectureEntry("ToyForCausalLM", ToyConfig, build_toy, model_types=("toy",)))
+    try:
+        cfg = {"architectures": ["ToyForCausalLM"], "model_type": "toy", "vocab_size": 50, "width": 24, "inter": 40}
+        write_random_model(cfg, tmp_path, seed=11)
+        model = load_model(tmp_path, dtype="float32")
+        assert [s is not None for s in model.state_requirements()] == [True, False, True] and len(model.cache_requirements()) == 1
+        runner = make_runner(model, page_size=4, max_tokens=128, max_requests=3)
+        reqs = {"a": torch.randint(0, 50, (37,)).tolist(), "b": torch.randint(0, 50, (9,)).tolist()}
+        with torch.inference_mode():
+            whole = {k: runner.step([StepEntry(k + "w", v, list(range(len(v))))]).cpu() for k, v in reqs.items()}
+            runner.end(["aw", "bw"])
+            parts = {"a": [], "b": []}
+            parts["a"].append(runner.step([StepEntry("a", reqs["a"][:5], list(range(5)))]).cpu())
+            mixed = runner.step([StepEntry("b", reqs["b"][:8], list(range(8))), StepEntry("a", reqs["a"][5:6], [0])]).cpu()
+            parts["b"].append(mixed[:8]), parts["a"].append(mixed[8:])
+            mixed = runner.step([StepEntry("a", reqs["a"][6:], list(range(31))), StepEntry("b", reqs["b"][8:], [0])]).cpu()
+            parts["a"].append(mixed[:31]), parts["b"].append(mixed[31:])
+            runner.end(["a", "b"])
+        for k in reqs:
+            assert torch.allclose(torch.cat(parts[k]), whole[k], atol=1e-5, rtol=1e-4)
+        # and the whole against plain arithmetic of the same description
+        _, w = plain_llama.read_model_folder(tmp_path)
+        def ffn(x, p):
+            return plain_llama.swiglu_mlp(x, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
+        def toy_layer(x):
+            n = plain_llama.rms_norm(x, w["l0.n1.weight"], 1e-5)
+            x = x + (torch.cumsum(n, 0) / torch.arange(1, len(n) + 1)[:, None]) @ w["l0.toy.mix.weight"].T
+            return x + ffn(plain_llama.rms_norm(x, w["l0.n2.weight"], 1e-5), "l0.")
+        def attn_layer(x):
+            n, T = plain_llama.rms_norm(x, w["l1.n1.weight"], 1e-5), x.shape[0]
+            q = (n @ w["l1.attn.q_proj.weight"].T).view(T, 2, 16).transpose(0, 1)
+            k = (n @ w["l1.attn.k_proj.weight"].T).view(T, 1, 16).transpose(0, 1)
+            v = (n @ w["l1.attn.v_proj.weight"].T).view(T, 1, 16).transpose(0, 1)
+            x = x + plain_llama.causal_attention(q, k, v, 2).transpose(0, 1).reshape(T, 32) @ w["l1.attn.o_proj.weight"].T
+            return x + ffn(plain_llama.rms_norm(x, w["l1.n2.weight"], 1e-5), "l1.")
+        x = toy_layer(attn_layer(toy_layer(w["emb.weight"][torch.tensor(reqs["a"])])))
+        want = plain_llama.rms_norm(x, w["final.weight"], 1e-5) @ w["head.weight"].T
+        assert torch.allclose(whole["a"].double(), want, atol=2e-5, rtol=1e-4), (whole["a"].double() - want).abs().max()
+    finally:
+        unregister_part("mixer", "running_mean")
+        unregister_architecture("ToyForCausalLM")

@@ -1,0 +1,95 @@
+"""Replay of the same requests cut in different ways, in 32-bit and in bfloat16, against the plain
+implementation: whole; most in one step and the last 32 tokens one by one; in portions of changing
+size down to two tokens; and mixed, up to four live requests with so few pages that they are used again."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import TINY
+from gpu_common import check_rows, need_gpu, requests_for
+from replay_util import (InProcessReplayer, gather, peak_tokens, run_trace_program, trace_mixed, trace_portions,
+                         trace_tail_decode, trace_whole)
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [7, 13, 1, 97, 128, 64, 2, 50], "B": [1, 5, 17, 40, 96, 211, 130, 64], "C": [3, 129, 70, 256, 31, 16, 200, 65]}
+
+
+def _requests(name):
+    config, seed = TINY[name]
+    return requests_for(config, seed, LENGTHS[name])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_every_way_of_cutting_agrees_with_the_plain_implementation(model_folders, name, dtype):
+    need_gpu()
+    folder, requests = model_folders[name], _requests(name)
+    rows = {}
+    for maker in (trace_whole, trace_tail_decode, trace_portions):
+        steps, index = maker(requests)
+        replayer = InProcessReplayer(folder, dtype, max_tokens=peak_tokens(steps))
+        rows[maker.__name__] = gather(replayer.run(steps), index)
+        check_rows(rows[maker.__name__], folder, requests, dtype)
+        assert replayer.runner.cache.free_pages() == [replayer.runner.cache.num_pages]
+    if dtype == "float32":
+        # the 32-bit kernels keep each row's arithmetic independent of the cut: bit-equal
+        whole = rows["trace_whole"]
+        for other in ("trace_tail_decode", "trace_portions"):
+            for key, got in rows[other].items():
+                assert np.array_equal(got[0], whole[key][0]), f"{other} differs from whole at {key}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("seed", [0, 1])
+def test_mixed_batches_on_a_tight_pool(model_folders, name, dtype, seed):
+    need_gpu()
+    folder, requests = model_folders[name], _requests(name)
+    steps, index = trace_mixed(requests, seed=seed)
+    assert max(len(s["entries"]) for s in steps) == 4
+    assert any(len(e["tokens"]) > 1 for s in steps for e in s["entries"] if any(len(o["tokens"]) == 1 for o in s["entries"]))
+    peak = peak_tokens(steps)
+    assert peak < sum(-(-len(t) // 64) * 64 for t in requests.values())      # pages must be used again
+    replayer = InProcessReplayer(folder, dtype, max_tokens=peak)
+    rows = gather(replayer.run(steps), index)
+    check_rows(rows, folder, requests, dtype)
+    cache = replayer.runner.cache
+    assert cache.free_pages() == [cache.num_pages] and not cache.live_requests
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_folders, tmp_path, dtype):
+    """bin/trace_run itself: the file protocol, `done` lines, page reuse, both dtypes."""
+    need_gpu()
+    folder, requests = model_folders["B"], _requests("B")
+    steps, index = trace_mixed(requests, seed=3)
+    extra, extra_index = trace_tail_decode({"r4": requests["r4"]}, tail=8)
+    for s in extra:                       # append after the mixed part, with later step numbers
+        s["step"] += len(steps)
+    index.update({(st + len(steps), row): key for (st, row), key in extra_index.items()})
+    steps = steps + extra
+    steps.insert(3, {"step": 1000, "entries": [], "end": []})      # a step that brings nothing
+    results = run_trace_program(folder, dtype, peak_tokens(steps), steps, tmp_path / "out")
+    check_rows(gather(results, index), folder, requests, dtype)
+
+
+def test_peaky_attention_shows_a_lost_key(model_folders, tmp_path):
+    """Random weights give nearly flat attention, which would hide a lost key among hundreds.
+    With q and k projections scaled up the scores spread, so every key counts."""
+    need_gpu()
+    from safetensors.torch import load_file, save_file
+    import shutil
+    folder = tmp_path / "peaky"
+    shutil.copytree(model_folders["C"], folder)
+    tensors = load_file(str(folder / "model.safetensors"))
+    for key in tensors:
+        if key.endswith("q_proj.weight") or key.endswith("k_proj.weight"):
+            tensors[key] = (tensors[key].float() * 12).to(torch.bfloat16)
+    save_file(tensors, str(folder / "model.safetensors"))
+    config, seed = TINY["C"]
+    requests = requests_for(config, seed + 7, [300, 77, 130, 610])
+    for maker in (trace_whole, trace_portions, trace_mixed):
+        steps, index = maker(requests)
+        replayer = InProcessReplayer(folder, "float32", max_tokens=peak_tokens(steps))
+        check_rows(gather(replayer.run(steps), index), folder, requests, "float32")

@@ -102,8 +102,8 @@ class CacheGroup:
     allocator: PageAllocator
     pool: torch.Tensor | None             # [layers_in_group, pages, 2, kv_heads, page_size, head_dim]
     table_device: torch.Tensor | None     # [max_slots, max_pages] int32
-    pending_index: list[int] = field(default_factory=list)   # flat indices into table_device
-    pending_value: list[int] = field(default_factory=list)
+    pending: dict[int, int] = field(default_factory=dict)    # flat index into table_device -> page id;
+                                                             # the last change to an entry wins
 
 
 @dataclass
@@ -234,8 +234,7 @@ class CacheManager:
                 page = group.allocator.alloc()
                 logical = len(request.pages[gi])
                 request.pages[gi].append(page)
-                group.pending_index.append(request.slot * self.max_pages_per_request + logical)
-                group.pending_value.append(page)
+                group.pending[request.slot * self.max_pages_per_request + logical] = page
         request.length = start + n_tokens
         return start
 
@@ -256,8 +255,7 @@ class CacheManager:
                 if page >= 0:
                     group.allocator.release(page)
                     request.pages[gi][logical] = -1
-                    group.pending_index.append(request.slot * self.max_pages_per_request + logical)
-                    group.pending_value.append(-1)
+                    group.pending[request.slot * self.max_pages_per_request + logical] = -1
                     released += 1
                 request.first_live[gi] += 1
         return released
@@ -269,8 +267,7 @@ class CacheManager:
             for logical, page in enumerate(request.pages[gi]):
                 if page >= 0:
                     group.allocator.release(page)
-                    group.pending_index.append(request.slot * self.max_pages_per_request + logical)
-                    group.pending_value.append(-1)
+                    group.pending[request.slot * self.max_pages_per_request + logical] = -1
         del self._requests[request_id]
         self._free_slots.append(request.slot)
 
@@ -279,11 +276,13 @@ class CacheManager:
 
     # -------------------------------------------------------------- device
     def drain_table_updates(self) -> list[tuple[list[int], list[int]]]:
-        """Queued (flat index, page id) changes of every group's device table; clears the queues."""
+        """Queued (flat index, page id) changes of every group's device table; clears the queues.
+
+        Every index appears once (they are applied by one scatter launch, whose writes are unordered)."""
         out = []
         for group in self.groups:
-            out.append((group.pending_index, group.pending_value))
-            group.pending_index, group.pending_value = [], []
+            out.append((list(group.pending.keys()), list(group.pending.values())))
+            group.pending = {}
         return out
 
     def kv_binding(self, cache_layer: int) -> GroupBinding:
