@@ -1,0 +1,371 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Llama-3.1-8B layer sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on stdout.  ``value`` is decoded tokens a second at batch 8 (device-timed over exactly K
+decode steps after W warm-up steps, prompts of 2,048 random ids, decoding on from there); ``e2e`` is the
+same through the Python entry point with host tokens in and out; ``prefill`` is one 2,048-token prompt;
+``points`` holds decoding at batch 1 and 64; ``roofline`` relates the decode step to the measured HBM
+bandwidth.  Weights are random (N(0, 0.02), norm weights 1) and token ids synthetic: there is no
+network for checkpoints or datasets.  Several GPUs are not supported: one line says so, exit code 2.
+
+The reference has no single-GPU Llama-3.1-8B number; its own harness times ``generate`` on random
+prompts with a device synchronisation on both sides (src/torchinferno/benchmarks/torchinferno_llama.py:169-194,
+347-348), which is what ``--impl reference`` does with the unmodified reference from ``baseline/_ref``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# Layer sizes of Llama-3.1-8B (the third configuration of BASELINE.json).
+LLAMA_8B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 128256, "hidden_size": 4096,
+    "intermediate_size": 14336, "num_hidden_layers": 32, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "max_position_embeddings": 131072, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "torch_dtype": "bfloat16",
+}
+FULL_LAYERS = 32
+PROMPT_LEN = 2048
+CONTEXT = 4096
+PAGE_SIZE = 16
+METRIC = "decode tok/s at batch 8 (Llama-3.1-8B bf16, 2048-token prompts, decode towards 4096 context)"
+
+
+def load_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        data = json.loads(path.read_text())
+        return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]),
+                "bf16_tflops_sustained": float(data.get("bf16_tflops_sustained", data["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0) -> None:
+        self.lines: list[str] = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def mark(self) -> int:
+        return len(self.lines)
+
+    def stop(self) -> None:
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, start: int = 0, end: int | None = None) -> dict:
+        rows = [l.split(", ") for l in self.lines[start:end] if l.count(",") >= 6]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        clocks = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].strip().lower() == "active" for r in rows)]
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": float(rows[0][1]),
+                "power_w_max": max(float(r[2]) for r in rows), "samples": len(rows), "reasons": reasons}
+
+
+# ------------------------------------------------------------------- ours
+def model_numbers(model, layers: int) -> dict:
+    cfg = model.spec.config
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    heads, kv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer_params = h * (heads + 2 * kv) * d + heads * d * h + 3 * h * i
+    return {"matmul_params": layers * per_layer_params + v * h, "per_layer_params": per_layer_params,
+            "kv_bytes_per_token": layers * 2 * kv * d * 2, "heads": heads, "head_dim": d, "layers": layers,
+            "lm_head_params": v * h}
+
+
+def prefill_requests(runner, ids, prompts, chunk: int) -> list[int]:
+    """Run the prompts through the step function in portions; returns the first drawn token of each."""
+    import torch
+    from torchinferno_b200.engine.batch import StepEntry
+    from torchinferno_b200.kernels import ops
+    first = []
+    for rid, prompt in zip(ids, prompts):
+        logits = None
+        for pos in range(0, len(prompt), chunk):
+            part = prompt[pos:pos + chunk]
+            last = pos + chunk >= len(prompt)
+            logits = runner.step([StepEntry(rid, part, [len(part) - 1] if last else [])])
+        out = torch.empty(1, dtype=torch.int32, device=logits.device)
+        ops.sample(logits, out)
+        first.append(int(out.item()))
+    return first
+
+
+def timed_decode(runner, batch: int, steps: int, warmup: int, numbers: dict, sampler, seed: int) -> dict:
+    """Prefill ``batch`` prompts, then time exactly ``steps`` device-side decode steps."""
+    import torch
+    from torchinferno_b200.kernels import ops
+    vocab = runner.model.spec.vocab_size
+    g = torch.Generator().manual_seed(seed)
+    prompts = torch.randint(0, vocab, (batch, PROMPT_LEN), generator=g).tolist()
+    ids = [f"b{batch}-{i}" for i in range(batch)]
+    first = prefill_requests(runner, ids, prompts, PROMPT_LEN)
+    temps, seeds = [0.0] * batch, list(range(batch))
+    drawn = runner.decode_loop(ids, first, warmup, temperature=temps, seeds=seeds)   # captures the graph too
+    torch.cuda.synchronize()
+    last = drawn[-1].tolist() if warmup else first
+    start_context = PROMPT_LEN + warmup
+    launches_before, replays_before = ops.launch_count(), runner.graph_replays
+    mark = sampler.mark()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    runner.decode_loop(ids, last, steps, temperature=temps, seeds=seeds)
+    end.record()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end)
+    clocks = sampler.summary(mark, sampler.mark())
+    graph = runner._graphs[batch]
+    launches = (ops.launch_count() - launches_before) + (runner.graph_replays - replays_before) * graph.launches
+    mean_context = start_context + (steps + 1) / 2            # cached tokens a step reads, on average
+    step_bytes = numbers["matmul_params"] * 2 + batch * mean_context * numbers["kv_bytes_per_token"]
+    runner.end(ids)
+    return {"batch": batch, "steps": steps, "ms": ms, "ms_per_step": ms / steps, "tokens_per_s": batch * steps / (ms / 1e3),
+            "context_from": start_context, "context_to": start_context + steps, "step_bytes": step_bytes,
+            "achieved_gbs": step_bytes / (ms / steps / 1e3) / 1e9, "launches": launches, "clocks": clocks}
+
+
+def timed_prefill(runner, numbers: dict, iters: int, warmup: int, seed: int) -> dict:
+    import torch
+    from torchinferno_b200.engine.batch import StepEntry
+    vocab = runner.model.spec.vocab_size
+    g = torch.Generator().manual_seed(seed)
+    times = []
+    for it in range(warmup + iters):
+        prompt = torch.randint(0, vocab, (PROMPT_LEN,), generator=g).tolist()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        runner.step([StepEntry(f"p{it}", prompt, [PROMPT_LEN - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        runner.end([f"p{it}"])
+        if it >= warmup:
+            times.append(begin.elapsed_time(end))
+    ms = statistics.median(times)
+    t = PROMPT_LEN
+    linear = 2 * t * (numbers["matmul_params"] - numbers["lm_head_params"]) + 2 * numbers["lm_head_params"]
+    attention = numbers["layers"] * 4 * numbers["heads"] * numbers["head_dim"] * t * (t + 1) / 2   # causal
+    return {"ms": ms, "tokens": t, "flops": linear + attention, "value": t / (ms / 1e3)}
+
+
+def timed_e2e(model, batch: int, steps: int, warmup: int, seed: int) -> dict:
+    """Through the Python entry point: host token ids in, host token ids out, every step."""
+    import torch
+    from torchinferno_b200.config.engine_config import EngineConfig
+    from torchinferno_b200.engine.engine import InferenceEngine
+    from torchinferno_b200.engine.types import GenerateRequest, SamplingConfig
+    config = EngineConfig(model="<in memory>", dtype="bfloat16", page_size=PAGE_SIZE, max_batch_size=batch,
+                          max_num_batched_tokens=PROMPT_LEN, prefill_chunk_size=PROMPT_LEN,
+                          kv_cache_tokens=batch * (PROMPT_LEN + warmup + steps + 2 * PAGE_SIZE))
+    engine = InferenceEngine(model, config)
+    g = torch.Generator().manual_seed(seed + 99)
+    prompts = torch.randint(0, model.spec.vocab_size, (batch, PROMPT_LEN), generator=g).tolist()
+    for i, prompt in enumerate(prompts):
+        engine.submit(GenerateRequest(f"e{i}", prompt_token_ids=prompt,
+                                      sampling=SamplingConfig(max_tokens=warmup + steps + 1, temperature=0.0)))
+    # run until every request decodes, plus the warm-up steps
+    while any(r.prefilling for r in engine.scheduler.running) or engine.scheduler.waiting:
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    h2d0, d2h0 = engine.stats["h2d_bytes"], engine.stats["d2h_bytes"]
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    tokens = 0
+    for _ in range(steps):
+        tokens += sum(1 for e in engine.step() if e.token is not None)
+    end.record()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end)
+    for i in range(batch):
+        engine.cancel(f"e{i}")
+    return {"value": tokens / (ms / 1e3), "unit": "tok/s", "ms_per_step": ms / steps, "tokens": tokens,
+            "h2d_bytes_per_step": (engine.stats["h2d_bytes"] - h2d0) / steps,
+            "d2h_bytes_per_step": (engine.stats["d2h_bytes"] - d2h0) / steps}
+
+
+def run_ours(args) -> dict:
+    import torch
+    from torchinferno_b200.engine.factory import make_runner, random_model
+    from torchinferno_b200.kernels.library import library_path, load_library
+    peaks = load_peaks()
+    load_library()
+    config = dict(LLAMA_8B)
+    config["num_hidden_layers"] = args.layers
+    sampler = ClockSampler()
+    with torch.inference_mode():
+        model = random_model(config, seed=0, dtype="bfloat16")
+        numbers = model_numbers(model, args.layers)
+        biggest = max([args.batch] + args.points)
+        pool_tokens = biggest * (CONTEXT + 2 * PAGE_SIZE)
+        runner = make_runner(model, page_size=PAGE_SIZE, max_tokens=pool_tokens, max_requests=biggest,
+                             max_request_tokens=CONTEXT + PAGE_SIZE, check_errors=False)
+        prefill = timed_prefill(runner, numbers, iters=5, warmup=3, seed=1)
+        main = timed_decode(runner, args.batch, args.steps, args.warmup, numbers, sampler, seed=2)
+        points = {}
+        for b in args.points:
+            r = timed_decode(runner, b, args.point_steps, args.warmup, numbers, sampler, seed=3 + b)
+            points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
+            points[f"decode_b{b}_ms_per_step"] = round(r["ms_per_step"], 4)
+            points[f"decode_b{b}_hbm_frac"] = round(r["achieved_gbs"] / peaks["hbm_gbs"], 4)
+        del runner
+        torch.cuda.empty_cache()
+        e2e = timed_e2e(model, args.batch, min(args.steps, args.e2e_steps), args.warmup, seed=4)
+    sampler.stop()
+    peak_flops = peaks["bf16_tflops"] * 1e12
+    record = {
+        "metric": METRIC, "value": round(main["tokens_per_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights N(0,0.02), norm weights 1",
+        "impl": "ours",
+        "config": {
+            "model": "Llama-3.1-8B sizes", "layers": args.layers, "layers_of_model": FULL_LAYERS, "hidden": 4096,
+            "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 14336, "vocab": 128256, "global_batch": args.batch,
+            "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "context_from": main["context_from"],
+            "context_to": main["context_to"], "page_size": PAGE_SIZE, "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (weights of a step: %.1f GB)" % (numbers["matmul_params"] * 2 / 1e9),
+            "peaks": peaks["source"],
+        },
+        "clocks": main["clocks"],
+        "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
+        "gpu_launches": main["launches"],
+        "prefill": {"value": round(prefill["value"], 1), "tokens": prefill["tokens"], "ms": round(prefill["ms"], 3),
+                    "frac": round(prefill["flops"] / (prefill["ms"] / 1e3) / peak_flops, 4),
+                    "peak_tflops": peaks["bf16_tflops"]},
+        "roofline": {"bound": "hbm", "achieved": round(main["achieved_gbs"], 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(main["achieved_gbs"] / peaks["hbm_gbs"], 4), "bytes_per_step": int(main["step_bytes"])},
+        "points": points,
+        "library": library_path(),
+    }
+    return record
+
+
+# -------------------------------------------------------------- reference
+def run_reference(args) -> dict:
+    """The unmodified reference from baseline/_ref: its Llama3PipelineForCausalLM.generate on the same sizes."""
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "torchinferno").is_dir():
+        return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --no-index --no-deps --target baseline/_ref)"}
+    sys.path.insert(0, str(ref))
+    os.environ.setdefault("HF_HUB_OFFLINE", "1")
+    try:
+        import tempfile
+
+        import torch
+        from safetensors.torch import save_file
+        from torchinferno.models.llama3.pipeline import Llama3PipelineForCausalLM
+    except Exception as exc:  # noqa: BLE001 - whatever stops the import is the reason
+        return {"impl": "reference", "unavailable": f"reference cannot be imported: {type(exc).__name__}: {exc}"[:300]}
+    from torchinferno_b200.weights.random_init import build_model, random_tensor
+    config = dict(LLAMA_8B)
+    config["num_hidden_layers"] = args.layers
+    config.pop("head_dim")                       # not a key of the reference's configuration
+    sampler = ClockSampler()
+    with tempfile.TemporaryDirectory(dir=os.environ.get("TMPDIR")) as tmp, torch.inference_mode():
+        folder = Path(tmp)
+        spec_model = build_model({**config, "head_dim": 128}, dtype=torch.bfloat16, device="cpu")
+        tensors = {name: random_tensor(ws, 0, device="cuda", dtype=torch.bfloat16).cpu()
+                   for name, ws in spec_model.expected_tensors().items()}
+        save_file(tensors, str(folder / "model.safetensors"))
+        (folder / "model.safetensors.index.json").write_text(json.dumps(
+            {"metadata": {}, "weight_map": {k: "model.safetensors" for k in tensors}}))
+        (folder / "config.json").write_text(json.dumps(config))
+        del tensors
+        model = Llama3PipelineForCausalLM.from_pretrained(str(folder), devices=["cuda:0"], dtype=torch.bfloat16)
+        g = torch.Generator().manual_seed(2)
+        prompts = torch.randint(0, config["vocab_size"], (args.batch, PROMPT_LEN), generator=g).cuda()
+        # the reference's generate() is one call; its decode steps are timed as (whole - prefill only)
+        def timed(new_tokens):
+            torch.cuda.synchronize()
+            b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            b.record()
+            model.generate(prompts, max_new_tokens=new_tokens, temperature=0.0)
+            e.record()
+            torch.cuda.synchronize()
+            return b.elapsed_time(e)
+        for _ in range(max(1, min(args.warmup, 3))):
+            timed(2)
+        mark = sampler.mark()
+        short = timed(1)
+        long = timed(1 + args.steps)
+        clocks = sampler.summary(mark, sampler.mark())
+    sampler.stop()
+    ms = long - short
+    return {"metric": METRIC, "value": round(args.batch * args.steps / (ms / 1e3), 1), "unit": "tok/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights",
+            "impl": "reference", "clocks": clocks,
+            "config": {"model": "Llama-3.1-8B sizes", "layers": args.layers, "layers_of_model": FULL_LAYERS,
+                       "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
+                       "path": "Llama3PipelineForCausalLM.generate (dense cache, torch ops)"},
+            "prefill": {"ms": round(short, 3), "tokens": args.batch * PROMPT_LEN,
+                        "value": round(args.batch * PROMPT_LEN / (short / 1e3), 1)}}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=2032)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
+    parser.add_argument("--points", type=int, nargs="*", default=[1, 64], help="other batch sizes to decode at")
+    parser.add_argument("--point-steps", type=int, default=None, help="decode steps of the other batch sizes (default: --steps)")
+    parser.add_argument("--e2e-steps", type=int, default=512)
+    args = parser.parse_args()
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"metric": METRIC, "unsupported": f"this engine runs on one GPU; --gpus {args.gpus} is not supported",
+                              "n_gpus": args.gpus}))
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.point_steps is None:
+        args.point_steps = args.steps
+    if PROMPT_LEN + args.warmup + max(args.steps, args.point_steps) + 1 > CONTEXT + PAGE_SIZE:
+        parser.error(f"--warmup + --steps must stay within the {CONTEXT}-token context after a {PROMPT_LEN}-token prompt")
+    record = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

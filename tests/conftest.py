@@ -43,7 +43,23 @@ TINY_C = {
                      "original_max_position_embeddings": 128},
     "rms_norm_eps": 3e-6, "tie_word_embeddings": False,
 }
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+# Head sizes the tensor-core attention kernels are built for (64 with groups of 2, 128 with groups of 4).
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 300, "hidden_size": 256, "intermediate_size": 320, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "max_position_embeddings": 1024,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 256},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+}
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 270, "hidden_size": 160, "intermediate_size": 224, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 1, "head_dim": 128, "max_position_embeddings": 1024,
+    "rope_theta": 10000.0, "rope_scaling": None, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+}
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
 
 
 @pytest.fixture(scope="session")

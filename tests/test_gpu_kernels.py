@@ -203,8 +203,12 @@ def test_rope_append(dtype, heads, kv_heads, d, rot, inter, page):
 
 
 # -------------------------------------------------------------- attention
-def attention_case(dtype, heads, kv_heads, d, page, entries, window=0, seed=0, standout=None):
-    """entries: list of (kv_start, q_len).  Returns kernel output and the float64 reference."""
+def attention_case(dtype, heads, kv_heads, d, page, entries, window=0, seed=0, standout=None, kernel="simt", splits=None):
+    """entries: list of (kv_start, q_len).  Returns kernel output and the float64 reference.
+
+    kernel "simt": the CUDA-core kernel; "mma": the tensor-core pair (portions by the prefill kernel,
+    single tokens by the split decode kernel, as the engine dispatches them); "mma_prefill": the
+    prefill kernel alone for every entry.  ``splits`` = (num_splits, chunk) forces a split."""
     from torchinferno_b200.kernels import ops
     lengths = [s + n for s, n in entries]
     pool, table, slots = paged_layout(len(entries), lengths, page, kv_heads, d, dtype, seed=seed)
@@ -232,9 +236,20 @@ def attention_case(dtype, heads, kv_heads, d, page, entries, window=0, seed=0, s
     out = torch.empty_like(q_all, device="cuda")
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
     i32 = lambda xs: dev(torch.tensor(xs, dtype=torch.int32))
-    ops.paged_attention_simt(dev(q_all), dev(pool), out, i32(q_start), i32([s for s, _ in entries]), i32(slots),
-                             dev(table), len(entries), max(n for _, n in entries), heads, kv_heads, d,
-                             1.0 / math.sqrt(d), window=window, error_word=err)
+    scale, max_q = 1.0 / math.sqrt(d), max(n for _, n in entries)
+    args = (dev(q_all), dev(pool), out, i32(q_start), i32([s for s, _ in entries]), i32(slots), dev(table), len(entries))
+    if kernel == "simt":
+        ops.paged_attention_simt(*args, max_q, heads, kv_heads, d, scale, window=window, error_word=err)
+    elif kernel == "mma_prefill":
+        ops.prefill_attention(*args, max_q, heads, kv_heads, d, scale, window=window)
+    else:
+        out.fill_(float("nan"))
+        singles = sum(1 for _, n in entries if n == 1)
+        if singles < len(entries):
+            ops.prefill_attention(*args, max_q, heads, kv_heads, d, scale, window=window, skip_single=singles > 0)
+        if singles:
+            ns, ch = splits or (None, None)
+            ops.decode_attention(*args, heads, kv_heads, d, scale, max(lengths), window=window, num_splits=ns, chunk=ch)
     assert int(err) == 0
     return out.cpu(), torch.cat(refs)
 
@@ -280,6 +295,48 @@ def test_paged_attention_rows_do_not_depend_on_the_batch():
     assert torch.equal(alone, mixed[:9])
 
 
+BF16_ATTN = dict(atol=2e-2, rtol=2e-2)
+MMA_SHAPES = [(4, 2, 64, 16), (8, 2, 128, 16), (32, 8, 128, 16), (3, 1, 64, 4), (6, 6, 128, 1), (40, 2, 64, 5), (7, 1, 128, 64)]
+
+
+@pytest.mark.parametrize("heads, kv_heads, d, page", MMA_SHAPES)
+@pytest.mark.parametrize("kernel", ["mma", "mma_prefill"])
+def test_tensor_core_attention_ragged_batch(heads, kv_heads, d, page, kernel):
+    need_gpu()
+    # a whole prompt over several tiles, decodes at short and long contexts, portions that start and
+    # end off the tile edges, a first token, a two-token portion
+    entries = [(0, 150), (130, 1), (31, 2), (0, 1), (63, 66), (700, 1), (64, 1), (255, 129)]
+    out, ref = attention_case(torch.bfloat16, heads, kv_heads, d, page, entries, kernel=kernel)
+    assert torch.isfinite(out).all()
+    assert torch.allclose(out.double(), ref, **BF16_ATTN), (out.double() - ref).abs().max()
+
+
+@pytest.mark.parametrize("splits", [(1, 1024), (2, 512), (3, 320), (16, 64), (9, 128)])
+def test_split_decode_attention_is_the_same_for_every_split(splits):
+    need_gpu()
+    entries = [(900, 1), (0, 1), (63, 1), (64, 1), (517, 1)]
+    out, ref = attention_case(torch.bfloat16, 8, 2, 128, 16, entries, kernel="mma", splits=splits, seed=2)
+    assert torch.allclose(out.double(), ref, **BF16_ATTN), (out.double() - ref).abs().max()
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 65, 200])
+@pytest.mark.parametrize("kernel", ["mma", "mma_prefill"])
+def test_tensor_core_attention_window_edges(window, kernel):
+    need_gpu()
+    entries = [(0, 190), (300, 1), (95, 70), (63, 1)]
+    out, ref = attention_case(torch.bfloat16, 4, 2, 64, 16, entries, window=window, seed=3, kernel=kernel)
+    assert torch.allclose(out.double(), ref, **BF16_ATTN), (out.double() - ref).abs().max()
+
+
+@pytest.mark.parametrize("standout", [0, 3, 511, 512, 700])
+def test_tensor_core_attention_finds_one_far_key_among_hundreds(standout):
+    need_gpu()
+    entries = [(900, 1), (640, 70)]
+    out, ref = attention_case(torch.bfloat16, 8, 2, 64, 16, entries, seed=5, standout=standout, kernel="mma")
+    assert ref.abs().max() > 3
+    assert torch.allclose(out.double(), ref, atol=6e-2, rtol=2e-2)
+
+
 def test_attention_refuses_what_it_cannot_do():
     need_gpu()
     from torchinferno_b200.kernels import ops
@@ -298,6 +355,11 @@ def test_attention_refuses_what_it_cannot_do():
         call(5, 2, 32)                                              # heads not a multiple of kv heads
     with pytest.raises(ops.KernelError, match="CUDA tensor"):
         ops.swiglu(torch.zeros(2, 4), torch.zeros(2, 2))            # no CPU path
+    assert ops.attention_mma_supports(128, 4) and not ops.attention_mma_supports(48, 4)
+    q = torch.zeros(4, 4 * 48, device="cuda", dtype=torch.bfloat16)
+    pool = torch.zeros(2, 2, 2, 16, 48, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="size"):              # the tensor-core kernels take 64 and 128 only
+        ops.prefill_attention(q, pool, torch.empty_like(q), i32([0, 4]), i32([0]), i32([0]), i32([[0, 1]]), 1, 4, 4, 2, 48, 1.0)
 
 
 # --------------------------------------------------------------- sampling

@@ -12,7 +12,9 @@ from replay_util import (InProcessReplayer, gather, peak_tokens, run_trace_progr
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [7, 13, 1, 97, 128, 64, 2, 50], "B": [1, 5, 17, 40, 96, 211, 130, 64], "C": [3, 129, 70, 256, 31, 16, 200, 65]}
+LENGTHS = {"A": [7, 13, 1, 97, 128, 64, 2, 50], "B": [1, 5, 17, 40, 96, 211, 130, 64], "C": [3, 129, 70, 256, 31, 16, 200, 65],
+           "D": [1, 64, 65, 300, 17, 129, 2, 700], "E": [5, 128, 63, 257, 1, 90, 420, 33]}
+NAMES = ["A", "B", "C", "D", "E"]
 
 
 def _requests(name):
@@ -21,7 +23,7 @@ def _requests(name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", NAMES)
 def test_every_way_of_cutting_agrees_with_the_plain_implementation(model_folders, name, dtype):
     need_gpu()
     folder, requests = model_folders[name], _requests(name)
@@ -41,7 +43,7 @@ def test_every_way_of_cutting_agrees_with_the_plain_implementation(model_folders
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", NAMES)
 @pytest.mark.parametrize("seed", [0, 1])
 def test_mixed_batches_on_a_tight_pool(model_folders, name, dtype, seed):
     need_gpu()

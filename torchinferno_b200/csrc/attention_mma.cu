@@ -1,0 +1,579 @@
+// Paged attention on tensor cores (bf16 in, fp32 softmax and accumulation), for head sizes that
+// are multiples of 64 up to 128:
+//
+//   prefill_attention_kernel   portions of prompts: a block owns 64 rows (token, query head) of one
+//                              kv head and walks the keys up to the causal edge, flash-attention style
+//   decode_attention_kernel    single tokens: the context of one (request, kv head) is split over
+//                              blocks ("split-K"); each block streams its keys once for all query heads
+//                              of the group and leaves (max, sum, unnormalised output) in scratch
+//   decode_merge_kernel        combines the partial results exactly (fp32)
+//
+// Formula as in attention_simt.cu (src/torchinferno/models/llama3/raw_ops.py:44-51; streaming form
+// src/torchinferno/kernels/triton_ops.py:2555-2574, whose grid is (batch, kv_heads) with no split
+// over the context: triton_ops.py:2661).  Keys and values come from the pages by block table
+// (layout [pages][2][kv_heads][page_size][head_dim]); any page size works, since every key row is
+// fetched by its own address.  Keys past a block's last query position are never read from memory
+// (they may be unwritten): their shared-memory rows are zero-filled, and they are masked.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace tib {
+
+constexpr int kBN = 64;        // keys per tile
+constexpr int kMmaThreads = 128;
+
+struct MmaAttnArgs {
+  const int* q_start;
+  const int* kv_start;
+  const int* slots;
+  const int* block_table;
+  int table_stride;
+  int heads, kv_heads, group;
+  int page_size;
+  int64_t page_stride;
+  int num_pages;
+  int window;
+  float scale_log2;      // scale * log2(e)
+  int chunk;             // decode: keys per split (multiple of kBN)
+  int num_splits;        // decode
+  int skip_single;       // prefill: leave single-token entries to the decode kernel
+};
+
+// ----------------------------------------------------------------- PTX bits
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are zero-filled, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Shared-memory tile [rows][D] of bf16 with the 16-byte chunks of a row XOR-swizzled by (row & 7),
+// so that the eight rows an ldmatrix touches fall into different banks.
+template <int D> __device__ __forceinline__ __nv_bfloat16* tile_at(__nv_bfloat16* tile, int row, int col) {
+  const int chunk = (col >> 3) ^ (row & 7);
+  return tile + row * D + chunk * 8 + (col & 7);
+}
+
+// Fetch keys [key0, key0 + kBN) of one kv head into k_tile / v_tile.  Keys outside
+// [first_key, last_key] and keys whose page is gone are zero-filled.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_tile, __nv_bfloat16* v_tile,
+                                             const __nv_bfloat16* pool, const int* table, int kvh, int key0,
+                                             int first_key, int last_key, const MmaAttnArgs& a) {
+  constexpr int CPR = D / 8;
+  const int64_t v_off = (int64_t)a.kv_heads * a.page_size * D;
+  for (int idx = threadIdx.x; idx < kBN * CPR; idx += kMmaThreads) {
+    const int r = idx / CPR, c = idx - r * CPR;
+    const int kp = key0 + r;
+    bool valid = kp >= first_key && kp <= last_key;
+    const __nv_bfloat16* src = pool;
+    if (valid) {
+      const int page = table[kp / a.page_size];
+      valid = page >= 0 && page < a.num_pages;
+      if (valid) src = pool + (int64_t)page * a.page_stride + ((int64_t)kvh * a.page_size + kp % a.page_size) * D + c * 8;
+    }
+    const int off = r * D + ((c ^ (r & 7)) << 3);
+    cp_async16(k_tile + off, src, valid);
+    cp_async16(v_tile + off, valid ? src + v_off : pool, valid);
+  }
+}
+
+// One 16-row by 16-key step of the streaming softmax for a warp: scores s (two n-tiles) are
+// already scaled and masked (-inf).  Updates m, l (per-thread partial sums), rescales o and
+// returns the probabilities packed as the A fragment of the P.V product.
+template <int ONT>
+__device__ __forceinline__ void softmax_step(float (&s)[2][4], float (&m)[2], float (&l)[2], float (&o)[ONT][4],
+                                             uint32_t (&p)[4]) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {  // h = 0: row g, h = 1: row g + 8
+    float mx = fmaxf(fmaxf(s[0][2 * h], s[0][2 * h + 1]), fmaxf(s[1][2 * h], s[1][2 * h + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m[h], mx);
+    const float base = m_new == -CUDART_INF_F ? 0.f : m_new;
+    const float alpha = exp2f(m[h] - base);
+    m[h] = m_new;
+    float sum = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      s[nt][2 * h] = exp2f(s[nt][2 * h] - base);
+      s[nt][2 * h + 1] = exp2f(s[nt][2 * h + 1] - base);
+      sum += s[nt][2 * h] + s[nt][2 * h + 1];
+    }
+    l[h] = l[h] * alpha + sum;
+#pragma unroll
+    for (int n = 0; n < ONT; ++n) {
+      o[n][2 * h] *= alpha;
+      o[n][2 * h + 1] *= alpha;
+    }
+  }
+  p[0] = pack_bf16(s[0][0], s[0][1]);
+  p[1] = pack_bf16(s[0][2], s[0][3]);
+  p[2] = pack_bf16(s[1][0], s[1][1]);
+  p[3] = pack_bf16(s[1][2], s[1][3]);
+}
+
+// s[2][4] = Q(16 x D) . K(16 keys x D)^T for the keys [slab, slab + 16) of a tile.
+template <int D>
+__device__ __forceinline__ void qk_slab(float (&s)[2][4], const uint32_t (&qf)[D / 16][4], __nv_bfloat16* k_tile,
+                                        int slab, int lane) {
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s[nt][j] = 0.f;
+  const int krow = slab + (lane & 7) + ((lane >> 4) << 3);
+  const int kcol = ((lane >> 3) & 1) << 3;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    uint32_t b[4];
+    ldmatrix_x4(b, tile_at<D>(k_tile, krow, ks * 16 + kcol));
+    mma_bf16(s[0], qf[ks], b[0], b[1]);
+    mma_bf16(s[1], qf[ks], b[2], b[3]);
+  }
+}
+
+// o(16 x D) += P(16 x 16 keys) . V(16 keys x D) for the keys [slab, slab + 16) of a tile.
+template <int D>
+__device__ __forceinline__ void pv_slab(float (&o)[D / 8][4], const uint32_t (&p)[4], __nv_bfloat16* v_tile, int slab,
+                                        int lane) {
+  const int vrow = slab + (lane & 7) + (((lane >> 3) & 1) << 3);
+  const int vcol = (lane >> 4) << 3;
+#pragma unroll
+  for (int dn = 0; dn < D / 16; ++dn) {
+    uint32_t b[4];
+    ldmatrix_x4_trans(b, tile_at<D>(v_tile, vrow, dn * 16 + vcol));
+    mma_bf16(o[2 * dn], p, b[0], b[1]);
+    mma_bf16(o[2 * dn + 1], p, b[2], b[3]);
+  }
+}
+
+// ------------------------------------------------------------------ prefill
+template <int D, int STAGES>
+__global__ void __launch_bounds__(kMmaThreads)
+prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
+                         __nv_bfloat16* __restrict__ out, MmaAttnArgs a) {
+  constexpr int BM = 64;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [BM][D]
+  __nv_bfloat16* k_s = q_s + BM * D;                                 // [STAGES][kBN][D]
+  __nv_bfloat16* v_s = k_s + STAGES * kBN * D;
+
+  const int entry = blockIdx.z, kvh = blockIdx.y;
+  const int row0 = a.q_start[entry];
+  const int q_len = a.q_start[entry + 1] - row0;
+  if (q_len == 1 && a.skip_single) return;
+  const int tok_per_tile = BM / a.group;
+  const int tile = gridDim.x - 1 - blockIdx.x;  // the longest tiles start first
+  const int t0 = tile * tok_per_tile;
+  if (t0 >= q_len) return;
+  const int nt = min(tok_per_tile, q_len - t0);
+  const int nrows = nt * a.group;
+  const int pos0 = a.kv_start[entry] + t0;
+  const int last_pos = pos0 + nt - 1;
+  const int first_key = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+  const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q_width = a.heads * D;
+
+  // queries of the tile -> shared memory (rows beyond nrows are zero)
+  constexpr int CPR = D / 8;
+  for (int idx = threadIdx.x; idx < BM * CPR; idx += kMmaThreads) {
+    const int r = idx / CPR, c = idx - r * CPR;
+    const bool valid = r < nrows;
+    const int t = r / a.group, g = r - t * a.group;
+    const __nv_bfloat16* src = valid ? q + (size_t)(row0 + t0 + t) * q_width + (kvh * a.group + g) * D + c * 8 : q;
+    cp_async16(q_s + r * D + ((c ^ (r & 7)) << 3), src, valid);
+  }
+  cp_async_commit();
+
+  const int kt0 = first_key / kBN, kt1 = last_pos / kBN;
+  const int n_tiles = kt1 - kt0 + 1;
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (st < n_tiles)
+      load_kv_tile<D>(k_s + st * kBN * D, v_s + st * kBN * D, pool, table, kvh, (kt0 + st) * kBN, first_key, last_pos, a);
+    cp_async_commit();
+  }
+
+  // the warp's 16 query rows as A fragments
+  uint32_t qf[D / 16][4];
+  cp_async_wait<STAGES - 1>();
+  __syncthreads();
+  {
+    const int qrow = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+    const int qcol = (lane >> 4) << 3;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qf[ks], tile_at<D>(q_s, qrow, ks * 16 + qcol));
+  }
+
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[n][j] = 0.f;
+
+  // positions of this thread's two rows (padded rows take the last position: harmless and finite)
+  const int g_row = lane >> 2, tig = lane & 3;
+  int qpos[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + g_row + 8 * h;
+    qpos[h] = r < nrows ? pos0 + r / a.group : last_pos;
+  }
+
+  for (int it = 0; it < n_tiles; ++it) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();
+    {
+      const int nxt = it + STAGES - 1;
+      if (nxt < n_tiles) {
+        const int st = nxt % STAGES;
+        load_kv_tile<D>(k_s + st * kBN * D, v_s + st * kBN * D, pool, table, kvh, (kt0 + nxt) * kBN, first_key, last_pos, a);
+      }
+      cp_async_commit();
+    }
+    __nv_bfloat16* k_tile = k_s + (it % STAGES) * kBN * D;
+    __nv_bfloat16* v_tile = v_s + (it % STAGES) * kBN * D;
+    const int key_base = (kt0 + it) * kBN;
+    // tiles wholly inside every row's allowed range need no mask
+    const bool need_mask = key_base + kBN - 1 > pos0 || (a.window > 0 && key_base < last_pos - a.window + 1);
+#pragma unroll
+    for (int kk = 0; kk < kBN / 16; ++kk) {
+      float s[2][4];
+      qk_slab<D>(s, qf, k_tile, kk * 16, lane);
+#pragma unroll
+      for (int n2 = 0; n2 < 2; ++n2)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float v = s[n2][j] * a.scale_log2;
+          if (need_mask) {
+            const int key = key_base + kk * 16 + n2 * 8 + tig * 2 + (j & 1);
+            const int qp = qpos[j >> 1];
+            const bool ok = key <= qp && (a.window <= 0 || key > qp - a.window);
+            v = ok ? v : -CUDART_INF_F;
+          }
+          s[n2][j] = v;
+        }
+      uint32_t p[4];
+      softmax_step<D / 8>(s, m, l, o, p);
+      pv_slab<D>(o, p, v_tile, kk * 16, lane);
+    }
+  }
+  cp_async_wait<0>();
+
+  // normalise and store
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float sum = l[h];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    const int r = warp * 16 + g_row + 8 * h;
+    if (r >= nrows) continue;
+    const float inv = 1.f / sum;
+    const int t = r / a.group, g = r - t * a.group;
+    __nv_bfloat16* dst = out + (size_t)(row0 + t0 + t) * q_width + (kvh * a.group + g) * D;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const uint32_t v = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+      *reinterpret_cast<uint32_t*>(dst + n * 8 + tig * 2) = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------- decode
+// grid: (num_splits, kv_heads * row_tiles, n_entries).  partial_o: [entries][heads][splits][D] fp32,
+// partial_ml: [entries][heads][splits][2] fp32 (max in log2 units, sum).
+template <int D, int STAGES>
+__global__ void __launch_bounds__(kMmaThreads)
+decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
+                        float* __restrict__ partial_o, float* __restrict__ partial_ml,
+                        __nv_bfloat16* __restrict__ out, MmaAttnArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [16][D]
+  __nv_bfloat16* k_s = q_s + 16 * D;                                 // [STAGES][kBN][D]
+  __nv_bfloat16* v_s = k_s + STAGES * kBN * D;
+
+  const int entry = blockIdx.z, split = blockIdx.x;
+  const int row_tiles = (a.group + 15) / 16;
+  const int kvh = blockIdx.y / row_tiles, rt = blockIdx.y - kvh * row_tiles;
+  const int row0 = a.q_start[entry];
+  if (a.q_start[entry + 1] - row0 != 1) return;  // portions belong to the prefill kernel
+  const int g0 = rt * 16;
+  const int nrows = min(16, a.group - g0);
+  const int pos = a.kv_start[entry];
+  const int first_key = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int kb = first_key / kBN * kBN + split * a.chunk;
+  const int ke = min(kb + a.chunk, pos + 1);  // exclusive
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g_row = lane >> 2, tig = lane & 3;
+  const int head0 = kvh * a.group + g0;
+
+  if (kb > pos) {  // nothing in this split: an empty partial, which the merge ignores
+    if (a.num_splits > 1 && threadIdx.x < nrows) {
+      float* ml = partial_ml + (((size_t)entry * a.heads + head0 + threadIdx.x) * a.num_splits + split) * 2;
+      ml[0] = -CUDART_INF_F;
+      ml[1] = 0.f;
+    }
+    return;
+  }
+  const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
+
+  constexpr int CPR = D / 8;
+  for (int idx = threadIdx.x; idx < 16 * CPR; idx += kMmaThreads) {
+    const int r = idx / CPR, c = idx - r * CPR;
+    const bool valid = r < nrows;
+    const __nv_bfloat16* src = valid ? q + (size_t)row0 * a.heads * D + (head0 + r) * D + c * 8 : q;
+    cp_async16(q_s + r * D + ((c ^ (r & 7)) << 3), src, valid);
+  }
+  cp_async_commit();
+
+  const int n_tiles = (ke - kb + kBN - 1) / kBN;
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (st < n_tiles)
+      load_kv_tile<D>(k_s + st * kBN * D, v_s + st * kBN * D, pool, table, kvh, kb + st * kBN, first_key, pos, a);
+    cp_async_commit();
+  }
+  uint32_t qf[D / 16][4];
+  cp_async_wait<STAGES - 1>();
+  __syncthreads();
+  {
+    const int qrow = (lane & 7) + (((lane >> 3) & 1) << 3);
+    const int qcol = (lane >> 4) << 3;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qf[ks], tile_at<D>(q_s, qrow, ks * 16 + qcol));
+  }
+
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[n][j] = 0.f;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();
+    {
+      const int nxt = it + STAGES - 1;
+      if (nxt < n_tiles) {
+        const int st = nxt % STAGES;
+        load_kv_tile<D>(k_s + st * kBN * D, v_s + st * kBN * D, pool, table, kvh, kb + nxt * kBN, first_key, pos, a);
+      }
+      cp_async_commit();
+    }
+    __nv_bfloat16* k_tile = k_s + (it % STAGES) * kBN * D;
+    __nv_bfloat16* v_tile = v_s + (it % STAGES) * kBN * D;
+    const int key_base = kb + it * kBN + warp * 16;  // each warp takes 16 keys of the tile
+    if (key_base > pos) continue;                    // (uniform in the warp)
+    float s[2][4];
+    qk_slab<D>(s, qf, k_tile, warp * 16, lane);
+#pragma unroll
+    for (int n2 = 0; n2 < 2; ++n2)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int key = key_base + n2 * 8 + tig * 2 + (j & 1);
+        const bool ok = key <= pos && key >= first_key && key < ke;
+        s[n2][j] = ok ? s[n2][j] * a.scale_log2 : -CUDART_INF_F;
+      }
+    uint32_t p[4];
+    softmax_step<D / 8>(s, m, l, o, p);
+    pv_slab<D>(o, p, v_tile, warp * 16, lane);
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // all warps are done with the tiles: their memory is reused below
+
+  // merge the four warps (each saw a quarter of the keys) in shared memory
+  float* red_o = reinterpret_cast<float*>(k_s);          // [4][16][D]
+  float* red_ml = red_o + 4 * 16 * D;                    // [4][16][2]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float sum = l[h];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    const int r = g_row + 8 * h;
+    if (tig == 0) {
+      red_ml[(warp * 16 + r) * 2] = m[h];
+      red_ml[(warp * 16 + r) * 2 + 1] = sum;
+    }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      red_o[(warp * 16 + r) * D + n * 8 + tig * 2] = o[n][2 * h];
+      red_o[(warp * 16 + r) * D + n * 8 + tig * 2 + 1] = o[n][2 * h + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nrows * D; idx += kMmaThreads) {
+    const int r = idx / D, dd = idx - r * D;
+    float mm = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red_ml[(w * 16 + r) * 2]);
+    const float base = mm == -CUDART_INF_F ? 0.f : mm;
+    float acc = 0.f, sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float wgt = exp2f(red_ml[(w * 16 + r) * 2] - base);
+      acc += red_o[(w * 16 + r) * D + dd] * wgt;
+      sum += red_ml[(w * 16 + r) * 2 + 1] * wgt;
+    }
+    if (a.num_splits == 1) {
+      out[(size_t)row0 * a.heads * D + (head0 + r) * D + dd] = __float2bfloat16_rn(acc / sum);
+    } else {
+      const size_t slot = ((size_t)entry * a.heads + head0 + r) * a.num_splits + split;
+      partial_o[slot * D + dd] = acc;
+      if (dd == 0) {
+        partial_ml[slot * 2] = mm;
+        partial_ml[slot * 2 + 1] = sum;
+      }
+    }
+  }
+}
+
+// grid: (heads, n_entries), D threads.
+template <int D>
+__global__ void __launch_bounds__(D)
+decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+                    __nv_bfloat16* __restrict__ out, const int* __restrict__ q_start, int heads, int num_splits) {
+  const int entry = blockIdx.y, head = blockIdx.x;
+  const int row0 = q_start[entry];
+  if (q_start[entry + 1] - row0 != 1) return;
+  const size_t base_slot = ((size_t)entry * heads + head) * num_splits;
+  float mm = -CUDART_INF_F;
+  for (int s = 0; s < num_splits; ++s) mm = fmaxf(mm, partial_ml[(base_slot + s) * 2]);
+  float acc = 0.f, sum = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float ms = partial_ml[(base_slot + s) * 2];
+    if (ms == -CUDART_INF_F) continue;  // an empty split wrote no output
+    const float wgt = exp2f(ms - mm);
+    acc += partial_o[(base_slot + s) * D + threadIdx.x] * wgt;
+    sum += partial_ml[(base_slot + s) * 2 + 1] * wgt;
+  }
+  out[(size_t)row0 * heads * D + head * D + threadIdx.x] = __float2bfloat16_rn(acc / sum);
+}
+
+template <int D>
+static int launch_prefill(const void* q, const void* pool, void* out, const MmaAttnArgs& a, int n_entries,
+                          int max_q_len, cudaStream_t stream) {
+  constexpr int STAGES = 2;
+  const size_t smem = sizeof(__nv_bfloat16) * ((size_t)64 * D + 2 * (size_t)STAGES * kBN * D);
+  auto kern = prefill_attention_kernel<D, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int tok_per_tile = 64 / a.group;
+  dim3 grid(ceil_div(max_q_len, tok_per_tile), a.kv_heads, n_entries);
+  kern<<<grid, kMmaThreads, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, (__nv_bfloat16*)out, a);
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}
+
+template <int D>
+static int launch_decode(const void* q, const void* pool, float* partial_o, float* partial_ml, void* out,
+                         const MmaAttnArgs& a, int n_entries, cudaStream_t stream) {
+  constexpr int STAGES = 3;
+  size_t smem = sizeof(__nv_bfloat16) * ((size_t)16 * D + 2 * (size_t)STAGES * kBN * D);
+  const size_t reduce = sizeof(__nv_bfloat16) * 16 * D + sizeof(float) * (4 * 16 * D + 4 * 16 * 2);
+  if (reduce > smem) smem = reduce;
+  auto kern = decode_attention_kernel<D, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int row_tiles = (a.group + 15) / 16;
+  dim3 grid(a.num_splits, a.kv_heads * row_tiles, n_entries);
+  kern<<<grid, kMmaThreads, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, partial_o, partial_ml,
+                                            (__nv_bfloat16*)out, a);
+  TIB_LAUNCH_CHECK();
+  if (a.num_splits > 1) {
+    dim3 mgrid(a.heads, n_entries);
+    decode_merge_kernel<D><<<mgrid, D, 0, stream>>>(partial_o, partial_ml, (__nv_bfloat16*)out, a.q_start, a.heads, a.num_splits);
+    TIB_LAUNCH_CHECK();
+  }
+  return TIB_OK;
+}
+
+static int fill_args(MmaAttnArgs& a, const int* q_start, const int* kv_start, const int* slots, const int* block_table,
+                     int table_stride, int heads, int kv_heads, int head_dim, int page_size, int64_t page_stride,
+                     int num_pages, int window, float scale) {
+  if (!q_start || !kv_start || !slots || !block_table) return TIB_E_ARG;
+  if (heads < 1 || kv_heads < 1 || heads % kv_heads != 0 || page_size < 1) return TIB_E_SIZE;
+  if (head_dim != 64 && head_dim != 128) return TIB_E_SIZE;
+  if (page_stride % 8 != 0) return TIB_E_ALIGN;  // 16-byte copies of key rows
+  a.q_start = q_start; a.kv_start = kv_start; a.slots = slots; a.block_table = block_table;
+  a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads; a.group = heads / kv_heads;
+  a.page_size = page_size; a.page_stride = page_stride; a.num_pages = num_pages; a.window = window;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.chunk = kBN; a.num_splits = 1; a.skip_single = 0;
+  return TIB_OK;
+}
+
+}  // namespace tib
+
+using namespace tib;
+
+// Which head sizes the tensor-core attention kernels are built for.
+TIB_API int tib_attention_mma_supports(int head_dim, int group) {
+  return (head_dim == 64 || head_dim == 128) && group >= 1 && group <= 64;
+}
+
+// Portions of prompts (and, unless skip_single, single tokens too).  bf16 only.
+TIB_API int tib_prefill_attention(const void* q, const void* pool, void* out, const int* q_start,
+                                  const int* kv_start, const int* slots, const int* block_table,
+                                  int table_stride, int n_entries, int max_q_len, int heads, int kv_heads,
+                                  int head_dim, int page_size, int64_t page_stride, int num_pages, int window,
+                                  float scale, int skip_single, cudaStream_t stream) {
+  if (n_entries == 0 || max_q_len == 0) return TIB_OK;
+  if (!q || !pool || !out) return TIB_E_ARG;
+  MmaAttnArgs a;
+  int rc = fill_args(a, q_start, kv_start, slots, block_table, table_stride, heads, kv_heads, head_dim, page_size,
+                     page_stride, num_pages, window, scale);
+  if (rc != TIB_OK) return rc;
+  if (a.group > 64 || n_entries > 65535 || kv_heads > 65535) return TIB_E_SIZE;
+  a.skip_single = skip_single;
+  return head_dim == 64 ? launch_prefill<64>(q, pool, out, a, n_entries, max_q_len, stream)
+                        : launch_prefill<128>(q, pool, out, a, n_entries, max_q_len, stream);
+}
+
+// Single-token entries, context split into num_splits parts of `chunk` keys (a multiple of 64;
+// num_splits * chunk must cover the longest context).  scratch_o: [n_entries * heads * num_splits *
+// head_dim] floats, scratch_ml: [n_entries * heads * num_splits * 2] floats (unused when num_splits == 1).
+TIB_API int tib_decode_attention(const void* q, const void* pool, void* out, float* scratch_o, float* scratch_ml,
+                                 const int* q_start, const int* kv_start, const int* slots, const int* block_table,
+                                 int table_stride, int n_entries, int heads, int kv_heads, int head_dim,
+                                 int page_size, int64_t page_stride, int num_pages, int window, float scale,
+                                 int num_splits, int chunk, cudaStream_t stream) {
+  if (n_entries == 0) return TIB_OK;
+  if (!q || !pool || !out) return TIB_E_ARG;
+  if (num_splits < 1 || chunk < kBN || chunk % kBN != 0) return TIB_E_SIZE;
+  if (num_splits > 1 && (!scratch_o || !scratch_ml)) return TIB_E_ARG;
+  MmaAttnArgs a;
+  int rc = fill_args(a, q_start, kv_start, slots, block_table, table_stride, heads, kv_heads, head_dim, page_size,
+                     page_stride, num_pages, window, scale);
+  if (rc != TIB_OK) return rc;
+  const int row_tiles = (a.group + 15) / 16;
+  if (n_entries > 65535 || (int64_t)kv_heads * row_tiles > 65535) return TIB_E_SIZE;
+  a.num_splits = num_splits;
+  a.chunk = chunk;
+  return head_dim == 64 ? launch_decode<64>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream)
+                        : launch_decode<128>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream);
+}

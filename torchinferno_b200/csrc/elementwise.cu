@@ -111,6 +111,19 @@ __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict_
   }
 }
 
+__global__ void advance_decode_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
+                                      int* __restrict__ positions, int* __restrict__ draw_positions,
+                                      int* __restrict__ history, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const int t = sampled[i];
+    token_ids[i] = t;
+    positions[i] += 1;
+    if (draw_positions) draw_positions[i] += 1;
+    if (history) history[i] = t;
+  }
+}
+
 static inline int norm_threads(int hidden) {
   int t = ((hidden + 3) / 4 + 31) / 32 * 32;  // about four elements a thread
   if (t < 32) t = 32;
@@ -211,6 +224,17 @@ TIB_API int tib_scatter_i32(int* dst, const int* index, const int* value, int n,
   if (n == 0) return TIB_OK;
   if (!dst || !index || !value || n < 0) return TIB_E_ARG;
   scatter_i32_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(dst, index, value, n, dst_size);
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}
+
+// After a decode step on the device: the drawn tokens become the next inputs and every
+// request moves one position on.  history (optional) receives the drawn tokens.
+TIB_API int tib_advance_decode(int* token_ids, const int* sampled, int* positions, int* draw_positions,
+                               int* history, int n, cudaStream_t stream) {
+  if (n == 0) return TIB_OK;
+  if (!token_ids || !sampled || !positions || n < 0) return TIB_E_ARG;
+  advance_decode_kernel<<<ceil_div(n, 128), 128, 0, stream>>>(token_ids, sampled, positions, draw_positions, history, n);
   TIB_LAUNCH_CHECK();
   return TIB_OK;
 }

@@ -49,7 +49,9 @@ class StepBatch:
     n_entries: int
     n_logits: int
     max_q_len: int
-    max_kv_len: int
+    max_kv_len: int               # bound on the longest context (cached + new tokens) of an entry
+    n_single: int = 0             # entries that bring one token
+    n_multi: int = 0              # entries that bring more
     entries: list[EntryPlacement] = field(default_factory=list)
     h2d_bytes: int = 0
 
@@ -95,6 +97,7 @@ def build_batch(placements: list[EntryPlacement], tokens: list[Sequence[int]], w
         slots=views[5], logit_rows=views[6], n_tokens=len(token_ids), n_entries=len(placements),
         n_logits=len(logit_rows), max_q_len=max((p.q_len for p in placements), default=0),
         max_kv_len=max((p.kv_start + p.q_len for p in placements), default=0),
+        n_single=sum(1 for p in placements if p.q_len == 1), n_multi=sum(1 for p in placements if p.q_len > 1),
         entries=placements, h2d_bytes=total * 4)
     updates = [(views[7 + 2 * i], views[8 + 2 * i]) for i in range(len(table_updates))]
     return batch, updates

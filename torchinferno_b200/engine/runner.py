@@ -23,13 +23,46 @@ class StepError(RuntimeError):
     pass
 
 
+class _DecodeGraph:
+    """The forward pass of a pure decode batch of ``n`` requests, captured once and replayed.
+
+    The reference replays whole-step decode graphs over static buffers that are refilled outside
+    the graph (src/torchinferno/runtime/paged_serving.py:333-397) and pads the batch by repeating a
+    row; here a graph is captured per exact batch size, so no padded row ever touches the cache.
+    The static integers are: token ids, positions (also the number of cached tokens, since each
+    request brings one token), slots (also the slot of each token), and the fixed ranges
+    q_start = 0..n and logit_rows = 0..n-1.
+    """
+
+    def __init__(self, n: int, device: torch.device, max_kv_len: int) -> None:
+        self.n = n
+        self.buffer = torch.zeros(5 * n + 1, dtype=torch.int32, device=device)
+        self.token_ids, self.positions, self.slots = (self.buffer[i * n:(i + 1) * n] for i in range(3))
+        self.q_start = self.buffer[3 * n: 4 * n + 1]
+        self.logit_rows = self.buffer[4 * n + 1: 5 * n + 1]
+        self.q_start.copy_(torch.arange(n + 1, dtype=torch.int32))
+        self.logit_rows.copy_(torch.arange(n, dtype=torch.int32))
+        self.batch = StepBatch(
+            token_ids=self.token_ids, positions=self.positions, token_slot=self.slots, q_start=self.q_start,
+            kv_start=self.positions, slots=self.slots, logit_rows=self.logit_rows, n_tokens=n, n_entries=n,
+            n_logits=n, max_q_len=1, max_kv_len=max_kv_len, n_single=n, n_multi=0, entries=[])
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+        self.launches = 0          # kernels of this library inside the graph
+
+
 class ModelRunner:
-    def __init__(self, model, cache: CacheManager, *, check_errors: bool = True) -> None:
+    def __init__(self, model, cache: CacheManager, *, check_errors: bool = True, use_cuda_graphs: bool = True) -> None:
         self.model = model
         self.cache = cache
         self.check_errors = check_errors
         self.last_batch: StepBatch | None = None
         self.steps = 0
+        # a mixer with per-request state walks the entries on the host: no graph for such a model
+        self.use_cuda_graphs = use_cuda_graphs
+        self._graph_ok = all(spec is None for spec in model.state_requirements())
+        self._graphs: dict[int, _DecodeGraph] = {}
+        self.graph_replays = 0
 
     # --------------------------------------------------------------- step
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -68,6 +101,10 @@ class ModelRunner:
         if new_requests > cache.free_slots():
             raise StepError(f"the step opens {new_requests} requests, {cache.free_slots()} slots are free")
 
+        if (self.use_cuda_graphs and self._graph_ok and cache.device.type == "cuda"
+                and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries)):
+            return self._decode_step(entries)
+
         placements: list[EntryPlacement] = []
         row = 0
         for entry in entries:
@@ -89,6 +126,102 @@ class ModelRunner:
         if self.check_errors:
             self.raise_on_device_error()
         return logits
+
+    # ------------------------------------------------------- decode graphs
+    def _apply_table_updates(self) -> int:
+        """Upload and apply queued block-table changes; returns the bytes copied to the device."""
+        copied = 0
+        for group, (index, value) in zip(self.cache.groups, self.cache.drain_table_updates()):
+            if not index:
+                continue
+            host = torch.tensor([index, value], dtype=torch.int32).pin_memory()
+            dev = host.to(self.cache.device, non_blocking=True)
+            ops.scatter_i32(group.table_device, dev[0], dev[1])
+            copied += host.numel() * 4
+        return copied
+
+    def _graph_for(self, n: int) -> _DecodeGraph:
+        if n not in self._graphs:
+            self._graphs[n] = _DecodeGraph(n, self.cache.device, self.cache.max_request_tokens)
+        return self._graphs[n]
+
+    def _run_decode_graph(self, g: _DecodeGraph) -> torch.Tensor:
+        """Logits [n, vocab] for the decode batch described by ``g``'s static buffers."""
+        if g.graph is None:
+            # First use at this batch size: run once outside a graph (this also does every lazy
+            # set-up of libraries and kernels), then capture the same pass for later steps.
+            logits = self.model.forward(g.batch, self.cache)
+            torch.cuda.synchronize(self.cache.device)
+            before = ops.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                g.logits = self.model.forward(g.batch, self.cache)
+            g.launches = ops.launch_count() - before
+            g.graph = graph
+            return logits
+        g.graph.replay()
+        self.graph_replays += 1
+        return g.logits
+
+    def _decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        cache = self.cache
+        n = len(entries)
+        g = self._graph_for(n)
+        starts = []
+        for entry in entries:
+            if entry.request_id not in cache:
+                cache.open(entry.request_id)
+            starts.append(cache.extend(entry.request_id, 1))
+        slots = [cache.slot(e.request_id) for e in entries]
+        host = torch.tensor([int(e.tokens[0]) for e in entries] + starts + slots, dtype=torch.int32).pin_memory()
+        g.buffer[:3 * n].copy_(host, non_blocking=True)
+        copied = host.numel() * 4 + self._apply_table_updates()
+        g.batch.h2d_bytes = copied
+        g.batch.entries = [EntryPlacement(e.request_id, s, i, 1, st) for i, (e, s, st) in enumerate(zip(entries, slots, starts))]
+        self.last_batch = g.batch
+        logits = self._run_decode_graph(g)
+        for entry in entries:
+            cache.release_behind_window(entry.request_id)
+        self.steps += 1
+        if self.check_errors:
+            self.raise_on_device_error()
+        return logits
+
+    def decode_loop(self, request_ids: Sequence[Hashable], tokens: Sequence[int], steps: int, *,
+                    temperature: Sequence[float] | None = None, seeds: Sequence[int] | None = None) -> torch.Tensor:
+        """Decode ``steps`` tokens for each request without a host round trip per token.
+
+        Every request must be open; ``tokens[i]`` is its next input token (the last one drawn, not
+        yet in the cache).  Each step runs the captured decode pass, draws the next tokens on the
+        device and feeds them back; the host only runs ahead with page bookkeeping.  Returns the
+        drawn tokens [steps, n] (int32, on the device).  Nothing stops a request early.
+        """
+        cache = self.cache
+        n = len(request_ids)
+        if not (self._graph_ok and cache.device.type == "cuda"):
+            raise StepError("decode_loop needs a CUDA device and a model without per-request host state")
+        g = self._graph_for(n)
+        lengths = [cache.length(r) for r in request_ids]
+        slots = [cache.slot(r) for r in request_ids]
+        dev = cache.device
+        g.buffer[:3 * n].copy_(torch.tensor(list(map(int, tokens)) + lengths + slots, dtype=torch.int32).pin_memory(),
+                               non_blocking=True)
+        draw_positions = torch.tensor([l + 1 for l in lengths], dtype=torch.int32).to(dev)
+        temps = None if temperature is None else torch.tensor(list(temperature), dtype=torch.float32).to(dev)
+        seed_t = None if seeds is None else torch.tensor(list(seeds), dtype=torch.int64).to(dev)
+        history = torch.empty((steps, n), dtype=torch.int32, device=dev)
+        sampled = torch.empty(n, dtype=torch.int32, device=dev)
+        for step in range(steps):
+            for request_id in request_ids:
+                cache.extend(request_id, 1)
+            self._apply_table_updates()
+            logits = self._run_decode_graph(g)
+            ops.sample(logits, sampled, temps, seed_t, draw_positions)
+            ops.advance_decode(g.token_ids, sampled, g.positions, draw_positions, history[step])
+            for request_id in request_ids:
+                cache.release_behind_window(request_id)
+            self.steps += 1
+        return history
 
     def end(self, request_ids: Iterable[Hashable]) -> None:
         """These requests are finished: what they hold is given back."""

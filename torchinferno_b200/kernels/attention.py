@@ -16,7 +16,16 @@ from torchinferno_b200.kernels import ops
 def paged_attention(q: torch.Tensor, out: torch.Tensor, ctx, heads: int, kv_heads: int, head_dim: int,
                     scale: float, window: int | None) -> torch.Tensor:
     batch, kv = ctx.batch, ctx.kv
+    win = int(window or 0)
+    if q.dtype == torch.bfloat16 and ops.attention_mma_supports(head_dim, heads // kv_heads):
+        args = (q, kv.pool, out, batch.q_start, batch.kv_start, batch.slots, kv.block_table, batch.n_entries)
+        if batch.n_multi:
+            ops.prefill_attention(*args, batch.max_q_len, heads, kv_heads, head_dim, scale, window=win,
+                                  skip_single=batch.n_single > 0)
+        if batch.n_single:
+            ops.decode_attention(*args, heads, kv_heads, head_dim, scale, batch.max_kv_len, window=win)
+        return out
     return ops.paged_attention_simt(
         q, kv.pool, out, batch.q_start, batch.kv_start, batch.slots, kv.block_table,
         batch.n_entries, batch.max_q_len, heads, kv_heads, head_dim, scale,
-        window=int(window or 0), error_word=ctx.error_word)
+        window=win, error_word=ctx.error_word)

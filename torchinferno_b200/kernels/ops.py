@@ -79,7 +79,8 @@ def lib() -> ctypes.CDLL:
     library = load_library()
     if not _signatures_set:
         for fn in ("tib_embedding", "tib_add_rmsnorm", "tib_rmsnorm", "tib_swiglu", "tib_cast",
-                   "tib_scatter_i32", "tib_rope_append", "tib_paged_attention_simt", "tib_gemm_f32", "tib_sample"):
+                   "tib_scatter_i32", "tib_advance_decode", "tib_rope_append", "tib_paged_attention_simt", "tib_gemm_f32", "tib_sample",
+                   "tib_attention_mma_supports", "tib_prefill_attention", "tib_decode_attention"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
     return library
@@ -258,3 +259,92 @@ def scatter_i32(dst: torch.Tensor, index: torch.Tensor, value: torch.Tensor) -> 
     _check("scatter_i32", lib().tib_scatter_i32(_ptr(dst), _ptr(index), _ptr(value), c_int(index.numel()),
                                                 c_int64(dst.numel()), _stream()))
     return dst
+
+
+def advance_decode(token_ids: torch.Tensor, sampled: torch.Tensor, positions: torch.Tensor,
+                   draw_positions: torch.Tensor | None = None, history: torch.Tensor | None = None) -> None:
+    """token_ids = sampled; positions += 1; draw_positions += 1; history = sampled (all int32, length n)."""
+    n = token_ids.numel()
+    for name, t in (("token_ids", token_ids), ("sampled", sampled), ("positions", positions),
+                    ("draw_positions", draw_positions), ("history", history)):
+        if t is not None:
+            _need(t, name, torch.int32)
+            if t.numel() < n:
+                raise KernelError(f"advance_decode: {name} is shorter than token_ids")
+    _check("advance_decode", lib().tib_advance_decode(_ptr(token_ids), _ptr(sampled), _ptr(positions),
+                                                      _ptr(draw_positions), _ptr(history), c_int(n), _stream()))
+
+
+def attention_mma_supports(head_dim: int, group: int) -> bool:
+    """Whether the tensor-core attention kernels are built for this head size and group size."""
+    return bool(lib().tib_attention_mma_supports(c_int(head_dim), c_int(group)))
+
+
+def _check_attention_args(q, pool, out, q_start, kv_start, slots, block_table, n_entries, heads, kv_heads, head_dim):
+    _need(q, "q", torch.bfloat16), _need(pool, "pool", torch.bfloat16), _need(out, "out", torch.bfloat16)
+    for name, t in (("q_start", q_start), ("kv_start", kv_start), ("slots", slots), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if pool.dim() != 5 or pool.shape[1] != 2 or pool.shape[2] != kv_heads or pool.shape[4] != head_dim:
+        raise KernelError(f"attention: pool shape {tuple(pool.shape)} does not fit")
+    if q.numel() != out.numel() or q.numel() % (heads * head_dim):
+        raise KernelError("attention: q / out do not fit the head counts")
+    if q_start.numel() < n_entries + 1 or kv_start.numel() < n_entries or slots.numel() < n_entries:
+        raise KernelError("attention: entry arrays are shorter than n_entries")
+
+
+def prefill_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor,
+                      kv_start: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, n_entries: int,
+                      max_q_len: int, heads: int, kv_heads: int, head_dim: int, scale: float, window: int = 0,
+                      skip_single: bool = False) -> torch.Tensor:
+    """Causal attention of prompt portions over the paged cache on tensor cores (bf16)."""
+    _check_attention_args(q, pool, out, q_start, kv_start, slots, block_table, n_entries, heads, kv_heads, head_dim)
+    _check("prefill_attention", lib().tib_prefill_attention(
+        _ptr(q), _ptr(pool), _ptr(out), _ptr(q_start), _ptr(kv_start), _ptr(slots), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(n_entries), c_int(max_q_len), c_int(heads), c_int(kv_heads), c_int(head_dim),
+        c_int(pool.shape[3]), c_int64(pool.stride(0)), c_int(pool.shape[0]), c_int(window), c_float(scale),
+        c_int(int(skip_single)), _stream()))
+    return out
+
+
+def decode_split(n_entries: int, heads: int, kv_heads: int, max_kv_len: int, target_blocks: int = 592) -> tuple[int, int]:
+    """(num_splits, chunk): how the longest context is cut so that about ``target_blocks`` blocks run."""
+    group = heads // kv_heads
+    blocks = max(1, n_entries * kv_heads * ((group + 15) // 16))
+    tiles = max(1, -(-max_kv_len // 64))
+    splits = max(1, min(-(-tiles // 2), -(-target_blocks // blocks)))   # at least two tiles a split
+    per = -(-tiles // splits)
+    return -(-tiles // per), per * 64
+
+
+def decode_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor,
+                     kv_start: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, n_entries: int,
+                     heads: int, kv_heads: int, head_dim: int, scale: float, max_kv_len: int, window: int = 0,
+                     scratch: torch.Tensor | None = None, num_splits: int | None = None,
+                     chunk: int | None = None) -> torch.Tensor:
+    """Attention of single tokens over the paged cache, the context split over blocks (bf16).
+
+    Entries that bring more than one token are skipped.  ``max_kv_len`` bounds the longest context
+    (keys 0 .. position) of the batch; ``scratch`` (fp32, at least n_entries * heads * num_splits *
+    (head_dim + 2) elements) holds the partial results when there is more than one split.
+    """
+    _check_attention_args(q, pool, out, q_start, kv_start, slots, block_table, n_entries, heads, kv_heads, head_dim)
+    if num_splits is None or chunk is None:
+        num_splits, chunk = decode_split(n_entries, heads, kv_heads, max_kv_len)
+    if num_splits * chunk < max_kv_len:
+        raise KernelError("decode_attention: num_splits * chunk does not cover the longest context")
+    scratch_o = scratch_ml = None
+    if num_splits > 1:
+        need = n_entries * heads * num_splits * (head_dim + 2)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        _need(scratch, "scratch", torch.float32)
+        if scratch.numel() < need:
+            raise KernelError("decode_attention: scratch is too small")
+        scratch_o = scratch
+        scratch_ml = scratch[n_entries * heads * num_splits * head_dim:]
+    _check("decode_attention", lib().tib_decode_attention(
+        _ptr(q), _ptr(pool), _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), _ptr(q_start), _ptr(kv_start), _ptr(slots),
+        _ptr(block_table), c_int(block_table.stride(0)), c_int(n_entries), c_int(heads), c_int(kv_heads), c_int(head_dim),
+        c_int(pool.shape[3]), c_int64(pool.stride(0)), c_int(pool.shape[0]), c_int(window), c_float(scale),
+        c_int(num_splits), c_int(chunk), _stream()))
+    return out
