@@ -30,6 +30,7 @@ struct MmaAttnArgs {
   int table_stride;
   int heads, kv_heads, group;
   int page_size;
+  int page_shift;        // log2(page_size) when it is a power of two, else -1
   int64_t page_stride;
   int num_pages;
   int window;
@@ -82,18 +83,33 @@ template <int D>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_tile, __nv_bfloat16* v_tile,
                                              const __nv_bfloat16* pool, const int* table, int kvh, int key0,
                                              int first_key, int last_key, const MmaAttnArgs& a) {
-  constexpr int CPR = D / 8;
+  constexpr int CPR = D / 8;                       // 16-byte chunks per key row
+  constexpr int ROWS = kMmaThreads / CPR;          // rows fetched by one pass of the block
+  constexpr int PASSES = kBN / ROWS;
   const int64_t v_off = (int64_t)a.kv_heads * a.page_size * D;
-  for (int idx = threadIdx.x; idx < kBN * CPR; idx += kMmaThreads) {
-    const int r = idx / CPR, c = idx - r * CPR;
-    const int kp = key0 + r;
-    bool valid = kp >= first_key && kp <= last_key;
-    const __nv_bfloat16* src = pool;
-    if (valid) {
-      const int page = table[kp / a.page_size];
-      valid = page >= 0 && page < a.num_pages;
-      if (valid) src = pool + (int64_t)page * a.page_stride + ((int64_t)kvh * a.page_size + kp % a.page_size) * D + c * 8;
+  const int c = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
+  // first all page ids (independent loads, one latency), then all copies
+  int page[PASSES], within[PASSES];
+#pragma unroll
+  for (int i = 0; i < PASSES; ++i) {
+    const int kp = key0 + r0 + i * ROWS;
+    const bool valid = kp >= first_key && kp <= last_key;
+    int idx, off;
+    if (a.page_shift >= 0) {
+      idx = kp >> a.page_shift;
+      off = kp & (a.page_size - 1);
+    } else {
+      idx = kp / a.page_size;
+      off = kp - idx * a.page_size;
     }
+    within[i] = off;
+    page[i] = valid ? __ldg(table + idx) : -1;
+  }
+#pragma unroll
+  for (int i = 0; i < PASSES; ++i) {
+    const int r = r0 + i * ROWS;
+    const bool valid = page[i] >= 0 && page[i] < a.num_pages;
+    const __nv_bfloat16* src = valid ? pool + (int64_t)page[i] * a.page_stride + ((int64_t)kvh * a.page_size + within[i]) * D + c * 8 : pool;
     const int off = r * D + ((c ^ (r & 7)) << 3);
     cp_async16(k_tile + off, src, valid);
     cp_async16(v_tile + off, valid ? src + v_off : pool, valid);
@@ -521,7 +537,9 @@ static int fill_args(MmaAttnArgs& a, const int* q_start, const int* kv_start, co
   if (page_stride % 8 != 0) return TIB_E_ALIGN;  // 16-byte copies of key rows
   a.q_start = q_start; a.kv_start = kv_start; a.slots = slots; a.block_table = block_table;
   a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads; a.group = heads / kv_heads;
-  a.page_size = page_size; a.page_stride = page_stride; a.num_pages = num_pages; a.window = window;
+  a.page_size = page_size; a.page_shift = -1;
+  for (int sft = 0; sft < 31; ++sft) if ((1 << sft) == page_size) a.page_shift = sft;
+  a.page_stride = page_stride; a.num_pages = num_pages; a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.chunk = kBN; a.num_splits = 1; a.skip_single = 0;
   return TIB_OK;

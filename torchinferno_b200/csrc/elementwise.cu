@@ -61,6 +61,54 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restric
   }
 }
 
+// bf16 rows whose width is a multiple of 8 and at most 8 * 1024: every thread keeps its eight
+// elements in registers, so the row is read once (16-byte loads) and written once.
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_bf16x8_kernel(const __nv_bfloat16* __restrict__ delta, float* __restrict__ residual,
+                          const int* __restrict__ rows, const float* __restrict__ weight,
+                          __nv_bfloat16* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int orow = blockIdx.x;
+  const int srow = rows ? rows[orow] : orow;
+  const int c = threadIdx.x * 8;
+  const bool active = c < hidden;
+  const bool write_back = (delta != nullptr) && (rows == nullptr);
+  float h[8];
+  float ss = 0.f;
+  if (active) {
+    float* res = residual + (size_t)srow * hidden + c;
+    const float4 r0 = *reinterpret_cast<const float4*>(res), r1 = *reinterpret_cast<const float4*>(res + 4);
+    h[0] = r0.x; h[1] = r0.y; h[2] = r0.z; h[3] = r0.w; h[4] = r1.x; h[5] = r1.y; h[6] = r1.z; h[7] = r1.w;
+    if (delta) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(delta + (size_t)srow * hidden + c);
+      const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(d2[i]);
+        h[2 * i] += f.x;
+        h[2 * i + 1] += f.y;
+      }
+    }
+    if (write_back) {
+      *reinterpret_cast<float4*>(res) = make_float4(h[0], h[1], h[2], h[3]);
+      *reinterpret_cast<float4*>(res + 4) = make_float4(h[4], h[5], h[6], h[7]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += h[i] * h[i];
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = rsqrtf(total / (float)hidden + eps);
+  if (active) {
+    const float4 w0 = *reinterpret_cast<const float4*>(weight + c), w1 = *reinterpret_cast<const float4*>(weight + c + 4);
+    const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    uint4 packed;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(h[2 * i] * inv * w[2 * i], h[2 * i + 1] * inv * w[2 * i + 1]);
+    *reinterpret_cast<uint4*>(out + (size_t)orow * hidden + c) = packed;
+  }
+}
+
 // Plain RMSNorm of rows held in type T (for parts that norm something other
 // than the residual stream, e.g. per-head norms).
 template <typename T>
@@ -92,6 +140,28 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     const float g = to_f32(src[col]);
     const float u = to_f32(src[inter + col]);
     out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+// bf16, intermediate width a multiple of 8: 16-byte loads and stores.
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
+                                     int inter, int64_t total_vec) {
+  const int per_row = inter >> 3;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / per_row;
+    const int col = (int)(i - row * per_row) << 3;
+    const __nv_bfloat16* src = gate_up + row * 2 * (int64_t)inter + col;
+    const uint4 graw = *reinterpret_cast<const uint4*>(src), uraw = *reinterpret_cast<const uint4*>(src + inter);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+    uint4 packed;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+      o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + row * (int64_t)inter + col) = packed;
   }
 }
 
@@ -159,7 +229,11 @@ TIB_API int tib_add_rmsnorm(const void* delta, float* residual, const int* rows,
   const int threads = norm_threads(hidden);
   if (dtype == TIB_F32)
     add_rmsnorm_kernel<float><<<n_out, threads, 0, stream>>>((const float*)delta, residual, rows, weight, (float*)out, hidden, eps);
-  else if (dtype == TIB_BF16)
+  else if (dtype == TIB_BF16 && hidden % 8 == 0 && hidden <= 8192 &&
+           (((uintptr_t)residual | (uintptr_t)weight | (uintptr_t)out | (uintptr_t)delta) & 15) == 0) {
+    const int vec_threads = ((hidden / 8) + 31) / 32 * 32;
+    add_rmsnorm_bf16x8_kernel<<<n_out, vec_threads, 0, stream>>>((const __nv_bfloat16*)delta, residual, rows, weight, (__nv_bfloat16*)out, hidden, eps);
+  } else if (dtype == TIB_BF16)
     add_rmsnorm_kernel<__nv_bfloat16><<<n_out, threads, 0, stream>>>((const __nv_bfloat16*)delta, residual, rows, weight, (__nv_bfloat16*)out, hidden, eps);
   else
     return TIB_E_DTYPE;
@@ -191,7 +265,10 @@ TIB_API int tib_swiglu(const void* gate_up, void* out, int n_rows, int inter, in
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == TIB_F32)
     swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
-  else if (dtype == TIB_BF16)
+  else if (dtype == TIB_BF16 && inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+    const int64_t vec = total / 8, want_v = (vec + threads - 1) / threads;
+    swiglu_bf16x8_kernel<<<(int)(want_v < 148 * 16 ? want_v : 148 * 16), threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, vec);
+  } else if (dtype == TIB_BF16)
     swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
   else
     return TIB_E_DTYPE;

@@ -92,6 +92,73 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
   }
 }
 
+// bf16, full rotate-half rotation, head size a multiple of 16: every work item is eight dims of
+// the lower half and their partners in the upper half (two 16-byte loads and stores).
+__global__ void __launch_bounds__(256)
+rope_append_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                          __nv_bfloat16* __restrict__ pool, const int* __restrict__ positions,
+                          const int* __restrict__ token_slot, const int* __restrict__ block_table,
+                          int table_stride, const float* __restrict__ inv_freq, int heads, int kv_heads,
+                          int head_dim, int page_size, int64_t page_stride, int num_pages, int write_kv,
+                          int* __restrict__ error_word) {
+  extern __shared__ float cs[];  // cos[d/2], sin[d/2]
+  const int tok = blockIdx.x;
+  const int pos = positions[tok];
+  const int half = head_dim >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float ang = (float)pos * inv_freq[i];
+    cs[i] = cosf(ang);
+    cs[half + i] = sinf(ang);
+  }
+  __syncthreads();
+  const int q_width = heads * head_dim, kv_width = kv_heads * head_dim;
+  const __nv_bfloat16* row = qkv + (size_t)tok * (q_width + 2 * kv_width);
+  const int chunks = half >> 3;                 // work items per head
+  __nv_bfloat16* kpage = nullptr;
+  int off = 0;
+  if (write_kv) {
+    const int page = block_table[(size_t)token_slot[tok] * table_stride + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+      if (error_word && threadIdx.x == 0) atomicExch(error_word, 1 + tok);
+      write_kv = 0;
+    } else {
+      kpage = pool + (size_t)page * page_stride;
+      off = pos % page_size;
+    }
+  }
+  const int rot_heads = heads + (write_kv ? kv_heads : 0);
+  for (int w = threadIdx.x; w < rot_heads * chunks; w += blockDim.x) {
+    const int hh = w / chunks, c = (w - hh * chunks) << 3;
+    const __nv_bfloat16* src = row + hh * head_dim;   // q heads then k heads are contiguous in qkv
+    __nv_bfloat16* dst = hh < heads ? q_out + (size_t)tok * q_width + hh * head_dim
+                                    : kpage + ((size_t)(hh - heads) * page_size + off) * head_dim;
+    const uint4 lraw = *reinterpret_cast<const uint4*>(src + c), hraw = *reinterpret_cast<const uint4*>(src + half + c);
+    const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&lraw);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hraw);
+    uint4 lo_out, hi_out;
+    __nv_bfloat162* lo2 = reinterpret_cast<__nv_bfloat162*>(&lo_out);
+    __nv_bfloat162* hi2 = reinterpret_cast<__nv_bfloat162*>(&hi_out);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 lo = __bfloat1622float2(l2[k]), hi = __bfloat1622float2(h2[k]);
+      const float c0 = cs[c + 2 * k], c1 = cs[c + 2 * k + 1], s0 = cs[half + c + 2 * k], s1 = cs[half + c + 2 * k + 1];
+      lo2[k] = __floats2bfloat162_rn(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
+      hi2[k] = __floats2bfloat162_rn(hi.x * c0 + lo.x * s0, hi.y * c1 + lo.y * s1);
+    }
+    *reinterpret_cast<uint4*>(dst + c) = lo_out;
+    *reinterpret_cast<uint4*>(dst + half + c) = hi_out;
+  }
+  if (!write_kv) return;
+  __nv_bfloat16* vpage = kpage + (size_t)kv_heads * page_size * head_dim;
+  const __nv_bfloat16* vsrc = row + q_width + kv_width;
+  const int vchunks = head_dim >> 3;
+  for (int w = threadIdx.x; w < kv_heads * vchunks; w += blockDim.x) {
+    const int hh = w / vchunks, c = (w - hh * vchunks) << 3;
+    *reinterpret_cast<uint4*>(vpage + ((size_t)hh * page_size + off) * head_dim + c) =
+        *reinterpret_cast<const uint4*>(vsrc + hh * head_dim + c);
+  }
+}
+
 }  // namespace tib
 
 using namespace tib;
@@ -118,6 +185,11 @@ TIB_API int tib_rope_append(const void* qkv, void* q_out, void* pool, const int*
         (const float*)qkv, (float*)q_out, (float*)pool, positions, token_slot, block_table,
         table_stride, inv_freq, heads, kv_heads, head_dim, rot_dim, interleaved, page_size,
         page_stride, num_pages, write_kv, error_word);
+  else if (dtype == TIB_BF16 && rot_dim == head_dim && !interleaved && head_dim % 16 == 0 &&
+           (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pool) & 15) == 0 && (page_stride % 8 == 0 || !write_kv))
+    rope_append_bf16x8_kernel<<<n_tokens, threads, smem, stream>>>(
+        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, positions, token_slot, block_table,
+        table_stride, inv_freq, heads, kv_heads, head_dim, page_size, page_stride, num_pages, write_kv, error_word);
   else if (dtype == TIB_BF16)
     rope_append_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, positions,
