@@ -1,0 +1,197 @@
+"""Time single kernels of the engine in isolation and relate them to the B200's measured peaks.
+
+    python -m torchinferno_b200.bench_kernels decode-attention --batch 8 --context 2048
+    python -m torchinferno_b200.bench_kernels prefill-attention --tokens 2048
+    python -m torchinferno_b200.bench_kernels gemm --rows 8
+    python -m torchinferno_b200.bench_kernels elementwise --rows 2048
+
+Each run prints one JSON line per case: microseconds (median of CUDA-event timings, an L2 flush
+between iterations), the bytes or flops the kernel has to move or do, and the fraction of the
+measured copy bandwidth or tensor throughput (``MEASURED_PEAKS.json`` at the repository root when
+present).  The same commands, small, are what the ``ncu`` summaries under ``profiles/`` were taken
+from.  The reference keeps such microbenchmarks as stand-alone scripts (``scripts/`` in its tree).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import statistics
+from pathlib import Path
+
+import torch
+
+from torchinferno_b200.kernels import ops
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        data = json.loads(path.read_text())
+        return {"hbm_gbs": data["hbm_gbs"], "bf16_tflops": data["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class Timer:
+    def __init__(self, iters: int, warmup: int = 3) -> None:
+        self.iters, self.warmup = iters, warmup
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")   # larger than the 126 MB L2
+
+    def __call__(self, fn) -> float:
+        for _ in range(self.warmup):
+            fn()
+        times = []
+        for _ in range(self.iters):
+            self.flush.zero_()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(begin.elapsed_time(end) * 1e3)
+        return statistics.median(times)
+
+
+def report(name: str, us: float, *, bytes_moved: float | None = None, flops: float | None = None, **extra) -> None:
+    p = peaks()
+    line = {"kernel": name, "us": round(us, 2), **extra}
+    if bytes_moved is not None:
+        line["gbs"] = round(bytes_moved / us / 1e3, 1)
+        line["hbm_frac"] = round(bytes_moved / us / 1e3 / p["hbm_gbs"], 4)
+    if flops is not None:
+        line["tflops"] = round(flops / us / 1e6, 1)
+        line["tensor_frac"] = round(flops / us / 1e6 / p["bf16_tflops"], 4)
+    line["peaks"] = p["source"]
+    print(json.dumps(line), flush=True)
+
+
+def paged_cache(batch: int, context: int, kv_heads: int, head_dim: int, page: int):
+    """A filled pool with shuffled pages and the block table of ``batch`` requests of ``context`` tokens."""
+    pages_per = -(-context // page)
+    total = batch * pages_per
+    pool = (torch.randn(total, 2, kv_heads, page, head_dim, device="cuda") * 0.5).to(torch.bfloat16)
+    order = torch.randperm(total, device="cuda", dtype=torch.int32)
+    table = order.view(batch, pages_per).contiguous()
+    return pool, table
+
+
+def run_decode_attention(args) -> None:
+    h, k, d = args.heads, args.kv_heads, args.head_dim
+    pool, table = paged_cache(args.batch, args.context, k, d, args.page_size)
+    n = args.batch
+    q = torch.randn(n, h * d, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    q_start, kv_start, slots = i32(list(range(n + 1))), i32([args.context - 1] * n), i32(list(range(n)))
+    timer = Timer(args.iters)
+    kv_bytes = n * args.context * 2 * k * d * 2
+    targets = args.target_blocks or [None]
+    for target in targets:
+        if target is None:
+            splits, chunk = ops.decode_split(n, h, k, args.context)
+        else:
+            splits, chunk = ops.decode_split(n, h, k, args.context, target_blocks=target)
+        scratch = torch.empty(n * h * splits * (d + 2), dtype=torch.float32, device="cuda")
+        fn = lambda: ops.decode_attention(q, pool, out, q_start, kv_start, slots, table, n, h, k, d, 1 / math.sqrt(d),
+                                          args.context, scratch=scratch, num_splits=splits, chunk=chunk)
+        report("decode_attention+merge", timer(fn), bytes_moved=kv_bytes, batch=n, context=args.context,
+               splits=splits, chunk=chunk, heads=h, kv_heads=k, head_dim=d)
+
+
+def run_prefill_attention(args) -> None:
+    h, k, d, t = args.heads, args.kv_heads, args.head_dim, args.tokens
+    pool, table = paged_cache(args.batch, t, k, d, args.page_size)
+    n = args.batch
+    q = torch.randn(n * t, h * d, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    q_start, kv_start, slots = i32([i * t for i in range(n + 1)]), i32([0] * n), i32(list(range(n)))
+    fn = lambda: ops.prefill_attention(q, pool, out, q_start, kv_start, slots, table, n, t, h, k, d, 1 / math.sqrt(d))
+    flops = n * 4 * h * d * t * (t + 1) / 2
+    report("prefill_attention", Timer(args.iters)(fn), flops=flops, batch=n, tokens=t, heads=h, kv_heads=k, head_dim=d,
+           note="causal flops")
+
+
+def run_gemm(args) -> None:
+    shapes = {"qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (28672, 4096), "down": (4096, 14336), "lm_head": (128256, 4096)}
+    timer = Timer(args.iters)
+    for name, (n, k) in shapes.items():
+        if args.only and name not in args.only:
+            continue
+        w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+        x = torch.randn(args.rows, k, device="cuda").to(torch.bfloat16)
+        out = torch.empty(args.rows, n, dtype=torch.bfloat16, device="cuda")
+        common = dict(bytes_moved=n * k * 2, flops=2 * args.rows * n * k, rows=args.rows, n=n, k=k)
+        if ops.gemm_skinny_supports(args.rows, n, k):
+            report(f"gemm_skinny[{name}]", timer(lambda: ops.gemm_skinny(x, w, out)), **common)
+        report(f"library_gemm[{name}]", timer(lambda: torch.mm(x, w.t(), out=out)), **common)
+
+
+def run_elementwise(args) -> None:
+    rows, hidden, inter = args.rows, args.hidden, args.intermediate
+    timer = Timer(args.iters)
+    delta = torch.randn(rows, hidden, device="cuda").to(torch.bfloat16)
+    residual = torch.randn(rows, hidden, device="cuda")
+    weight = torch.ones(hidden, device="cuda")
+    out = torch.empty_like(delta)
+    report("add_rmsnorm", timer(lambda: ops.add_rmsnorm(delta, residual, weight, 1e-5, out)),
+           bytes_moved=rows * hidden * (2 + 4 + 4 + 2), rows=rows, hidden=hidden)
+    gate_up = torch.randn(rows, 2 * inter, device="cuda").to(torch.bfloat16)
+    act = torch.empty(rows, inter, dtype=torch.bfloat16, device="cuda")
+    report("swiglu", timer(lambda: ops.swiglu(gate_up, act)), bytes_moved=rows * inter * 6, rows=rows, intermediate=inter)
+    h, k, d = args.heads, args.kv_heads, args.head_dim
+    qkv = torch.randn(rows, (h + 2 * k) * d, device="cuda").to(torch.bfloat16)
+    q_out = torch.empty(rows, h * d, dtype=torch.bfloat16, device="cuda")
+    pool, table = paged_cache(1, rows, k, d, args.page_size)
+    positions = torch.arange(rows, dtype=torch.int32, device="cuda")
+    slot = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).cuda()
+    report("rope_append", timer(lambda: ops.rope_append(qkv, q_out, pool, positions, slot, table, inv_freq, h, k, d)),
+           bytes_moved=rows * ((h + 2 * k) * d * 2 + (h + 2 * k) * d * 2), rows=rows)
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(prog="python -m torchinferno_b200.bench_kernels", description=__doc__.splitlines()[0])
+    sub = parser.add_subparsers(dest="command", required=True)
+
+    def common(p):
+        p.add_argument("--heads", type=int, default=32)
+        p.add_argument("--kv-heads", type=int, default=8)
+        p.add_argument("--head-dim", type=int, default=128)
+        p.add_argument("--page-size", type=int, default=16)
+        p.add_argument("--iters", type=int, default=20)
+
+    p = sub.add_parser("decode-attention")
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=2048)
+    p.add_argument("--target-blocks", type=int, nargs="*", default=None, help="try these block-count targets for the split")
+    common(p)
+    p.set_defaults(func=run_decode_attention)
+    p = sub.add_parser("prefill-attention")
+    p.add_argument("--batch", type=int, default=1)
+    p.add_argument("--tokens", type=int, default=2048)
+    common(p)
+    p.set_defaults(func=run_prefill_attention)
+    p = sub.add_parser("gemm")
+    p.add_argument("--rows", type=int, default=8)
+    p.add_argument("--only", nargs="*", default=None)
+    p.add_argument("--iters", type=int, default=20)
+    p.set_defaults(func=run_gemm)
+    p = sub.add_parser("elementwise")
+    p.add_argument("--rows", type=int, default=2048)
+    p.add_argument("--hidden", type=int, default=4096)
+    p.add_argument("--intermediate", type=int, default=14336)
+    common(p)
+    p.set_defaults(func=run_elementwise)
+    args = parser.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench_kernels needs a CUDA device")
+    with torch.inference_mode():
+        args.func(args)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -116,15 +116,17 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_tile, __nv_bfloat1
   }
 }
 
-// One 16-row by 16-key step of the streaming softmax for a warp: scores s (two n-tiles) are
+// One step of the streaming softmax for a warp's 16 rows over NT n-tiles of 8 keys: scores s are
 // already scaled and masked (-inf).  Updates m, l (per-thread partial sums), rescales o and
-// returns the probabilities packed as the A fragment of the P.V product.
-template <int ONT>
-__device__ __forceinline__ void softmax_step(float (&s)[2][4], float (&m)[2], float (&l)[2], float (&o)[ONT][4],
-                                             uint32_t (&p)[4]) {
+// returns the probabilities packed as the A fragments of the P.V product (one per 16 keys).
+template <int NT, int ONT>
+__device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&o)[ONT][4],
+                                             uint32_t (&p)[NT / 2][4]) {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {  // h = 0: row g, h = 1: row g + 8
-    float mx = fmaxf(fmaxf(s[0][2 * h], s[0][2 * h + 1]), fmaxf(s[1][2 * h], s[1][2 * h + 1]));
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * h], s[nt][2 * h + 1]));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float m_new = fmaxf(m[h], mx);
@@ -133,41 +135,77 @@ __device__ __forceinline__ void softmax_step(float (&s)[2][4], float (&m)[2], fl
     m[h] = m_new;
     float sum = 0.f;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
+    for (int nt = 0; nt < NT; ++nt) {
       s[nt][2 * h] = exp2f(s[nt][2 * h] - base);
       s[nt][2 * h + 1] = exp2f(s[nt][2 * h + 1] - base);
       sum += s[nt][2 * h] + s[nt][2 * h + 1];
     }
     l[h] = l[h] * alpha + sum;
+    if (__any_sync(0xffffffffu, alpha != 1.f)) {  // once the running max has settled nothing is rescaled
 #pragma unroll
-    for (int n = 0; n < ONT; ++n) {
-      o[n][2 * h] *= alpha;
-      o[n][2 * h + 1] *= alpha;
+      for (int n = 0; n < ONT; ++n) {
+        o[n][2 * h] *= alpha;
+        o[n][2 * h + 1] *= alpha;
+      }
     }
   }
-  p[0] = pack_bf16(s[0][0], s[0][1]);
-  p[1] = pack_bf16(s[0][2], s[0][3]);
-  p[2] = pack_bf16(s[1][0], s[1][1]);
-  p[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+    p[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    p[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    p[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    p[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+  }
+}
+
+// s[8][4] = Q(16 x D) . K(64 keys x D)^T for a whole tile: eight independent accumulators per k step.
+template <int D>
+__device__ __forceinline__ void qk_tile(float (&s)[kBN / 8][4], const uint32_t (&qf)[D / 16][4], __nv_bfloat16* k_tile,
+                                        int lane) {
+#pragma unroll
+  for (int nt = 0; nt < kBN / 8; ++nt)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s[nt][j] = 0.f;
+  const int krow = (lane & 7) + ((lane >> 4) << 3);
+  const int kcol = ((lane >> 3) & 1) << 3;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+    for (int kk = 0; kk < kBN / 16; ++kk) {
+      uint32_t b[4];
+      ldmatrix_x4(b, tile_at<D>(k_tile, kk * 16 + krow, ks * 16 + kcol));
+      mma_bf16(s[2 * kk], qf[ks], b[0], b[1]);
+      mma_bf16(s[2 * kk + 1], qf[ks], b[2], b[3]);
+    }
+  }
 }
 
 // s[2][4] = Q(16 x D) . K(16 keys x D)^T for the keys [slab, slab + 16) of a tile.
 template <int D>
 __device__ __forceinline__ void qk_slab(float (&s)[2][4], const uint32_t (&qf)[D / 16][4], __nv_bfloat16* k_tile,
                                         int slab, int lane) {
+  // even and odd k steps go to accumulators of their own: four independent chains instead of two
+  float e[2][4];
 #pragma unroll
   for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) s[nt][j] = 0.f;
+    for (int j = 0; j < 4; ++j) s[nt][j] = e[nt][j] = 0.f;
   const int krow = slab + (lane & 7) + ((lane >> 4) << 3);
   const int kcol = ((lane >> 3) & 1) << 3;
 #pragma unroll
-  for (int ks = 0; ks < D / 16; ++ks) {
-    uint32_t b[4];
+  for (int ks = 0; ks < D / 16; ks += 2) {
+    uint32_t b[4], c[4];
     ldmatrix_x4(b, tile_at<D>(k_tile, krow, ks * 16 + kcol));
+    ldmatrix_x4(c, tile_at<D>(k_tile, krow, (ks + 1) * 16 + kcol));
     mma_bf16(s[0], qf[ks], b[0], b[1]);
     mma_bf16(s[1], qf[ks], b[2], b[3]);
+    mma_bf16(e[0], qf[ks + 1], c[0], c[1]);
+    mma_bf16(e[1], qf[ks + 1], c[2], c[3]);
   }
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s[nt][j] += e[nt][j];
 }
 
 // o(16 x D) += P(16 x 16 keys) . V(16 keys x D) for the keys [slab, slab + 16) of a tile.
@@ -276,27 +314,25 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     const int key_base = (kt0 + it) * kBN;
     // tiles wholly inside every row's allowed range need no mask
     const bool need_mask = key_base + kBN - 1 > pos0 || (a.window > 0 && key_base < last_pos - a.window + 1);
+    float s[kBN / 8][4];
+    qk_tile<D>(s, qf, k_tile, lane);
 #pragma unroll
-    for (int kk = 0; kk < kBN / 16; ++kk) {
-      float s[2][4];
-      qk_slab<D>(s, qf, k_tile, kk * 16, lane);
+    for (int n2 = 0; n2 < kBN / 8; ++n2)
 #pragma unroll
-      for (int n2 = 0; n2 < 2; ++n2)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float v = s[n2][j] * a.scale_log2;
-          if (need_mask) {
-            const int key = key_base + kk * 16 + n2 * 8 + tig * 2 + (j & 1);
-            const int qp = qpos[j >> 1];
-            const bool ok = key <= qp && (a.window <= 0 || key > qp - a.window);
-            v = ok ? v : -CUDART_INF_F;
-          }
-          s[n2][j] = v;
+      for (int j = 0; j < 4; ++j) {
+        float v = s[n2][j] * a.scale_log2;
+        if (need_mask) {
+          const int key = key_base + n2 * 8 + tig * 2 + (j & 1);
+          const int qp = qpos[j >> 1];
+          const bool ok = key <= qp && (a.window <= 0 || key > qp - a.window);
+          v = ok ? v : -CUDART_INF_F;
         }
-      uint32_t p[4];
-      softmax_step<D / 8>(s, m, l, o, p);
-      pv_slab<D>(o, p, v_tile, kk * 16, lane);
-    }
+        s[n2][j] = v;
+      }
+    uint32_t p[kBN / 16][4];
+    softmax_step<kBN / 8, D / 8>(s, m, l, o, p);
+#pragma unroll
+    for (int kk = 0; kk < kBN / 16; ++kk) pv_slab<D>(o, p[kk], v_tile, kk * 16, lane);
   }
   cp_async_wait<0>();
 
@@ -415,9 +451,9 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         const bool ok = key <= pos && key >= first_key && key < ke;
         s[n2][j] = ok ? s[n2][j] * a.scale_log2 : -CUDART_INF_F;
       }
-    uint32_t p[4];
-    softmax_step<D / 8>(s, m, l, o, p);
-    pv_slab<D>(o, p, v_tile, warp * 16, lane);
+    uint32_t p[1][4];
+    softmax_step<2, D / 8>(s, m, l, o, p);
+    pv_slab<D>(o, p[0], v_tile, warp * 16, lane);
   }
   cp_async_wait<0>();
   __syncthreads();  // all warps are done with the tiles: their memory is reused below

@@ -23,6 +23,8 @@ enum TibError : int {
   TIB_E_ALIGN = -3,      // a pointer or stride that is not aligned as required
   TIB_E_SMEM = -4,       // needs more shared memory than an SM offers
   TIB_E_ARG = -5,        // null pointer or inconsistent arguments
+  TIB_E_WAIT = -6,       // a bounded device-side wait ran out
+  TIB_E_SCRATCH = -7,    // needs more scratch than the library's built-in array holds
 };
 
 #define TIB_LAUNCH_CHECK()                         \

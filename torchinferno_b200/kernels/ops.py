@@ -22,6 +22,7 @@ _ERRORS = {
     -4: "needs more shared memory than an SM offers",
     -5: "null pointer or inconsistent arguments",
     -6: "the device-side wait limit was reached (kernel gave up)",
+    -7: "needs more scratch than the library's built-in array holds",
 }
 
 
@@ -80,7 +81,8 @@ def lib() -> ctypes.CDLL:
     if not _signatures_set:
         for fn in ("tib_embedding", "tib_add_rmsnorm", "tib_rmsnorm", "tib_swiglu", "tib_cast",
                    "tib_scatter_i32", "tib_advance_decode", "tib_rope_append", "tib_paged_attention_simt", "tib_gemm_f32", "tib_sample",
-                   "tib_attention_mma_supports", "tib_prefill_attention", "tib_decode_attention"):
+                   "tib_attention_mma_supports", "tib_prefill_attention", "tib_decode_attention",
+                   "tib_gemm_skinny", "tib_gemm_skinny_supports"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
     return library
@@ -306,7 +308,7 @@ def prefill_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_
     return out
 
 
-def decode_split(n_entries: int, heads: int, kv_heads: int, max_kv_len: int, target_blocks: int = 592) -> tuple[int, int]:
+def decode_split(n_entries: int, heads: int, kv_heads: int, max_kv_len: int, target_blocks: int = 148) -> tuple[int, int]:
     """(num_splits, chunk): how the longest context is cut so that about ``target_blocks`` blocks run."""
     group = heads // kv_heads
     blocks = max(1, n_entries * kv_heads * ((group + 15) // 16))
@@ -347,4 +349,23 @@ def decode_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_s
         _ptr(block_table), c_int(block_table.stride(0)), c_int(n_entries), c_int(heads), c_int(kv_heads), c_int(head_dim),
         c_int(pool.shape[3]), c_int64(pool.stride(0)), c_int(pool.shape[0]), c_int(window), c_float(scale),
         c_int(num_splits), c_int(chunk), _stream()))
+    return out
+
+
+def gemm_skinny_supports(m: int, n: int, k: int) -> bool:
+    return bool(lib().tib_gemm_skinny_supports(c_int(m), c_int(n), c_int(k)))
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] (bf16 or fp32) = x[M, K] . w[N, K]^T for M <= 64: one pass over the weights."""
+    for name, t in (("x", x), ("w", w)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gemm_skinny: {name} must be a 2-D bf16 CUDA tensor with unit inner stride")
+    _need(out, "out")
+    (m, k), (n, k2) = x.shape, w.shape
+    if k != k2 or out.shape != (m, n):
+        raise KernelError(f"gemm_skinny: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    _check("gemm_skinny", lib().tib_gemm_skinny(_ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k),
+                                                c_int64(x.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)),
+                                                c_int(_code(out.dtype)), _stream()))
     return out
