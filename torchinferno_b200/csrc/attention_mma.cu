@@ -631,3 +631,85 @@ TIB_API int tib_decode_attention(const void* q, const void* pool, void* out, flo
   return head_dim == 64 ? launch_decode<64>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream)
                         : launch_decode<128>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc (or any allocator) at the time they need
+// attention: code that runs inside another framework's memory plan with a fixed budget, a real-time
+// loop that may not take the allocator's lock or tolerate its latency, or a plug-in whose host
+// forbids allocation after start-up.  tib_decode_attention needs scratch for the partial results of
+// its context splits; here that scratch is a fixed array in the library's own device image.
+//
+//  * The array holds TIB_NOALLOC_SCRATCH_FLOATS floats (16 MiB).  Every GPU that loads this library
+//    carries it until the process exits, whether or not this entry point is ever called.
+//  * A call needs n_entries * heads * num_splits * (head_dim + 2) floats; a call that needs more is
+//    refused with TIB_E_SCRATCH and nothing is launched.  With num_splits == 1 no scratch is used.
+//  * The first call on a device looks the array's device address up (cudaGetSymbolAddress, with that
+//    device current) and keeps it; make that first call before any stream capture begins.
+//  * All calls share the one array, and it keeps what the last call left.  Nothing in it has to
+//    start at zero: every call writes each (entry, head, split) record it later reads.  Two calls
+//    that overlap on the GPU (different streams, no ordering between them) race on the array; order
+//    them on one stream or with events.
+//  * No cudaMalloc, cudaFree or allocating library routine is called here.
+#define TIB_NOALLOC_SCRATCH_FLOATS (4 * 1024 * 1024)
+static __device__ __align__(256) float tib_noalloc_scratch[TIB_NOALLOC_SCRATCH_FLOATS];
+
+static float* noalloc_scratch_address(int* status) {
+  // In host code `tib_noalloc_scratch` names a host-side shadow of the symbol, not device memory;
+  // the device address must be asked for, once per device, with that device current.
+  constexpr int kMaxDevices = 64;
+  static float* address[kMaxDevices] = {nullptr};
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) { *status = (int)e; return nullptr; }
+  if (device < 0 || device >= kMaxDevices) { *status = TIB_E_ARG; return nullptr; }
+  if (address[device] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, tib_noalloc_scratch);
+    if (e != cudaSuccess) { *status = (int)e; return nullptr; }
+    address[device] = ptr;
+  }
+  *status = TIB_OK;
+  return address[device];
+}
+
+// How many floats of the built-in scratch a call would use (0 when num_splits == 1).
+TIB_API long long tib_decode_attention_noalloc_need(int n_entries, int heads, int head_dim, int num_splits) {
+  if (num_splits <= 1) return 0;
+  return (long long)n_entries * heads * num_splits * (head_dim + 2);
+}
+
+TIB_API long long tib_decode_attention_noalloc_capacity(void) { return TIB_NOALLOC_SCRATCH_FLOATS; }
+
+// Same contract as tib_decode_attention, minus the two scratch pointers.  The caller passes inputs
+// and outputs; the partial results live in the library's own array (see above).
+TIB_API int tib_decode_attention_noalloc(const void* q, const void* pool, void* out, const int* q_start,
+                                         const int* kv_start, const int* slots, const int* block_table,
+                                         int table_stride, int n_entries, int heads, int kv_heads, int head_dim,
+                                         int page_size, int64_t page_stride, int num_pages, int window, float scale,
+                                         int num_splits, int chunk, cudaStream_t stream) {
+  if (n_entries == 0) return TIB_OK;
+  if (!q || !pool || !out) return TIB_E_ARG;
+  if (num_splits < 1 || chunk < kBN || chunk % kBN != 0) return TIB_E_SIZE;
+  MmaAttnArgs a;
+  int rc = fill_args(a, q_start, kv_start, slots, block_table, table_stride, heads, kv_heads, head_dim, page_size,
+                     page_stride, num_pages, window, scale);
+  if (rc != TIB_OK) return rc;
+  const int row_tiles = (a.group + 15) / 16;
+  if (n_entries > 65535 || (int64_t)kv_heads * row_tiles > 65535) return TIB_E_SIZE;
+  const long long need = tib_decode_attention_noalloc_need(n_entries, heads, head_dim, num_splits);
+  if (need > TIB_NOALLOC_SCRATCH_FLOATS) return TIB_E_SCRATCH;
+  float* scratch_o = nullptr;
+  float* scratch_ml = nullptr;
+  if (num_splits > 1) {
+    float* base = noalloc_scratch_address(&rc);
+    if (rc != TIB_OK) return rc;
+    scratch_o = base;
+    scratch_ml = base + (size_t)n_entries * heads * num_splits * head_dim;
+  }
+  a.num_splits = num_splits;
+  a.chunk = chunk;
+  return head_dim == 64 ? launch_decode<64>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream)
+                        : launch_decode<128>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream);
+}
