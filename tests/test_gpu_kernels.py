@@ -311,7 +311,7 @@ def test_tensor_core_attention_ragged_batch(heads, kv_heads, d, page, kernel):
     assert torch.allclose(out.double(), ref, **BF16_ATTN), (out.double() - ref).abs().max()
 
 
-@pytest.mark.parametrize("splits", [(1, 1024), (2, 512), (3, 320), (16, 64), (9, 128)])
+@pytest.mark.parametrize("splits", [(1, 1024), (2, 512), (3, 320), (16, 64), (9, 128), (1, 0), (2, 0), (5, 0), (32, 0)])
 def test_split_decode_attention_is_the_same_for_every_split(splits):
     need_gpu()
     entries = [(900, 1), (0, 1), (63, 1), (64, 1), (517, 1)]

@@ -90,7 +90,7 @@ def run_decode_attention(args) -> None:
     targets = args.target_blocks or [None]
     for target in targets:
         if target is None:
-            splits, chunk = ops.decode_split(n, h, k, args.context)
+            splits, chunk = ops.decode_num_splits(n, h, k), 0
         else:
             splits, chunk = ops.decode_split(n, h, k, args.context, target_blocks=target)
         scratch = torch.empty(n * h * splits * (d + 2), dtype=torch.float32, device="cuda")

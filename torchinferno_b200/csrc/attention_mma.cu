@@ -35,7 +35,7 @@ struct MmaAttnArgs {
   int num_pages;
   int window;
   float scale_log2;      // scale * log2(e)
-  int chunk;             // decode: keys per split (multiple of kBN)
+  int chunk;             // decode: keys per split (multiple of kBN); 0: each request's context / num_splits
   int num_splits;        // decode
   int skip_single;       // prefill: leave single-token entries to the decode kernel
 };
@@ -377,8 +377,13 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int nrows = min(16, a.group - g0);
   const int pos = a.kv_start[entry];
   const int first_key = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-  const int kb = first_key / kBN * kBN + split * a.chunk;
-  const int ke = min(kb + a.chunk, pos + 1);  // exclusive
+  // chunk == 0: this request's own context is cut into num_splits equal parts (multiples of kBN),
+  // so every split has work whatever bound the host knew when it chose the grid
+  const int first_tile_key = first_key / kBN * kBN;
+  const int chunk = a.chunk > 0 ? a.chunk
+                                : max(kBN, ((pos + 1 - first_tile_key + a.num_splits - 1) / a.num_splits + kBN - 1) / kBN * kBN);
+  const int kb = first_tile_key + split * chunk;
+  const int ke = min(kb + chunk, pos + 1);  // exclusive
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g_row = lane >> 2, tig = lane & 3;
   const int head0 = kvh * a.group + g0;
@@ -609,7 +614,8 @@ TIB_API int tib_prefill_attention(const void* q, const void* pool, void* out, co
 }
 
 // Single-token entries, context split into num_splits parts of `chunk` keys (a multiple of 64;
-// num_splits * chunk must cover the longest context).  scratch_o: [n_entries * heads * num_splits *
+// num_splits * chunk must cover the longest context), or, with chunk == 0, each request's own
+// context split into num_splits equal parts.  scratch_o: [n_entries * heads * num_splits *
 // head_dim] floats, scratch_ml: [n_entries * heads * num_splits * 2] floats (unused when num_splits == 1).
 TIB_API int tib_decode_attention(const void* q, const void* pool, void* out, float* scratch_o, float* scratch_ml,
                                  const int* q_start, const int* kv_start, const int* slots, const int* block_table,
@@ -618,7 +624,7 @@ TIB_API int tib_decode_attention(const void* q, const void* pool, void* out, flo
                                  int num_splits, int chunk, cudaStream_t stream) {
   if (n_entries == 0) return TIB_OK;
   if (!q || !pool || !out) return TIB_E_ARG;
-  if (num_splits < 1 || chunk < kBN || chunk % kBN != 0) return TIB_E_SIZE;
+  if (num_splits < 1 || chunk < 0 || (chunk > 0 && chunk < kBN) || chunk % kBN != 0) return TIB_E_SIZE;
   if (num_splits > 1 && (!scratch_o || !scratch_ml)) return TIB_E_ARG;
   MmaAttnArgs a;
   int rc = fill_args(a, q_start, kv_start, slots, block_table, table_stride, heads, kv_heads, head_dim, page_size,

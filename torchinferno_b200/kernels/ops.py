@@ -309,13 +309,20 @@ def prefill_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_
 
 
 def decode_split(n_entries: int, heads: int, kv_heads: int, max_kv_len: int, target_blocks: int = 148) -> tuple[int, int]:
-    """(num_splits, chunk): how the longest context is cut so that about ``target_blocks`` blocks run."""
+    """(num_splits, chunk) for a known longest context: about ``target_blocks`` blocks, two tiles a split at least."""
     group = heads // kv_heads
     blocks = max(1, n_entries * kv_heads * ((group + 15) // 16))
     tiles = max(1, -(-max_kv_len // 64))
-    splits = max(1, min(-(-tiles // 2), -(-target_blocks // blocks)))   # at least two tiles a split
+    splits = max(1, min(-(-tiles // 2), -(-target_blocks // blocks)))
     per = -(-tiles // splits)
     return -(-tiles // per), per * 64
+
+
+def decode_num_splits(n_entries: int, heads: int, kv_heads: int, target_blocks: int = 148, most: int = 32) -> int:
+    """How many parts each request's context is cut into when the kernel sizes the parts itself."""
+    group = heads // kv_heads
+    blocks = max(1, n_entries * kv_heads * ((group + 15) // 16))
+    return max(1, min(most, -(-target_blocks // blocks)))
 
 
 def decode_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor,
@@ -326,13 +333,15 @@ def decode_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_s
     """Attention of single tokens over the paged cache, the context split over blocks (bf16).
 
     Entries that bring more than one token are skipped.  ``max_kv_len`` bounds the longest context
-    (keys 0 .. position) of the batch; ``scratch`` (fp32, at least n_entries * heads * num_splits *
+    (keys 0 .. position) of the batch when ``num_splits`` and ``chunk`` are given (by default the kernel
+    cuts each request's own context into equal parts); ``scratch`` (fp32, at least n_entries * heads * num_splits *
     (head_dim + 2) elements) holds the partial results when there is more than one split.
     """
     _check_attention_args(q, pool, out, q_start, kv_start, slots, block_table, n_entries, heads, kv_heads, head_dim)
     if num_splits is None or chunk is None:
-        num_splits, chunk = decode_split(n_entries, heads, kv_heads, max_kv_len)
-    if num_splits * chunk < max_kv_len:
+        # each request's own context is cut into num_splits equal parts by the kernel (chunk 0)
+        num_splits, chunk = decode_num_splits(n_entries, heads, kv_heads), 0
+    elif chunk != 0 and num_splits * chunk < max_kv_len:
         raise KernelError("decode_attention: num_splits * chunk does not cover the longest context")
     scratch_o = scratch_ml = None
     if num_splits > 1:
