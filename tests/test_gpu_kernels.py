@@ -116,6 +116,40 @@ def test_gemm_f32_is_true_fp32_and_row_independent(m, n, k, wdtype):
     assert torch.equal(one[0], out[m // 2])               # a row does not depend on the rows beside it
 
 
+@pytest.mark.parametrize("m, n, k", [(1, 64, 64), (8, 4096, 4096), (16, 1000, 512), (33, 129 * 8, 96 * 2 + 64), (64, 6144, 4096)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_skinny(m, n, k, out_dtype):
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    x, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, scale=0.05, seed=3)
+    out = ops.gemm_skinny(dev(x), dev(w), torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda"))
+    want = x.double() @ w.double().T
+    bound = (1e-2 if out_dtype == torch.bfloat16 else 1e-4) * want.abs().max() + 1e-6
+    assert (as_ref(out) - want).abs().max() <= bound
+    with pytest.raises(ops.KernelError, match="size"):
+        ops.gemm_skinny(dev(rnd(65, 64, dtype=torch.bfloat16)), dev(rnd(8, 64, dtype=torch.bfloat16)), torch.empty(65, 8, dtype=out_dtype, device="cuda"))
+    with pytest.raises(ops.KernelError, match="size"):
+        ops.gemm_skinny(dev(rnd(4, 48, dtype=torch.bfloat16)), dev(rnd(8, 48, dtype=torch.bfloat16)), torch.empty(4, 8, dtype=out_dtype, device="cuda"))
+
+
+@pytest.mark.parametrize("m, n, k", [(128, 256, 64), (1, 8, 64), (200, 520, 192), (77, 1000, 4096), (300, 264, 1024), (2048, 512, 14336)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05(m, n, k, out_dtype):
+    """The TMA / tcgen05 / TMEM product against float64, with rows and columns that do not fill the
+    128 x 256 tiles, a long K (many trips round the stage ring), and both output types."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    x, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, scale=0.05, seed=3)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.gemm_tcgen05(dev(x), dev(w), torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda"), err)
+    assert int(err) == 0                                   # no bounded wait ran out
+    want = (x.cuda().double() @ w.cuda().double().T).cpu()
+    bound = (1e-2 if out_dtype == torch.bfloat16 else 2e-5) * want.abs().max() + 1e-6
+    assert (as_ref(out) - want).abs().max() <= bound
+    with pytest.raises(ops.KernelError, match="size"):     # K must be a multiple of 64
+        ops.gemm_tcgen05(dev(rnd(4, 96, dtype=torch.bfloat16)), dev(rnd(8, 96, dtype=torch.bfloat16)), torch.empty(4, 8, dtype=out_dtype, device="cuda"))
+
+
 # -------------------------------------------------------------- RoPE + KV
 def paged_layout(n_requests, lengths, page_size, kv_heads, d, dtype, spare_pages=3, seed=0):
     """A pool with NaN everywhere, shuffled page ids, and block tables for the given lengths."""

@@ -1,0 +1,277 @@
+// bf16 projections on the 5th-generation tensor cores: out[M, N] = x[M, K] . w[N, K]^T.
+//
+// One block computes one 128 x 256 tile of the output.  Its warps have fixed roles:
+//   warp 0, one lane   TMA producer: `cp.async.bulk.tensor.2d` copies a 128 x 64 slice of x and a
+//                      256 x 64 slice of w into a ring of 128-byte-swizzled shared-memory stages
+//   warp 1, one lane   issues `tcgen05.mma.cta_group::1.kind::f16` (M 128, N 256, K 16) on the stages;
+//                      `tcgen05.commit` hands a stage back to the producer and, at the end, the
+//                      accumulator to the epilogue.  Warp 1 also owns the TMEM allocation.
+//   warps 2..5         epilogue: `tcgen05.ld` reads the fp32 accumulator (TMEM lane = output row,
+//                      TMEM column = output column), converts and stores it.
+// Full / empty mbarriers order producer, MMA and epilogue.  Every wait on an mbarrier is bounded: when
+// the limit is reached the waiting role records a code in `error_word`, all roles leave their loops,
+// the block still meets at the final barrier and frees its TMEM, and the host raises.
+//
+// The reference sends these products to cuBLAS (src/torchinferno/models/llama3/tensor_parallel.py:11176-11198).
+#include "common.cuh"
+#include <cuda.h>
+
+namespace tib {
+
+constexpr int kTcBM = 128, kTcBN = 256, kTcBK = 64, kTcStages = 4;
+constexpr int kTcThreads = 192;
+constexpr uint32_t kTcStageBytes = (kTcBM + kTcBN) * kTcBK * 2;  // 48 KB
+constexpr uint32_t kTcSmemBytes = kTcStages * kTcStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait (non-blocking tests, about 0.2 s in all): false when the limit was reached; the caller
+// records it and gives up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if (i > 64) __nanosleep(32);
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16), 128-byte swizzle:
+// groups of 8 rows lie 1024 bytes apart (stride byte offset), version 1, layout type 2.
+__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);   // start address
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
+  d |= (uint64_t)1 << 46;                        // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: D fp32, A and B bf16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTcBN >> 3) << 17) | ((uint32_t)(kTcBM >> 4) << 24);
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr));
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    TOut* __restrict__ out, int M, int N, int K, int64_t ldo, int* __restrict__ error_word) {
+  extern __shared__ unsigned char smem_raw[];
+  // stages must start on 1024-byte boundaries (128-byte swizzle repeats every 8 rows of 128 bytes)
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + kTcStages * kTcStageBytes;       // full[4], empty[4], accum, tmem slot
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (kTcStages + s); };
+  const uint32_t accum_bar = bars + 8u * (2 * kTcStages);
+  const uint32_t tmem_slot = bars + 8u * (2 * kTcStages + 1);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * kTcBM, n0 = blockIdx.x * kTcBN;
+  const int k_blocks = K / kTcBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTcStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tmem_slot), "r"((uint32_t)kTcBN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = kb % kTcStages;
+        const uint32_t phase = (kb / kTcStages) & 1;
+        if (!mbar_wait(empty_bar(s), phase ^ 1)) {
+          if (error_word) atomicExch(error_word, 0x7C0001);
+          break;
+        }
+        mbar_expect_tx(full_bar(s), kTcStageBytes);
+        const uint32_t a_dst = base + s * kTcStageBytes, b_dst = a_dst + kTcBM * kTcBK * 2;
+        tma_load_2d(a_dst, &map_x, kb * kTcBK, m0, full_bar(s));
+        tma_load_2d(b_dst, &map_w, kb * kTcBK, n0, full_bar(s));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; ++kb) {
+        const int s = kb % kTcStages;
+        const uint32_t phase = (kb / kTcStages) & 1;
+        if (!mbar_wait(full_bar(s), phase)) {
+          if (error_word) atomicExch(error_word, 0x7C0002);
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t a_src = base + s * kTcStageBytes, b_src = a_src + kTcBM * kTcBK * 2;
+#pragma unroll
+        for (int k = 0; k < kTcBK / 16; ++k) {
+          // 16 bf16 = 32 bytes further along K inside the 128-byte swizzle atom
+          umma_f16(tmem_base, umma_desc_k128(a_src + k * 32), umma_desc_k128(b_src + k * 32), (kb | k) != 0);
+        }
+        umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
+      }
+      umma_commit(accum_bar);        // (also on failure, so that the epilogue does not wait in vain)
+    }
+  } else {
+    // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    if (mbar_wait(accum_bar, 0)) {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+      for (int c = 0; c < kTcBN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 32, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        const int col = n0 + c * 32;
+        if (row < M && col < N) {
+          TOut* dst = out + (size_t)row * ldo + col;
+          if (col + 32 <= N) {
+            if constexpr (sizeof(TOut) == 2) {
+              uint4 packed[4];
+              __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(packed);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) p2[j] = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+#pragma unroll
+              for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = packed[j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+          } else {
+            for (int j = 0; j < 32 && col + j < N; ++j) dst[j] = from_f32<TOut>(__uint_as_float(v[j]));
+          }
+        }
+      }
+    } else if (error_word && lane == 0) {
+      atomicExch(error_word, 0x7C0003);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)kTcBN) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+// A [rows, K] bf16 matrix with row stride ld (elements), read in boxes of box_rows x 64 with 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int64_t ld, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return TIB_E_ARG;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kTcBK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? TIB_OK : TIB_E_ARG;
+}
+
+}  // namespace tib
+
+using namespace tib;
+
+// Whether tib_gemm_tcgen05 takes this shape: K a multiple of 64, N a multiple of 8.
+TIB_API int tib_gemm_tcgen05_supports(int M, int N, int K) {
+  return M >= 1 && N >= 8 && N % 8 == 0 && K >= 64 && K % 64 == 0;
+}
+
+// x: [M, K] bf16 (row stride ldx), w: [N, K] bf16 (row stride ldw), out: [M, N] bf16 or fp32 (row stride ldo).
+// Base addresses and row strides must be multiples of 16 bytes.  error_word (device, optional) receives a
+// non-zero code if a bounded wait inside the kernel ran out.
+TIB_API int tib_gemm_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, int64_t ldx, int64_t ldw,
+                             int64_t ldo, int out_dtype, int* error_word, cudaStream_t stream) {
+  if (M == 0 || N == 0) return TIB_OK;
+  if (!x || !w || !out) return TIB_E_ARG;
+  if (!tib_gemm_tcgen05_supports(M, N, K)) return TIB_E_SIZE;
+  if ((((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) || ldx % 8 || ldw % 8 || ldo % 8) return TIB_E_ALIGN;
+  CUtensorMap map_x, map_w;
+  int rc = make_map(&map_x, x, M, K, ldx, kTcBM);
+  if (rc != TIB_OK) return rc;
+  rc = make_map(&map_w, w, N, K, ldw, kTcBN);
+  if (rc != TIB_OK) return rc;
+  dim3 grid(ceil_div(N, kTcBN), ceil_div(M, kTcBM));
+  if (grid.y > 65535) return TIB_E_SIZE;
+  cudaError_t e;
+  if (out_dtype == TIB_BF16) {
+    auto kern = gemm_tcgen05_kernel<__nv_bfloat16>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<grid, kTcThreads, kTcSmemBytes, stream>>>(map_x, map_w, (__nv_bfloat16*)out, M, N, K, ldo, error_word);
+  } else if (out_dtype == TIB_F32) {
+    auto kern = gemm_tcgen05_kernel<float>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<grid, kTcThreads, kTcSmemBytes, stream>>>(map_x, map_w, (float*)out, M, N, K, ldo, error_word);
+  } else {
+    return TIB_E_DTYPE;
+  }
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}
