@@ -1,6 +1,7 @@
 // bf16 projections on the 5th-generation tensor cores: out[M, N] = x[M, K] . w[N, K]^T.
 //
-// One block computes one 128 x 256 tile of the output.  Its warps have fixed roles:
+// A block computes 128 x 256 tiles of the output, one after the other (one block per SM).  Its warps
+// have fixed roles:
 //   warp 0, one lane   TMA producer: `cp.async.bulk.tensor.2d` copies a 128 x 64 slice of x and a
 //                      256 x 64 slice of w into a ring of 128-byte-swizzled shared-memory stages
 //   warp 1, one lane   issues `tcgen05.mma.cta_group::1.kind::f16` (M 128, N 256, K 16) on the stages;
@@ -8,7 +9,7 @@
 //                      accumulator to the epilogue.  Warp 1 also owns the TMEM allocation.
 //   warps 2..5         epilogue: `tcgen05.ld` reads the fp32 accumulator (TMEM lane = output row,
 //                      TMEM column = output column), converts and stores it.
-// Full / empty mbarriers order producer, MMA and epilogue.  Every wait on an mbarrier is bounded: when
+// Full / empty mbarriers order producer, MMA and epilogue; two accumulators in TMEM alternate.  Every wait on an mbarrier is bounded: when
 // the limit is reached the waiting role records a code in `error_word`, all roles leave their loops,
 // the block still meets at the final barrier and frees its TMEM, and the host raises.
 //
@@ -86,6 +87,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                : "r"(taddr));
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+
+// Persistent: a block walks the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...  Tile t is row tile
+// t % m_tiles of column tile t / m_tiles, so blocks that run together share slices of w (the big
+// operand), which then come from HBM once and from L2 for the other row tiles.  Two accumulators
+// (2 x 256 TMEM columns) alternate, so the epilogue of one tile runs under the MMAs of the next.
 template <typename TOut>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -93,27 +102,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   extern __shared__ unsigned char smem_raw[];
   // stages must start on 1024-byte boundaries (128-byte swizzle repeats every 8 rows of 128 bytes)
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bars = base + kTcStages * kTcStageBytes;       // full[4], empty[4], accum, tmem slot
+  const uint32_t bars = base + kTcStages * kTcStageBytes;       // full[4], empty[4], acc_full[2], acc_empty[2], tmem slot
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (kTcStages + s); };
-  const uint32_t accum_bar = bars + 8u * (2 * kTcStages);
-  const uint32_t tmem_slot = bars + 8u * (2 * kTcStages + 1);
+  auto acc_full_bar = [&](int b) { return bars + 8u * (2 * kTcStages + b); };
+  auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * kTcStages + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * kTcStages + 4);
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kTcBM, n0 = blockIdx.x * kTcBN;
   const int k_blocks = K / kTcBK;
+  const int m_tiles = (M + kTcBM - 1) / kTcBM, n_tiles = (N + kTcBN - 1) / kTcBN;
+  const int num_tiles = m_tiles * n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 4);   // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tmem_slot), "r"((uint32_t)kTcBN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tmem_slot), "r"(2u * kTcBN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -123,51 +137,76 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = kb % kTcStages;
-        const uint32_t phase = (kb / kTcStages) & 1;
-        if (!mbar_wait(empty_bar(s), phase ^ 1)) {
-          if (error_word) atomicExch(error_word, 0x7C0001);
-          break;
+      uint32_t it = 0;   // k blocks issued so far: picks the stage and its phase
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int m0 = (t % m_tiles) * kTcBM, n0 = (t / m_tiles) * kTcBN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kTcStages;
+          const uint32_t phase = (it / kTcStages) & 1;
+          if (!mbar_wait(empty_bar(s), phase ^ 1)) {
+            if (error_word) atomicExch(error_word, 0x7C0001);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(full_bar(s), kTcStageBytes);
+          const uint32_t a_dst = base + s * kTcStageBytes, b_dst = a_dst + kTcBM * kTcBK * 2;
+          tma_load_2d(a_dst, &map_x, kb * kTcBK, m0, full_bar(s));
+          tma_load_2d(b_dst, &map_w, kb * kTcBK, n0, full_bar(s));
         }
-        mbar_expect_tx(full_bar(s), kTcStageBytes);
-        const uint32_t a_dst = base + s * kTcStageBytes, b_dst = a_dst + kTcBM * kTcBK * 2;
-        tma_load_2d(a_dst, &map_x, kb * kTcBK, m0, full_bar(s));
-        tma_load_2d(b_dst, &map_w, kb * kTcBK, n0, full_bar(s));
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      uint32_t it = 0;
       bool ok = true;
-      for (int kb = 0; kb < k_blocks && ok; ++kb) {
-        const int s = kb % kTcStages;
-        const uint32_t phase = (kb / kTcStages) & 1;
-        if (!mbar_wait(full_bar(s), phase)) {
-          if (error_word) atomicExch(error_word, 0x7C0002);
+      int j = 0;         // tiles done by this block: picks the accumulator and its phase
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++j) {
+        const int b = j & 1;
+        const uint32_t tmem_acc = tmem_base + b * kTcBN;
+        if (!mbar_wait(acc_empty_bar(b), ((j >> 1) & 1) ^ 1)) {   // the epilogue has drained this accumulator
+          if (error_word) atomicExch(error_word, 0x7C0004);
           ok = false;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t a_src = base + s * kTcStageBytes, b_src = a_src + kTcBM * kTcBK * 2;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kTcStages;
+          const uint32_t phase = (it / kTcStages) & 1;
+          if (!mbar_wait(full_bar(s), phase)) {
+            if (error_word) atomicExch(error_word, 0x7C0002);
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint32_t a_src = base + s * kTcStageBytes, b_src = a_src + kTcBM * kTcBK * 2;
 #pragma unroll
-        for (int k = 0; k < kTcBK / 16; ++k) {
-          // 16 bf16 = 32 bytes further along K inside the 128-byte swizzle atom
-          umma_f16(tmem_base, umma_desc_k128(a_src + k * 32), umma_desc_k128(b_src + k * 32), (kb | k) != 0);
+          for (int k = 0; k < kTcBK / 16; ++k) {
+            // 16 bf16 = 32 bytes further along K inside the 128-byte swizzle atom
+            umma_f16(tmem_acc, umma_desc_k128(a_src + k * 32), umma_desc_k128(b_src + k * 32), (kb | k) != 0);
+          }
+          umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
         }
-        umma_commit(empty_bar(s));   // the stage is free once these MMAs have read it
+        umma_commit(acc_full_bar(b));  // (also on failure, so that the epilogue does not wait in vain)
       }
-      umma_commit(accum_bar);        // (also on failure, so that the epilogue does not wait in vain)
     }
   } else {
     // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
-    if (mbar_wait(accum_bar, 0)) {
+    int j = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++j) {
+      const int m0 = (t % m_tiles) * kTcBM, n0 = (t / m_tiles) * kTcBN;
+      const int b = j & 1;
+      const int row = m0 + quarter * 32 + lane;
+      if (!mbar_wait(acc_full_bar(b), (j >> 1) & 1)) {
+        if (error_word && lane == 0) atomicExch(error_word, 0x7C0003);
+        break;
+      }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll 1
       for (int c = 0; c < kTcBN / 32; ++c) {
         uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 32, v);
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + b * kTcBN + c * 32, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
         const int col = n0 + c * 32;
         if (row < M && col < N) {
@@ -177,28 +216,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
               uint4 packed[4];
               __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(packed);
 #pragma unroll
-              for (int j = 0; j < 16; ++j) p2[j] = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+              for (int q = 0; q < 16; ++q) p2[q] = __floats2bfloat162_rn(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
 #pragma unroll
-              for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = packed[j];
+              for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(dst)[q] = packed[q];
             } else {
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              for (int q = 0; q < 8; ++q)
+                reinterpret_cast<uint4*>(dst)[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
             }
           } else {
-            for (int j = 0; j < 32 && col + j < N; ++j) dst[j] = from_f32<TOut>(__uint_as_float(v[j]));
+            for (int q = 0; q < 32 && col + q < N; ++q) dst[q] = from_f32<TOut>(__uint_as_float(v[q]));
           }
         }
       }
-    } else if (error_word && lane == 0) {
-      atomicExch(error_word, 0x7C0003);
+      // this warp has read its quarter of the accumulator: hand it back to the MMA warp
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(b));
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)kTcBN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2u * kTcBN) : "memory");
   }
 }
 
@@ -256,8 +297,11 @@ TIB_API int tib_gemm_tcgen05(const void* x, const void* w, void* out, int M, int
   if (rc != TIB_OK) return rc;
   rc = make_map(&map_w, w, N, K, ldw, kTcBN);
   if (rc != TIB_OK) return rc;
-  dim3 grid(ceil_div(N, kTcBN), ceil_div(M, kTcBM));
-  if (grid.y > 65535) return TIB_E_SIZE;
+  const int64_t tiles = (int64_t)ceil_div(M, kTcBM) * ceil_div(N, kTcBN);
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return TIB_E_ARG;
+  if (tiles > 0x7fffffff) return TIB_E_SIZE;
+  dim3 grid((unsigned)(tiles < sms ? tiles : sms));
   cudaError_t e;
   if (out_dtype == TIB_BF16) {
     auto kern = gemm_tcgen05_kernel<__nv_bfloat16>;
