@@ -126,7 +126,9 @@ def run_gemm(args) -> None:
         common = dict(bytes_moved=n * k * 2, flops=2 * args.rows * n * k, rows=args.rows, n=n, k=k)
         if ops.gemm_skinny_supports(args.rows, n, k):
             report(f"gemm_skinny[{name}]", timer(lambda: ops.gemm_skinny(x, w, out)), **common)
-        if ops.gemm_tcgen05_supports(args.rows, n, k):
+        if ops.gemm_tcgen05_swapab_supports(args.rows, n, k):
+            report(f"gemm_tcgen05_swapab[{name}]", timer(lambda: ops.gemm_tcgen05_swapab(x, w, out)), **common)
+        elif ops.gemm_tcgen05_supports(args.rows, n, k):
             report(f"gemm_tcgen05[{name}]", timer(lambda: ops.gemm_tcgen05(x, w, out)), **common)
         report(f"library_gemm[{name}]", timer(lambda: torch.mm(x, w.t(), out=out)), **common)
 

@@ -243,6 +243,191 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   }
 }
 
+// ------------------------------------------------------------------ few rows (decode): swap A and B
+// With at most 64 rows of x the product is a stream of w.  Here w is the 128-row operand of the MMA
+// (a tile of 128 output features) and the rows of x are its N dimension (padded to 16 .. 64), so the
+// accumulator is the transposed output tile: TMEM lane = feature, column = token.  K is split over the
+// blocks of a thread-block cluster (up to 8) so that enough blocks stream w at once; the partial
+// tiles meet in distributed shared memory: every block owns a band of the 128 features, receives that
+// band from its peers with st.shared::cluster, sums it and stores it.  No scratch in global memory,
+// no second kernel.
+constexpr int kSwStages = 3;
+constexpr uint32_t kSwWBytes = 128 * kTcBK * 2;   // 16 KB of w per stage
+constexpr int kSwRedRows = 136;                   // splits * ceil(128 / splits) <= 135 for up to 8 splits
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void umma_f16_idesc(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr));
+}
+
+// NPAD: rows of x padded to a multiple of 16 (16, 32, 48 or 64).
+template <int NPAD, typename TOut>
+__global__ void __launch_bounds__(kTcThreads)
+gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                           TOut* __restrict__ out, int M, int N, int K, int64_t ldo, int* __restrict__ error_word) {
+  constexpr uint32_t kXBytes = NPAD * kTcBK * 2;
+  constexpr uint32_t kStage = kSwWBytes + ((kXBytes + 1023u) & ~1023u);   // both parts start on 1024-byte boundaries
+  constexpr uint32_t kTmemCols = NPAD <= 32 ? 32 : 64;
+  constexpr int kRedStride = NPAD + 4;                                     // floats per row of the reduction buffer
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t red = base + kSwStages * kStage;                          // [splits][rows_per][kRedStride] floats
+  const uint32_t bars = red + kSwRedRows * kRedStride * 4;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (kSwStages + s); };
+  const uint32_t acc_bar = bars + 8u * (2 * kSwStages);
+  const uint32_t tmem_slot = bars + 8u * (2 * kSwStages + 1);
+  unsigned char* smem_gen = smem_raw + (base - smem_u32(smem_raw));        // generic pointer to `base`
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - base));
+  const float* red_gen = reinterpret_cast<const float*>(smem_gen + (red - base));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t splits = cluster_size(), rank = cluster_rank();
+  const int n0 = (blockIdx.x / splits) * 128;
+  const int k_blocks = K / kTcBK;
+  const int kb0 = (int)((int64_t)k_blocks * rank / splits), kb1 = (int)((int64_t)k_blocks * (rank + 1) / splits);
+  const int rows_per = (128 + splits - 1) / splits;                        // features each block of the cluster owns
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kSwStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  if (splits > 1) cluster_arrive();   // "this block runs and its shared memory exists"; waited for before the exchange
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = kb0; kb < kb1; ++kb) {
+        const int it = kb - kb0, s = it % kSwStages;
+        const uint32_t phase = (it / kSwStages) & 1;
+        if (!mbar_wait(empty_bar(s), phase ^ 1)) {
+          if (error_word) atomicExch(error_word, 0x7C0011);
+          break;
+        }
+        mbar_expect_tx(full_bar(s), kSwWBytes + kXBytes);
+        const uint32_t w_dst = base + s * kStage, x_dst = w_dst + kSwWBytes;
+        tma_load_2d(w_dst, &map_w, kb * kTcBK, n0, full_bar(s));
+        tma_load_2d(x_dst, &map_x, kb * kTcBK, 0, full_bar(s));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        const int it = kb - kb0, s = it % kSwStages;
+        const uint32_t phase = (it / kSwStages) & 1;
+        if (!mbar_wait(full_bar(s), phase)) {
+          if (error_word) atomicExch(error_word, 0x7C0012);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t w_src = base + s * kStage, x_src = w_src + kSwWBytes;
+#pragma unroll
+        for (int k = 0; k < kTcBK / 16; ++k)
+          umma_f16_idesc(tmem_base, umma_desc_k128(w_src + k * 32), umma_desc_k128(x_src + k * 32), idesc, (it | k) != 0);
+        umma_commit(empty_bar(s));
+      }
+      umma_commit(acc_bar);
+    }
+  }
+
+  __syncwarp();
+  // every thread takes part in the cluster barriers; warps 2..5 also move the accumulator
+  float acc[NPAD];
+  const int quarter = warp & 3;
+  const int f = quarter * 32 + lane;                 // feature (row of w) within the tile
+  bool have = false;
+  if (warp >= 2) {
+    if (kb1 > kb0 && mbar_wait(acc_bar, 0)) {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < NPAD / 16; ++c) {
+        uint32_t v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+        for (int q = 0; q < 16; ++q) acc[c * 16 + q] = __uint_as_float(v[q]);
+      }
+      have = true;
+    } else if (kb1 > kb0) {
+      if (error_word && lane == 0) atomicExch(error_word, 0x7C0013);
+    }
+    if (!have) {
+#pragma unroll
+      for (int q = 0; q < NPAD; ++q) acc[q] = 0.f;   // a block without k blocks adds nothing
+    }
+  }
+  if (splits == 1) {
+    if (warp >= 2 && n0 + f < N) {
+#pragma unroll
+      for (int m = 0; m < NPAD; ++m)
+        if (m < M) out[(size_t)m * ldo + n0 + f] = from_f32<TOut>(acc[m]);   // lanes = consecutive features
+    }
+  } else {
+    cluster_wait();                                  // all blocks of the cluster run: their shared memory may be written
+    if (warp >= 2) {
+      const uint32_t owner = f / rows_per, local = f - owner * rows_per;
+      const uint32_t dst = map_to_cta(red + ((rank * rows_per + local) * kRedStride) * 4, owner);
+#pragma unroll
+      for (int q = 0; q < NPAD; q += 4) st_cluster_f32x4(dst + q * 4, acc[q], acc[q + 1], acc[q + 2], acc[q + 3]);
+    }
+    cluster_arrive();
+    cluster_wait();                                  // every partial band has arrived
+    const int first = rank * rows_per;
+    const int mine = max(0, min(rows_per, 128 - first));
+    for (int idx = threadIdx.x; idx < mine * M; idx += kTcThreads) {
+      const int m = idx / mine, lr = idx - m * mine; // consecutive threads = consecutive features
+      float sum = 0.f;
+      for (uint32_t sp = 0; sp < splits; ++sp) sum += red_gen[(sp * rows_per + lr) * kRedStride + m];
+      if (n0 + first + lr < N) out[(size_t)m * ldo + n0 + first + lr] = from_f32<TOut>(sum);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -281,6 +466,87 @@ using namespace tib;
 // Whether tib_gemm_tcgen05 takes this shape: K a multiple of 64, N a multiple of 8.
 TIB_API int tib_gemm_tcgen05_supports(int M, int N, int K) {
   return M >= 1 && N >= 8 && N % 8 == 0 && K >= 64 && K % 64 == 0;
+}
+
+template <int NPAD, typename TOut>
+static int launch_swapab(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int M, int N, int K, int64_t ldo,
+                         int splits, int* error_word, cudaStream_t stream) {
+  constexpr uint32_t x_bytes = NPAD * kTcBK * 2;
+  constexpr uint32_t stage = kSwWBytes + ((x_bytes + 1023u) & ~1023u);
+  constexpr uint32_t smem = 1024 + kSwStages * stage + kSwRedRows * (NPAD + 4) * 4 + 256;
+  auto kern = gemm_tcgen05_swapab_kernel<NPAD, TOut>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(ceil_div(N, 128) * splits));
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, (TOut*)out, M, N, K, ldo, error_word);
+  if (e != cudaSuccess) return (int)e;
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}
+
+// How many ways K is split (= blocks of a cluster) for a product with few rows: the split that fills
+// the SMs' block slots most evenly, fewest splits first.
+static int swapab_splits(int N, int K, int sms, int blocks_per_sm) {
+  const int tiles = ceil_div(N, 128), k_blocks = K / kTcBK, slots = sms * blocks_per_sm;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= 8 && s * 2 <= k_blocks; ++s) {
+    const int units = tiles * s;
+    const double eff = (double)units / ((double)ceil_div(units, slots) * slots);
+    if (eff > best_eff + 0.02) {
+      best_eff = eff;
+      best = s;
+    }
+  }
+  return best;
+}
+
+// Whether tib_gemm_tcgen05_swapab takes this shape: at most 64 rows, K a multiple of 64, N a multiple of 8.
+TIB_API int tib_gemm_tcgen05_swapab_supports(int M, int N, int K) {
+  return M >= 1 && M <= 64 && N >= 8 && N % 8 == 0 && K >= 64 && K % 64 == 0;
+}
+
+// Few rows (decode): x: [M <= 64, K] bf16, w: [N, K] bf16, out: [M, N] bf16 or fp32.  splits: 0 lets the
+// library choose how many blocks share K (1..8), else that many.
+TIB_API int tib_gemm_tcgen05_swapab(const void* x, const void* w, void* out, int M, int N, int K, int64_t ldx,
+                                    int64_t ldw, int64_t ldo, int out_dtype, int splits, int* error_word,
+                                    cudaStream_t stream) {
+  if (M == 0 || N == 0) return TIB_OK;
+  if (!x || !w || !out) return TIB_E_ARG;
+  if (!tib_gemm_tcgen05_swapab_supports(M, N, K)) return TIB_E_SIZE;
+  if ((((uintptr_t)x | (uintptr_t)w) & 15) || ldx % 8 || ldw % 8) return TIB_E_ALIGN;
+  if (out_dtype != TIB_BF16 && out_dtype != TIB_F32) return TIB_E_DTYPE;
+  const int npad = (M + 15) / 16 * 16;
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return TIB_E_ARG;
+  if (splits <= 0) splits = swapab_splits(N, K, sms, npad <= 32 ? 3 : 2);
+  if (splits > 8 || splits > K / kTcBK) return TIB_E_SIZE;
+  CUtensorMap map_w, map_x;
+  int rc = make_map(&map_w, w, N, K, ldw, 128);
+  if (rc != TIB_OK) return rc;
+  rc = make_map(&map_x, x, M, K, ldx, npad);
+  if (rc != TIB_OK) return rc;
+#define TIB_SWAPAB(NP)                                                                                              \
+  (out_dtype == TIB_BF16 ? launch_swapab<NP, __nv_bfloat16>(map_w, map_x, out, M, N, K, ldo, splits, error_word, stream) \
+                         : launch_swapab<NP, float>(map_w, map_x, out, M, N, K, ldo, splits, error_word, stream))
+  switch (npad) {
+    case 16: return TIB_SWAPAB(16);
+    case 32: return TIB_SWAPAB(32);
+    case 48: return TIB_SWAPAB(48);
+    default: return TIB_SWAPAB(64);
+  }
+#undef TIB_SWAPAB
 }
 
 // x: [M, K] bf16 (row stride ldx), w: [N, K] bf16 (row stride ldw), out: [M, N] bf16 or fp32 (row stride ldo).

@@ -82,7 +82,8 @@ def lib() -> ctypes.CDLL:
         for fn in ("tib_embedding", "tib_add_rmsnorm", "tib_rmsnorm", "tib_swiglu", "tib_cast",
                    "tib_scatter_i32", "tib_advance_decode", "tib_rope_append", "tib_paged_attention_simt", "tib_gemm_f32", "tib_sample",
                    "tib_attention_mma_supports", "tib_prefill_attention", "tib_decode_attention",
-                   "tib_gemm_skinny", "tib_gemm_skinny_supports", "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports"):
+                   "tib_gemm_skinny", "tib_gemm_skinny_supports", "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
+                   "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
     return library
@@ -396,4 +397,26 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, error_word
     _check("gemm_tcgen05", lib().tib_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k),
                                                   c_int64(x.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)),
                                                   c_int(_code(out.dtype)), _ptr(error_word), _stream()))
+    return out
+
+
+def gemm_tcgen05_swapab_supports(m: int, n: int, k: int) -> bool:
+    return bool(lib().tib_gemm_tcgen05_swapab_supports(c_int(m), c_int(n), c_int(k)))
+
+
+def gemm_tcgen05_swapab(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, error_word: torch.Tensor | None = None,
+                        splits: int = 0) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w[N, K]^T for M <= 64 on tcgen05 tensor cores with the operands swapped: w is
+    streamed by TMA as the 128-row operand, K is split over a thread-block cluster (``splits`` = 0: chosen
+    by the library) and the partial tiles are summed through distributed shared memory."""
+    for name, t in (("x", x), ("w", w)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gemm_tcgen05_swapab: {name} must be a 2-D bf16 CUDA tensor with unit inner stride")
+    _need(out, "out")
+    (m, k), (n, k2) = x.shape, w.shape
+    if k != k2 or out.shape != (m, n):
+        raise KernelError(f"gemm_tcgen05_swapab: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    _check("gemm_tcgen05_swapab", lib().tib_gemm_tcgen05_swapab(
+        _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)), c_int64(w.stride(0)),
+        c_int64(out.stride(0)), c_int(_code(out.dtype)), c_int(splits), _ptr(error_word), _stream()))
     return out
