@@ -251,7 +251,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 // tiles meet in distributed shared memory: every block owns a band of the 128 features, receives that
 // band from its peers with st.shared::cluster, sums it and stores it.  No scratch in global memory,
 // no second kernel.
-constexpr int kSwStages = 3;
+// Stages of the w / x ring by padded row count: two blocks fit on an SM (their start-up and epilogue
+// overlap each other's streaming), so each gets what half the shared memory holds.
+constexpr int sw_stages(int npad) { return npad <= 16 ? 5 : npad <= 32 ? 4 : 3; }
 constexpr uint32_t kSwWBytes = 128 * kTcBK * 2;   // 16 KB of w per stage
 constexpr int kSwRedRows = 136;                   // splits * ceil(128 / splits) <= 135 for up to 8 splits
 
@@ -296,6 +298,7 @@ gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
   constexpr uint32_t kStage = kSwWBytes + ((kXBytes + 1023u) & ~1023u);   // both parts start on 1024-byte boundaries
   constexpr uint32_t kTmemCols = NPAD <= 32 ? 32 : 64;
   constexpr int kRedStride = NPAD + 4;                                     // floats per row of the reduction buffer
+  constexpr int kSwStages = sw_stages(NPAD);
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t red = base + kSwStages * kStage;                          // [splits][rows_per][kRedStride] floats
@@ -473,7 +476,7 @@ static int launch_swapab(const CUtensorMap& map_w, const CUtensorMap& map_x, voi
                          int splits, int* error_word, cudaStream_t stream) {
   constexpr uint32_t x_bytes = NPAD * kTcBK * 2;
   constexpr uint32_t stage = kSwWBytes + ((x_bytes + 1023u) & ~1023u);
-  constexpr uint32_t smem = 1024 + kSwStages * stage + kSwRedRows * (NPAD + 4) * 4 + 256;
+  constexpr uint32_t smem = 1024 + sw_stages(NPAD) * stage + kSwRedRows * (NPAD + 4) * 4 + 256;
   auto kern = gemm_tcgen05_swapab_kernel<NPAD, TOut>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
@@ -495,17 +498,20 @@ static int launch_swapab(const CUtensorMap& map_w, const CUtensorMap& map_x, voi
   return TIB_OK;
 }
 
-// How many ways K is split (= blocks of a cluster) for a product with few rows: the split that fills
-// the SMs' block slots most evenly, fewest splits first.
+// How many ways K is split (= blocks of a cluster) for a product with few rows.  Cost model: the blocks
+// run in rounds of `slots`; a block costs a fixed start-up (launch, pipeline fill, epilogue, cluster
+// exchange) plus its share of the tile's bytes at one SM's share of the memory bandwidth.
 static int swapab_splits(int N, int K, int sms, int blocks_per_sm) {
   const int tiles = ceil_div(N, 128), k_blocks = K / kTcBK, slots = sms * blocks_per_sm;
+  const double fixed_us = 3.0, tile_us = 128.0 * K * 2.0 / 44e3;   // 44 GB/s = 6.5 TB/s over 148 SMs
   int best = 1;
-  double best_eff = 0.0;
+  double best_cost = 1e30;
   for (int s = 1; s <= 8 && s * 2 <= k_blocks; ++s) {
-    const int units = tiles * s;
-    const double eff = (double)units / ((double)ceil_div(units, slots) * slots);
-    if (eff > best_eff + 0.02) {
-      best_eff = eff;
+    const int rounds = ceil_div(tiles * s, slots);
+    const double share = (double)(tiles * s < slots ? 1 : blocks_per_sm);   // blocks that share an SM's bandwidth
+    const double cost = rounds * (fixed_us + (s > 1 ? 1.0 : 0.0) + tile_us / s * share);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
       best = s;
     }
   }
@@ -530,7 +536,7 @@ TIB_API int tib_gemm_tcgen05_swapab(const void* x, const void* w, void* out, int
   const int npad = (M + 15) / 16 * 16;
   int device = 0, sms = 0;
   if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return TIB_E_ARG;
-  if (splits <= 0) splits = swapab_splits(N, K, sms, npad <= 32 ? 3 : 2);
+  if (splits <= 0) splits = swapab_splits(N, K, sms, 2);
   if (splits > 8 || splits > K / kTcBK) return TIB_E_SIZE;
   CUtensorMap map_w, map_x;
   int rc = make_map(&map_w, w, N, K, ldw, 128);
