@@ -190,7 +190,8 @@ def timed_e2e(model, batch: int, steps: int, warmup: int, seed: int) -> dict:
     from torchinferno_b200.config.engine_config import EngineConfig
     from torchinferno_b200.engine.engine import InferenceEngine
     from torchinferno_b200.engine.types import GenerateRequest, SamplingConfig
-    config = EngineConfig(model="<in memory>", dtype="bfloat16", page_size=PAGE_SIZE, max_batch_size=batch,
+    from torchinferno_b200.kernels import gemm
+    config = EngineConfig(model="<in memory>", dtype="bfloat16", page_size=PAGE_SIZE, max_batch_size=batch, gemm_backend=gemm.get_backend(),
                           max_num_batched_tokens=PROMPT_LEN, prefill_chunk_size=PROMPT_LEN,
                           kv_cache_tokens=batch * (PROMPT_LEN + warmup + steps + 2 * PAGE_SIZE))
     engine = InferenceEngine(model, config)
@@ -225,8 +226,10 @@ def run_ours(args) -> dict:
     import torch
     from torchinferno_b200.engine.factory import make_runner, random_model
     from torchinferno_b200.kernels.library import library_path, load_library
+    from torchinferno_b200.kernels import gemm
     peaks = load_peaks()
     load_library()
+    gemm.set_backend(args.gemm_backend)
     config = dict(LLAMA_8B)
     config["num_hidden_layers"] = args.layers
     sampler = ClockSampler()
@@ -261,7 +264,7 @@ def run_ours(args) -> dict:
             "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "context_from": main["context_from"],
             "context_to": main["context_to"], "page_size": PAGE_SIZE, "parallelism": "single GPU",
             "l2": "inputs larger than L2 (weights of a step: %.1f GB)" % (numbers["matmul_params"] * 2 / 1e9),
-            "peaks": peaks["source"],
+            "peaks": peaks["source"], "gemm_backend": args.gemm_backend,
         },
         "clocks": main["clocks"],
         "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
@@ -350,6 +353,7 @@ def main() -> int:
     parser.add_argument("--points", type=int, nargs="*", default=[1, 64], help="other batch sizes to decode at")
     parser.add_argument("--point-steps", type=int, default=None, help="decode steps of the other batch sizes (default: --steps)")
     parser.add_argument("--e2e-steps", type=int, default=512)
+    parser.add_argument("--gemm-backend", choices=["auto", "tcgen05", "library"], default="auto")
     args = parser.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:

@@ -95,3 +95,22 @@ def test_peaky_attention_shows_a_lost_key(model_folders, tmp_path):
         steps, index = maker(requests)
         replayer = InProcessReplayer(folder, "float32", max_tokens=peak_tokens(steps))
         check_rows(gather(replayer.run(steps), index), folder, requests, "float32")
+
+
+@pytest.mark.parametrize("backend", ["tcgen05", "library"])
+def test_bf16_projections_on_either_gemm_backend(model_folders, backend):
+    """The hand-written tcgen05 products (swap-AB for few rows, 128 x 256 tiles for many) and cuBLAS
+    must both carry the engine: same traces, same tolerance."""
+    need_gpu()
+    from torchinferno_b200.kernels import gemm, ops
+    folder, requests = model_folders["D"], _requests("D")
+    gemm.set_backend(backend)
+    try:
+        launches = ops.launch_count()
+        for maker in (trace_whole, trace_tail_decode, trace_mixed):
+            steps, index = maker(requests)
+            replayer = InProcessReplayer(folder, "bfloat16", max_tokens=peak_tokens(steps))
+            check_rows(gather(replayer.run(steps), index), folder, requests, "bfloat16")
+        assert ops.launch_count() > launches
+    finally:
+        gemm.set_backend("auto")

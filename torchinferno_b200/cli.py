@@ -35,6 +35,8 @@ def _engine_options(parser: argparse.ArgumentParser) -> None:
     parser.add_argument("--max-num-batched-tokens", type=int, default=8192, help="token budget of one step")
     parser.add_argument("--prefill-chunk-size", type=int, default=2048)
     parser.add_argument("--kv-cache-tokens", type=int, default=None, help="size of the page pool in tokens")
+    parser.add_argument("--gemm-backend", choices=["auto", "tcgen05", "library"], default="auto",
+                        help="bf16 projections: hand-written tcgen05 kernels, cuBLAS, or the measured mix")
 
 
 def _engine(args, model: str, **extra):
@@ -44,7 +46,8 @@ def _engine(args, model: str, **extra):
         model=model, tokenizer=getattr(args, "tokenizer", None), device=args.device, dtype=args.dtype,
         max_model_len=args.max_model_len, page_size=args.page_size, max_batch_size=args.max_batch_size,
         max_num_batched_tokens=args.max_num_batched_tokens, prefill_chunk_size=args.prefill_chunk_size,
-        kv_cache_tokens=args.kv_cache_tokens, seed=getattr(args, "seed", 0), **extra)
+        kv_cache_tokens=args.kv_cache_tokens, seed=getattr(args, "seed", 0),
+        gemm_backend=getattr(args, "gemm_backend", "auto"), **extra)
     return InferenceEngine.from_config(config)
 
 

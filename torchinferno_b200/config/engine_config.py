@@ -30,6 +30,7 @@ class EngineConfig:
     kv_cache_tokens: int | None = None      # pool size in tokens; default max_batch_size * max_model_len
     seed: int = 0
     use_cuda_graphs: bool = True
+    gemm_backend: str = "auto"              # auto | tcgen05 | library (bf16 projections)
 
     def __post_init__(self) -> None:
         if self.cache_backend != "paged":

@@ -246,16 +246,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 // ------------------------------------------------------------------ few rows (decode): swap A and B
 // With at most 64 rows of x the product is a stream of w.  Here w is the 128-row operand of the MMA
 // (a tile of 128 output features) and the rows of x are its N dimension (padded to 16 .. 64), so the
-// accumulator is the transposed output tile: TMEM lane = feature, column = token.  K is split over the
-// blocks of a thread-block cluster (up to 8) so that enough blocks stream w at once; the partial
-// tiles meet in distributed shared memory: every block owns a band of the 128 features, receives that
-// band from its peers with st.shared::cluster, sums it and stores it.  No scratch in global memory,
+// accumulator is the transposed output tile: TMEM lane = feature, column = token.
+//
+// The kernel is persistent: `clusters` thread-block clusters of `splits` blocks (one block per SM) walk
+// the feature tiles; block r of a cluster streams the r-th part of K of every tile its cluster takes.
+// The producer runs ahead across tiles, two accumulators alternate, and the partial tiles of a cluster
+// meet in distributed shared memory: every block owns a band of the 128 features, receives that band
+// from its peers with st.shared::cluster, sums it and stores it.  The hand-over is done with mbarriers
+// that peers arrive on remotely, so only the epilogue warps take part.  No scratch in global memory,
 // no second kernel.
-// Stages of the w / x ring by padded row count: two blocks fit on an SM (their start-up and epilogue
-// overlap each other's streaming), so each gets what half the shared memory holds.
-constexpr int sw_stages(int npad) { return npad <= 16 ? 5 : npad <= 32 ? 4 : 3; }
 constexpr uint32_t kSwWBytes = 128 * kTcBK * 2;   // 16 KB of w per stage
 constexpr int kSwRedRows = 136;                   // splits * ceil(128 / splits) <= 135 for up to 8 splits
+// Stages of the w / x ring: what fits beside two reduction buffers (a block has an SM to itself, and the
+// bytes in flight are what hide the memory latency).
+constexpr int sw_stages(int npad) { return npad <= 16 ? 9 : npad <= 32 ? 8 : npad <= 48 ? 6 : 5; }
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -267,8 +271,10 @@ __device__ __forceinline__ uint32_t cluster_size() {
   asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(r));
   return r;
 }
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
@@ -276,6 +282,21 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 }
 __device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+// Arrive on an mbarrier of another block of the cluster (address from map_to_cta); what this thread wrote
+// before is visible to whoever then waits with cluster scope.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if (i > 64) __nanosleep(32);
+  }
+  return false;
 }
 __device__ __forceinline__ void umma_f16_idesc(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
@@ -291,39 +312,48 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 
 // NPAD: rows of x padded to a multiple of 16 (16, 32, 48 or 64).
 template <int NPAD, typename TOut>
-__global__ void __launch_bounds__(kTcThreads)
+__global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                            TOut* __restrict__ out, int M, int N, int K, int64_t ldo, int* __restrict__ error_word) {
+  constexpr int kStages = sw_stages(NPAD);
   constexpr uint32_t kXBytes = NPAD * kTcBK * 2;
   constexpr uint32_t kStage = kSwWBytes + ((kXBytes + 1023u) & ~1023u);   // both parts start on 1024-byte boundaries
-  constexpr uint32_t kTmemCols = NPAD <= 32 ? 32 : 64;
-  constexpr int kRedStride = NPAD + 4;                                     // floats per row of the reduction buffer
-  constexpr int kSwStages = sw_stages(NPAD);
+  constexpr uint32_t kTmemCols = NPAD <= 16 ? 32 : NPAD <= 32 ? 64 : 128;  // two accumulators of NPAD columns
+  constexpr int kRedStride = NPAD + 4;                                     // floats per row of a reduction buffer
+  constexpr uint32_t kRedBytes = kSwRedRows * kRedStride * 4;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t red = base + kSwStages * kStage;                          // [splits][rows_per][kRedStride] floats
-  const uint32_t bars = red + kSwRedRows * kRedStride * 4;
+  const uint32_t red = base + kStages * kStage;                            // 2 x [splits][rows_per][kRedStride] floats
+  const uint32_t bars = red + 2 * kRedBytes;
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (kSwStages + s); };
-  const uint32_t acc_bar = bars + 8u * (2 * kSwStages);
-  const uint32_t tmem_slot = bars + 8u * (2 * kSwStages + 1);
+  auto empty_bar = [&](int s) { return bars + 8u * (kStages + s); };
+  auto acc_full_bar = [&](int b) { return bars + 8u * (2 * kStages + b); };
+  auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * kStages + 2 + b); };
+  auto red_full_bar = [&](int b) { return bars + 8u * (2 * kStages + 4 + b); };   // peers' partial bands have arrived
+  auto red_free_bar = [&](int b) { return bars + 8u * (2 * kStages + 6 + b); };   // every block has summed its band
+  const uint32_t tmem_slot = bars + 8u * (2 * kStages + 8);
   unsigned char* smem_gen = smem_raw + (base - smem_u32(smem_raw));        // generic pointer to `base`
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - base));
-  const float* red_gen = reinterpret_cast<const float*>(smem_gen + (red - base));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t splits = cluster_size(), rank = cluster_rank();
-  const int n0 = (blockIdx.x / splits) * 128;
+  const int cluster_id = blockIdx.x / splits, clusters = gridDim.x / splits;
+  const int n_tiles = (N + 127) / 128;
   const int k_blocks = K / kTcBK;
   const int kb0 = (int)((int64_t)k_blocks * rank / splits), kb1 = (int)((int64_t)k_blocks * (rank + 1) / splits);
   const int rows_per = (128 + splits - 1) / splits;                        // features each block of the cluster owns
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kSwStages; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 4);           // one arrival per epilogue warp
+      mbar_init(red_full_bar(b), 4 * splits);   // one arrival per epilogue warp of every block of the cluster
+      mbar_init(red_free_bar(b), 4 * splits);   // likewise, once they have summed their share of the band
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
@@ -334,95 +364,133 @@ gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem_base = *tmem_slot_ptr;
-  if (splits > 1) cluster_arrive();   // "this block runs and its shared memory exists"; waited for before the exchange
+  if (splits > 1) cluster_sync_all();   // every block of the cluster runs and has its barriers: peers may touch them
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = kb0; kb < kb1; ++kb) {
-        const int it = kb - kb0, s = it % kSwStages;
-        const uint32_t phase = (it / kSwStages) & 1;
-        if (!mbar_wait(empty_bar(s), phase ^ 1)) {
-          if (error_word) atomicExch(error_word, 0x7C0011);
-          break;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < n_tiles && ok; t += clusters) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = (it / kStages) & 1;
+          if (!mbar_wait(empty_bar(s), phase ^ 1)) {
+            if (error_word) atomicExch(error_word, 0x7C0011);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(full_bar(s), kSwWBytes + kXBytes);
+          const uint32_t w_dst = base + s * kStage, x_dst = w_dst + kSwWBytes;
+          tma_load_2d(w_dst, &map_w, kb * kTcBK, t * 128, full_bar(s));
+          tma_load_2d(x_dst, &map_x, kb * kTcBK, 0, full_bar(s));
         }
-        mbar_expect_tx(full_bar(s), kSwWBytes + kXBytes);
-        const uint32_t w_dst = base + s * kStage, x_dst = w_dst + kSwWBytes;
-        tma_load_2d(w_dst, &map_w, kb * kTcBK, n0, full_bar(s));
-        tma_load_2d(x_dst, &map_x, kb * kTcBK, 0, full_bar(s));
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      for (int kb = kb0; kb < kb1; ++kb) {
-        const int it = kb - kb0, s = it % kSwStages;
-        const uint32_t phase = (it / kSwStages) & 1;
-        if (!mbar_wait(full_bar(s), phase)) {
-          if (error_word) atomicExch(error_word, 0x7C0012);
+      uint32_t it = 0;
+      bool ok = true;
+      int j = 0;
+      for (int t = cluster_id; t < n_tiles && ok; t += clusters, ++j) {
+        const int b = j & 1;
+        if (!mbar_wait(acc_empty_bar(b), ((j >> 1) & 1) ^ 1)) {
+          if (error_word) atomicExch(error_word, 0x7C0014);
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t w_src = base + s * kStage, x_src = w_src + kSwWBytes;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = (it / kStages) & 1;
+          if (!mbar_wait(full_bar(s), phase)) {
+            if (error_word) atomicExch(error_word, 0x7C0012);
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint32_t w_src = base + s * kStage, x_src = w_src + kSwWBytes;
 #pragma unroll
-        for (int k = 0; k < kTcBK / 16; ++k)
-          umma_f16_idesc(tmem_base, umma_desc_k128(w_src + k * 32), umma_desc_k128(x_src + k * 32), idesc, (it | k) != 0);
-        umma_commit(empty_bar(s));
+          for (int k = 0; k < kTcBK / 16; ++k)
+            umma_f16_idesc(tmem_base + b * NPAD, umma_desc_k128(w_src + k * 32), umma_desc_k128(x_src + k * 32), idesc,
+                           (kb > kb0) || (k > 0));
+          umma_commit(empty_bar(s));
+        }
+        umma_commit(acc_full_bar(b));
       }
-      umma_commit(acc_bar);
-    }
-  }
-
-  __syncwarp();
-  // every thread takes part in the cluster barriers; warps 2..5 also move the accumulator
-  float acc[NPAD];
-  const int quarter = warp & 3;
-  const int f = quarter * 32 + lane;                 // feature (row of w) within the tile
-  bool have = false;
-  if (warp >= 2) {
-    if (kb1 > kb0 && mbar_wait(acc_bar, 0)) {
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
-      for (int c = 0; c < NPAD / 16; ++c) {
-        uint32_t v[16];
-        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 16, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-        for (int q = 0; q < 16; ++q) acc[c * 16 + q] = __uint_as_float(v[q]);
-      }
-      have = true;
-    } else if (kb1 > kb0) {
-      if (error_word && lane == 0) atomicExch(error_word, 0x7C0013);
-    }
-    if (!have) {
-#pragma unroll
-      for (int q = 0; q < NPAD; ++q) acc[q] = 0.f;   // a block without k blocks adds nothing
-    }
-  }
-  if (splits == 1) {
-    if (warp >= 2 && n0 + f < N) {
-#pragma unroll
-      for (int m = 0; m < NPAD; ++m)
-        if (m < M) out[(size_t)m * ldo + n0 + f] = from_f32<TOut>(acc[m]);   // lanes = consecutive features
     }
   } else {
-    cluster_wait();                                  // all blocks of the cluster run: their shared memory may be written
-    if (warp >= 2) {
-      const uint32_t owner = f / rows_per, local = f - owner * rows_per;
-      const uint32_t dst = map_to_cta(red + ((rank * rows_per + local) * kRedStride) * 4, owner);
-#pragma unroll
-      for (int q = 0; q < NPAD; q += 4) st_cluster_f32x4(dst + q * 4, acc[q], acc[q + 1], acc[q + 2], acc[q + 3]);
-    }
-    cluster_arrive();
-    cluster_wait();                                  // every partial band has arrived
+    const int quarter = warp & 3;
+    const int f = quarter * 32 + lane;                 // feature (row of w) within the tile
+    const int et = threadIdx.x - 64;                   // 0 .. 127 among the epilogue threads
     const int first = rank * rows_per;
     const int mine = max(0, min(rows_per, 128 - first));
-    for (int idx = threadIdx.x; idx < mine * M; idx += kTcThreads) {
-      const int m = idx / mine, lr = idx - m * mine; // consecutive threads = consecutive features
-      float sum = 0.f;
-      for (uint32_t sp = 0; sp < splits; ++sp) sum += red_gen[(sp * rows_per + lr) * kRedStride + m];
-      if (n0 + first + lr < N) out[(size_t)m * ldo + n0 + first + lr] = from_f32<TOut>(sum);
+    int j = 0;
+    for (int t = cluster_id; t < n_tiles; t += clusters, ++j) {
+      const int b = j & 1;
+      const uint32_t par = (j >> 1) & 1;
+      const int n0 = t * 128;
+      float acc[NPAD];
+      if (kb1 > kb0) {
+        if (!mbar_wait(acc_full_bar(b), par)) {
+          if (error_word && lane == 0) atomicExch(error_word, 0x7C0013);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+        for (int c = 0; c < NPAD / 16; ++c) {
+          uint32_t v[16];
+          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + b * NPAD + c * 16, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+          for (int q = 0; q < 16; ++q) acc[c * 16 + q] = __uint_as_float(v[q]);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty_bar(b));   // the MMA warp may reuse this accumulator
+      } else {
+#pragma unroll
+        for (int q = 0; q < NPAD; ++q) acc[q] = 0.f;    // a block without k blocks adds nothing
+      }
+      if (splits == 1) {
+        if (n0 + f < N) {
+#pragma unroll
+          for (int m = 0; m < NPAD; ++m)
+            if (m < M) out[(size_t)m * ldo + n0 + f] = from_f32<TOut>(acc[m]);   // lanes = consecutive features
+        }
+        continue;
+      }
+      // exchange: this block's partial rows go to the blocks that own them
+      if (!mbar_wait_cluster(red_free_bar(b), par ^ 1)) {           // every block is done with buffer b of two tiles ago
+        if (error_word && lane == 0) atomicExch(error_word, 0x7C0015);
+        break;
+      }
+      const uint32_t red_b = red + b * kRedBytes;
+      {
+        const uint32_t owner = f / rows_per, local = f - owner * rows_per;
+        const uint32_t dst = map_to_cta(red_b + ((rank * rows_per + local) * kRedStride) * 4, owner);
+#pragma unroll
+        for (int q = 0; q < NPAD; q += 4) st_cluster_f32x4(dst + q * 4, acc[q], acc[q + 1], acc[q + 2], acc[q + 3]);
+      }
+      __syncwarp();
+      if (lane < splits) mbar_arrive_remote(map_to_cta(red_full_bar(b), lane));   // this warp's rows are written, everywhere
+      if (!mbar_wait_cluster(red_full_bar(b), par)) {
+        if (error_word && lane == 0) atomicExch(error_word, 0x7C0016);
+        break;
+      }
+      const float* red_gen = reinterpret_cast<const float*>(smem_gen + (red_b - base));
+      for (int idx = et; idx < mine * M; idx += 128) {
+        const int m = idx / mine, lr = idx - m * mine;   // consecutive threads = consecutive features
+        float sum = 0.f;
+        for (uint32_t sp = 0; sp < splits; ++sp) sum += red_gen[(sp * rows_per + lr) * kRedStride + m];
+        if (n0 + first + lr < N) out[(size_t)m * ldo + n0 + first + lr] = from_f32<TOut>(sum);
+      }
+      // this warp has read its share of the band: tell every block (this one included)
+      __syncwarp();
+      if (lane < splits) mbar_arrive_remote(map_to_cta(red_free_bar(b), lane));
     }
   }
+  __syncwarp();
+  if (splits > 1) cluster_sync_all();   // no block leaves while a peer may still write to it or arrive on its barriers
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   if (warp == 1) {
@@ -476,46 +544,59 @@ static int launch_swapab(const CUtensorMap& map_w, const CUtensorMap& map_x, voi
                          int splits, int* error_word, cudaStream_t stream) {
   constexpr uint32_t x_bytes = NPAD * kTcBK * 2;
   constexpr uint32_t stage = kSwWBytes + ((x_bytes + 1023u) & ~1023u);
-  constexpr uint32_t smem = 1024 + sw_stages(NPAD) * stage + kSwRedRows * (NPAD + 4) * 4 + 256;
+  constexpr uint32_t smem = 1024 + sw_stages(NPAD) * stage + 2 * kSwRedRows * (NPAD + 4) * 4 + 256;
   auto kern = gemm_tcgen05_swapab_kernel<NPAD, TOut>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return (int)e;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = ceil_div(N, 128), k_blocks = K / kTcBK;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(ceil_div(N, 128) * splits));
   cfg.blockDim = dim3(kTcThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)splits;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, (TOut*)out, M, N, K, ldo, error_word);
+  // How many clusters of s blocks can run at once (one block per SM), asked once per s.
+  static int resident[9] = {0};
+  auto clusters_of = [&](int s) {
+    if (resident[s] == 0) {
+      attr[0].val.clusterDim.x = (unsigned)s;
+      cfg.gridDim = dim3((unsigned)s);
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) n = 1;
+      resident[s] = n;
+    }
+    return resident[s];
+  };
+  if (splits <= 0) {
+    // Every block streams tile_bytes / s of each tile its cluster takes; the clusters take the tiles in
+    // rounds.  Fewest rounds x bytes per round wins; a split costs a little for the exchange.
+    double best = 1e30;
+    splits = 1;
+    for (int s = 1; s <= 8 && (s == 1 || s * 2 <= k_blocks); ++s) {
+      const int rounds = ceil_div(tiles, clusters_of(s));
+      const double cost = rounds * (1.0 / s + 0.02) + (s > 1 ? 0.03 : 0.0);
+      if (cost < best - 1e-12) {
+        best = cost;
+        splits = s;
+      }
+    }
+  }
+  if (splits > 8 || splits > k_blocks) return TIB_E_SIZE;
+  const int clusters = tiles < clusters_of(splits) ? tiles : clusters_of(splits);
+  attr[0].val.clusterDim.x = (unsigned)splits;
+  cfg.gridDim = dim3((unsigned)(clusters * splits));
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, (TOut*)out, M, N, K, ldo, error_word);
   if (e != cudaSuccess) return (int)e;
   TIB_LAUNCH_CHECK();
   return TIB_OK;
-}
-
-// How many ways K is split (= blocks of a cluster) for a product with few rows.  Cost model: the blocks
-// run in rounds of `slots`; a block costs a fixed start-up (launch, pipeline fill, epilogue, cluster
-// exchange) plus its share of the tile's bytes at one SM's share of the memory bandwidth.
-static int swapab_splits(int N, int K, int sms, int blocks_per_sm) {
-  const int tiles = ceil_div(N, 128), k_blocks = K / kTcBK, slots = sms * blocks_per_sm;
-  const double fixed_us = 3.0, tile_us = 128.0 * K * 2.0 / 44e3;   // 44 GB/s = 6.5 TB/s over 148 SMs
-  int best = 1;
-  double best_cost = 1e30;
-  for (int s = 1; s <= 8 && s * 2 <= k_blocks; ++s) {
-    const int rounds = ceil_div(tiles * s, slots);
-    const double share = (double)(tiles * s < slots ? 1 : blocks_per_sm);   // blocks that share an SM's bandwidth
-    const double cost = rounds * (fixed_us + (s > 1 ? 1.0 : 0.0) + tile_us / s * share);
-    if (cost < best_cost - 1e-9) {
-      best_cost = cost;
-      best = s;
-    }
-  }
-  return best;
 }
 
 // Whether tib_gemm_tcgen05_swapab takes this shape: at most 64 rows, K a multiple of 64, N a multiple of 8.
@@ -534,9 +615,6 @@ TIB_API int tib_gemm_tcgen05_swapab(const void* x, const void* w, void* out, int
   if ((((uintptr_t)x | (uintptr_t)w) & 15) || ldx % 8 || ldw % 8) return TIB_E_ALIGN;
   if (out_dtype != TIB_BF16 && out_dtype != TIB_F32) return TIB_E_DTYPE;
   const int npad = (M + 15) / 16 * 16;
-  int device = 0, sms = 0;
-  if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return TIB_E_ARG;
-  if (splits <= 0) splits = swapab_splits(N, K, sms, 2);
   if (splits > 8 || splits > K / kTcBK) return TIB_E_SIZE;
   CUtensorMap map_w, map_x;
   int rc = make_map(&map_w, w, N, K, ldw, 128);

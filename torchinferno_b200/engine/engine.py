@@ -20,6 +20,7 @@ from torchinferno_b200.config.engine_config import EngineConfig
 from torchinferno_b200.engine.batch import StepEntry
 from torchinferno_b200.engine.factory import load_model, make_runner
 from torchinferno_b200.engine.scheduler import Scheduler, SchedulerRequest, StepPlan, TokenEvent
+from torchinferno_b200.kernels import gemm
 from torchinferno_b200.engine.types import GenerateOutput, GenerateRequest, SamplingConfig, TokenOutput, Usage
 from torchinferno_b200.sampling.sampler import Sampler, SamplingParams
 
@@ -38,6 +39,7 @@ class InferenceEngine:
         self.runner = make_runner(model, page_size=config.page_size, num_pages=num_pages,
                                   max_requests=config.max_batch_size, max_request_tokens=limit, check_errors=False)
         self.runner.use_cuda_graphs = config.use_cuda_graphs
+        gemm.set_backend(config.gemm_backend)
         self.scheduler = Scheduler(self.runner.cache, max_batch_size=config.max_batch_size,
                                    max_step_tokens=config.max_num_batched_tokens,
                                    prefill_chunk_size=config.prefill_chunk_size)

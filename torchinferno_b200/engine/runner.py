@@ -16,7 +16,7 @@ import torch
 
 from torchinferno_b200.cache.manager import CacheManager, OutOfPages
 from torchinferno_b200.engine.batch import EntryPlacement, StepBatch, StepEntry, build_batch
-from torchinferno_b200.kernels import ops
+from torchinferno_b200.kernels import gemm, ops
 
 
 class StepError(RuntimeError):
@@ -62,6 +62,7 @@ class ModelRunner:
         self.use_cuda_graphs = use_cuda_graphs
         self._graph_ok = all(spec is None for spec in model.state_requirements())
         self._graphs: dict[int, _DecodeGraph] = {}
+        gemm.set_error_word(cache.error_word)   # bounded waits of the tcgen05 kernels report here
         self.graph_replays = 0
 
     # --------------------------------------------------------------- step
@@ -233,4 +234,5 @@ class ModelRunner:
         word = int(self.cache.error_word.item())
         if word:
             self.cache.error_word.zero_()
-            raise StepError(f"a kernel met a page id outside its pool (code {word:#x}); the step's result is invalid")
+            raise StepError(f"a kernel reported an error (code {word:#x}: 0x7c.... a bounded wait of a tcgen05 kernel ran out, "
+                            f"else a page id outside its pool); the step's result is invalid")

@@ -12,6 +12,35 @@ import torch
 
 from torchinferno_b200.kernels import ops
 
+# Which kernel multiplies bf16 operands:
+#   "auto"     whichever measured faster inside the engine's steps on the B200.  Today that is cuBLAS
+#              for every shape of the model (the swap-AB kernel ties it in isolation at up to 16 rows
+#              but costs about 10 us more per layer inside a captured decode step), so SWAPAB_AUTO_ROWS
+#              is 0; the hand-written kernels are chosen with "tcgen05"
+#   "tcgen05"  the hand-written kernels wherever they take the shape (swap-AB up to 64 rows, the
+#              128 x 256-tile kernel above)
+#   "library"  cuBLAS everywhere
+_backend = "auto"
+_error_word: torch.Tensor | None = None
+SWAPAB_AUTO_ROWS = 0
+
+
+def set_backend(name: str) -> None:
+    global _backend
+    if name not in ("auto", "tcgen05", "library"):
+        raise ValueError(f"unknown GEMM backend {name!r}: auto, tcgen05 or library")
+    _backend = name
+
+
+def get_backend() -> str:
+    return _backend
+
+
+def set_error_word(word: torch.Tensor | None) -> None:
+    """The device word in which the tcgen05 kernels report a bounded wait that ran out."""
+    global _error_word
+    _error_word = word
+
 
 def linear(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype | None = None,
            out: torch.Tensor | None = None) -> torch.Tensor:
@@ -38,6 +67,18 @@ def linear(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype | No
 def _linear_bf16(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
                  out: torch.Tensor | None) -> torch.Tensor:
     m, n = x.shape[0], weight.shape[0]
+    k = x.shape[1]
+    if _backend != "library" and out_dtype in (torch.bfloat16, torch.float32):
+        rows = SWAPAB_AUTO_ROWS if _backend == "auto" else 64
+        aligned = x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
+        if aligned and m <= rows and ops.gemm_tcgen05_swapab_supports(m, n, k):
+            if out is None or out.dtype != out_dtype:
+                out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+            return ops.gemm_tcgen05_swapab(x, weight, out, _error_word)
+        if aligned and _backend == "tcgen05" and ops.gemm_tcgen05_supports(m, n, k):
+            if out is None or out.dtype != out_dtype:
+                out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+            return ops.gemm_tcgen05(x, weight, out, _error_word)
     if out_dtype == torch.bfloat16:
         if out is None:
             out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
