@@ -1,0 +1,62 @@
+"""Llama-3.1-8B layer sizes (hidden 4096, 32 heads / 8 kv heads of 128, intermediate 14336, vocabulary
+128256, llama3 rope scaling), two layers so that the plain implementation can follow on the CPU.
+Checks the kernels at the sizes the benchmark runs: 32-bit against the plain implementation under
+different cuts, bfloat16 within its tolerance."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+from gpu_common import BF16_REL, need_gpu
+from replay_util import InProcessReplayer, gather, peak_tokens, trace_mixed, trace_portions, trace_whole
+
+pytestmark = pytest.mark.gpu
+
+LARGE = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 128256, "hidden_size": 4096,
+    "intermediate_size": 14336, "num_hidden_layers": 2, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "max_position_embeddings": 131072, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+}
+
+
+@pytest.fixture(scope="module")
+def large_folder(tmp_path_factory):
+    from torchinferno_b200.weights.random_init import write_random_model
+    folder = tmp_path_factory.mktemp("large")
+    write_random_model(LARGE, folder, seed=5)
+    return folder
+
+
+@pytest.fixture(scope="module")
+def large_reference(large_folder):
+    g = torch.Generator().manual_seed(77)
+    requests = {f"r{i}": torch.randint(0, LARGE["vocab_size"], (n,), generator=g).tolist() for i, n in enumerate([70, 33, 130])}
+    config, weights = plain_llama.read_model_folder(large_folder, dtype=torch.float32)
+    want = {k: plain_llama.forward(config, weights, v).double().numpy() for k, v in requests.items()}
+    return requests, want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_large_layer_sizes_under_every_cut(large_folder, large_reference, dtype):
+    need_gpu()
+    requests, want = large_reference
+    for maker in (trace_whole, trace_portions, trace_mixed):
+        steps, index = maker(requests)
+        replayer = InProcessReplayer(large_folder, dtype, max_tokens=peak_tokens(steps))
+        rows = gather(replayer.run(steps), index)
+        worst = 0.0
+        for (name, pos), got_list in rows.items():
+            ref = want[name]
+            for got in got_list:
+                assert np.isfinite(got).all()
+                err = np.abs(got.astype(np.float64) - ref[pos]).max()
+                # the plain implementation runs in float32 here (the model is too large for float64 on the
+                # CPU), so its own rounding counts: 1e-4 of the largest logit in 32-bit
+                bound = (1e-4 if dtype == "float32" else BF16_REL) * np.abs(ref).max()
+                worst = max(worst, err / bound)
+                assert err <= bound, f"{maker.__name__} {name}@{pos} ({dtype}): {err:.3e} > {bound:.3e}"
+        del replayer
+        torch.cuda.empty_cache()
