@@ -87,12 +87,8 @@ def run_decode_attention(args) -> None:
     q_start, kv_start, slots = i32(list(range(n + 1))), i32([args.context - 1] * n), i32(list(range(n)))
     timer = Timer(args.iters)
     kv_bytes = n * args.context * 2 * k * d * 2
-    targets = args.target_blocks or [None]
-    for target in targets:
-        if target is None:
-            splits, chunk = ops.decode_num_splits(n, h, k), 0
-        else:
-            splits, chunk = ops.decode_split(n, h, k, args.context, target_blocks=target)
+    for forced in (args.splits or [None]):
+        splits, chunk = (ops.decode_num_splits(n, h, k) if forced is None else forced), 0
         scratch = torch.empty(n * h * splits * (d + 2), dtype=torch.float32, device="cuda")
         fn = lambda: ops.decode_attention(q, pool, out, q_start, kv_start, slots, table, n, h, k, d, 1 / math.sqrt(d),
                                           args.context, scratch=scratch, num_splits=splits, chunk=chunk)
@@ -170,7 +166,7 @@ def main(argv=None) -> int:
     p = sub.add_parser("decode-attention")
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=2048)
-    p.add_argument("--target-blocks", type=int, nargs="*", default=None, help="try these block-count targets for the split")
+    p.add_argument("--splits", type=int, nargs="*", default=None, help="try these numbers of context splits")
     common(p)
     p.set_defaults(func=run_decode_attention)
     p = sub.add_parser("prefill-attention")
