@@ -225,14 +225,17 @@ __device__ __forceinline__ void pv_slab(float (&o)[D / 8][4], const uint32_t (&p
 
 // ------------------------------------------------------------------ prefill
 template <int D, int STAGES>
-__global__ void __launch_bounds__(kMmaThreads)
+__global__ void __launch_bounds__(kMmaThreads, D <= 64 ? 4 : 3)
 prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
                          __nv_bfloat16* __restrict__ out, MmaAttnArgs a) {
   constexpr int BM = 64;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [BM][D]
-  __nv_bfloat16* k_s = q_s + BM * D;                                 // [STAGES][kBN][D]
+  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [STAGES][kBN][D]
   __nv_bfloat16* v_s = k_s + STAGES * kBN * D;
+  // The queries only pass through shared memory on their way to registers: they borrow the key buffer of
+  // the last stage, which is first filled inside the loop, after every warp has taken its fragments.
+  static_assert(BM == kBN, "the query tile borrows one key stage");
+  __nv_bfloat16* q_s = k_s + (STAGES - 1) * kBN * D;                 // [BM][D]
 
   const int entry = blockIdx.z, kvh = blockIdx.y;
   const int row0 = a.q_start[entry];
@@ -535,7 +538,7 @@ template <int D>
 static int launch_prefill(const void* q, const void* pool, void* out, const MmaAttnArgs& a, int n_entries,
                           int max_q_len, cudaStream_t stream) {
   constexpr int STAGES = 2;
-  const size_t smem = sizeof(__nv_bfloat16) * ((size_t)64 * D + 2 * (size_t)STAGES * kBN * D);
+  const size_t smem = sizeof(__nv_bfloat16) * (2 * (size_t)STAGES * kBN * D);
   auto kern = prefill_attention_kernel<D, STAGES>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
