@@ -28,10 +28,10 @@ def test_random_folder_has_every_tensor_and_loads(tmp_path):
     report = load_weights(model, tmp_path)
     assert report["tensors"] == len(tensors) and report["stored_dtypes"] == ["bfloat16"]
     block = model.blocks[0]
-    assert block.mixer.qkv_weight.shape == ((4 + 2 * 2) * 16, 64) and block.mixer.qkv_weight.dtype == torch.bfloat16
-    assert torch.equal(block.mixer.qkv_weight[:64], tensors["model.layers.0.self_attn.q_proj.weight"])
-    assert torch.equal(block.mixer.qkv_weight[64:96], tensors["model.layers.0.self_attn.k_proj.weight"])
-    assert torch.equal(block.feed_forward.gate_up_weight[128:], tensors["model.layers.0.mlp.up_proj.weight"])
+    assert block.mixer.qkv_weight.tensor.shape == ((4 + 2 * 2) * 16, 64) and block.mixer.qkv_weight.dtype == torch.bfloat16
+    assert torch.equal(block.mixer.qkv_weight.tensor[:64], tensors["model.layers.0.self_attn.q_proj.weight"])
+    assert torch.equal(block.mixer.qkv_weight.tensor[64:96], tensors["model.layers.0.self_attn.k_proj.weight"])
+    assert torch.equal(block.feed_forward.gate_up_weight.tensor[128:], tensors["model.layers.0.mlp.up_proj.weight"])
     assert block.mixer_norm.weight.dtype == torch.float32          # vectors are widened
     assert model.head is not model.embedding
 

@@ -54,6 +54,7 @@ class InferenceEngine:
     def from_config(cls, config: EngineConfig) -> "InferenceEngine":
         if config.model_kind not in ("auto", "llama3", "llama"):
             raise ValueError(f"model_kind={config.model_kind!r} is not known; use 'auto'")
+        gemm.set_backend(config.gemm_backend)   # decides the layout the weights are bound in
         model = load_model(config.model, dtype=config.dtype, device=config.device or "cuda:0")
         return cls(model, config, _load_tokenizer(config))
 

@@ -42,9 +42,44 @@ def set_error_word(word: torch.Tensor | None) -> None:
     _error_word = word
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype | None = None,
+class LinearWeight:
+    """A projection matrix as the chosen kernels want it laid out.
+
+    Checkpoints store [out, in].  The hand-written kernels read that layout (K-major rows).  cuBLAS is
+    measurably faster on few rows when the matrix is stored [in, out] (at 8 rows of the 8B sizes: qkv
+    14.8 -> 12.5 us, gate/up 42.4 -> 37.8 us, down 26.8 -> 25.3 us; no difference at 2,048 rows), which is
+    what the reference's optional pre-transposed copies for M <= 64 are for
+    (src/torchinferno/models/llama3/tensor_parallel.py:11201-11239).  Only one layout is kept.
+    """
+
+    def __init__(self, weight: torch.Tensor, *, allow_transpose: bool = True) -> None:
+        self.out_features, self.in_features = weight.shape
+        self.transposed = bool(allow_transpose and weight.dtype == torch.bfloat16 and weight.is_cuda
+                               and _backend != "tcgen05")
+        self.tensor = weight.t().contiguous() if self.transposed else weight.contiguous()
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.tensor.dtype
+
+    def rows(self, start: int, stop: int) -> "LinearWeight":
+        """The projection onto output features start .. stop-1 (a view, nothing is copied)."""
+        view = object.__new__(LinearWeight)
+        view.out_features, view.in_features, view.transposed = stop - start, self.in_features, self.transposed
+        view.tensor = self.tensor[:, start:stop] if self.transposed else self.tensor[start:stop]
+        return view
+
+    def nbytes(self) -> int:
+        return self.tensor.numel() * self.tensor.element_size()
+
+
+def linear(x: torch.Tensor, weight: "torch.Tensor | LinearWeight", *, out_dtype: torch.dtype | None = None,
            out: torch.Tensor | None = None) -> torch.Tensor:
-    """``x``: [tokens, in]; ``weight``: [out, in]; returns [tokens, out] in ``out_dtype``."""
+    """``x``: [tokens, in]; ``weight``: [out, in] (or a :class:`LinearWeight`); returns [tokens, out] in ``out_dtype``."""
+    if isinstance(weight, LinearWeight):
+        if weight.transposed:
+            return _linear_library_kn(x, weight.tensor, out_dtype or x.dtype, out)
+        weight = weight.tensor
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
         raise ops.KernelError(f"linear: shapes {tuple(x.shape)} and {tuple(weight.shape)} do not fit")
     if not x.is_cuda or not weight.is_cuda:
@@ -62,6 +97,25 @@ def linear(x: torch.Tensor, weight: torch.Tensor, *, out_dtype: torch.dtype | No
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise ops.KernelError(f"linear: unsupported dtypes {x.dtype} / {weight.dtype}")
     return _linear_bf16(x, weight, out_dtype, out)
+
+
+def _linear_library_kn(x: torch.Tensor, weight_kn: torch.Tensor, out_dtype: torch.dtype,
+                       out: torch.Tensor | None) -> torch.Tensor:
+    """cuBLAS on a matrix stored [in, out]."""
+    if x.dim() != 2 or x.shape[1] != weight_kn.shape[0]:
+        raise ops.KernelError(f"linear: shapes {tuple(x.shape)} and [in, out] = {tuple(weight_kn.shape)} do not fit")
+    if _backend == "tcgen05":
+        raise ops.KernelError("linear: these weights were laid out for the library; bind the model after "
+                              "choosing the tcgen05 backend")
+    if out_dtype == torch.bfloat16:
+        if out is None:
+            out = torch.empty((x.shape[0], weight_kn.shape[1]), dtype=torch.bfloat16, device=x.device)
+        return torch.mm(x, weight_kn, out=out)
+    result = torch.mm(x, weight_kn, out_dtype=torch.float32)
+    if out is not None:
+        out.copy_(result)
+        return out
+    return result
 
 
 def _linear_bf16(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,

@@ -71,15 +71,15 @@ class CausalLM:
         seen: dict[int, int] = {}
 
         def note(t: torch.Tensor | None) -> None:
-            if t is not None:
+            if isinstance(t, torch.Tensor):
                 seen[t.data_ptr()] = t.numel() * t.element_size()
 
         note(self.head)
         parts = [part for block in self.blocks for _, part in block.named_parts()] + [self.final_norm]
         for part in parts:
             for key, value in vars(part).items():
-                if isinstance(value, torch.Tensor) and key.endswith("weight"):
-                    note(value)
+                if key.endswith("weight"):
+                    note(getattr(value, "tensor", value) if not isinstance(value, torch.Tensor) else value)
         return sum(seen.values())
 
     # -------------------------------------------------------------- needs

@@ -19,7 +19,7 @@ from typing import Mapping
 import torch
 
 from torchinferno_b200.kernels import attention as attention_kernels
-from torchinferno_b200.kernels.gemm import linear
+from torchinferno_b200.kernels.gemm import LinearWeight, linear
 from torchinferno_b200.parts.base import (CacheSpec, LayerContext, Mixer, PartSpec, WeightSpec,
                                           build_part, register_part)
 
@@ -40,8 +40,8 @@ class GQAAttention(Mixer):
         if not isinstance(position, PartSpec):
             position = PartSpec(**position)
         self.position = build_part("position", position, dtype=dtype, device=device)
-        self.qkv_weight: torch.Tensor | None = None
-        self.o_weight: torch.Tensor | None = None
+        self.qkv_weight: LinearWeight | None = None
+        self.o_weight: LinearWeight | None = None
 
     def weight_specs(self) -> list[WeightSpec]:
         q, k, v, o = self.names
@@ -51,8 +51,8 @@ class GQAAttention(Mixer):
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         q, k, v, o = self.names
-        self.qkv_weight = torch.cat([weights[q], weights[k], weights[v]], dim=0).contiguous()
-        self.o_weight = weights[o].contiguous()
+        self.qkv_weight = LinearWeight(torch.cat([weights[q], weights[k], weights[v]], dim=0))
+        self.o_weight = LinearWeight(weights[o], allow_transpose=False)   # (cuBLAS is no faster on [in, out] here)
 
     def cache_spec(self) -> CacheSpec:
         return CacheSpec(self.kv_heads, self.head_dim, self.window)
@@ -67,7 +67,7 @@ class GQAAttention(Mixer):
             qkv = linear(x, self.qkv_weight)
             self.position.encode_and_store(qkv, q, ctx, h, k, d)
         else:
-            q_only = linear(x, self.qkv_weight[: h * d])
+            q_only = linear(x, self.qkv_weight.rows(0, h * d))
             self.position.encode_and_store(q_only, q, ctx, h, 0, d)
         out = torch.empty_like(q)
         attention_kernels.paged_attention(q, out, ctx, h, k, d, self.scale,

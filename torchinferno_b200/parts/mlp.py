@@ -13,7 +13,7 @@ from typing import Mapping
 import torch
 
 from torchinferno_b200.kernels import ops
-from torchinferno_b200.kernels.gemm import linear
+from torchinferno_b200.kernels.gemm import LinearWeight, linear
 from torchinferno_b200.parts.base import FeedForward, LayerContext, WeightSpec, register_part
 
 
@@ -24,8 +24,8 @@ class SwiGLUFeedForward(FeedForward):
         super().__init__(dtype=dtype, device=device)
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.names = (gate_name, up_name, down_name)
-        self.gate_up_weight: torch.Tensor | None = None
-        self.down_weight: torch.Tensor | None = None
+        self.gate_up_weight: LinearWeight | None = None
+        self.down_weight: LinearWeight | None = None
 
     def weight_specs(self) -> list[WeightSpec]:
         g, u, d = self.names
@@ -35,8 +35,8 @@ class SwiGLUFeedForward(FeedForward):
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         g, u, d = self.names
-        self.gate_up_weight = torch.cat([weights[g], weights[u]], dim=0).contiguous()
-        self.down_weight = weights[d].contiguous()
+        self.gate_up_weight = LinearWeight(torch.cat([weights[g], weights[u]], dim=0))
+        self.down_weight = LinearWeight(weights[d])
 
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         gate_up = linear(x, self.gate_up_weight)
