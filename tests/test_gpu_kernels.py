@@ -276,6 +276,8 @@ def attention_case(dtype, heads, kv_heads, d, page, entries, window=0, seed=0, s
         ops.paged_attention_simt(*args, max_q, heads, kv_heads, d, scale, window=window, error_word=err)
     elif kernel == "mma_prefill":
         ops.prefill_attention(*args, max_q, heads, kv_heads, d, scale, window=window)
+    elif kernel == "tcgen05_prefill":
+        ops.prefill_attention_tcgen05(*args, max_q, heads, kv_heads, d, scale, window=window, error_word=err)
     else:
         out.fill_(float("nan"))
         singles = sum(1 for _, n in entries if n == 1)
@@ -343,6 +345,35 @@ def test_tensor_core_attention_ragged_batch(heads, kv_heads, d, page, kernel):
     out, ref = attention_case(torch.bfloat16, heads, kv_heads, d, page, entries, kernel=kernel)
     assert torch.isfinite(out).all()
     assert torch.allclose(out.double(), ref, **BF16_ATTN), (out.double() - ref).abs().max()
+
+
+TC_SHAPES = [(4, 2, 64, 16), (8, 2, 128, 16), (32, 8, 128, 16), (3, 1, 64, 8), (6, 6, 128, 32), (16, 2, 64, 64), (7, 1, 128, 128)]
+
+
+@pytest.mark.parametrize("heads, kv_heads, d, page", TC_SHAPES)
+def test_tcgen05_prefill_attention_ragged_batch(heads, kv_heads, d, page):
+    need_gpu()
+    entries = [(0, 150), (130, 1), (31, 2), (0, 1), (63, 66), (700, 1), (64, 1), (255, 129), (0, 300)]
+    out, ref = attention_case(torch.bfloat16, heads, kv_heads, d, page, entries, kernel="tcgen05_prefill")
+    assert torch.isfinite(out).all()
+    assert torch.allclose(out.double(), ref, **BF16_ATTN), (out.double() - ref).abs().max()
+
+
+@pytest.mark.parametrize("window", [1, 5, 128, 129, 200])
+def test_tcgen05_prefill_attention_window_edges(window):
+    need_gpu()
+    entries = [(0, 190), (300, 1), (95, 70), (63, 1), (120, 140)]
+    out, ref = attention_case(torch.bfloat16, 4, 2, 64, 16, entries, window=window, seed=3, kernel="tcgen05_prefill")
+    assert torch.allclose(out.double(), ref, **BF16_ATTN), (out.double() - ref).abs().max()
+
+
+@pytest.mark.parametrize("standout", [0, 3, 511, 512, 700])
+def test_tcgen05_prefill_attention_finds_one_far_key(standout):
+    need_gpu()
+    entries = [(900, 1), (640, 70)]
+    out, ref = attention_case(torch.bfloat16, 8, 2, 64, 16, entries, seed=5, standout=standout, kernel="tcgen05_prefill")
+    assert ref.abs().max() > 3
+    assert torch.allclose(out.double(), ref, atol=6e-2, rtol=2e-2)
 
 
 @pytest.mark.parametrize("splits", [(1, 1024), (2, 512), (3, 320), (16, 64), (9, 128), (1, 0), (2, 0), (5, 0), (32, 0)])

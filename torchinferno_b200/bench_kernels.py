@@ -106,8 +106,13 @@ def run_prefill_attention(args) -> None:
     q_start, kv_start, slots = i32([i * t for i in range(n + 1)]), i32([0] * n), i32(list(range(n)))
     fn = lambda: ops.prefill_attention(q, pool, out, q_start, kv_start, slots, table, n, t, h, k, d, 1 / math.sqrt(d))
     flops = n * 4 * h * d * t * (t + 1) / 2
-    report("prefill_attention", Timer(args.iters)(fn), flops=flops, batch=n, tokens=t, heads=h, kv_heads=k, head_dim=d,
+    timer = Timer(args.iters)
+    report("prefill_attention[mma.sync]", timer(fn), flops=flops, batch=n, tokens=t, heads=h, kv_heads=k, head_dim=d,
            note="causal flops")
+    if ops.prefill_attention_tcgen05_supports(d, h // k, args.page_size):
+        fn5 = lambda: ops.prefill_attention_tcgen05(q, pool, out, q_start, kv_start, slots, table, n, t, h, k, d, 1 / math.sqrt(d))
+        report("prefill_attention[tcgen05]", timer(fn5), flops=flops, batch=n, tokens=t, heads=h, kv_heads=k, head_dim=d,
+               note="causal flops")
 
 
 def run_gemm(args) -> None:

@@ -1,0 +1,382 @@
+// Causal attention of prompt portions over the paged cache on the 5th-generation tensor cores.
+//
+// A block owns 128 rows (token, query head of one GQA group) of one kv head and walks the keys in
+// tiles of 128 up to the causal edge.  Per tile:
+//   S = Q . K^T      `tcgen05.mma` (M 128, N 128, K = head_dim), both operands K-major in 128-byte-
+//                    swizzled shared memory, accumulator S in TMEM (128 columns)
+//   softmax          four warps, one thread per row: `tcgen05.ld` S, mask, running max / sum in fp32,
+//                    P as bf16 into shared memory (the A operand of the next product), O in TMEM
+//                    rescaled with `tcgen05.ld` / `tcgen05.st` when a row's maximum moved
+//   O += P . V       `tcgen05.mma` (M 128, N = head_dim, K = 128 keys); V is used as it lies in the
+//                    cache ([key][head_dim]: an MN-major B operand)
+// Warp 0 (one lane) is the TMA producer: Q by one 3-D tile copy (dims: head_dim, head, token), K and
+// V page by page through a 2-D view of the layer's pages ([page rows, head_dim]); pages past the
+// block's last query are fetched from an out-of-range coordinate, which fills zeros.  Warp 1 (one
+// lane) issues the MMAs.  Every mbarrier wait is bounded; on a timeout a code goes to `error_word`
+// and all roles fall through to the common exit.
+//
+// Formula as in attention_mma.cu / attention_simt.cu (src/torchinferno/models/llama3/raw_ops.py:44-51).
+// The reference uses FlashInfer's paged prefill here (src/torchinferno/runtime/paged_serving.py:267-276).
+#include "tcgen05.cuh"
+#include <math_constants.h>
+
+namespace tib {
+
+constexpr int kFaBM = 128, kFaBN = 128;
+constexpr int kFaThreads = 192;
+constexpr int kFaStages = 2;
+
+struct FaArgs {
+  const int* q_start;
+  const int* kv_start;
+  const int* slots;
+  const int* block_table;
+  int table_stride;
+  int heads, kv_heads, group;
+  int page_size, page_shift;
+  int num_pages;
+  int window;
+  float scale_log2;
+  int skip_single;
+  int n_tokens;
+  int* error_word;
+};
+
+template <int D>
+struct FaSmem {
+  static constexpr uint32_t kQ = kFaBM * D * 2;          // two sub-tiles of [128 rows][64] when D = 128
+  static constexpr uint32_t kKV = kFaBN * D * 2;         // one K or V tile
+  static constexpr uint32_t kP = kFaBM * kFaBN * 2;      // two sub-tiles of [128 rows][64 keys]
+  static constexpr uint32_t kTotal = 1024 + kQ + kFaStages * 2 * kKV + kP + 256;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kFaThreads, 1)
+prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                                 __nv_bfloat16* __restrict__ out, FaArgs a) {
+  using L = FaSmem<D>;
+  constexpr int DH = D / 64;                             // 64-wide sub-tiles along head_dim
+  constexpr uint32_t kSub = 128 * 64 * 2;                // bytes of one [128][64] sub-tile
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_s = base;
+  auto k_s = [&](int s) { return base + L::kQ + s * 2 * L::kKV; };
+  auto v_s = [&](int s) { return base + L::kQ + s * 2 * L::kKV + L::kKV; };
+  const uint32_t p_s = base + L::kQ + kFaStages * 2 * L::kKV;
+  const uint32_t bars = p_s + L::kP;
+  const uint32_t q_full = bars;
+  auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto kv_empty = [&](int s) { return bars + 8u * (1 + kFaStages + s); };
+  const uint32_t s_full = bars + 8u * (1 + 2 * kFaStages);
+  const uint32_t p_full = bars + 8u * (2 + 2 * kFaStages);
+  const uint32_t o_final = bars + 8u * (3 + 2 * kFaStages);
+  const uint32_t tmem_slot = bars + 8u * (4 + 2 * kFaStages);
+  unsigned char* smem_gen = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - base));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int entry = blockIdx.z, kvh = blockIdx.y;
+  const int row0 = a.q_start[entry];
+  const int q_len = a.q_start[entry + 1] - row0;
+  const int tok_per_tile = kFaBM / a.group;
+  const int tile = gridDim.x - 1 - blockIdx.x;           // the longest tiles start first
+  const int t0 = tile * tok_per_tile;
+  // (uniform exits before any barrier or TMEM use)
+  if ((q_len == 1 && a.skip_single) || t0 >= q_len) return;
+  const int nt = min(tok_per_tile, q_len - t0);
+  const int nrows = nt * a.group;
+  const int pos0 = a.kv_start[entry] + t0;
+  const int last_pos = pos0 + nt - 1;
+  const int first_key = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+  const int kt0 = first_key / kFaBN, kt1 = last_pos / kFaBN;
+  const int n_tiles = kt1 - kt0 + 1;
+  const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
+  constexpr uint32_t kTmemCols = 256;                    // S: columns 0..127, O: columns 128..128+D-1
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kFaStages; ++s) {
+      mbar_init(kv_full(s), 1);
+      mbar_init(kv_empty(s), 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_final, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // queries: one 3-D box (64 dims, `group` heads, tok_per_tile tokens) per 64-wide half of head_dim
+      mbar_expect_tx(q_full, (uint32_t)(tok_per_tile * a.group * D * 2));
+#pragma unroll
+      for (int h = 0; h < DH; ++h) tma_load_3d(q_s + h * kSub, &map_q, h * 64, kvh * a.group, row0 + t0, q_full);
+      const int pages_per_tile = kFaBN >> a.page_shift;
+      const int rows_per_page_head = a.page_size;
+      const int oob_row = a.num_pages * 2 * a.kv_heads * a.page_size;   // first row past the tensor: reads zeros
+      for (int it = 0; it < n_tiles; ++it) {
+        const int s = it % kFaStages;
+        const uint32_t phase = (it / kFaStages) & 1;
+        if (!mbar_wait(kv_empty(s), phase ^ 1)) {
+          if (a.error_word) atomicExch(a.error_word, 0x7C0021);
+          break;
+        }
+        mbar_expect_tx(kv_full(s), 2 * L::kKV);
+        const int key0 = (kt0 + it) * kFaBN;
+        for (int pg = 0; pg < pages_per_tile; ++pg) {
+          const int kp = key0 + pg * a.page_size;
+          int page = -1;
+          if (kp <= last_pos && kp + a.page_size > first_key) page = table[kp >> a.page_shift];
+          const bool ok = page >= 0 && page < a.num_pages;
+          const int krow = ok ? ((page * 2 + 0) * a.kv_heads + kvh) * rows_per_page_head : oob_row;
+          const int vrow = ok ? ((page * 2 + 1) * a.kv_heads + kvh) * rows_per_page_head : oob_row;
+          const uint32_t off = (uint32_t)(pg * a.page_size) * 128u;      // rows of 128 bytes in a sub-tile
+#pragma unroll
+          for (int h = 0; h < DH; ++h) {
+            tma_load_2d(k_s(s) + h * kSub + off, &map_kv, h * 64, krow, kv_full(s));
+            tma_load_2d(v_s(s) + h * kSub + off, &map_kv, h * 64, vrow, kv_full(s));
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kFaBN >> 3) << 17) | ((uint32_t)(kFaBM >> 4) << 24);
+      constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) /* B is MN-major */ |
+                                   ((uint32_t)(D >> 3) << 17) | ((uint32_t)(kFaBM >> 4) << 24);
+      bool ok = mbar_wait(q_full, 0);
+      if (!ok && a.error_word) atomicExch(a.error_word, 0x7C0022);
+      for (int it = 0; it < n_tiles && ok; ++it) {
+        const int s = it % kFaStages;
+        const uint32_t phase = (it / kFaStages) & 1;
+        if (!mbar_wait(kv_full(s), phase)) {
+          if (a.error_word) atomicExch(a.error_word, 0x7C0023);
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        // S = Q . K^T over head_dim in steps of 16
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t sub = (kk >> 2) * kSub, inner = (kk & 3) * 32;
+          umma_f16_idesc(tmem_s, umma_desc_k128(q_s + sub + inner), umma_desc_k128(k_s(s) + sub + inner), idesc_s, kk != 0);
+        }
+        umma_commit(s_full);
+        // wait for P (and the rescaled O), then O += P . V over the 128 keys in steps of 16
+        if (!mbar_wait(p_full, it & 1)) {
+          if (a.error_word) atomicExch(a.error_word, 0x7C0024);
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+        for (int kk = 0; kk < kFaBN / 16; ++kk) {
+          const uint32_t psub = (kk >> 2) * kSub, pinner = (kk & 3) * 32;
+          umma_f16_idesc(tmem_o, umma_desc_k128(p_s + psub + pinner), umma_desc_mn128(v_s(s) + kk * 16 * 128, kSub), idesc_o,
+                         (it | kk) != 0);
+        }
+        umma_commit(kv_empty(s));
+      }
+      umma_commit(o_final);
+    }
+  } else {
+    // softmax and epilogue: thread = row
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    const int qpos = r < nrows ? pos0 + r / a.group : last_pos;
+    float m = -CUDART_INF_F, l = 0.f;
+    unsigned char* p_row = smem_gen + (p_s - base) + r * 128;
+    bool ok = true;
+    for (int it = 0; it < n_tiles; ++it) {
+      if (!mbar_wait(s_full, it & 1)) {
+        if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C0025);
+        ok = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const int key_base = (kt0 + it) * kFaBN;
+      const bool need_mask = key_base + kFaBN - 1 > pos0 || (a.window > 0 && key_base < last_pos - a.window + 1);
+      // pass 1: the row's maximum over the tile
+      float sv[kFaBN];
+#pragma unroll
+      for (int c = 0; c < kFaBN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_s + lane_sel + c * 32, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float x = __uint_as_float(v[j]) * a.scale_log2;
+          if (need_mask) {
+            const int key = key_base + c * 32 + j;
+            const bool allowed = key <= qpos && (a.window <= 0 || key > qpos - a.window);
+            x = allowed ? x : -CUDART_INF_F;
+          }
+          sv[c * 32 + j] = x;
+        }
+      }
+      float mx = m;
+#pragma unroll
+      for (int j = 0; j < kFaBN; ++j) mx = fmaxf(mx, sv[j]);
+      const float basev = mx == -CUDART_INF_F ? 0.f : mx;
+      const float alpha = exp2f(m - basev);
+      m = mx;
+      float sum = 0.f;
+      // P (bf16) into shared memory, in the swizzled K-major layout of an MMA A operand
+#pragma unroll
+      for (int c8 = 0; c8 < kFaBN / 8; ++c8) {
+        uint4 packed;
+        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float e0 = exp2f(sv[c8 * 8 + 2 * j] - basev), e1 = exp2f(sv[c8 * 8 + 2 * j + 1] - basev);
+          sum += e0 + e1;
+          p2[j] = __floats2bfloat162_rn(e0, e1);
+        }
+        const int sub = c8 >> 3, cc = c8 & 7;
+        *reinterpret_cast<uint4*>(p_row + sub * kSub + ((cc ^ (r & 7)) << 4)) = packed;
+      }
+      l = l * alpha + sum;
+      // O of the earlier tiles is scaled to the new maximum (the commit behind s_full also covers the
+      // previous P . V, so O is at rest)
+      if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tmem_o + lane_sel + c * 32, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+          tmem_st32(tmem_o + lane_sel + c * 32, v);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+      }
+      // values of keys past the block's last query may never have been written: they must not be NaN
+      if (key_base + kFaBN - 1 > last_pos) {
+        const int s = it % kFaStages;
+        for (int key = max(last_pos + 1, key_base) + quarter; key < key_base + kFaBN; key += 4) {
+          const int kr = key - key_base;
+          for (int cb = lane; cb < D / 8; cb += 32)   // 16-byte chunks of the row (position in the swizzle does not matter: all zero)
+            *reinterpret_cast<uint4*>(smem_gen + (v_s(s) - base) + (cb >> 3) * kSub + kr * 128 + ((cb & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes (P, zeros) before the MMA reads them
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      mbar_arrive(p_full);
+    }
+    if (ok && mbar_wait(o_final, 0)) {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const float inv = 1.f / l;
+      const bool store = r < nrows;
+      const int t = r / a.group, g = r - t * a.group;
+      __nv_bfloat16* dst = out + (size_t)(row0 + t0 + t) * a.heads * D + (kvh * a.group + g) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_o + lane_sel + c * 32, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        if (store) {
+          uint4 packed[4];
+          __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(packed);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) p2[j] = __floats2bfloat162_rn(__uint_as_float(v[2 * j]) * inv, __uint_as_float(v[2 * j + 1]) * inv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst + c * 32)[j] = packed[j];
+        }
+      }
+    } else if (ok && a.error_word && lane == 0) {
+      atomicExch(a.error_word, 0x7C0026);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+template <int D>
+static int launch_fa(const void* q, const void* pool, void* out, FaArgs& a, int n_entries, int max_q_len,
+                     int64_t page_stride, cudaStream_t stream) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return TIB_E_ARG;
+  const int tok_per_tile = kFaBM / a.group;
+  CUtensorMap map_q, map_kv;
+  {
+    // q: [tokens][heads][D] -> dims (D, heads, tokens); a box is 64 dims x group heads x tok_per_tile tokens
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)a.heads, (cuuint64_t)a.n_tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)a.heads * D * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)a.group, (cuuint32_t)tok_per_tile};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    if (fn(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return TIB_E_ARG;
+  }
+  {
+    // one layer's pages as rows of D: [pages * 2 * kv_heads * page_size][D]; a box is 64 dims x one page of one head
+    const cuuint64_t rows = (cuuint64_t)a.num_pages * 2 * a.kv_heads * a.page_size;
+    const cuuint64_t dims[2] = {(cuuint64_t)D, rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)a.page_size};
+    const cuuint32_t elem[2] = {1, 1};
+    if (fn(&map_kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return TIB_E_ARG;
+  }
+  (void)page_stride;
+  auto kern = prefill_attention_tcgen05_kernel<D>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FaSmem<D>::kTotal);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid(ceil_div(max_q_len, tok_per_tile), a.kv_heads, n_entries);
+  kern<<<grid, kFaThreads, FaSmem<D>::kTotal, stream>>>(map_q, map_kv, (__nv_bfloat16*)out, a);
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}
+
+}  // namespace tib
+
+using namespace tib;
+
+// Whether tib_prefill_attention_tcgen05 takes these sizes: head_dim 64 or 128, a group that divides into
+// 128 rows, pages of 8 .. 128 tokens (a power of two), contiguous pages.
+TIB_API int tib_prefill_attention_tcgen05_supports(int head_dim, int group, int page_size) {
+  const bool pow2 = page_size > 0 && (page_size & (page_size - 1)) == 0;
+  return (head_dim == 64 || head_dim == 128) && group >= 1 && group <= 128 && pow2 && page_size >= 8 && page_size <= 128;
+}
+
+// Same contract as tib_prefill_attention (bf16).  n_tokens: rows of q / out.  page_stride must equal
+// 2 * kv_heads * page_size * head_dim (pages packed back to back).
+TIB_API int tib_prefill_attention_tcgen05(const void* q, const void* pool, void* out, const int* q_start,
+                                          const int* kv_start, const int* slots, const int* block_table,
+                                          int table_stride, int n_entries, int max_q_len, int n_tokens, int heads,
+                                          int kv_heads, int head_dim, int page_size, int64_t page_stride, int num_pages,
+                                          int window, float scale, int skip_single, int* error_word, cudaStream_t stream) {
+  if (n_entries == 0 || max_q_len == 0) return TIB_OK;
+  if (!q || !pool || !out || !q_start || !kv_start || !slots || !block_table) return TIB_E_ARG;
+  if (heads < 1 || kv_heads < 1 || heads % kv_heads != 0) return TIB_E_SIZE;
+  if (!tib_prefill_attention_tcgen05_supports(head_dim, heads / kv_heads, page_size)) return TIB_E_SIZE;
+  if (page_stride != (int64_t)2 * kv_heads * page_size * head_dim) return TIB_E_ALIGN;
+  if ((((uintptr_t)q | (uintptr_t)pool | (uintptr_t)out) & 15) != 0) return TIB_E_ALIGN;
+  if (n_entries > 65535 || kv_heads > 65535) return TIB_E_SIZE;
+  FaArgs a;
+  a.q_start = q_start; a.kv_start = kv_start; a.slots = slots; a.block_table = block_table;
+  a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads; a.group = heads / kv_heads;
+  a.page_size = page_size; a.page_shift = 0;
+  while ((1 << a.page_shift) < page_size) ++a.page_shift;
+  a.num_pages = num_pages; a.window = window; a.scale_log2 = scale * 1.4426950408889634f;
+  a.skip_single = skip_single; a.n_tokens = n_tokens; a.error_word = error_word;
+  return head_dim == 64 ? launch_fa<64>(q, pool, out, a, n_entries, max_q_len, page_stride, stream)
+                        : launch_fa<128>(q, pool, out, a, n_entries, max_q_len, page_stride, stream);
+}

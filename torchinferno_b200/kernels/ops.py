@@ -82,6 +82,7 @@ def lib() -> ctypes.CDLL:
         for fn in ("tib_embedding", "tib_add_rmsnorm", "tib_rmsnorm", "tib_swiglu", "tib_cast",
                    "tib_scatter_i32", "tib_advance_decode", "tib_rope_append", "tib_paged_attention_simt", "tib_gemm_f32", "tib_sample",
                    "tib_attention_mma_supports", "tib_prefill_attention", "tib_decode_attention",
+                   "tib_prefill_attention_tcgen05", "tib_prefill_attention_tcgen05_supports",
                    "tib_gemm_skinny", "tib_gemm_skinny_supports", "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
                    "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports"):
             getattr(library, fn).restype = c_int
@@ -423,4 +424,23 @@ def gemm_tcgen05_swapab(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err
     _check("gemm_tcgen05_swapab", lib().tib_gemm_tcgen05_swapab(
         _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)), c_int64(w.stride(0)),
         c_int64(out.stride(0)), c_int(_code(out.dtype)), c_int(splits), _ptr(error_word), _stream()))
+    return out
+
+
+def prefill_attention_tcgen05_supports(head_dim: int, group: int, page_size: int) -> bool:
+    return bool(lib().tib_prefill_attention_tcgen05_supports(c_int(head_dim), c_int(group), c_int(page_size)))
+
+
+def prefill_attention_tcgen05(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor,
+                              kv_start: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, n_entries: int,
+                              max_q_len: int, heads: int, kv_heads: int, head_dim: int, scale: float, window: int = 0,
+                              skip_single: bool = False, error_word: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of prompt portions over the paged cache on tcgen05 tensor cores (bf16): S and O in
+    TMEM, Q / K / V tiles by TMA, softmax in fp32 by one thread per row."""
+    _check_attention_args(q, pool, out, q_start, kv_start, slots, block_table, n_entries, heads, kv_heads, head_dim)
+    _check("prefill_attention_tcgen05", lib().tib_prefill_attention_tcgen05(
+        _ptr(q), _ptr(pool), _ptr(out), _ptr(q_start), _ptr(kv_start), _ptr(slots), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(n_entries), c_int(max_q_len), c_int(q.numel() // (heads * head_dim)),
+        c_int(heads), c_int(kv_heads), c_int(head_dim), c_int(pool.shape[3]), c_int64(pool.stride(0)), c_int(pool.shape[0]),
+        c_int(window), c_float(scale), c_int(int(skip_single)), _ptr(error_word), _stream()))
     return out
