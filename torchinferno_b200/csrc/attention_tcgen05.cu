@@ -23,7 +23,8 @@
 namespace tib {
 
 constexpr int kFaBM = 128, kFaBN = 128;
-constexpr int kFaThreads = 192;
+constexpr int kFaSoftmaxWarps = 8;                      // two threads per row, each with half the columns
+constexpr int kFaThreads = 64 + 32 * kFaSoftmaxWarps;
 constexpr int kFaStages = 2;
 
 struct FaArgs {
@@ -47,7 +48,8 @@ struct FaSmem {
   static constexpr uint32_t kQ = kFaBM * D * 2;          // two sub-tiles of [128 rows][64] when D = 128
   static constexpr uint32_t kKV = kFaBN * D * 2;         // one K or V tile
   static constexpr uint32_t kP = kFaBM * kFaBN * 2;      // two sub-tiles of [128 rows][64 keys]
-  static constexpr uint32_t kTotal = 1024 + kQ + kFaStages * 2 * kKV + kP + 256;
+  static constexpr uint32_t kExchange = 2 * 128 * 4;     // row maxima / sums passed between the two halves
+  static constexpr uint32_t kTotal = 1024 + kQ + kFaStages * 2 * kKV + kP + kExchange + 256;
 };
 
 template <int D>
@@ -63,7 +65,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   auto k_s = [&](int s) { return base + L::kQ + s * 2 * L::kKV; };
   auto v_s = [&](int s) { return base + L::kQ + s * 2 * L::kKV + L::kKV; };
   const uint32_t p_s = base + L::kQ + kFaStages * 2 * L::kKV;
-  const uint32_t bars = p_s + L::kP;
+  const uint32_t xch_s = p_s + L::kP;
+  const uint32_t bars = xch_s + L::kExchange;
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bars + 8u * (1 + kFaStages + s); };
@@ -100,7 +103,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       mbar_init(kv_empty(s), 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 32 * kFaSoftmaxWarps);
     mbar_init(o_final, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -115,38 +118,44 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
 
   if (warp == 0) {
+    // The whole warp produces: lane 0 waits and arms the barrier, then lane pg looks up page pg of the
+    // tile and issues its copies, so the eight table look-ups of a tile cost one latency, not eight.
     if (lane == 0) {
       // queries: one 3-D box (64 dims, `group` heads, tok_per_tile tokens) per 64-wide half of head_dim
       mbar_expect_tx(q_full, (uint32_t)(tok_per_tile * a.group * D * 2));
 #pragma unroll
       for (int h = 0; h < DH; ++h) tma_load_3d(q_s + h * kSub, &map_q, h * 64, kvh * a.group, row0 + t0, q_full);
-      const int pages_per_tile = kFaBN >> a.page_shift;
-      const int rows_per_page_head = a.page_size;
-      const int oob_row = a.num_pages * 2 * a.kv_heads * a.page_size;   // first row past the tensor: reads zeros
-      for (int it = 0; it < n_tiles; ++it) {
-        const int s = it % kFaStages;
-        const uint32_t phase = (it / kFaStages) & 1;
-        if (!mbar_wait(kv_empty(s), phase ^ 1)) {
-          if (a.error_word) atomicExch(a.error_word, 0x7C0021);
-          break;
-        }
-        mbar_expect_tx(kv_full(s), 2 * L::kKV);
-        const int key0 = (kt0 + it) * kFaBN;
-        for (int pg = 0; pg < pages_per_tile; ++pg) {
-          const int kp = key0 + pg * a.page_size;
-          int page = -1;
-          if (kp <= last_pos && kp + a.page_size > first_key) page = table[kp >> a.page_shift];
-          const bool ok = page >= 0 && page < a.num_pages;
-          const int krow = ok ? ((page * 2 + 0) * a.kv_heads + kvh) * rows_per_page_head : oob_row;
-          const int vrow = ok ? ((page * 2 + 1) * a.kv_heads + kvh) * rows_per_page_head : oob_row;
-          const uint32_t off = (uint32_t)(pg * a.page_size) * 128u;      // rows of 128 bytes in a sub-tile
+    }
+    const int pages_per_tile = kFaBN >> a.page_shift;
+    const int oob_row = a.num_pages * 2 * a.kv_heads * a.page_size;   // first row past the tensor: reads zeros
+    for (int it = 0; it < n_tiles; ++it) {
+      const int s = it % kFaStages;
+      const uint32_t phase = (it / kFaStages) & 1;
+      const int key0 = (kt0 + it) * kFaBN;
+      // the page id can be fetched while lane 0 waits for the stage
+      const int kp = key0 + lane * a.page_size;
+      int page = -1;
+      if (lane < pages_per_tile && kp <= last_pos && kp + a.page_size > first_key) page = __ldg(table + (kp >> a.page_shift));
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(kv_empty(s), phase ^ 1) ? 1 : 0;
+        if (!ok && a.error_word) atomicExch(a.error_word, 0x7C0021);
+        if (ok) mbar_expect_tx(kv_full(s), 2 * L::kKV);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < pages_per_tile) {
+        const bool have = page >= 0 && page < a.num_pages;
+        const int krow = have ? ((page * 2 + 0) * a.kv_heads + kvh) * a.page_size : oob_row;
+        const int vrow = have ? ((page * 2 + 1) * a.kv_heads + kvh) * a.page_size : oob_row;
+        const uint32_t off = (uint32_t)(lane * a.page_size) * 128u;      // rows of 128 bytes in a sub-tile
 #pragma unroll
-          for (int h = 0; h < DH; ++h) {
-            tma_load_2d(k_s(s) + h * kSub + off, &map_kv, h * 64, krow, kv_full(s));
-            tma_load_2d(v_s(s) + h * kSub + off, &map_kv, h * 64, vrow, kv_full(s));
-          }
+        for (int h = 0; h < DH; ++h) {
+          tma_load_2d(k_s(s) + h * kSub + off, &map_kv, h * 64, krow, kv_full(s));
+          tma_load_2d(v_s(s) + h * kSub + off, &map_kv, h * 64, vrow, kv_full(s));
         }
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -189,100 +198,121 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       umma_commit(o_final);
     }
   } else {
-    // softmax and epilogue: thread = row
-    const int quarter = warp & 3;
+    // softmax and epilogue: two threads per row; `half` 0 takes keys (and output dims) 0..63 of a tile,
+    // half 1 the rest.  The halves exchange their row maxima through shared memory once per tile.
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     const int qpos = r < nrows ? pos0 + r / a.group : last_pos;
-    float m = -CUDART_INF_F, l = 0.f;
-    unsigned char* p_row = smem_gen + (p_s - base) + r * 128;
-    bool ok = true;
+    constexpr int HC = kFaBN / 2;                          // score columns per thread
+    constexpr int OC = D / 2;                              // output columns per thread
+    float m = -CUDART_INF_F, l = 0.f;                      // m in log2 units (scaled); l: this half's share of the sum
+    float* xch = reinterpret_cast<float*>(smem_gen + (xch_s - base));   // [2][128]
+    unsigned char* p_row = smem_gen + (p_s - base) + half * kSub + r * 128;
+    bool ok = true;                                        // after a timeout the loop keeps its barriers but does no work
     for (int it = 0; it < n_tiles; ++it) {
-      if (!mbar_wait(s_full, it & 1)) {
+      if (ok && !mbar_wait(s_full, it & 1)) {
         if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C0025);
         ok = false;
-        break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const int key_base = (kt0 + it) * kFaBN;
-      const bool need_mask = key_base + kFaBN - 1 > pos0 || (a.window > 0 && key_base < last_pos - a.window + 1);
-      // pass 1: the row's maximum over the tile
-      float sv[kFaBN];
+      const int key_base = (kt0 + it) * kFaBN + half * HC;
+      const bool need_mask = key_base + HC - 1 > pos0 || (a.window > 0 && key_base < last_pos - a.window + 1);
+      float sv[HC];
+      float mx = -CUDART_INF_F;
+      if (ok) {
 #pragma unroll
-      for (int c = 0; c < kFaBN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tmem_s + lane_sel + c * 32, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float x = __uint_as_float(v[j]) * a.scale_log2;
-          if (need_mask) {
-            const int key = key_base + c * 32 + j;
-            const bool allowed = key <= qpos && (a.window <= 0 || key > qpos - a.window);
-            x = allowed ? x : -CUDART_INF_F;
-          }
-          sv[c * 32 + j] = x;
-        }
-      }
-      float mx = m;
-#pragma unroll
-      for (int j = 0; j < kFaBN; ++j) mx = fmaxf(mx, sv[j]);
-      const float basev = mx == -CUDART_INF_F ? 0.f : mx;
-      const float alpha = exp2f(m - basev);
-      m = mx;
-      float sum = 0.f;
-      // P (bf16) into shared memory, in the swizzled K-major layout of an MMA A operand
-#pragma unroll
-      for (int c8 = 0; c8 < kFaBN / 8; ++c8) {
-        uint4 packed;
-        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float e0 = exp2f(sv[c8 * 8 + 2 * j] - basev), e1 = exp2f(sv[c8 * 8 + 2 * j + 1] - basev);
-          sum += e0 + e1;
-          p2[j] = __floats2bfloat162_rn(e0, e1);
-        }
-        const int sub = c8 >> 3, cc = c8 & 7;
-        *reinterpret_cast<uint4*>(p_row + sub * kSub + ((cc ^ (r & 7)) << 4)) = packed;
-      }
-      l = l * alpha + sum;
-      // O of the earlier tiles is scaled to the new maximum (the commit behind s_full also covers the
-      // previous P . V, so O is at rest)
-      if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < HC / 32; ++c) {
           uint32_t v[32];
-          tmem_ld32(tmem_o + lane_sel + c * 32, v);
+          tmem_ld32(tmem_s + lane_sel + half * HC + c * 32, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-          tmem_st32(tmem_o + lane_sel + c * 32, v);
+          for (int j = 0; j < 32; ++j) {
+            float x = __uint_as_float(v[j]);
+            if (need_mask) {
+              const int key = key_base + c * 32 + j;
+              const bool allowed = key <= qpos && (a.window <= 0 || key > qpos - a.window);
+              x = allowed ? x : -CUDART_INF_F;
+            }
+            sv[c * 32 + j] = x;
+            mx = fmaxf(mx, x);
+          }
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
       }
-      // values of keys past the block's last query may never have been written: they must not be NaN
-      if (key_base + kFaBN - 1 > last_pos) {
-        const int s = it % kFaStages;
-        for (int key = max(last_pos + 1, key_base) + quarter; key < key_base + kFaBN; key += 4) {
-          const int kr = key - key_base;
-          for (int cb = lane; cb < D / 8; cb += 32)   // 16-byte chunks of the row (position in the swizzle does not matter: all zero)
-            *reinterpret_cast<uint4*>(smem_gen + (v_s(s) - base) + (cb >> 3) * kSub + kr * 128 + ((cb & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+      xch[half * 128 + r] = mx;
+      asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kFaSoftmaxWarps) : "memory");
+      mx = fmaxf(mx, xch[(half ^ 1) * 128 + r]);
+      asm volatile("bar.sync 2, %0;\n" ::"n"(32 * kFaSoftmaxWarps) : "memory");   // (the slots may be rewritten next tile)
+      const float m_new = fmaxf(m, mx == -CUDART_INF_F ? -CUDART_INF_F : mx * a.scale_log2);
+      const float basev = m_new == -CUDART_INF_F ? 0.f : m_new;
+      float alpha;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(alpha) : "f"(m - basev));
+      m = m_new;
+      if (ok) {
+        float sum = 0.f;
+        // P (bf16) into shared memory, in the swizzled K-major layout of an MMA A operand
+#pragma unroll
+        for (int c8 = 0; c8 < HC / 8; ++c8) {
+          uint4 packed;
+          __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float e0, e1;
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(fmaf(sv[c8 * 8 + 2 * j], a.scale_log2, -basev)));
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fmaf(sv[c8 * 8 + 2 * j + 1], a.scale_log2, -basev)));
+            sum += e0 + e1;
+            p2[j] = __floats2bfloat162_rn(e0, e1);
+          }
+          *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) << 4)) = packed;
+        }
+        l = l * alpha + sum;
+        // O of the earlier tiles is scaled to the new maximum (the commit behind s_full also covers the
+        // previous P . V, so O is at rest)
+        if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+          for (int c = 0; c < OC / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tmem_o + lane_sel + half * OC + c * 32, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+            tmem_st32(tmem_o + lane_sel + half * OC + c * 32, v);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+        }
+        // values of keys past the block's last query may never have been written: they must not be NaN
+        const int tile_base = (kt0 + it) * kFaBN;
+        if (tile_base + kFaBN - 1 > last_pos) {
+          const int s = it % kFaStages;
+          for (int key = max(last_pos + 1, tile_base) + (warp - 2); key < tile_base + kFaBN; key += kFaSoftmaxWarps) {
+            const int kr = key - tile_base;
+            for (int cb = lane; cb < D / 8; cb += 32)   // 16-byte chunks of the row (all zero, so the swizzle does not matter)
+              *reinterpret_cast<uint4*>(smem_gen + (v_s(s) - base) + (cb >> 3) * kSub + kr * 128 + ((cb & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+          }
         }
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes (P, zeros) before the MMA reads them
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       mbar_arrive(p_full);
     }
-    if (ok && mbar_wait(o_final, 0)) {
+    if (ok && !mbar_wait(o_final, 0)) {
+      if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C0026);
+      ok = false;
+    }
+    // the two halves of a row add their shares of the softmax sum
+    xch[half * 128 + r] = l;
+    asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kFaSoftmaxWarps) : "memory");
+    l += xch[(half ^ 1) * 128 + r];
+    if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const float inv = 1.f / l;
       const bool store = r < nrows;
       const int t = r / a.group, g = r - t * a.group;
-      __nv_bfloat16* dst = out + (size_t)(row0 + t0 + t) * a.heads * D + (kvh * a.group + g) * D;
+      __nv_bfloat16* dst = out + (size_t)(row0 + t0 + t) * a.heads * D + (kvh * a.group + g) * D + half * OC;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < OC / 32; ++c) {
         uint32_t v[32];
-        tmem_ld32(tmem_o + lane_sel + c * 32, v);
+        tmem_ld32(tmem_o + lane_sel + half * OC + c * 32, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
         if (store) {
           uint4 packed[4];
@@ -293,8 +323,6 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst + c * 32)[j] = packed[j];
         }
       }
-    } else if (ok && a.error_word && lane == 0) {
-      atomicExch(a.error_word, 0x7C0026);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");

@@ -23,12 +23,15 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait (non-blocking tests, about 0.2 s in all): false when the limit was reached; the caller
-// records it and gives up.
+// Bounded wait: false when the limit was reached (the caller records it and gives up).  Each try blocks
+// in hardware for up to about a microsecond (the suspend-time hint), so a waiting role takes no issue
+// slots from the warps that share its scheduler; 2^18 tries bound the whole wait to a fraction of a second.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if (i > 64) __nanosleep(32);
+  for (uint32_t i = 0; i < (1u << 18); ++i) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+    if (ok) return true;
   }
   return false;
 }
