@@ -49,7 +49,7 @@ struct FaSmem {
   static constexpr uint32_t kKV = kFaBN * D * 2;         // one K or V tile
   static constexpr uint32_t kP = kFaBM * kFaBN * 2;      // two sub-tiles of [128 rows][64 keys]
   static constexpr uint32_t kExchange = 2 * 128 * 4;     // row maxima / sums passed between the two halves
-  static constexpr uint32_t kTotal = 1024 + kQ + kFaStages * 2 * kKV + kP + kExchange + 256;
+  static constexpr uint32_t kTotal = 1024 + kQ + kFaStages * 2 * kKV + 2 * kP + kExchange + 256;
 };
 
 template <int D>
@@ -65,15 +65,16 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   auto k_s = [&](int s) { return base + L::kQ + s * 2 * L::kKV; };
   auto v_s = [&](int s) { return base + L::kQ + s * 2 * L::kKV + L::kKV; };
   const uint32_t p_s = base + L::kQ + kFaStages * 2 * L::kKV;
-  const uint32_t xch_s = p_s + L::kP;
+  const uint32_t xch_s = p_s + 2 * L::kP;                  // (two P buffers alternate)
   const uint32_t bars = xch_s + L::kExchange;
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bars + 8u * (1 + kFaStages + s); };
-  const uint32_t s_full = bars + 8u * (1 + 2 * kFaStages);
-  const uint32_t p_full = bars + 8u * (2 + 2 * kFaStages);
-  const uint32_t o_final = bars + 8u * (3 + 2 * kFaStages);
-  const uint32_t tmem_slot = bars + 8u * (4 + 2 * kFaStages);
+  auto s_full = [&](int b) { return bars + 8u * (1 + 2 * kFaStages + b); };
+  auto p_full = [&](int b) { return bars + 8u * (3 + 2 * kFaStages + b); };
+  const uint32_t pv_done = bars + 8u * (5 + 2 * kFaStages);
+  const uint32_t o_final = bars + 8u * (6 + 2 * kFaStages);
+  const uint32_t tmem_slot = bars + 8u * (7 + 2 * kFaStages);
   unsigned char* smem_gen = smem_raw + (base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - base));
 
@@ -94,7 +95,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int kt0 = first_key / kFaBN, kt1 = last_pos / kFaBN;
   const int n_tiles = kt1 - kt0 + 1;
   const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
-  constexpr uint32_t kTmemCols = 256;                    // S: columns 0..127, O: columns 128..128+D-1
+  constexpr uint32_t kTmemCols = 512;                    // S (two buffers): columns 0..255, O: columns 256..256+D-1
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -102,8 +103,11 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 32 * kFaSoftmaxWarps);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(s_full(b), 1);
+      mbar_init(p_full(b), 32 * kFaSoftmaxWarps);
+    }
+    mbar_init(pv_done, 1);
     mbar_init(o_final, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -115,7 +119,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem_base = *tmem_slot_ptr;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 256;   // S buffer b at tmem_s + 128 b
 
   if (warp == 0) {
     // The whole warp produces: lane 0 waits and arms the barrier, then lane pg looks up page pg of the
@@ -164,6 +168,18 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                    ((uint32_t)(D >> 3) << 17) | ((uint32_t)(kFaBM >> 4) << 24);
       bool ok = mbar_wait(q_full, 0);
       if (!ok && a.error_word) atomicExch(a.error_word, 0x7C0022);
+      // O += P . V of tile `j` (its V in stage j % stages, its P in buffer j & 1)
+      auto issue_pv = [&](int j) {
+        const int s = j % kFaStages;
+#pragma unroll
+        for (int kk = 0; kk < kFaBN / 16; ++kk) {
+          const uint32_t psub = (kk >> 2) * kSub, pinner = (kk & 3) * 32;
+          umma_f16_idesc(tmem_o, umma_desc_k128(p_s + (j & 1) * L::kP + psub + pinner),
+                         umma_desc_mn128(v_s(s) + kk * 16 * 128, kSub), idesc_o, (j | kk) != 0);
+        }
+        umma_commit(kv_empty(s));   // the stage goes back to the producer
+        umma_commit(pv_done);       // O is at rest again
+      };
       for (int it = 0; it < n_tiles && ok; ++it) {
         const int s = it % kFaStages;
         const uint32_t phase = (it / kFaStages) & 1;
@@ -173,27 +189,34 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        // S = Q . K^T over head_dim in steps of 16
+        // S = Q . K^T over head_dim in steps of 16, into S buffer it & 1: it runs while the softmax warps
+        // are still busy with the tile before
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t sub = (kk >> 2) * kSub, inner = (kk & 3) * 32;
-          umma_f16_idesc(tmem_s, umma_desc_k128(q_s + sub + inner), umma_desc_k128(k_s(s) + sub + inner), idesc_s, kk != 0);
+          umma_f16_idesc(tmem_s + (it & 1) * kFaBN, umma_desc_k128(q_s + sub + inner), umma_desc_k128(k_s(s) + sub + inner),
+                         idesc_s, kk != 0);
         }
-        umma_commit(s_full);
-        // wait for P (and the rescaled O), then O += P . V over the 128 keys in steps of 16
-        if (!mbar_wait(p_full, it & 1)) {
-          if (a.error_word) atomicExch(a.error_word, 0x7C0024);
-          ok = false;
-          break;
+        umma_commit(s_full(it & 1));
+        if (it > 0) {
+          // P of the tile before (and the rescaled O) are ready: O += P . V
+          if (!mbar_wait(p_full((it - 1) & 1), ((it - 1) >> 1) & 1)) {
+            if (a.error_word) atomicExch(a.error_word, 0x7C0024);
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          issue_pv(it - 1);
         }
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
-        for (int kk = 0; kk < kFaBN / 16; ++kk) {
-          const uint32_t psub = (kk >> 2) * kSub, pinner = (kk & 3) * 32;
-          umma_f16_idesc(tmem_o, umma_desc_k128(p_s + psub + pinner), umma_desc_mn128(v_s(s) + kk * 16 * 128, kSub), idesc_o,
-                         (it | kk) != 0);
+      }
+      if (ok) {
+        const int last = n_tiles - 1;
+        if (mbar_wait(p_full(last & 1), (last >> 1) & 1)) {
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          issue_pv(last);
+        } else if (a.error_word) {
+          atomicExch(a.error_word, 0x7C0024);
         }
-        umma_commit(kv_empty(s));
       }
       umma_commit(o_final);
     }
@@ -208,10 +231,11 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     constexpr int OC = D / 2;                              // output columns per thread
     float m = -CUDART_INF_F, l = 0.f;                      // m in log2 units (scaled); l: this half's share of the sum
     float* xch = reinterpret_cast<float*>(smem_gen + (xch_s - base));   // [2][128]
-    unsigned char* p_row = smem_gen + (p_s - base) + half * kSub + r * 128;
+    unsigned char* p_row0 = smem_gen + (p_s - base) + half * kSub + r * 128;
     bool ok = true;                                        // after a timeout the loop keeps its barriers but does no work
     for (int it = 0; it < n_tiles; ++it) {
-      if (ok && !mbar_wait(s_full, it & 1)) {
+      unsigned char* p_row = p_row0 + (it & 1) * L::kP;
+      if (ok && !mbar_wait(s_full(it & 1), (it >> 1) & 1)) {
         if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C0025);
         ok = false;
       }
@@ -224,7 +248,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
         for (int c = 0; c < HC / 32; ++c) {
           uint32_t v[32];
-          tmem_ld32(tmem_s + lane_sel + half * HC + c * 32, v);
+          tmem_ld32(tmem_s + lane_sel + (it & 1) * kFaBN + half * HC + c * 32, v);
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -266,9 +290,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) << 4)) = packed;
         }
         l = l * alpha + sum;
-        // O of the earlier tiles is scaled to the new maximum (the commit behind s_full also covers the
-        // previous P . V, so O is at rest)
-        if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // O of the earlier tiles is scaled to the new maximum, once the P . V of the tile before is done
+        if (it > 0 && !mbar_wait(pv_done, (it - 1) & 1)) {
+          if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C0027);
+          ok = false;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        if (ok && it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
           for (int c = 0; c < OC / 32; ++c) {
             uint32_t v[32];
@@ -293,7 +321,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes (P, zeros) before the MMA reads them
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-      mbar_arrive(p_full);
+      mbar_arrive(p_full(it & 1));
     }
     if (ok && !mbar_wait(o_final, 0)) {
       if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C0026);
