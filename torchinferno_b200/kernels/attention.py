@@ -3,14 +3,20 @@
 All kernels here read the ragged batch the same way: entry e owns the token
 rows q_start[e] .. q_start[e+1]-1, its first query token stands at position
 kv_start[e] of the request, and its pages are row slots[e] of the block table.
-A kernel that does not take a shape is passed over; the CUDA-core kernel takes
-every shape, and is the only one used in 32-bit.
+A kernel that does not take a shape is passed over: portions of prompts go to the
+tcgen05 kernel (head size 64 or 128, pages of 8 .. 128 tokens), else to the
+mma.sync kernel (head size 64 or 128, any page size), else to the CUDA-core
+kernel, which takes every shape and is the only one used in 32-bit.
 """
 from __future__ import annotations
 
 import torch
 
 from torchinferno_b200.kernels import ops
+
+
+# Portions of prompts go to the tcgen05 kernel where it takes the shape (set False to compare with mma.sync).
+PREFILL_TCGEN05 = True
 
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, ctx, heads: int, kv_heads: int, head_dim: int,
@@ -20,8 +26,14 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, ctx, heads: int, kv_head
     if q.dtype == torch.bfloat16 and ops.attention_mma_supports(head_dim, heads // kv_heads):
         args = (q, kv.pool, out, batch.q_start, batch.kv_start, batch.slots, kv.block_table, batch.n_entries)
         if batch.n_multi:
-            ops.prefill_attention(*args, batch.max_q_len, heads, kv_heads, head_dim, scale, window=win,
-                                  skip_single=batch.n_single > 0)
+            if (PREFILL_TCGEN05 and ops.prefill_attention_tcgen05_supports(head_dim, heads // kv_heads, kv.page_size)
+                    and kv.pool.stride(0) == 2 * kv_heads * kv.page_size * head_dim):
+                # TMA tiles, S and O in TMEM (pages of 8 .. 128 tokens)
+                ops.prefill_attention_tcgen05(*args, batch.max_q_len, heads, kv_heads, head_dim, scale, window=win,
+                                              skip_single=batch.n_single > 0, error_word=ctx.error_word)
+            else:
+                ops.prefill_attention(*args, batch.max_q_len, heads, kv_heads, head_dim, scale, window=win,
+                                      skip_single=batch.n_single > 0)
         if batch.n_single:
             ops.decode_attention(*args, heads, kv_heads, head_dim, scale, batch.max_kv_len, window=win)
         return out
