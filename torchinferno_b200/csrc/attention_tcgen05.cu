@@ -245,21 +245,33 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       float sv[HC];
       float mx = -CUDART_INF_F;
       if (ok) {
+        // two copies of the loop, so that tiles wholly inside the causal triangle pay nothing for the mask
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < HC / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld32(tmem_s + lane_sel + (it & 1) * kFaBN + half * HC + c * 32, v);
-          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          for (int c = 0; c < HC / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tmem_s + lane_sel + (it & 1) * kFaBN + half * HC + c * 32, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = __uint_as_float(v[j]);
-            if (need_mask) {
+            for (int j = 0; j < 32; ++j) {
               const int key = key_base + c * 32 + j;
               const bool allowed = key <= qpos && (a.window <= 0 || key > qpos - a.window);
-              x = allowed ? x : -CUDART_INF_F;
+              const float x = allowed ? __uint_as_float(v[j]) : -CUDART_INF_F;
+              sv[c * 32 + j] = x;
+              mx = fmaxf(mx, x);
             }
-            sv[c * 32 + j] = x;
-            mx = fmaxf(mx, x);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < HC / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tmem_s + lane_sel + (it & 1) * kFaBN + half * HC + c * 32, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              sv[c * 32 + j] = __uint_as_float(v[j]);
+              mx = fmaxf(mx, sv[c * 32 + j]);
+            }
           }
         }
       }
