@@ -206,7 +206,7 @@ def timed_e2e(model, batch: int, steps: int, warmup: int, seed: int) -> dict:
     for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()
-    h2d0, d2h0 = engine.stats["h2d_bytes"], engine.stats["d2h_bytes"]
+    h2d0, d2h0, ahead0 = engine.stats["h2d_bytes"], engine.stats["d2h_bytes"], engine.stats["steps_ahead"]
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     begin.record()
     tokens = 0
@@ -219,7 +219,9 @@ def timed_e2e(model, batch: int, steps: int, warmup: int, seed: int) -> dict:
         engine.cancel(f"e{i}")
     return {"value": tokens / (ms / 1e3), "unit": "tok/s", "ms_per_step": ms / steps, "tokens": tokens,
             "h2d_bytes_per_step": (engine.stats["h2d_bytes"] - h2d0) / steps,
-            "d2h_bytes_per_step": (engine.stats["d2h_bytes"] - d2h0) / steps}
+            "d2h_bytes_per_step": (engine.stats["d2h_bytes"] - d2h0) / steps,
+            # steps launched before the host had read the tokens of the step before (async scheduling)
+            "steps_launched_ahead": engine.stats["steps_ahead"] - ahead0}
 
 
 def run_ours(args) -> dict:

@@ -54,6 +54,44 @@ def test_greedy_generation_equals_the_plain_implementation_fp32(model_folders):
         assert engine.runner.cache.free_pages() == [engine.runner.cache.num_pages]
 
 
+def test_async_scheduling_gives_the_same_tokens(model_folders):
+    """Tiny B, fp32: the same requests (greedy and seeded sampling, one of them ending at a stop token while
+    the step after it already runs, another cancelled in flight) with the next step launched ahead of the
+    host and without; and a request id used again at once."""
+    need_gpu()
+    config, seed = TINY["B"]
+    prompts = list(requests_for(config, seed, [5, 17, 3]).values())
+    results = {}
+    for ahead in (False, True):
+        with engine_for(model_folders["B"], "float32", page_size=16, max_batch_size=4, async_scheduling=ahead) as engine:
+            greedy = engine.generate_many(requests(prompts, 20))
+            stop = (greedy[1].token_ids[7],)
+            stopped = engine.generate_many(requests(prompts, 20, stop=stop))
+            again = engine.generate(requests(prompts[:1], 6)[0])      # the id "g0" once more, right after
+            warm = engine.generate_many(requests(prompts, 14, temperature=0.7, seeds=[11, 12, 13]))
+            # cancel one of two requests while steps are in flight
+            for r in requests(prompts[:2], 12):
+                engine.submit(r)
+            got = []
+            for i in range(40):
+                for event in engine.step():
+                    if event.request_id == "g0" and event.token is not None:
+                        got.append(event.token)
+                if i == 4:
+                    engine.cancel("g1")
+                if not engine.scheduler.has_work():
+                    break
+            results[ahead] = ([o.token_ids for o in greedy], [(o.token_ids, o.finish_reason) for o in stopped],
+                              again.token_ids, [o.token_ids for o in warm], got)
+            assert engine.stats["steps_ahead"] > 20 if ahead else engine.stats["steps_ahead"] == 0
+            engine.step()                                             # a step left in flight is dropped
+            assert engine.runner.cache.free_pages() == [engine.runner.cache.num_pages]
+            engine.runner.cache.audit()
+    assert results[True] == results[False]
+    assert any(reason == "stop" for _, reason in results[True][1])
+    assert results[True][2] == results[True][0][0][:6] and results[True][4] == list(results[True][0][0][:12])
+
+
 def test_seeded_temperature_generation_fp32(model_folders):
     """Tiny B: five prompts (1, 5, 17, 40, 96 tokens), pages of 16, portions of 32, twelve tokens at
     temperature 0.8.  Each token must be the Gumbel-max choice of the plain logits for the engine's own

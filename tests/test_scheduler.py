@@ -201,3 +201,86 @@ def test_cancel_frees_pages_and_row():
     assert sched.cancel("a") is None
     sched.cancel("b")
     assert cache.free_pages() == [16] and not sched.has_work()
+
+
+def drive_ahead(cache, sched, max_steps=500):
+    """As ``drive``, but as the engine does with async scheduling: the next step is planned and 'launched'
+    before the running one is committed, whenever ``plan_ahead`` allows it."""
+    from torchinferno_b200.engine.scheduler import UNKNOWN_TOKEN
+    seen, outputs, ahead_steps = {}, {}, 0
+    launched = None            # (plan, sampled) of a step that runs but is not yet committed
+    for _ in range(max_steps):
+        if launched is None:
+            if not sched.has_work():
+                break
+            plan = sched.plan()
+            for rid in plan.preempted:
+                seen.pop(rid, None)
+            launched = (plan, run_plan(cache, sched, plan, seen))
+        plan, sampled = launched
+        launched = None
+        ahead = sched.plan_ahead(plan)
+        if ahead is not None:
+            ahead_steps += 1
+            assert [e.request_id for e in ahead.entries] == [e.request_id for e in plan.entries]
+            assert all(e.tokens == (UNKNOWN_TOKEN,) for e in ahead.entries)
+            # the device feeds the drawn tokens in; the fake model does the same
+            fed = type(ahead)(ahead.step, tuple(type(e)(e.request_id, (sampled[e.request_id],), e.start, True, "decode")
+                                                for e in ahead.entries))
+            launched = (ahead, run_plan(cache, sched, fed, seen))
+        for event in sched.commit(plan, sampled):
+            if event.token is not None:
+                outputs.setdefault(event.request_id, []).append(event.token)
+            if event.finished:
+                outputs.setdefault(event.request_id, []).append(event.finish_reason)
+        if launched is not None and not any(e.request_id in sched._by_id for e in launched[0].entries):
+            launched = None
+        cache.audit()
+    assert not sched.has_work(), "the scheduler did not finish"
+    return outputs, ahead_steps
+
+
+def test_planning_ahead_gives_the_same_tokens_and_skips_a_request_that_stopped():
+    prompts = {"a": [3, 1, 4, 1, 5], "b": [9, 2, 6], "c": [5, 3, 5, 8, 9, 7]}
+    stop = (expected(prompts["b"], 6)[3],)          # b stops at its fourth token, mid-flight
+    want = {"a": expected(prompts["a"], 9), "b": expected(prompts["b"], 9, stop), "c": expected(prompts["c"], 7)}
+    assert want["b"][-1] == "stop"
+    cache, sched = make(num_pages=32)
+    for rid, prompt in prompts.items():
+        sched.submit(SchedulerRequest(rid, list(prompt), 9 if rid != "c" else 7, stop_token_ids=stop if rid == "b" else ()))
+    outputs, ahead_steps = drive_ahead(cache, sched)
+    assert outputs == want
+    assert ahead_steps >= 4
+    assert cache.free_pages() == [32] and cache.free_slots() == 4
+
+
+def test_planning_ahead_declines_when_a_decision_is_needed():
+    cache, sched = make(num_pages=8, page_size=4, max_requests=2)
+    sched.submit(SchedulerRequest("a", [1, 2, 3], 20))
+    seen = {}
+    plan = sched.plan()
+    sampled = run_plan(cache, sched, plan, seen)
+    sched.submit(SchedulerRequest("b", [4, 5], 4))
+    assert sched.plan_ahead(plan) is None                     # somebody waits: admission is a decision
+    sched.cancel("b")
+    ahead = sched.plan_ahead(plan)
+    assert ahead is not None and ahead.entries[0].start == 3
+    sched.commit(plan, sampled)
+    # a request that ends by length after the running step is not run further
+    cache2, sched2 = make()
+    sched2.submit(SchedulerRequest("x", [1, 2], 2))
+    p0 = sched2.plan()
+    s0 = run_plan(cache2, sched2, p0, {})
+    assert sched2.plan_ahead(p0) is not None                  # one more token is still to come after this one
+    sched2.commit(p0, s0)
+    p1 = sched2.plan()
+    run_plan(cache2, sched2, p1, {"x": {0: 1, 1: 2}})
+    assert sched2.plan_ahead(p1) is None                      # p1 draws the last token
+    # pages: both requests fill their last page, and none is free for the tokens after
+    cache3, sched3 = make(num_pages=3, page_size=4, max_requests=2)
+    sched3.submit(SchedulerRequest("y", list(range(8)), 3))
+    sched3.submit(SchedulerRequest("z", list(range(4)), 3))
+    p = sched3.plan()
+    assert len(p.entries) == 2
+    run_plan(cache3, sched3, p, {})
+    assert cache3.free_pages() == [0] and sched3.plan_ahead(p) is None

@@ -6,7 +6,7 @@ Names and defaults the reference has are kept as they are
 ``max_batch_size=64``, ``cache_backend`` (only "paged" exists here).  Options
 for several GPUs, disaggregation and servers are not carried.  Added: the
 per-step token budget, the prompt portion size, the size of the page pool and
-the default sampling seed.
+the default sampling seed, and ``async_scheduling``.
 """
 from __future__ import annotations
 
@@ -30,6 +30,7 @@ class EngineConfig:
     kv_cache_tokens: int | None = None      # pool size in tokens; default max_batch_size * max_model_len
     seed: int = 0
     use_cuda_graphs: bool = True
+    async_scheduling: bool = True           # launch the next decode step before the host has read this one's tokens
     gemm_backend: str = "auto"              # auto | tcgen05 | library (bf16 projections)
 
     def __post_init__(self) -> None:

@@ -19,10 +19,31 @@ import torch
 from torchinferno_b200.config.engine_config import EngineConfig
 from torchinferno_b200.engine.batch import StepEntry
 from torchinferno_b200.engine.factory import load_model, make_runner
-from torchinferno_b200.engine.scheduler import Scheduler, SchedulerRequest, StepPlan, TokenEvent
+from torchinferno_b200.engine.scheduler import Scheduler, SchedulerRequest, StepPlan, TokenEvent, UNKNOWN_TOKEN
 from torchinferno_b200.kernels import gemm
 from torchinferno_b200.engine.types import GenerateOutput, GenerateRequest, SamplingConfig, TokenOutput, Usage
 from torchinferno_b200.sampling.sampler import Sampler, SamplingParams
+
+
+class _Launched:
+    """A step that runs on the device: its plan, the drawn tokens there and on their way to the host."""
+
+    def __init__(self, plan: StepPlan, requests: list, drawing: list, device_tokens: torch.Tensor | None) -> None:
+        self.plan, self.requests, self.drawing, self.device_tokens = plan, requests, drawing, device_tokens
+        self.host_tokens: torch.Tensor | None = None
+        self.arrived: torch.cuda.Event | None = None
+        if device_tokens is not None and device_tokens.numel():
+            self.host_tokens = torch.empty(device_tokens.shape, dtype=device_tokens.dtype, pin_memory=True)
+            self.host_tokens.copy_(device_tokens, non_blocking=True)
+            self.arrived = torch.cuda.Event()
+            self.arrived.record()
+
+    def tokens(self) -> dict[Hashable, int]:
+        """Wait for the copy to the host and return {request: token}."""
+        if self.host_tokens is None:
+            return {}
+        self.arrived.synchronize()
+        return {e.request_id: int(t) for e, t in zip(self.drawing, self.host_tokens.tolist())}
 
 
 class InferenceEngine:
@@ -47,7 +68,8 @@ class InferenceEngine:
         self._requests: dict[Hashable, GenerateRequest] = {}
         self._cancelled: set[Hashable] = set()
         self._closed = False
-        self.stats = {"steps": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+        self._ahead: _Launched | None = None      # a step launched before the one before it was committed
+        self.stats = {"steps": 0, "steps_ahead": 0, "h2d_bytes": 0, "d2h_bytes": 0}
 
     # -------------------------------------------------------- construction
     @classmethod
@@ -69,6 +91,7 @@ class InferenceEngine:
             return
         for request_id in list(self._requests):
             self.cancel(request_id)
+        self._ahead = None
         self._closed = True
 
     # ------------------------------------------------------------ requests
@@ -106,33 +129,59 @@ class InferenceEngine:
 
     # ---------------------------------------------------------------- step
     def step(self) -> list[TokenEvent]:
-        """Plan one step, run it, draw tokens, and return what happened."""
-        plan = self.scheduler.plan()
-        if not plan.entries:
-            return []
-        sampled = self._run(plan)
-        return self.scheduler.commit(plan, sampled)
+        """Plan one step, run it, draw tokens, and return what happened.
 
-    def _run(self, plan: StepPlan) -> dict[Hashable, int]:
-        entries = [StepEntry(e.request_id, e.tokens, (len(e.tokens) - 1,) if e.samples else ()) for e in plan.entries]
+        With ``async_scheduling`` a decode step whose successor needs no decision (the same
+        requests go on, pages suffice, nobody waits) has that successor launched before its own
+        tokens are read: the device feeds the drawn tokens to the next step itself, and the host
+        reads them while that step runs.  A request that draws a stop token has then been run one
+        token too far; that row is dropped.
+        """
+        current, self._ahead = self._ahead, None
+        if current is not None:
+            # requests that ended while the step ran (a stop token, a cancellation) drop out of it
+            live = tuple(e for e, r in zip(current.plan.entries, current.requests)
+                         if self.scheduler._by_id.get(e.request_id) is r)
+            if not live:
+                current = None
+            elif len(live) < len(current.plan.entries):
+                current.plan = StepPlan(current.plan.step, live)
+        if current is None:
+            plan = self.scheduler.plan()
+            if not plan.entries:
+                return []
+            current = self._launch(plan, None)
+        if self.config.async_scheduling and current.device_tokens is not None and self.runner.use_cuda_graphs:
+            ahead = self.scheduler.plan_ahead(current.plan)
+            if ahead is not None and len(current.drawing) == len(ahead.entries):
+                self._ahead = self._launch(ahead, current.device_tokens)
+                self.stats["steps_ahead"] += 1
+        return self.scheduler.commit(current.plan, current.tokens())
+
+    def _launch(self, plan: StepPlan, fed: torch.Tensor | None) -> _Launched:
+        """Start a step on the device.  ``fed``: the tokens drawn by the step before, when the
+        plan was made ahead of them."""
         with torch.inference_mode():
-            logits = self.runner.step(entries)
+            if fed is not None:
+                logits = self.runner.decode_ahead([e.request_id for e in plan.entries], fed)
+            else:
+                assert all(t != UNKNOWN_TOKEN for e in plan.entries for t in e.tokens)
+                logits = self.runner.step([StepEntry(e.request_id, e.tokens, (len(e.tokens) - 1,) if e.samples else ())
+                                           for e in plan.entries])
+            self.stats["steps"] += 1
+            self.stats["h2d_bytes"] += self.runner.last_batch.h2d_bytes
             drawing = [e for e in plan.entries if e.samples]
+            requests = [self.scheduler._by_id[e.request_id] for e in plan.entries]
             if not drawing:
-                self.stats["steps"] += 1
-                self.stats["h2d_bytes"] += self.runner.last_batch.h2d_bytes
-                return {}
+                return _Launched(plan, requests, [], None)
             params, positions = [], []
             for e in drawing:
                 request = self.scheduler._by_id[e.request_id]
                 params.append(SamplingParams(request.temperature, request.seed))
                 positions.append(e.start + len(e.tokens))  # position of the token being drawn
             tokens = self.sampler.sample(logits, params, positions)
-            host = tokens.cpu()
-        self.stats["steps"] += 1
-        self.stats["h2d_bytes"] += self.runner.last_batch.h2d_bytes
-        self.stats["d2h_bytes"] += host.numel() * host.element_size()
-        return {e.request_id: int(t) for e, t in zip(drawing, host.tolist())}
+            self.stats["d2h_bytes"] += tokens.numel() * tokens.element_size()
+            return _Launched(plan, requests, drawing, tokens)
 
     # ------------------------------------------------------------ generate
     def generate_stream(self, request: GenerateRequest) -> Iterator[TokenOutput]:

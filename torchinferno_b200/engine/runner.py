@@ -164,7 +164,32 @@ class ModelRunner:
         self.graph_replays += 1
         return g.logits
 
-    def _decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def decode_ahead(self, request_ids: Sequence[Hashable], device_tokens: torch.Tensor) -> torch.Tensor:
+        """One decode step whose input tokens are still being drawn on the device.
+
+        ``device_tokens`` [n] int32 holds, in stream order, the token each open request drew in
+        the step before; the host need not have read it yet.  Otherwise as :meth:`step` with one
+        token and ``want=(0,)`` per request.
+        """
+        cache = self.cache
+        if not (self.use_cuda_graphs and self._graph_ok and cache.device.type == "cuda"):
+            raise StepError("decode_ahead needs the captured decode pass (a CUDA device, graphs on, no per-request host state)")
+        if device_tokens.dtype != torch.int32 or device_tokens.numel() != len(request_ids) or len(set(request_ids)) != len(request_ids):
+            raise StepError("decode_ahead takes one int32 device token per distinct request")
+        need = [0] * len(cache.groups)
+        for request_id in request_ids:
+            if request_id not in cache:
+                raise StepError(f"request {request_id!r} is not open")
+            if cache.length(request_id) + 1 > self.model.spec.max_positions:
+                raise StepError(f"request {request_id!r} is at the model's limit of {self.model.spec.max_positions} positions")
+            for g, n in enumerate(cache.pages_needed(request_id, 1)):
+                need[g] += n
+        for g, (n, f) in enumerate(zip(need, cache.free_pages())):
+            if n > f:
+                raise OutOfPages(f"the step needs {n} new pages of cache group {g}, {f} are free")
+        return self._decode_step([StepEntry(r, (0,), (0,)) for r in request_ids], device_tokens)
+
+    def _decode_step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         cache = self.cache
         n = len(entries)
         g = self._graph_for(n)
@@ -174,8 +199,13 @@ class ModelRunner:
                 cache.open(entry.request_id)
             starts.append(cache.extend(entry.request_id, 1))
         slots = [cache.slot(e.request_id) for e in entries]
-        host = torch.tensor([int(e.tokens[0]) for e in entries] + starts + slots, dtype=torch.int32).pin_memory()
-        g.buffer[:3 * n].copy_(host, non_blocking=True)
+        if device_tokens is None:
+            host = torch.tensor([int(e.tokens[0]) for e in entries] + starts + slots, dtype=torch.int32).pin_memory()
+            g.buffer[:3 * n].copy_(host, non_blocking=True)
+        else:
+            host = torch.tensor(starts + slots, dtype=torch.int32).pin_memory()
+            g.buffer[n:3 * n].copy_(host, non_blocking=True)
+            g.token_ids.copy_(device_tokens.reshape(n), non_blocking=True)
         copied = host.numel() * 4 + self._apply_table_updates()
         g.batch.h2d_bytes = copied
         g.batch.entries = [EntryPlacement(e.request_id, s, i, 1, st) for i, (e, s, st) in enumerate(zip(entries, slots, starts))]

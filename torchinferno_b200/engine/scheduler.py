@@ -34,6 +34,9 @@ from typing import Hashable, Sequence
 from torchinferno_b200.cache.manager import CacheManager
 
 
+UNKNOWN_TOKEN = -1   # input token of a step planned ahead: the token the running step is still drawing
+
+
 @dataclass
 class SchedulerRequest:
     request_id: Hashable
@@ -256,13 +259,47 @@ class Scheduler:
         completes = start + count == target
         return PlannedEntry(request.request_id, chunk, start, completes, "prefill")
 
+    # ---------------------------------------------------------- run ahead
+    def plan_ahead(self, running: StepPlan) -> StepPlan | None:
+        """The step after ``running``, decided before ``running``'s tokens are known, or None.
+
+        ``running`` has been launched but not committed.  If every running request draws a token
+        in it and goes on afterwards unless that token is a stop token, the next step is a decode
+        of the same requests in the same order, whose input tokens exist only on the device yet:
+        each entry carries ``UNKNOWN_TOKEN``.  Anything that needs a decision (a request waiting, a
+        request that ends by length, pages that would run out) returns None: the caller then
+        commits ``running`` first and plans as usual.  A request that does stop in ``running`` has
+        been run one token too far; :meth:`commit` skips its entry.
+        """
+        if self.waiting or not running.entries or len(running.entries) != len(self.running):
+            return None
+        need = [0] * len(self.cache.free_pages())
+        entries = []
+        for entry in running.entries:
+            request = self._by_id.get(entry.request_id)
+            if (request is None or request not in self.running or not entry.samples
+                    or len(request.generated) + 2 > request.max_new_tokens
+                    or entry.request_id not in self.cache
+                    or self.cache.length(entry.request_id) != entry.start + len(entry.tokens)):
+                return None
+            for g, n in enumerate(self.cache.pages_needed(entry.request_id, 1)):
+                need[g] += n
+            entries.append(PlannedEntry(entry.request_id, (UNKNOWN_TOKEN,), entry.start + len(entry.tokens), True, "decode"))
+        if any(n > f for n, f in zip(need, self.cache.free_pages())):
+            return None
+        plan = StepPlan(self._step, tuple(entries))
+        self._step += 1
+        return plan
+
     # ------------------------------------------------------------- commit
     def commit(self, plan: StepPlan, sampled: dict[Hashable, int]) -> list[TokenEvent]:
-        """Record what the step computed and the tokens drawn; finish and free what is done."""
+        """Record what the step computed and the tokens drawn; finish and free what is done.
+        Entries of requests that ended since the plan was made (a stop token or a cancellation
+        while a step planned ahead was running) are skipped."""
         events: list[TokenEvent] = []
         for entry in plan.entries:
-            request = self._by_id[entry.request_id]
-            if request.finish_reason is not None:
+            request = self._by_id.get(entry.request_id)
+            if request is None or request.finish_reason is not None:
                 continue
             request.computed = entry.start + len(entry.tokens)
             self.stats["decode_tokens" if entry.kind == "decode" else "prefill_tokens"] += len(entry.tokens)
