@@ -193,13 +193,13 @@ def timed_e2e(model, batch: int, steps: int, warmup: int, seed: int) -> dict:
     from torchinferno_b200.kernels import gemm
     config = EngineConfig(model="<in memory>", dtype="bfloat16", page_size=PAGE_SIZE, max_batch_size=batch, gemm_backend=gemm.get_backend(),
                           max_num_batched_tokens=PROMPT_LEN, prefill_chunk_size=PROMPT_LEN,
-                          kv_cache_tokens=batch * (PROMPT_LEN + warmup + steps + 2 * PAGE_SIZE))
+                          kv_cache_tokens=batch * (PROMPT_LEN + batch + warmup + steps + 2 * PAGE_SIZE))
     engine = InferenceEngine(model, config)
     g = torch.Generator().manual_seed(seed + 99)
     prompts = torch.randint(0, model.spec.vocab_size, (batch, PROMPT_LEN), generator=g).tolist()
     for i, prompt in enumerate(prompts):
         engine.submit(GenerateRequest(f"e{i}", prompt_token_ids=prompt,
-                                      sampling=SamplingConfig(max_tokens=warmup + steps + 1, temperature=0.0)))
+                                      sampling=SamplingConfig(max_tokens=batch + warmup + steps + 2, temperature=0.0)))
     # run until every request decodes, plus the warm-up steps
     while any(r.prefilling for r in engine.scheduler.running) or engine.scheduler.waiting:
         engine.step()
@@ -214,6 +214,8 @@ def timed_e2e(model, batch: int, steps: int, warmup: int, seed: int) -> dict:
         tokens += sum(1 for e in engine.step() if e.token is not None)
     end.record()
     torch.cuda.synchronize()
+    if tokens != batch * steps:   # (earlier requests decode while later prompts are computed: max_tokens leaves room for that)
+        raise RuntimeError(f"the end-to-end run drew {tokens} tokens, not {batch * steps}: a request ended inside the timed region")
     ms = begin.elapsed_time(end)
     for i in range(batch):
         engine.cancel(f"e{i}")
@@ -252,7 +254,7 @@ def run_ours(args) -> dict:
             points[f"decode_b{b}_hbm_frac"] = round(r["achieved_gbs"] / peaks["hbm_gbs"], 4)
         del runner
         torch.cuda.empty_cache()
-        e2e = timed_e2e(model, args.batch, min(args.steps, args.e2e_steps), args.warmup, seed=4)
+        e2e = timed_e2e(model, args.batch, min(args.steps, args.e2e_steps or args.steps), args.warmup, seed=4)
     sampler.stop()
     peak_flops = peaks["bf16_tflops"] * 1e12
     record = {
@@ -354,7 +356,7 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
     parser.add_argument("--points", type=int, nargs="*", default=[1, 64], help="other batch sizes to decode at")
     parser.add_argument("--point-steps", type=int, default=None, help="decode steps of the other batch sizes (default: --steps)")
-    parser.add_argument("--e2e-steps", type=int, default=512)
+    parser.add_argument("--e2e-steps", type=int, default=None, help="steps of the end-to-end run (default: --steps, the same contexts)")
     parser.add_argument("--gemm-backend", choices=["auto", "tcgen05", "library"], default="auto")
     args = parser.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
