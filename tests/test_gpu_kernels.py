@@ -242,7 +242,8 @@ def attention_case(dtype, heads, kv_heads, d, page, entries, window=0, seed=0, s
 
     kernel "simt": the CUDA-core kernel; "mma": the tensor-core pair (portions by the prefill kernel,
     single tokens by the split decode kernel, as the engine dispatches them); "mma_prefill": the
-    prefill kernel alone for every entry.  ``splits`` = (num_splits, chunk) forces a split."""
+    prefill kernel alone for every entry; "tma": as "mma" with the single tokens by the TMA decode kernel.
+    ``splits`` = (num_splits, chunk) forces a split."""
     from torchinferno_b200.kernels import ops
     lengths = [s + n for s, n in entries]
     pool, table, slots = paged_layout(len(entries), lengths, page, kv_heads, d, dtype, seed=seed)
@@ -285,7 +286,8 @@ def attention_case(dtype, heads, kv_heads, d, page, entries, window=0, seed=0, s
             ops.prefill_attention(*args, max_q, heads, kv_heads, d, scale, window=window, skip_single=singles > 0)
         if singles:
             ns, ch = splits or (None, None)
-            ops.decode_attention(*args, heads, kv_heads, d, scale, max(lengths), window=window, num_splits=ns, chunk=ch)
+            ops.decode_attention(*args, heads, kv_heads, d, scale, max(lengths), window=window, num_splits=ns, chunk=ch,
+                                 kernel="tma" if kernel == "tma" else "cp_async", error_word=err)
     assert int(err) == 0
     return out.cpu(), torch.cat(refs)
 
@@ -382,6 +384,57 @@ def test_split_decode_attention_is_the_same_for_every_split(splits):
     entries = [(900, 1), (0, 1), (63, 1), (64, 1), (517, 1)]
     out, ref = attention_case(torch.bfloat16, 8, 2, 128, 16, entries, kernel="mma", splits=splits, seed=2)
     assert torch.allclose(out.double(), ref, **BF16_ATTN), (out.double() - ref).abs().max()
+
+
+TMA_SHAPES = [(4, 2, 64, 16), (8, 2, 128, 16), (32, 8, 128, 16), (3, 1, 64, 8), (6, 6, 128, 32), (32, 2, 64, 64), (7, 1, 128, 8),
+              (12, 4, 128, 64)]
+
+
+@pytest.mark.parametrize("heads, kv_heads, d, page", TMA_SHAPES)
+def test_tma_decode_attention_ragged_batch(heads, kv_heads, d, page):
+    """Single tokens by the TMA kernel (portions beside them by the mma.sync prefill kernel): contexts of 1, 64, 65
+    tokens, ones that end in the middle of a page and of a tile, and a long one."""
+    need_gpu()
+    entries = [(0, 150), (130, 1), (31, 2), (0, 1), (63, 1), (700, 1), (64, 1), (255, 129), (1000, 1), (15, 1), (16, 1), (127, 1)]
+    out, ref = attention_case(torch.bfloat16, heads, kv_heads, d, page, entries, kernel="tma")
+    assert torch.isfinite(out).all()
+    assert torch.allclose(out.double(), ref, **BF16_ATTN), (out.double() - ref).abs().max()
+
+
+@pytest.mark.parametrize("splits", [(1, 1024), (2, 512), (3, 320), (16, 64), (9, 128), (1, 0), (2, 0), (5, 0), (32, 0)])
+def test_tma_decode_attention_is_the_same_for_every_split(splits):
+    need_gpu()
+    entries = [(900, 1), (0, 1), (63, 1), (64, 1), (517, 1)]
+    out, ref = attention_case(torch.bfloat16, 8, 2, 128, 16, entries, kernel="tma", splits=splits, seed=2)
+    assert torch.allclose(out.double(), ref, **BF16_ATTN), (out.double() - ref).abs().max()
+    other, _ = attention_case(torch.bfloat16, 8, 2, 128, 16, entries, kernel="mma", splits=splits, seed=2)
+    assert torch.allclose(out.float(), other.float(), atol=4e-3, rtol=1e-2)     # the two kernels do the same arithmetic
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 65, 200])
+def test_tma_decode_attention_window_edges(window):
+    need_gpu()
+    entries = [(300, 1), (63, 1), (64, 1), (199, 1), (200, 1), (1, 1), (777, 1)]
+    out, ref = attention_case(torch.bfloat16, 4, 2, 64, 16, entries, window=window, seed=3, kernel="tma")
+    assert torch.allclose(out.double(), ref, **BF16_ATTN), (out.double() - ref).abs().max()
+
+
+@pytest.mark.parametrize("standout", [0, 3, 511, 512, 700])
+def test_tma_decode_attention_finds_one_far_key(standout):
+    need_gpu()
+    entries = [(900, 1), (701, 1)]
+    out, ref = attention_case(torch.bfloat16, 8, 2, 64, 16, entries, seed=5, standout=standout, kernel="tma")
+    assert ref.abs().max() > 3
+    assert torch.allclose(out.double(), ref, atol=6e-2, rtol=2e-2)
+
+
+def test_tma_decode_attention_refuses_other_shapes():
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    assert not ops.decode_attention_tma_supports(96, 4, 16) and not ops.decode_attention_tma_supports(128, 32, 16)
+    assert not ops.decode_attention_tma_supports(128, 4, 5) and not ops.decode_attention_tma_supports(128, 4, 128)
+    with pytest.raises(ops.KernelError, match="does not take this shape"):
+        attention_case(torch.bfloat16, 4, 2, 64, 4, [(10, 1)], kernel="tma")
 
 
 @pytest.mark.parametrize("window", [1, 5, 64, 65, 200])

@@ -87,13 +87,15 @@ def run_decode_attention(args) -> None:
     q_start, kv_start, slots = i32(list(range(n + 1))), i32([args.context - 1] * n), i32(list(range(n)))
     timer = Timer(args.iters)
     kv_bytes = n * args.context * 2 * k * d * 2
+    kernels = ["cp_async"] + (["tma"] if ops.decode_attention_tma_supports(d, h // k, args.page_size) else [])
     for forced in (args.splits or [None]):
         splits, chunk = (ops.decode_num_splits(n, h, k) if forced is None else forced), 0
         scratch = torch.empty(n * h * splits * (d + 2), dtype=torch.float32, device="cuda")
-        fn = lambda: ops.decode_attention(q, pool, out, q_start, kv_start, slots, table, n, h, k, d, 1 / math.sqrt(d),
-                                          args.context, scratch=scratch, num_splits=splits, chunk=chunk)
-        report("decode_attention+merge", timer(fn), bytes_moved=kv_bytes, batch=n, context=args.context,
-               splits=splits, chunk=chunk, heads=h, kv_heads=k, head_dim=d)
+        for kernel in kernels:
+            fn = lambda: ops.decode_attention(q, pool, out, q_start, kv_start, slots, table, n, h, k, d, 1 / math.sqrt(d),
+                                              args.context, scratch=scratch, num_splits=splits, chunk=chunk, kernel=kernel)
+            report(f"decode_attention[{kernel}]+merge", timer(fn), bytes_moved=kv_bytes, batch=n, context=args.context,
+                   splits=splits, heads=h, kv_heads=k, head_dim=d)
 
 
 def run_prefill_attention(args) -> None:

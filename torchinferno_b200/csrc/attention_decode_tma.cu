@@ -1,0 +1,367 @@
+// Decode attention over the paged cache with the keys and values brought in by TMA.
+//
+// One block serves one (request, kv head, part of the context).  Warp 0 is the producer: it looks the
+// pages of a 64-key tile up in the block table and has the TMA unit copy them (one box per page and per
+// 64-wide half of the head) into a ring of shared-memory stages; no other thread computes an address or
+// touches global memory for keys and values.  Warps 1-4 are the consumers: each takes 16 keys of every
+// tile, S = Q.K^T and O += P.V on mma.sync (the query rows are the group's heads, padded to 16), with a
+// streaming softmax of its own in 32-bit; the four partial results are merged exactly at the end, and the
+// parts of a split context by decode_merge_kernel.  Stages are handed over with mbarriers (TMA arrival
+// "full", four consumer arrivals "empty"), so there is no block-wide barrier inside the loop, and two
+// blocks of three 32 KB stages each keep about 190 KB of copies in flight per SM.
+//
+// Same formula and contract as decode_attention_kernel in attention_mma.cu (formula:
+// src/torchinferno/models/llama3/raw_ops.py:44-51; the reference's decode kernel walks one
+// (batch, kv head) per program without a split: src/torchinferno/kernels/triton_ops.py:2555-2574, 2661).
+// Takes head sizes 64 and 128, groups up to 16 heads, pages of 8, 16, 32 or 64 tokens packed back to
+// back; other shapes stay with the cp.async kernel.
+#include "mma.cuh"
+#include "tcgen05.cuh"
+
+namespace tib {
+
+constexpr int kDtBN = 64;               // keys per tile
+constexpr int kDtConsumers = 4;         // warps; each takes kDtBN / 4 = 16 keys of a tile
+constexpr int kDtThreads = 32 * (1 + kDtConsumers);
+
+struct DtArgs {
+  const int* q_start;
+  const int* kv_start;
+  const int* slots;
+  const int* block_table;
+  int table_stride;
+  int heads, kv_heads, group;
+  int page_size, page_shift;
+  int num_pages;
+  int window;
+  float scale_log2;
+  int chunk, num_splits;
+  int* error_word;
+};
+
+template <int D>
+struct DtSmem {
+  static constexpr int kStages = D == 128 ? 3 : 6;
+  static constexpr uint32_t kSub = kDtBN * 128;                   // one 64-wide half of a tile: 64 rows of 128 bytes
+  static constexpr uint32_t kKV = (D / 64) * kSub;                // keys (or values) of one tile
+  static constexpr uint32_t kStage = 2 * kKV;
+  static constexpr uint32_t kReduce = sizeof(float) * (kDtConsumers * 16 * D + kDtConsumers * 16 * 2);
+  static constexpr uint32_t kData = kStages * kStage > kReduce ? kStages * kStage : kReduce;
+  static constexpr uint32_t kTotal = 1024 + kData + 16 * kStages;
+};
+
+// Address of element (row, col) of a tile half-by-half in the TMA's 128-byte swizzle: the 16-byte chunk
+// index within a 128-byte row is XORed with the row's low three bits.
+__device__ __forceinline__ uint32_t dt_at(uint32_t tile, int row, int col) {
+  return tile + (uint32_t)(col >> 6) * (kDtBN * 128) + (uint32_t)row * 128 + ((((col >> 3) & 7) ^ (row & 7)) << 4) + ((col & 7) << 1);
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// grid: (num_splits, kv_heads, n_entries).  partial_o: [entries][heads][splits][D] fp32, partial_ml:
+// [entries][heads][splits][2] fp32 (max in log2 units, sum).
+template <int D>
+__global__ void __launch_bounds__(kDtThreads)
+decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bfloat16* __restrict__ q,
+                            float* __restrict__ partial_o, float* __restrict__ partial_ml,
+                            __nv_bfloat16* __restrict__ out, DtArgs a) {
+  using L = DtSmem<D>;
+  constexpr int STAGES = L::kStages;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // the swizzle pattern repeats every 1024 bytes
+  unsigned char* smem_gen = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + L::kData;
+  auto full = [&](int s) { return bars + 8u * s; };
+  auto empty = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto k_s = [&](int s) { return base + (uint32_t)s * L::kStage; };
+  auto v_s = [&](int s) { return base + (uint32_t)s * L::kStage + L::kKV; };
+
+  const int entry = blockIdx.z, split = blockIdx.x, kvh = blockIdx.y;
+  const int row0 = a.q_start[entry];
+  if (a.q_start[entry + 1] - row0 != 1) return;          // portions belong to the prefill kernel
+  const int nrows = a.group;
+  const int pos = a.kv_start[entry];
+  const int first_key = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  // chunk == 0: this request's own context is cut into num_splits equal parts (multiples of a tile)
+  const int first_tile_key = first_key / kDtBN * kDtBN;
+  const int chunk = a.chunk > 0 ? a.chunk
+                                : max(kDtBN, ((pos + 1 - first_tile_key + a.num_splits - 1) / a.num_splits + kDtBN - 1) / kDtBN * kDtBN);
+  const int kb = first_tile_key + split * chunk;
+  const int ke = min(kb + chunk, pos + 1);               // exclusive
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head0 = kvh * a.group;
+
+  if (kb > pos) {  // nothing in this split: an empty partial, which the merge ignores
+    if (a.num_splits > 1 && threadIdx.x < nrows) {
+      float* ml = partial_ml + (((size_t)entry * a.heads + head0 + threadIdx.x) * a.num_splits + split) * 2;
+      ml[0] = -CUDART_INF_F;
+      ml[1] = 0.f;
+    }
+    return;
+  }
+  const int n_tiles = (ke - kb + kDtBN - 1) / kDtBN;
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_kv) : "memory");
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full(s), 1);
+      mbar_init(empty(s), kDtConsumers);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
+    const int pages_per_tile = kDtBN >> a.page_shift;
+    const int oob_row = a.num_pages * 2 * a.kv_heads * a.page_size;   // past the tensor: the copy fills zeros
+    bool ok = true;
+    for (int it = 0; it < n_tiles; ++it) {
+      const int s = it % STAGES;
+      const uint32_t round = it / STAGES;
+      const int key0 = kb + it * kDtBN;
+      int page = -1;
+      if (lane < pages_per_tile) {
+        const int kp = key0 + lane * a.page_size;
+        // pages wholly outside [first_key, pos] are not looked up: they may be gone or never taken
+        if (kp <= pos && kp + a.page_size > first_key) page = __ldg(table + (kp >> a.page_shift));
+      }
+      if (lane == 0) {
+        if (round > 0 && !mbar_wait(empty(s), (round - 1) & 1)) {
+          if (a.error_word) atomicExch(a.error_word, 0x7C0031);
+          ok = false;
+        }
+        if (ok) mbar_expect_tx(full(s), L::kStage);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < pages_per_tile) {
+        const bool have = page >= 0 && page < a.num_pages;
+        const int krow = have ? ((page * 2 + 0) * a.kv_heads + kvh) * a.page_size : oob_row;
+        const int vrow = have ? ((page * 2 + 1) * a.kv_heads + kvh) * a.page_size : oob_row;
+        const uint32_t off = (uint32_t)(lane * a.page_size) * 128u;
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          tma_load_2d(k_s(s) + h * L::kSub + off, &map_kv, h * 64, krow, full(s));
+          tma_load_2d(v_s(s) + h * L::kSub + off, &map_kv, h * 64, vrow, full(s));
+        }
+      }
+      __syncwarp();
+    }
+  } else {
+    // ----------------------------------------------------------------- consumers
+    const int cw = warp - 1;                    // which 16 keys of every tile
+    const int g_row = lane >> 2, tig = lane & 3;
+    // Q fragments straight from global memory: row g_row of the A operand is head head0 + g_row
+    uint32_t qf[D / 16][4];
+    {
+      const __nv_bfloat16* qrow = q + (size_t)row0 * a.heads * D + (size_t)(head0 + g_row) * D;
+      const __nv_bfloat16* qrow8 = qrow + 8 * D;
+      const bool v0 = g_row < nrows, v8 = g_row + 8 < nrows;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        qf[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + tig * 2) : 0u;
+        qf[ks][1] = v8 ? *reinterpret_cast<const uint32_t*>(qrow8 + ks * 16 + tig * 2) : 0u;
+        qf[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + tig * 2) : 0u;
+        qf[ks][3] = v8 ? *reinterpret_cast<const uint32_t*>(qrow8 + ks * 16 + 8 + tig * 2) : 0u;
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[n][j] = 0.f;
+
+    const int krow = cw * 16 + (lane & 7) + ((lane >> 4) << 3);
+    const int kcol = ((lane >> 3) & 1) << 3;
+    const int vrow = cw * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+    const int vcol = (lane >> 4) << 3;
+    bool ok = true;
+    for (int it = 0; it < n_tiles && ok; ++it) {
+      const int s = it % STAGES;
+      if (!mbar_wait(full(s), (it / STAGES) & 1)) {
+        if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C0032);
+        ok = false;
+        break;
+      }
+      const int key_base = kb + it * kDtBN + cw * 16;
+      if (key_base <= pos && key_base + 16 > first_key) {           // (uniform in the warp)
+        if (key_base + 15 > pos) {
+          // value rows of keys past the request's end may never have been written: they must not be NaN
+          const int r = lane >> 1;                                   // two lanes per row, half a 128-byte row each
+          if (key_base + r > pos) {
+#pragma unroll
+            for (int h = 0; h < D / 64; ++h) {
+              uint4* dst = reinterpret_cast<uint4*>(smem_gen + (v_s(s) - base) + h * L::kSub + (cw * 16 + r) * 128 + (lane & 1) * 64);
+#pragma unroll
+              for (int c = 0; c < 4; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
+          __syncwarp();
+        }
+        // s = Q(16 x D) . K(16 keys x D)^T, even and odd k steps in accumulators of their own
+        float sc[2][4], e[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) sc[nt][j] = e[nt][j] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ks += 2) {
+          uint32_t b[4], c[4];
+          ldsm_x4(b, dt_at(k_s(s), krow, ks * 16 + kcol));
+          ldsm_x4(c, dt_at(k_s(s), krow, (ks + 1) * 16 + kcol));
+          mma_bf16(sc[0], qf[ks], b[0], b[1]);
+          mma_bf16(sc[1], qf[ks], b[2], b[3]);
+          mma_bf16(e[0], qf[ks + 1], c[0], c[1]);
+          mma_bf16(e[1], qf[ks + 1], c[2], c[3]);
+        }
+#pragma unroll
+        for (int n2 = 0; n2 < 2; ++n2)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int key = key_base + n2 * 8 + tig * 2 + (j & 1);
+            const bool allowed = key <= pos && key >= first_key && key < ke;
+            sc[n2][j] = allowed ? (sc[n2][j] + e[n2][j]) * a.scale_log2 : -CUDART_INF_F;
+          }
+        uint32_t p[1][4];
+        softmax_step<2, D / 8>(sc, m, l, o, p);
+#pragma unroll
+        for (int dn = 0; dn < D / 16; ++dn) {
+          uint32_t b[4];
+          ldsm_x4_trans(b, dt_at(v_s(s), vrow, dn * 16 + vcol));
+          mma_bf16(o[2 * dn], p[0], b[0], b[1]);
+          mma_bf16(o[2 * dn + 1], p[0], b[2], b[3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty(s));
+    }
+  }
+  __syncthreads();  // every copy has landed and been read: the stages' memory is reused below
+
+  // merge the four consumer warps (each saw a quarter of the keys) in shared memory
+  float* red_o = reinterpret_cast<float*>(smem_gen);                 // [4][16][D]
+  float* red_ml = red_o + kDtConsumers * 16 * D;                     // [4][16][2]
+  if (warp > 0) {
+    const int cw = warp - 1, g_row = lane >> 2, tig = lane & 3;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float sum = l[h];
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      const int r = g_row + 8 * h;
+      if (tig == 0) {
+        red_ml[(cw * 16 + r) * 2] = m[h];
+        red_ml[(cw * 16 + r) * 2 + 1] = sum;
+      }
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) {
+        red_o[(cw * 16 + r) * D + n * 8 + tig * 2] = o[n][2 * h];
+        red_o[(cw * 16 + r) * D + n * 8 + tig * 2 + 1] = o[n][2 * h + 1];
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nrows * D; idx += kDtThreads) {
+    const int r = idx / D, dd = idx - r * D;
+    float mm = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < kDtConsumers; ++w) mm = fmaxf(mm, red_ml[(w * 16 + r) * 2]);
+    const float basev = mm == -CUDART_INF_F ? 0.f : mm;
+    float acc = 0.f, sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDtConsumers; ++w) {
+      const float wgt = exp2f(red_ml[(w * 16 + r) * 2] - basev);
+      acc += red_o[(w * 16 + r) * D + dd] * wgt;
+      sum += red_ml[(w * 16 + r) * 2 + 1] * wgt;
+    }
+    if (a.num_splits == 1) {
+      out[(size_t)row0 * a.heads * D + (head0 + r) * D + dd] = __float2bfloat16_rn(acc / sum);
+    } else {
+      const size_t slot = ((size_t)entry * a.heads + head0 + r) * a.num_splits + split;
+      partial_o[slot * D + dd] = acc;
+      if (dd == 0) {
+        partial_ml[slot * 2] = mm;
+        partial_ml[slot * 2 + 1] = sum;
+      }
+    }
+  }
+}
+
+template <int D>
+static int launch_decode_tma(const void* q, const void* pool, float* partial_o, float* partial_ml, void* out,
+                             const DtArgs& a, int n_entries, cudaStream_t stream) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return TIB_E_ARG;
+  CUtensorMap map_kv;
+  // one layer's pages as rows of D: [pages * 2 * kv_heads * page_size][D]; a box is 64 dims x one page of one head
+  const cuuint64_t rows = (cuuint64_t)a.num_pages * 2 * a.kv_heads * a.page_size;
+  const cuuint64_t dims[2] = {(cuuint64_t)D, rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)a.page_size};
+  const cuuint32_t elem[2] = {1, 1};
+  if (fn(&map_kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return TIB_E_ARG;
+  auto kern = decode_attention_tma_kernel<D>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DtSmem<D>::kTotal);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid(a.num_splits, a.kv_heads, n_entries);
+  kern<<<grid, kDtThreads, DtSmem<D>::kTotal, stream>>>(map_kv, (const __nv_bfloat16*)q, partial_o, partial_ml,
+                                                        (__nv_bfloat16*)out, a);
+  TIB_LAUNCH_CHECK();
+  if (a.num_splits > 1) {
+    dim3 mgrid(a.heads, n_entries);
+    decode_merge_kernel<D><<<mgrid, D, 0, stream>>>(partial_o, partial_ml, (__nv_bfloat16*)out, a.q_start, a.heads, a.num_splits);
+    TIB_LAUNCH_CHECK();
+  }
+  return TIB_OK;
+}
+
+}  // namespace tib
+
+using namespace tib;
+
+// Whether tib_decode_attention_tma takes these sizes.
+TIB_API int tib_decode_attention_tma_supports(int head_dim, int group, int page_size) {
+  return (head_dim == 64 || head_dim == 128) && group >= 1 && group <= 16 &&
+         (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
+}
+
+// Same contract as tib_decode_attention (bf16).  page_stride must equal 2 * kv_heads * page_size *
+// head_dim (pages packed back to back).  A bounded wait that runs out sets *error_word (0x7C003x).
+TIB_API int tib_decode_attention_tma(const void* q, const void* pool, void* out, float* scratch_o, float* scratch_ml,
+                                     const int* q_start, const int* kv_start, const int* slots, const int* block_table,
+                                     int table_stride, int n_entries, int heads, int kv_heads, int head_dim,
+                                     int page_size, int64_t page_stride, int num_pages, int window, float scale,
+                                     int num_splits, int chunk, int* error_word, cudaStream_t stream) {
+  if (n_entries == 0) return TIB_OK;
+  if (!q || !pool || !out || !q_start || !kv_start || !slots || !block_table) return TIB_E_ARG;
+  if (heads < 1 || kv_heads < 1 || heads % kv_heads != 0) return TIB_E_SIZE;
+  if (!tib_decode_attention_tma_supports(head_dim, heads / kv_heads, page_size)) return TIB_E_SIZE;
+  if (num_splits < 1 || num_splits > 65535 || chunk < 0 || chunk % kDtBN != 0) return TIB_E_SIZE;
+  if (num_splits > 1 && (!scratch_o || !scratch_ml)) return TIB_E_ARG;
+  if (page_stride != (int64_t)2 * kv_heads * page_size * head_dim) return TIB_E_ALIGN;
+  if ((((uintptr_t)q | (uintptr_t)pool | (uintptr_t)out) & 15) != 0) return TIB_E_ALIGN;
+  if (n_entries > 65535 || kv_heads > 65535) return TIB_E_SIZE;
+  if ((int64_t)num_pages * 2 * kv_heads * page_size >= ((int64_t)1 << 31)) return TIB_E_SIZE;   // row coordinates are 32-bit
+  DtArgs a;
+  a.q_start = q_start; a.kv_start = kv_start; a.slots = slots; a.block_table = block_table;
+  a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads; a.group = heads / kv_heads;
+  a.page_size = page_size; a.page_shift = 0;
+  while ((1 << a.page_shift) < page_size) ++a.page_shift;
+  a.num_pages = num_pages; a.window = window; a.scale_log2 = scale * 1.4426950408889634f;
+  a.chunk = chunk; a.num_splits = num_splits; a.error_word = error_word;
+  return head_dim == 64 ? launch_decode_tma<64>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream)
+                        : launch_decode_tma<128>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream);
+}

@@ -14,8 +14,7 @@
 // (layout [pages][2][kv_heads][page_size][head_dim]); any page size works, since every key row is
 // fetched by its own address.  Keys past a block's last query position are never read from memory
 // (they may be unwritten): their shared-memory rows are zero-filled, and they are masked.
-#include "common.cuh"
-#include <math_constants.h>
+#include "mma.cuh"
 
 namespace tib {
 
@@ -39,36 +38,6 @@ struct MmaAttnArgs {
   int num_splits;        // decode
   int skip_single;       // prefill: leave single-token entries to the decode kernel
 };
-
-// ----------------------------------------------------------------- PTX bits
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-  const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are zero-filled, nothing is read
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 
 // Shared-memory tile [rows][D] of bf16 with the 16-byte chunks of a row XOR-swizzled by (row & 7),
 // so that the eight rows an ldmatrix touches fall into different banks.
@@ -113,48 +82,6 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_tile, __nv_bfloat1
     const int off = r * D + ((c ^ (r & 7)) << 3);
     cp_async16(k_tile + off, src, valid);
     cp_async16(v_tile + off, valid ? src + v_off : pool, valid);
-  }
-}
-
-// One step of the streaming softmax for a warp's 16 rows over NT n-tiles of 8 keys: scores s are
-// already scaled and masked (-inf).  Updates m, l (per-thread partial sums), rescales o and
-// returns the probabilities packed as the A fragments of the P.V product (one per 16 keys).
-template <int NT, int ONT>
-__device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&o)[ONT][4],
-                                             uint32_t (&p)[NT / 2][4]) {
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {  // h = 0: row g, h = 1: row g + 8
-    float mx = -CUDART_INF_F;
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * h], s[nt][2 * h + 1]));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float m_new = fmaxf(m[h], mx);
-    const float base = m_new == -CUDART_INF_F ? 0.f : m_new;
-    const float alpha = exp2f(m[h] - base);
-    m[h] = m_new;
-    float sum = 0.f;
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      s[nt][2 * h] = exp2f(s[nt][2 * h] - base);
-      s[nt][2 * h + 1] = exp2f(s[nt][2 * h + 1] - base);
-      sum += s[nt][2 * h] + s[nt][2 * h + 1];
-    }
-    l[h] = l[h] * alpha + sum;
-    if (__any_sync(0xffffffffu, alpha != 1.f)) {  // once the running max has settled nothing is rescaled
-#pragma unroll
-      for (int n = 0; n < ONT; ++n) {
-        o[n][2 * h] *= alpha;
-        o[n][2 * h + 1] *= alpha;
-      }
-    }
-  }
-#pragma unroll
-  for (int kk = 0; kk < NT / 2; ++kk) {
-    p[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-    p[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-    p[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-    p[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
   }
 }
 
@@ -510,28 +437,6 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       }
     }
   }
-}
-
-// grid: (heads, n_entries), D threads.
-template <int D>
-__global__ void __launch_bounds__(D)
-decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
-                    __nv_bfloat16* __restrict__ out, const int* __restrict__ q_start, int heads, int num_splits) {
-  const int entry = blockIdx.y, head = blockIdx.x;
-  const int row0 = q_start[entry];
-  if (q_start[entry + 1] - row0 != 1) return;
-  const size_t base_slot = ((size_t)entry * heads + head) * num_splits;
-  float mm = -CUDART_INF_F;
-  for (int s = 0; s < num_splits; ++s) mm = fmaxf(mm, partial_ml[(base_slot + s) * 2]);
-  float acc = 0.f, sum = 0.f;
-  for (int s = 0; s < num_splits; ++s) {
-    const float ms = partial_ml[(base_slot + s) * 2];
-    if (ms == -CUDART_INF_F) continue;  // an empty split wrote no output
-    const float wgt = exp2f(ms - mm);
-    acc += partial_o[(base_slot + s) * D + threadIdx.x] * wgt;
-    sum += partial_ml[(base_slot + s) * 2 + 1] * wgt;
-  }
-  out[(size_t)row0 * heads * D + head * D + threadIdx.x] = __float2bfloat16_rn(acc / sum);
 }
 
 template <int D>

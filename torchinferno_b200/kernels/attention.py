@@ -35,7 +35,8 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, ctx, heads: int, kv_head
                 ops.prefill_attention(*args, batch.max_q_len, heads, kv_heads, head_dim, scale, window=win,
                                       skip_single=batch.n_single > 0)
         if batch.n_single:
-            ops.decode_attention(*args, heads, kv_heads, head_dim, scale, batch.max_kv_len, window=win)
+            ops.decode_attention(*args, heads, kv_heads, head_dim, scale, batch.max_kv_len, window=win,
+                                 error_word=ctx.error_word)
         return out
     return ops.paged_attention_simt(
         q, kv.pool, out, batch.q_start, batch.kv_start, batch.slots, kv.block_table,

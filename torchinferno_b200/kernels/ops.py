@@ -83,6 +83,7 @@ def lib() -> ctypes.CDLL:
                    "tib_scatter_i32", "tib_advance_decode", "tib_rope_append", "tib_paged_attention_simt", "tib_gemm_f32", "tib_sample",
                    "tib_attention_mma_supports", "tib_prefill_attention", "tib_decode_attention",
                    "tib_prefill_attention_tcgen05", "tib_prefill_attention_tcgen05_supports",
+                   "tib_decode_attention_tma", "tib_decode_attention_tma_supports",
                    "tib_gemm_skinny", "tib_gemm_skinny_supports", "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
                    "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports"):
             getattr(library, fn).restype = c_int
@@ -335,8 +336,12 @@ def decode_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_s
                      kv_start: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, n_entries: int,
                      heads: int, kv_heads: int, head_dim: int, scale: float, max_kv_len: int, window: int = 0,
                      scratch: torch.Tensor | None = None, num_splits: int | None = None,
-                     chunk: int | None = None) -> torch.Tensor:
+                     chunk: int | None = None, kernel: str = "auto", error_word: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of single tokens over the paged cache, the context split over blocks (bf16).
+
+    ``kernel``: "tma" (keys and values copied by the TMA unit; see ``decode_attention_tma_supports``),
+    "cp_async" (every key row fetched by its own address; any page size), or "auto": the first where
+    it takes the shape.
 
     Entries that bring more than one token are skipped.  ``max_kv_len`` bounds the longest context
     (keys 0 .. position) of the batch when ``num_splits`` and ``chunk`` are given (by default the kernel
@@ -359,12 +364,30 @@ def decode_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_s
             raise KernelError("decode_attention: scratch is too small")
         scratch_o = scratch
         scratch_ml = scratch[n_entries * heads * num_splits * head_dim:]
+    if kernel not in ("auto", "tma", "cp_async"):
+        raise KernelError(f"decode_attention: no kernel {kernel!r}")
+    packed = pool.stride(0) == 2 * kv_heads * pool.shape[3] * head_dim
+    tma = kernel != "cp_async" and packed and decode_attention_tma_supports(head_dim, heads // kv_heads, pool.shape[3])
+    if kernel == "tma" and not tma:
+        raise KernelError("decode_attention: the TMA kernel does not take this shape "
+                          f"(head_dim {head_dim}, group {heads // kv_heads}, pages of {pool.shape[3]}, packed={packed})")
+    if tma:
+        _check("decode_attention_tma", lib().tib_decode_attention_tma(
+            _ptr(q), _ptr(pool), _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), _ptr(q_start), _ptr(kv_start), _ptr(slots),
+            _ptr(block_table), c_int(block_table.stride(0)), c_int(n_entries), c_int(heads), c_int(kv_heads), c_int(head_dim),
+            c_int(pool.shape[3]), c_int64(pool.stride(0)), c_int(pool.shape[0]), c_int(window), c_float(scale),
+            c_int(num_splits), c_int(chunk), _ptr(error_word), _stream()))
+        return out
     _check("decode_attention", lib().tib_decode_attention(
         _ptr(q), _ptr(pool), _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), _ptr(q_start), _ptr(kv_start), _ptr(slots),
         _ptr(block_table), c_int(block_table.stride(0)), c_int(n_entries), c_int(heads), c_int(kv_heads), c_int(head_dim),
         c_int(pool.shape[3]), c_int64(pool.stride(0)), c_int(pool.shape[0]), c_int(window), c_float(scale),
         c_int(num_splits), c_int(chunk), _stream()))
     return out
+
+
+def decode_attention_tma_supports(head_dim: int, group: int, page_size: int) -> bool:
+    return bool(lib().tib_decode_attention_tma_supports(c_int(head_dim), c_int(group), c_int(page_size)))
 
 
 def gemm_skinny_supports(m: int, n: int, k: int) -> bool:
