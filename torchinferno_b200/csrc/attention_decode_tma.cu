@@ -36,6 +36,7 @@ struct DtArgs {
   int window;
   float scale_log2;
   int chunk, num_splits;
+  int* counters;         // [entries * kv_heads] zeros: the parts of a split context count themselves in; or null
   int* error_word;
 };
 
@@ -73,6 +74,12 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
                             __nv_bfloat16* __restrict__ out, DtArgs a) {
   using L = DtSmem<D>;
   constexpr int STAGES = L::kStages;
+  // Placed early (programmatic dependent launch), the block starts copying at once: the kernel before it
+  // in the stream writes only the newest token's keys and values and the queries, so everything older may
+  // be fetched while that kernel still runs.  pdl_wait() stands before the first read of the newest tile,
+  // before the queries are read, and before anything is written.
+  pdl_trigger();
+  __shared__ int ticket_s;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // the swizzle pattern repeats every 1024 bytes
   unsigned char* smem_gen = smem_raw + (base - smem_u32(smem_raw));
@@ -83,6 +90,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
   auto v_s = [&](int s) { return base + (uint32_t)s * L::kStage + L::kKV; };
 
   const int entry = blockIdx.z, split = blockIdx.x, kvh = blockIdx.y;
+  if (threadIdx.x == 0) asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_kv) : "memory");
+  const int slot = a.slots[entry];                        // (asked for together with the loads below: one latency)
   const int row0 = a.q_start[entry];
   if (a.q_start[entry + 1] - row0 != 1) return;          // portions belong to the prefill kernel
   const int nrows = a.group;
@@ -97,18 +106,19 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int head0 = kvh * a.group;
 
-  if (kb > pos) {  // nothing in this split: an empty partial, which the merge ignores
+  const bool empty_part = kb > pos;   // nothing in this part: an empty partial, which the merge ignores
+  if (empty_part) {
+    pdl_wait();
     if (a.num_splits > 1 && threadIdx.x < nrows) {
       float* ml = partial_ml + (((size_t)entry * a.heads + head0 + threadIdx.x) * a.num_splits + split) * 2;
       ml[0] = -CUDART_INF_F;
       ml[1] = 0.f;
     }
-    return;
   }
-  const int n_tiles = (ke - kb + kDtBN - 1) / kDtBN;
+  const int n_tiles = empty_part ? 0 : (ke - kb + kDtBN - 1) / kDtBN;
+  if (!empty_part) {
 
   if (threadIdx.x == 0) {
-    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_kv) : "memory");
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full(s), 1);
       mbar_init(empty(s), kDtConsumers);
@@ -122,14 +132,18 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
-    const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
+    const int* table = a.block_table + (size_t)slot * a.table_stride;
     const int pages_per_tile = kDtBN >> a.page_shift;
     const int oob_row = a.num_pages * 2 * a.kv_heads * a.page_size;   // past the tensor: the copy fills zeros
-    bool ok = true;
+    bool ok = true, waited = false;
     for (int it = 0; it < n_tiles; ++it) {
       const int s = it % STAGES;
       const uint32_t round = it / STAGES;
       const int key0 = kb + it * kDtBN;
+      if (!waited && key0 + kDtBN > pos) {   // the tile that holds the newest token
+        pdl_wait();
+        waited = true;
+      }
       int page = -1;
       if (lane < pages_per_tile) {
         const int kp = key0 + lane * a.page_size;
@@ -162,6 +176,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
     // ----------------------------------------------------------------- consumers
     const int cw = warp - 1;                    // which 16 keys of every tile
     const int g_row = lane >> 2, tig = lane & 3;
+    pdl_wait();
     // Q fragments straight from global memory: row g_row of the A operand is head head0 + g_row
     uint32_t qf[D / 16][4];
     {
@@ -247,6 +262,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
     }
   }
   __syncthreads();  // every copy has landed and been read: the stages' memory is reused below
+  pdl_wait();
 
   // merge the four consumer warps (each saw a quarter of the keys) in shared memory
   float* red_o = reinterpret_cast<float*>(smem_gen);                 // [4][16][D]
@@ -295,6 +311,57 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
       }
     }
   }
+  }  // (!empty_part)
+
+  // The parts of one (request, kv head) count themselves in; the one that arrives last merges them all, so
+  // no second kernel is needed.  The counter is left at zero for the next launch.
+  if (a.num_splits == 1 || a.counters == nullptr) return;
+  __threadfence();
+  __syncthreads();
+  int* counter = a.counters + (size_t)entry * a.kv_heads + kvh;
+  if (threadIdx.x == 0) ticket_s = atomicAdd(counter, 1);
+  __syncthreads();
+  if (ticket_s != a.num_splits - 1) return;
+  __threadfence();
+  // weights of the parts first (one load per (row, part), all in flight together), then the sums with the
+  // loads of several parts in flight: nothing here waits for one load after another
+  float* wgt_s = reinterpret_cast<float*>(smem_gen);                 // [nrows][num_splits] weights, then [nrows] 1 / sum
+  const int ns = a.num_splits;
+  const size_t slot0 = ((size_t)entry * a.heads + head0) * ns;       // (row r, part sp) is slot0 + r * ns + sp
+  for (int r = warp; r < nrows; r += kDtThreads / 32) {
+    float mm = -CUDART_INF_F;
+    for (int sp = lane; sp < ns; sp += 32) mm = fmaxf(mm, __ldcg(partial_ml + (slot0 + r * ns + sp) * 2));
+    mm = warp_max(mm);
+    float sum = 0.f;
+    for (int sp = lane; sp < ns; sp += 32) {
+      const float ms = __ldcg(partial_ml + (slot0 + r * ns + sp) * 2);
+      const float w = ms == -CUDART_INF_F ? 0.f : exp2f(ms - mm);     // an empty part wrote no output
+      wgt_s[r * ns + sp] = w;
+      sum += w == 0.f ? 0.f : w * __ldcg(partial_ml + (slot0 + r * ns + sp) * 2 + 1);
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) wgt_s[nrows * ns + r] = 1.f / sum;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nrows * (D / 4); idx += kDtThreads) {   // four output elements per thread
+    const int r = idx / (D / 4), d4 = idx - r * (D / 4);
+    const float4* po = reinterpret_cast<const float4*>(partial_o + (slot0 + r * ns) * D) + d4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int sp = 0; sp < ns; ++sp) {
+      const float w = wgt_s[r * ns + sp];
+      if (w != 0.f) {
+        const float4 v = __ldcg(po + (size_t)sp * (D / 4));
+        acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+      }
+    }
+    const float inv = wgt_s[nrows * ns + r];
+    uint2 packed;
+    packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+    packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(out + (size_t)row0 * a.heads * D + (head0 + r) * D + d4 * 4) = packed;
+  }
+  if (threadIdx.x == 0) *counter = 0;
 }
 
 template <int D>
@@ -317,12 +384,13 @@ static int launch_decode_tma(const void* q, const void* pool, float* partial_o, 
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DtSmem<D>::kTotal);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(a.num_splits, a.kv_heads, n_entries);
-  kern<<<grid, kDtThreads, DtSmem<D>::kTotal, stream>>>(map_kv, (const __nv_bfloat16*)q, partial_o, partial_ml,
-                                                        (__nv_bfloat16*)out, a);
+  TIB_LAUNCH_DEPENDENT(kern, grid, kDtThreads, DtSmem<D>::kTotal, stream, map_kv, (const __nv_bfloat16*)q, partial_o,
+                       partial_ml, (__nv_bfloat16*)out, a);
   TIB_LAUNCH_CHECK();
-  if (a.num_splits > 1) {
+  if (a.num_splits > 1 && a.counters == nullptr) {
     dim3 mgrid(a.heads, n_entries);
-    decode_merge_kernel<D><<<mgrid, D, 0, stream>>>(partial_o, partial_ml, (__nv_bfloat16*)out, a.q_start, a.heads, a.num_splits);
+    TIB_LAUNCH_DEPENDENT(decode_merge_kernel<D>, mgrid, D, (a.num_splits + 1) * sizeof(float), stream, (const float*)partial_o, (const float*)partial_ml,
+                         (__nv_bfloat16*)out, a.q_start, a.heads, a.num_splits);
     TIB_LAUNCH_CHECK();
   }
   return TIB_OK;
@@ -340,16 +408,19 @@ TIB_API int tib_decode_attention_tma_supports(int head_dim, int group, int page_
 
 // Same contract as tib_decode_attention (bf16).  page_stride must equal 2 * kv_heads * page_size *
 // head_dim (pages packed back to back).  A bounded wait that runs out sets *error_word (0x7C003x).
+// counters: n_entries * kv_heads ints that are zero (the kernel leaves them zero): with them the parts of a
+// split context are merged by the block that finishes last; without (null) by a second kernel.  Launches
+// that may overlap on the GPU need counters of their own.
 TIB_API int tib_decode_attention_tma(const void* q, const void* pool, void* out, float* scratch_o, float* scratch_ml,
                                      const int* q_start, const int* kv_start, const int* slots, const int* block_table,
                                      int table_stride, int n_entries, int heads, int kv_heads, int head_dim,
                                      int page_size, int64_t page_stride, int num_pages, int window, float scale,
-                                     int num_splits, int chunk, int* error_word, cudaStream_t stream) {
+                                     int num_splits, int chunk, int* counters, int* error_word, cudaStream_t stream) {
   if (n_entries == 0) return TIB_OK;
   if (!q || !pool || !out || !q_start || !kv_start || !slots || !block_table) return TIB_E_ARG;
   if (heads < 1 || kv_heads < 1 || heads % kv_heads != 0) return TIB_E_SIZE;
   if (!tib_decode_attention_tma_supports(head_dim, heads / kv_heads, page_size)) return TIB_E_SIZE;
-  if (num_splits < 1 || num_splits > 65535 || chunk < 0 || chunk % kDtBN != 0) return TIB_E_SIZE;
+  if (num_splits < 1 || num_splits > 1024 || chunk < 0 || chunk % kDtBN != 0) return TIB_E_SIZE;   // (the merge keeps a weight per part in shared memory)
   if (num_splits > 1 && (!scratch_o || !scratch_ml)) return TIB_E_ARG;
   if (page_stride != (int64_t)2 * kv_heads * page_size * head_dim) return TIB_E_ALIGN;
   if ((((uintptr_t)q | (uintptr_t)pool | (uintptr_t)out) & 15) != 0) return TIB_E_ALIGN;
@@ -361,7 +432,7 @@ TIB_API int tib_decode_attention_tma(const void* q, const void* pool, void* out,
   a.page_size = page_size; a.page_shift = 0;
   while ((1 << a.page_shift) < page_size) ++a.page_shift;
   a.num_pages = num_pages; a.window = window; a.scale_log2 = scale * 1.4426950408889634f;
-  a.chunk = chunk; a.num_splits = num_splits; a.error_word = error_word;
+  a.chunk = chunk; a.num_splits = num_splits; a.counters = counters; a.error_word = error_word;
   return head_dim == 64 ? launch_decode_tma<64>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream)
                         : launch_decode_tma<128>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream);
 }

@@ -471,7 +471,7 @@ static int launch_decode(const void* q, const void* pool, float* partial_o, floa
   TIB_LAUNCH_CHECK();
   if (a.num_splits > 1) {
     dim3 mgrid(a.heads, n_entries);
-    decode_merge_kernel<D><<<mgrid, D, 0, stream>>>(partial_o, partial_ml, (__nv_bfloat16*)out, a.q_start, a.heads, a.num_splits);
+    decode_merge_kernel<D><<<mgrid, D, (a.num_splits + 1) * sizeof(float), stream>>>(partial_o, partial_ml, (__nv_bfloat16*)out, a.q_start, a.heads, a.num_splits);
     TIB_LAUNCH_CHECK();
   }
   return TIB_OK;
@@ -532,7 +532,7 @@ TIB_API int tib_decode_attention(const void* q, const void* pool, void* out, flo
                                  int num_splits, int chunk, cudaStream_t stream) {
   if (n_entries == 0) return TIB_OK;
   if (!q || !pool || !out) return TIB_E_ARG;
-  if (num_splits < 1 || chunk < 0 || (chunk > 0 && chunk < kBN) || chunk % kBN != 0) return TIB_E_SIZE;
+  if (num_splits < 1 || num_splits > 4096 || chunk < 0 || (chunk > 0 && chunk < kBN) || chunk % kBN != 0) return TIB_E_SIZE;
   if (num_splits > 1 && (!scratch_o || !scratch_ml)) return TIB_E_ARG;
   MmaAttnArgs a;
   int rc = fill_args(a, q_start, kv_start, slots, block_table, table_stride, heads, kv_heads, head_dim, page_size,
@@ -605,7 +605,7 @@ TIB_API int tib_decode_attention_noalloc(const void* q, const void* pool, void* 
                                          int num_splits, int chunk, cudaStream_t stream) {
   if (n_entries == 0) return TIB_OK;
   if (!q || !pool || !out) return TIB_E_ARG;
-  if (num_splits < 1 || chunk < kBN || chunk % kBN != 0) return TIB_E_SIZE;
+  if (num_splits < 1 || num_splits > 4096 || chunk < kBN || chunk % kBN != 0) return TIB_E_SIZE;
   MmaAttnArgs a;
   int rc = fill_args(a, q_start, kv_start, slots, block_table, table_stride, heads, kv_heads, head_dim, page_size,
                      page_stride, num_pages, window, scale);

@@ -27,6 +27,13 @@ enum TibError : int {
   TIB_E_SCRATCH = -7,    // needs more scratch than the library's built-in array holds
 };
 
+// kernel<<<grid, block, smem, stream>>>(args) as a programmatic dependent launch (see launch_dependent below)
+#define TIB_LAUNCH_DEPENDENT(kernel, grid, block, smem, stream, ...)                                              \
+  do {                                                                                                            \
+    cudaError_t le__ = tib::launch_dependent(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__); \
+    if (le__ != cudaSuccess) return (int)le__;                                                                    \
+  } while (0)
+
 #define TIB_LAUNCH_CHECK()                         \
   do {                                             \
     cudaError_t e__ = cudaGetLastError();          \
@@ -72,6 +79,38 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   }
   __syncthreads();
   return scratch[32];
+}
+
+// --- programmatic dependent launch -------------------------------------------------------------
+// A kernel launched through launch_dependent() may be placed on the SMs while the kernel before it
+// in the stream is still draining; it must call pdl_wait() before it reads anything an earlier
+// kernel wrote (or writes anything an earlier kernel reads).  pdl_wait() returns once every kernel
+// before it has completed and its writes are visible; in a kernel launched the ordinary way it
+// returns at once.  pdl_trigger() lets the kernel after this one be placed early in the same way.
+// Every kernel of this library that is launched this way waits first thing, so completion is
+// transitive along the stream.  The switch is process-wide (tib_set_dependent_launch).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+inline int& dependent_launch_flag() {
+  static int on = 1;
+  return on;
+}
+
+template <typename... P, typename... A>
+static inline cudaError_t launch_dependent(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                           A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr = {};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = dependent_launch_flag() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

@@ -19,6 +19,8 @@ namespace tib {
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab) {
+  pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x;
   const int id = ids[row];
   float* dst = out + (size_t)row * hidden;
@@ -38,6 +40,8 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(const T* __restrict__ delta, float* __restrict__ residual,
                                    const int* __restrict__ rows, const float* __restrict__ weight,
                                    T* __restrict__ out, int hidden, float eps) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float scratch[33];
   const int orow = blockIdx.x;
   const int srow = rows ? rows[orow] : orow;
@@ -67,6 +71,8 @@ __global__ void __launch_bounds__(1024)
 add_rmsnorm_bf16x8_kernel(const __nv_bfloat16* __restrict__ delta, float* __restrict__ residual,
                           const int* __restrict__ rows, const float* __restrict__ weight,
                           __nv_bfloat16* __restrict__ out, int hidden, float eps) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float scratch[33];
   const int orow = blockIdx.x;
   const int srow = rows ? rows[orow] : orow;
@@ -114,6 +120,8 @@ add_rmsnorm_bf16x8_kernel(const __nv_bfloat16* __restrict__ delta, float* __rest
 template <typename T>
 __global__ void rmsnorm_t_kernel(const T* __restrict__ x, const float* __restrict__ weight,
                                  T* __restrict__ out, int hidden, float eps) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float scratch[33];
   const T* src = x + (size_t)blockIdx.x * hidden;
   float ss = 0.f;
@@ -132,6 +140,8 @@ __global__ void rmsnorm_t_kernel(const T* __restrict__ x, const float* __restric
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter,
                               int64_t total) {
+  pdl_wait();
+  pdl_trigger();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t row = i / inter;
@@ -146,6 +156,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 // bf16, intermediate width a multiple of 8: 16-byte loads and stores.
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
                                      int inter, int64_t total_vec) {
+  pdl_wait();
+  pdl_trigger();
   const int per_row = inter >> 3;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t row = i / per_row;
@@ -184,6 +196,8 @@ __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict_
 __global__ void advance_decode_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
                                       int* __restrict__ positions, int* __restrict__ draw_positions,
                                       int* __restrict__ history, int n) {
+  pdl_wait();
+  pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
     const int t = sampled[i];
@@ -211,9 +225,9 @@ TIB_API int tib_embedding(const int* ids, const void* table, float* out, int n_t
   if (!ids || !table || !out || n_tokens < 0 || hidden < 1 || vocab < 1) return TIB_E_ARG;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == TIB_F32)
-    embedding_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+    TIB_LAUNCH_DEPENDENT(embedding_kernel<float>, n_tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab);
   else if (dtype == TIB_BF16)
-    embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+    TIB_LAUNCH_DEPENDENT(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, ids, (const __nv_bfloat16*)table, out, hidden, vocab);
   else
     return TIB_E_DTYPE;
   TIB_LAUNCH_CHECK();
@@ -228,13 +242,13 @@ TIB_API int tib_add_rmsnorm(const void* delta, float* residual, const int* rows,
   if (!residual || !weight || !out || n_out < 0 || hidden < 1) return TIB_E_ARG;
   const int threads = norm_threads(hidden);
   if (dtype == TIB_F32)
-    add_rmsnorm_kernel<float><<<n_out, threads, 0, stream>>>((const float*)delta, residual, rows, weight, (float*)out, hidden, eps);
+    TIB_LAUNCH_DEPENDENT(add_rmsnorm_kernel<float>, n_out, threads, 0, stream, (const float*)delta, residual, rows, weight, (float*)out, hidden, eps);
   else if (dtype == TIB_BF16 && hidden % 8 == 0 && hidden <= 8192 &&
            (((uintptr_t)residual | (uintptr_t)weight | (uintptr_t)out | (uintptr_t)delta) & 15) == 0) {
     const int vec_threads = ((hidden / 8) + 31) / 32 * 32;
-    add_rmsnorm_bf16x8_kernel<<<n_out, vec_threads, 0, stream>>>((const __nv_bfloat16*)delta, residual, rows, weight, (__nv_bfloat16*)out, hidden, eps);
+    TIB_LAUNCH_DEPENDENT(add_rmsnorm_bf16x8_kernel, n_out, vec_threads, 0, stream, (const __nv_bfloat16*)delta, residual, rows, weight, (__nv_bfloat16*)out, hidden, eps);
   } else if (dtype == TIB_BF16)
-    add_rmsnorm_kernel<__nv_bfloat16><<<n_out, threads, 0, stream>>>((const __nv_bfloat16*)delta, residual, rows, weight, (__nv_bfloat16*)out, hidden, eps);
+    TIB_LAUNCH_DEPENDENT(add_rmsnorm_kernel<__nv_bfloat16>, n_out, threads, 0, stream, (const __nv_bfloat16*)delta, residual, rows, weight, (__nv_bfloat16*)out, hidden, eps);
   else
     return TIB_E_DTYPE;
   TIB_LAUNCH_CHECK();
@@ -247,9 +261,9 @@ TIB_API int tib_rmsnorm(const void* x, const float* weight, void* out, int n_row
   if (!x || !weight || !out || n_rows < 0 || hidden < 1) return TIB_E_ARG;
   const int threads = norm_threads(hidden);
   if (dtype == TIB_F32)
-    rmsnorm_t_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)x, weight, (float*)out, hidden, eps);
+    TIB_LAUNCH_DEPENDENT(rmsnorm_t_kernel<float>, n_rows, threads, 0, stream, (const float*)x, weight, (float*)out, hidden, eps);
   else if (dtype == TIB_BF16)
-    rmsnorm_t_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>((const __nv_bfloat16*)x, weight, (__nv_bfloat16*)out, hidden, eps);
+    TIB_LAUNCH_DEPENDENT(rmsnorm_t_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, (const __nv_bfloat16*)x, weight, (__nv_bfloat16*)out, hidden, eps);
   else
     return TIB_E_DTYPE;
   TIB_LAUNCH_CHECK();
@@ -264,12 +278,12 @@ TIB_API int tib_swiglu(const void* gate_up, void* out, int n_rows, int inter, in
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == TIB_F32)
-    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    TIB_LAUNCH_DEPENDENT(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, inter, total);
   else if (dtype == TIB_BF16 && inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
     const int64_t vec = total / 8, want_v = (vec + threads - 1) / threads;
-    swiglu_bf16x8_kernel<<<(int)(want_v < 148 * 16 ? want_v : 148 * 16), threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, vec);
+    TIB_LAUNCH_DEPENDENT(swiglu_bf16x8_kernel, (int)(want_v < 148 * 16 ? want_v : 148 * 16), threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, vec);
   } else if (dtype == TIB_BF16)
-    swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+    TIB_LAUNCH_DEPENDENT(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
   else
     return TIB_E_DTYPE;
   TIB_LAUNCH_CHECK();
@@ -311,7 +325,15 @@ TIB_API int tib_advance_decode(int* token_ids, const int* sampled, int* position
                                int* history, int n, cudaStream_t stream) {
   if (n == 0) return TIB_OK;
   if (!token_ids || !sampled || !positions || n < 0) return TIB_E_ARG;
-  advance_decode_kernel<<<ceil_div(n, 128), 128, 0, stream>>>(token_ids, sampled, positions, draw_positions, history, n);
+  TIB_LAUNCH_DEPENDENT(advance_decode_kernel, ceil_div(n, 128), 128, 0, stream, token_ids, sampled, positions, draw_positions, history, n);
   TIB_LAUNCH_CHECK();
   return TIB_OK;
+}
+
+// Programmatic dependent launch of this library's small kernels on (1, the default) or off (0);
+// returns the setting before.  Off, every kernel starts only when the one before it has ended.
+TIB_API int tib_set_dependent_launch(int on) {
+  const int before = tib::dependent_launch_flag();
+  tib::dependent_launch_flag() = on ? 1 : 0;
+  return before;
 }

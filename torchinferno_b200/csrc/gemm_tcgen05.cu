@@ -278,6 +278,7 @@ gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
   const int kb0 = (int)((int64_t)k_blocks * rank / splits), kb1 = (int)((int64_t)k_blocks * (rank + 1) / splits);
   const int rows_per = (128 + splits - 1) / splits;                        // features each block of the cluster owns
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), 1);
@@ -303,19 +304,31 @@ gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t it = 0;
+      // The weights do not depend on the kernel before this one, the rows of x do: the first ring of weight
+      // tiles is requested at once, and pdl_wait() stands before the first copy of x.
+      uint32_t it = 0, ahead = 0;
       bool ok = true;
+      for (int t = cluster_id; t < n_tiles && ahead < (uint32_t)kStages; t += clusters)
+        for (int kb = kb0; kb < kb1 && ahead < (uint32_t)kStages; ++kb, ++ahead) {
+          mbar_expect_tx(full_bar(ahead), kSwWBytes + kXBytes);
+          tma_load_2d(base + ahead * kStage, &map_w, kb * kTcBK, t * 128, full_bar(ahead));
+        }
+      pdl_wait();
       for (int t = cluster_id; t < n_tiles && ok; t += clusters) {
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1;
+          const uint32_t w_dst = base + s * kStage, x_dst = w_dst + kSwWBytes;
+          if (it < ahead) {   // (its weights are on their way)
+            tma_load_2d(x_dst, &map_x, kb * kTcBK, 0, full_bar(s));
+            continue;
+          }
           if (!mbar_wait(empty_bar(s), phase ^ 1)) {
             if (error_word) atomicExch(error_word, 0x7C0011);
             ok = false;
             break;
           }
           mbar_expect_tx(full_bar(s), kSwWBytes + kXBytes);
-          const uint32_t w_dst = base + s * kStage, x_dst = w_dst + kSwWBytes;
           tma_load_2d(w_dst, &map_w, kb * kTcBK, t * 128, full_bar(s));
           tma_load_2d(x_dst, &map_x, kb * kTcBK, 0, full_bar(s));
         }
@@ -354,6 +367,7 @@ gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       }
     }
   } else {
+    pdl_wait();                                        // `out` may be memory the kernel before still reads
     const int quarter = warp & 3;
     const int f = quarter * 32 + lane;                 // feature (row of w) within the tile
     const int et = threadIdx.x - 64;                   // 0 .. 127 among the epilogue threads
@@ -476,10 +490,12 @@ static int launch_swapab(const CUtensorMap& map_w, const CUtensorMap& map_x, voi
   cfg.blockDim = dim3(kTcThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // (see launch_dependent in common.cuh)
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   // How many clusters of s blocks can run at once (one block per SM), asked once per s.
@@ -512,6 +528,7 @@ static int launch_swapab(const CUtensorMap& map_w, const CUtensorMap& map_x, voi
   const int clusters = tiles < clusters_of(splits) ? tiles : clusters_of(splits);
   attr[0].val.clusterDim.x = (unsigned)splits;
   cfg.gridDim = dim3((unsigned)(clusters * splits));
+  cfg.numAttrs = dependent_launch_flag() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, (TOut*)out, M, N, K, ldo, error_word);
   if (e != cudaSuccess) return (int)e;
   TIB_LAUNCH_CHECK();

@@ -79,26 +79,43 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], f
   }
 }
 
-// grid: (heads, n_entries), D threads.
+// grid: (heads, n_entries), D threads.  The weights of the parts are computed first (one load per part,
+// all in flight together), then every thread sums its output element with several loads in flight.
 template <int D>
 __global__ void __launch_bounds__(D)
 decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                     __nv_bfloat16* __restrict__ out, const int* __restrict__ q_start, int heads, int num_splits) {
+  pdl_wait();   // (returns at once when the launch was an ordinary one)
+  pdl_trigger();
+  extern __shared__ float merge_w[];     // [num_splits] weights, then 1 / sum
   const int entry = blockIdx.y, head = blockIdx.x;
   const int row0 = q_start[entry];
   if (q_start[entry + 1] - row0 != 1) return;
   const size_t base_slot = ((size_t)entry * heads + head) * num_splits;
-  float mm = -CUDART_INF_F;
-  for (int s = 0; s < num_splits; ++s) mm = fmaxf(mm, partial_ml[(base_slot + s) * 2]);
-  float acc = 0.f, sum = 0.f;
-  for (int s = 0; s < num_splits; ++s) {
-    const float ms = partial_ml[(base_slot + s) * 2];
-    if (ms == -CUDART_INF_F) continue;  // an empty split wrote no output
-    const float wgt = exp2f(ms - mm);
-    acc += partial_o[(base_slot + s) * D + threadIdx.x] * wgt;
-    sum += partial_ml[(base_slot + s) * 2 + 1] * wgt;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float mm = -CUDART_INF_F;
+    for (int s = lane; s < num_splits; s += 32) mm = fmaxf(mm, partial_ml[(base_slot + s) * 2]);
+    mm = warp_max(mm);
+    float sum = 0.f;
+    for (int s = lane; s < num_splits; s += 32) {
+      const float ms = partial_ml[(base_slot + s) * 2];
+      const float w = ms == -CUDART_INF_F ? 0.f : exp2f(ms - mm);   // an empty part wrote no output
+      merge_w[s] = w;
+      sum += w == 0.f ? 0.f : w * partial_ml[(base_slot + s) * 2 + 1];
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) merge_w[num_splits] = 1.f / sum;
   }
-  out[(size_t)row0 * heads * D + head * D + threadIdx.x] = __float2bfloat16_rn(acc / sum);
+  __syncthreads();
+  const float* po = partial_o + base_slot * D + threadIdx.x;
+  float acc = 0.f;
+#pragma unroll 8
+  for (int s = 0; s < num_splits; ++s) {
+    const float w = merge_w[s];
+    acc += w == 0.f ? 0.f : w * po[(size_t)s * D];
+  }
+  out[(size_t)row0 * heads * D + head * D + threadIdx.x] = __float2bfloat16_rn(acc * merge_w[num_splits]);
 }
 
 }  // namespace tib

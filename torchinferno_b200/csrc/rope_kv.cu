@@ -25,6 +25,8 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
                                    int head_dim, int rot_dim, int interleaved, int page_size,
                                    int64_t page_stride, int num_pages, int write_kv,
                                    int* __restrict__ error_word) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
   const int tok = blockIdx.x;
   const int pos = positions[tok];
@@ -101,6 +103,8 @@ rope_append_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
                           int table_stride, const float* __restrict__ inv_freq, int heads, int kv_heads,
                           int head_dim, int page_size, int64_t page_stride, int num_pages, int write_kv,
                           int* __restrict__ error_word) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ float cs[];  // cos[d/2], sin[d/2]
   const int tok = blockIdx.x;
   const int pos = positions[tok];
@@ -181,17 +185,17 @@ TIB_API int tib_rope_append(const void* qkv, void* q_out, void* pool, const int*
   const size_t smem = (size_t)rot_dim * sizeof(float);
   if (smem > 48 * 1024) return TIB_E_SMEM;
   if (dtype == TIB_F32)
-    rope_append_kernel<float><<<n_tokens, threads, smem, stream>>>(
+    TIB_LAUNCH_DEPENDENT(rope_append_kernel<float>, n_tokens, threads, smem, stream,
         (const float*)qkv, (float*)q_out, (float*)pool, positions, token_slot, block_table,
         table_stride, inv_freq, heads, kv_heads, head_dim, rot_dim, interleaved, page_size,
         page_stride, num_pages, write_kv, error_word);
   else if (dtype == TIB_BF16 && rot_dim == head_dim && !interleaved && head_dim % 16 == 0 &&
            (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pool) & 15) == 0 && (page_stride % 8 == 0 || !write_kv))
-    rope_append_bf16x8_kernel<<<n_tokens, threads, smem, stream>>>(
+    TIB_LAUNCH_DEPENDENT(rope_append_bf16x8_kernel, n_tokens, threads, smem, stream,
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, positions, token_slot, block_table,
         table_stride, inv_freq, heads, kv_heads, head_dim, page_size, page_stride, num_pages, write_kv, error_word);
   else if (dtype == TIB_BF16)
-    rope_append_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(
+    TIB_LAUNCH_DEPENDENT(rope_append_kernel<__nv_bfloat16>, n_tokens, threads, smem, stream,
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, positions,
         token_slot, block_table, table_stride, inv_freq, heads, kv_heads, head_dim, rot_dim,
         interleaved, page_size, page_stride, num_pages, write_kv, error_word);

@@ -44,6 +44,8 @@ __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, int64_t row_stride, const float* __restrict__ temperature,
               const int64_t* __restrict__ seeds, const int* __restrict__ positions,
               int* __restrict__ out, int vocab) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float sv[32];
   __shared__ int si[32];
   const int row = blockIdx.x;
@@ -99,7 +101,7 @@ TIB_API int tib_sample(const float* logits, int64_t row_stride, const float* tem
   if (!logits || !out || n_rows < 0 || vocab < 1) return TIB_E_ARG;
   int threads = 1024;
   while (threads > 32 && threads / 2 >= vocab) threads /= 2;
-  sample_kernel<<<n_rows, threads, 0, stream>>>(logits, row_stride, temperature, seeds, positions, out, vocab);
+  TIB_LAUNCH_DEPENDENT(sample_kernel, n_rows, threads, 0, stream, logits, row_stride, temperature, seeds, positions, out, vocab);
   TIB_LAUNCH_CHECK();
   return TIB_OK;
 }

@@ -13,10 +13,12 @@ import torch
 from torchinferno_b200.kernels import ops
 
 # Which kernel multiplies bf16 operands:
-#   "auto"     whichever measured faster inside the engine's steps on the B200.  Today that is cuBLAS
-#              for every shape of the model (the swap-AB kernel ties it in isolation at up to 16 rows
-#              but costs about 10 us more per layer inside a captured decode step), so SWAPAB_AUTO_ROWS
-#              is 0; the hand-written kernels are chosen with "tcgen05"
+#   "auto"     whichever measured faster inside the engine's steps on the B200.  Inside a captured decode
+#              step of the 8B sizes at 8 rows (us, hand-written swap-AB / cuBLAS, time after the kernel
+#              before has ended): qkv 12.5 / 9.9, o 9.2 / 12.1, gate_up 40.7 / 36.3, down 23.3 / 21.9.
+#              So a weight may say that it wants the swap-AB kernel for few rows
+#              (LinearWeight(few_rows_tcgen05=True): the attention output projection does); everything
+#              else goes to cuBLAS (SWAPAB_AUTO_ROWS = 0).  All hand-written kernels: "tcgen05"
 #   "tcgen05"  the hand-written kernels wherever they take the shape (swap-AB up to 64 rows, the
 #              128 x 256-tile kernel above)
 #   "library"  cuBLAS everywhere
@@ -52,10 +54,13 @@ class LinearWeight:
     (src/torchinferno/models/llama3/tensor_parallel.py:11201-11239).  Only one layout is kept.
     """
 
-    def __init__(self, weight: torch.Tensor, *, allow_transpose: bool = True) -> None:
+    FEW_ROWS = 16      # up to this many rows a weight with few_rows_tcgen05 goes to the swap-AB kernel under "auto"
+
+    def __init__(self, weight: torch.Tensor, *, allow_transpose: bool = True, few_rows_tcgen05: bool = False) -> None:
         self.out_features, self.in_features = weight.shape
-        self.transposed = bool(allow_transpose and weight.dtype == torch.bfloat16 and weight.is_cuda
-                               and _backend != "tcgen05")
+        self.few_rows_tcgen05 = bool(few_rows_tcgen05 and weight.dtype == torch.bfloat16 and weight.is_cuda)
+        self.transposed = bool(allow_transpose and not self.few_rows_tcgen05 and weight.dtype == torch.bfloat16
+                               and weight.is_cuda and _backend != "tcgen05")
         self.tensor = weight.t().contiguous() if self.transposed else weight.contiguous()
 
     @property
@@ -66,6 +71,7 @@ class LinearWeight:
         """The projection onto output features start .. stop-1 (a view, nothing is copied)."""
         view = object.__new__(LinearWeight)
         view.out_features, view.in_features, view.transposed = stop - start, self.in_features, self.transposed
+        view.few_rows_tcgen05 = self.few_rows_tcgen05
         view.tensor = self.tensor[:, start:stop] if self.transposed else self.tensor[start:stop]
         return view
 
@@ -76,9 +82,11 @@ class LinearWeight:
 def linear(x: torch.Tensor, weight: "torch.Tensor | LinearWeight", *, out_dtype: torch.dtype | None = None,
            out: torch.Tensor | None = None) -> torch.Tensor:
     """``x``: [tokens, in]; ``weight``: [out, in] (or a :class:`LinearWeight`); returns [tokens, out] in ``out_dtype``."""
+    few_rows = 0
     if isinstance(weight, LinearWeight):
         if weight.transposed:
             return _linear_library_kn(x, weight.tensor, out_dtype or x.dtype, out)
+        few_rows = LinearWeight.FEW_ROWS if weight.few_rows_tcgen05 else 0
         weight = weight.tensor
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
         raise ops.KernelError(f"linear: shapes {tuple(x.shape)} and {tuple(weight.shape)} do not fit")
@@ -96,7 +104,7 @@ def linear(x: torch.Tensor, weight: "torch.Tensor | LinearWeight", *, out_dtype:
         return ops.cast(target, result)
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise ops.KernelError(f"linear: unsupported dtypes {x.dtype} / {weight.dtype}")
-    return _linear_bf16(x, weight, out_dtype, out)
+    return _linear_bf16(x, weight, out_dtype, out, few_rows)
 
 
 def _linear_library_kn(x: torch.Tensor, weight_kn: torch.Tensor, out_dtype: torch.dtype,
@@ -119,11 +127,11 @@ def _linear_library_kn(x: torch.Tensor, weight_kn: torch.Tensor, out_dtype: torc
 
 
 def _linear_bf16(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
-                 out: torch.Tensor | None) -> torch.Tensor:
+                 out: torch.Tensor | None, few_rows: int = 0) -> torch.Tensor:
     m, n = x.shape[0], weight.shape[0]
     k = x.shape[1]
     if _backend != "library" and out_dtype in (torch.bfloat16, torch.float32):
-        rows = SWAPAB_AUTO_ROWS if _backend == "auto" else 64
+        rows = max(SWAPAB_AUTO_ROWS, few_rows) if _backend == "auto" else 64
         aligned = x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
         if aligned and m <= rows and ops.gemm_tcgen05_swapab_supports(m, n, k):
             if out is None or out.dtype != out_dtype:

@@ -33,6 +33,13 @@ class KernelError(RuntimeError):
 _counter = {"launches": 0}
 
 
+def set_dependent_launch(on: bool) -> bool:
+    """Programmatic dependent launch of the library's small kernels (on by default): a kernel may be placed on
+    the SMs while the one before it drains and waits there for its data.  Returns the setting before.  A
+    captured graph keeps what was set when it was captured."""
+    return bool(lib().tib_set_dependent_launch(c_int(1 if on else 0)))
+
+
 def launch_count() -> int:
     """How many kernels of this library were launched by this process so far."""
     return _counter["launches"]
@@ -83,7 +90,7 @@ def lib() -> ctypes.CDLL:
                    "tib_scatter_i32", "tib_advance_decode", "tib_rope_append", "tib_paged_attention_simt", "tib_gemm_f32", "tib_sample",
                    "tib_attention_mma_supports", "tib_prefill_attention", "tib_decode_attention",
                    "tib_prefill_attention_tcgen05", "tib_prefill_attention_tcgen05_supports",
-                   "tib_decode_attention_tma", "tib_decode_attention_tma_supports",
+                   "tib_decode_attention_tma", "tib_decode_attention_tma_supports", "tib_set_dependent_launch",
                    "tib_gemm_skinny", "tib_gemm_skinny_supports", "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
                    "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports"):
             getattr(library, fn).restype = c_int
@@ -321,12 +328,12 @@ def decode_split(n_entries: int, heads: int, kv_heads: int, max_kv_len: int, tar
     return -(-tiles // per), per * 64
 
 
-def decode_num_splits(n_entries: int, heads: int, kv_heads: int, target_blocks: int = 256, most: int = 32) -> int:
+def decode_num_splits(n_entries: int, heads: int, kv_heads: int, target_blocks: int = 256, most: int = 16) -> int:
     """How many parts each request's context is cut into when the kernel sizes the parts itself.
 
     Measured on the B200 at 3,072 tokens of context (32 heads, 8 kv heads of 128): the kernel is fastest
-    with about 256 blocks in all, just under the two per SM that fit (batch 1: 16 or more splits, 4: 8,
-    8: 4, 16: 2, 32 and up: 1)."""
+    with about 256 blocks in all, just under the two per SM that fit (batch 1: 16 splits, 2: 8 to 16, 4: 8,
+    8: 4, 16: 2, 32 and up: 1); more parts than 16 cost more in the merge than they gain."""
     group = heads // kv_heads
     blocks = max(1, n_entries * kv_heads * ((group + 15) // 16))
     return max(1, min(most, target_blocks // blocks))
@@ -376,7 +383,8 @@ def decode_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_s
             _ptr(q), _ptr(pool), _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), _ptr(q_start), _ptr(kv_start), _ptr(slots),
             _ptr(block_table), c_int(block_table.stride(0)), c_int(n_entries), c_int(heads), c_int(kv_heads), c_int(head_dim),
             c_int(pool.shape[3]), c_int64(pool.stride(0)), c_int(pool.shape[0]), c_int(window), c_float(scale),
-            c_int(num_splits), c_int(chunk), _ptr(error_word), _stream()))
+            c_int(num_splits), c_int(chunk), _ptr(_split_counters(q.device, n_entries * kv_heads) if num_splits > 1 else None),
+            _ptr(error_word), _stream()))
         return out
     _check("decode_attention", lib().tib_decode_attention(
         _ptr(q), _ptr(pool), _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), _ptr(q_start), _ptr(kv_start), _ptr(slots),
@@ -384,6 +392,21 @@ def decode_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_s
         c_int(pool.shape[3]), c_int64(pool.stride(0)), c_int(pool.shape[0]), c_int(window), c_float(scale),
         c_int(num_splits), c_int(chunk), _stream()))
     return out
+
+
+_counters: dict[torch.device, torch.Tensor] = {}
+_COUNTERS = 65536     # allocated once per device, outside any graph capture that may come later
+
+
+def _split_counters(device: torch.device, n: int) -> torch.Tensor | None:
+    """Zeroed ints in which the parts of a split context count themselves in (the kernel leaves them zero).
+    One buffer per device: launches on one stream follow one another."""
+    if n > _COUNTERS:
+        return None            # (the kernel then merges with a second launch)
+    have = _counters.get(device)
+    if have is None:
+        have = _counters[device] = torch.zeros(_COUNTERS, dtype=torch.int32, device=device)
+    return have
 
 
 def decode_attention_tma_supports(head_dim: int, group: int, page_size: int) -> bool:

@@ -52,7 +52,9 @@ class GQAAttention(Mixer):
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         q, k, v, o = self.names
         self.qkv_weight = LinearWeight(torch.cat([weights[q], weights[k], weights[v]], dim=0))
-        self.o_weight = LinearWeight(weights[o], allow_transpose=False)   # (cuBLAS is no faster on [in, out] here)
+        # (at few rows the hand-written swap-AB kernel is ahead of cuBLAS on this shape, and starts to fetch the
+        # weights while the attention kernel drains)
+        self.o_weight = LinearWeight(weights[o], few_rows_tcgen05=True)
 
     def cache_spec(self) -> CacheSpec:
         return CacheSpec(self.kv_heads, self.head_dim, self.window)
