@@ -4,6 +4,7 @@
     python -m torchinferno_b200.bench_kernels prefill-attention --tokens 2048
     python -m torchinferno_b200.bench_kernels gemm --rows 8
     python -m torchinferno_b200.bench_kernels elementwise --rows 2048
+    python -m torchinferno_b200.bench_kernels step-timeline --layers 32 --batch 8 --context 3072
 
 Each run prints one JSON line per case: microseconds (median of CUDA-event timings, an L2 flush
 between iterations), the bytes or flops the kernel has to move or do, and the fraction of the
@@ -159,6 +160,63 @@ def run_elementwise(args) -> None:
            bytes_moved=rows * ((h + 2 * k) * d * 2 + (h + 2 * k) * d * 2), rows=rows)
 
 
+def run_step_timeline(args) -> None:
+    """Which kernels a captured decode step spends its time in: every kernel of one step with its start and
+    duration as the driver's activity records (CUPTI, through torch.profiler) give them, summed by kernel,
+    and one layer listed launch by launch (a negative gap: the kernel was placed before the one before it
+    had ended, by programmatic dependent launch, and its duration includes the wait)."""
+    import collections
+    from torch.profiler import ProfilerActivity, profile
+    from torchinferno_b200.engine.batch import StepEntry
+    from torchinferno_b200.engine.factory import make_runner, random_model
+    from torchinferno_b200.kernels import gemm
+    gemm.set_backend(args.gemm_backend)
+    config = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": args.vocab, "hidden_size": args.hidden,
+              "intermediate_size": args.intermediate, "num_hidden_layers": args.layers, "num_attention_heads": args.heads,
+              "num_key_value_heads": args.kv_heads, "head_dim": args.head_dim, "max_position_embeddings": 131072,
+              "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False}
+    model = random_model(config, seed=0, dtype="bfloat16")
+    n, ctx = args.batch, args.context
+    runner = make_runner(model, page_size=args.page_size, max_tokens=n * (ctx + 64), max_requests=n, check_errors=False)
+    prompts = torch.randint(0, args.vocab, (n, ctx), generator=torch.Generator().manual_seed(0)).tolist()
+    for i, prompt in enumerate(prompts):
+        runner.step([StepEntry(i, prompt, [ctx - 1])])
+    step = lambda: runner.step([StepEntry(i, [5], [0]) for i in range(n)])
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize()
+    if args.plain:           # (for a launch list under ncu: no second profiler in the process)
+        for _ in range(args.iters):
+            step()
+        torch.cuda.synchronize()
+        print(json.dumps({"steps": args.iters, "batch": n, "context": ctx, "layers": args.layers}))
+        return
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+    kernels = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and e.time_range.end > e.time_range.start),
+                     key=lambda e: e.time_range.start)
+    last = kernels[-(len(kernels) // 3):]
+    t0, t1 = last[0].time_range.start, max(e.time_range.end for e in last)
+    total = collections.defaultdict(lambda: [0, 0.0])
+    for e in last:
+        total[e.name[:64]][0] += 1
+        total[e.name[:64]][1] += e.time_range.end - e.time_range.start
+    print(json.dumps({"step_us": round(t1 - t0, 1), "kernels": len(last), "batch": n, "context": ctx, "layers": args.layers,
+                      "gemm_backend": args.gemm_backend}))
+    for name, (count, us) in sorted(total.items(), key=lambda kv: -kv[1][1]):
+        print(f"{us:9.1f} us  x{count:4d}  avg {us / count:7.2f}  {name}")
+    print("one layer, launch by launch (gap to the end of the kernel before, duration):")
+    per_layer = max(1, (len(last) - 3) // max(1, args.layers))
+    mid = len(last) // 2
+    end = None
+    for e in last[mid:mid + per_layer + 2]:
+        gap = 0.0 if end is None else e.time_range.start - end
+        print(f"  gap {gap:7.2f}  dur {e.time_range.end - e.time_range.start:7.2f}  {e.name[:70]}")
+        end = e.time_range.end
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="python -m torchinferno_b200.bench_kernels", description=__doc__.splitlines()[0])
     sub = parser.add_subparsers(dest="command", required=True)
@@ -192,6 +250,17 @@ def main(argv=None) -> int:
     p.add_argument("--intermediate", type=int, default=14336)
     common(p)
     p.set_defaults(func=run_elementwise)
+    p = sub.add_parser("step-timeline")
+    p.add_argument("--layers", type=int, default=32)
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=3072)
+    p.add_argument("--hidden", type=int, default=4096)
+    p.add_argument("--intermediate", type=int, default=14336)
+    p.add_argument("--vocab", type=int, default=128256)
+    p.add_argument("--gemm-backend", choices=["auto", "tcgen05", "library"], default="auto")
+    p.add_argument("--plain", action="store_true", help="run the steps without the activity profiler (for ncu)")
+    common(p)
+    p.set_defaults(func=run_step_timeline, iters=3)
     args = parser.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("bench_kernels needs a CUDA device")
