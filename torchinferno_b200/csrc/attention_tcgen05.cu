@@ -4,11 +4,12 @@
 // tiles of 128 up to the causal edge.  Per tile:
 //   S = Q . K^T      `tcgen05.mma` (M 128, N 128, K = head_dim), both operands K-major in 128-byte-
 //                    swizzled shared memory, accumulator S in TMEM (128 columns)
-//   softmax          four warps, one thread per row: `tcgen05.ld` S, mask, running max / sum in fp32,
-//                    P as bf16 into shared memory (the A operand of the next product), O in TMEM
-//                    rescaled with `tcgen05.ld` / `tcgen05.st` when a row's maximum moved
-//   O += P . V       `tcgen05.mma` (M 128, N = head_dim, K = 128 keys); V is used as it lies in the
-//                    cache ([key][head_dim]: an MN-major B operand)
+//   softmax          eight warps, two threads per row, each with 64 keys of the tile and a running max / sum
+//                    (fp32) and an output accumulator of its own: `tcgen05.ld` S, mask, P as bf16 into
+//                    shared memory (the A operand of the next product), O_half in TMEM rescaled with
+//                    `tcgen05.ld` / `tcgen05.st` when the row's maximum moved; merged exactly at the end
+//   O_h += P_h . V_h `tcgen05.mma` (M 128, N = head_dim, K = 64 keys per half); V is used as it lies in
+//                    the cache ([key][head_dim]: an MN-major B operand)
 // Warp 0 (one lane) is the TMA producer: Q by one 3-D tile copy (dims: head_dim, head, token), K and
 // V page by page through a 2-D view of the layer's pages ([page rows, head_dim]); pages past the
 // block's last query are fetched from an out-of-range coordinate, which fills zeros.  Warp 1 (one
@@ -48,8 +49,7 @@ struct FaSmem {
   static constexpr uint32_t kQ = kFaBM * D * 2;          // two sub-tiles of [128 rows][64] when D = 128
   static constexpr uint32_t kKV = kFaBN * D * 2;         // one K or V tile
   static constexpr uint32_t kP = kFaBM * kFaBN * 2;      // two sub-tiles of [128 rows][64 keys]
-  static constexpr uint32_t kExchange = 2 * 128 * 4;     // row maxima / sums passed between the two halves
-  static constexpr uint32_t kTotal = 1024 + kQ + kFaStages * 2 * kKV + 2 * kP + kExchange + 256;
+  static constexpr uint32_t kTotal = 1024 + kQ + kFaStages * 2 * kKV + 2 * kP + 256;
 };
 
 template <int D>
@@ -65,16 +65,19 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   auto k_s = [&](int s) { return base + L::kQ + s * 2 * L::kKV; };
   auto v_s = [&](int s) { return base + L::kQ + s * 2 * L::kKV + L::kKV; };
   const uint32_t p_s = base + L::kQ + kFaStages * 2 * L::kKV;
-  const uint32_t xch_s = p_s + 2 * L::kP;                  // (two P buffers alternate)
-  const uint32_t bars = xch_s + L::kExchange;
+  const uint32_t bars = p_s + 2 * L::kP;                   // (two P buffers alternate)
   const uint32_t q_full = bars;
-  auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bars + 8u * (1 + kFaStages + s); };
-  auto s_full = [&](int b) { return bars + 8u * (1 + 2 * kFaStages + b); };
-  auto p_full = [&](int b) { return bars + 8u * (3 + 2 * kFaStages + b); };
-  const uint32_t pv_done = bars + 8u * (5 + 2 * kFaStages);
-  const uint32_t o_final = bars + 8u * (6 + 2 * kFaStages);
-  const uint32_t tmem_slot = bars + 8u * (7 + 2 * kFaStages);
+  // keys and values have rings of their own: a key stage is free again once S of its tile is computed,
+  // long before the values of that tile are used, so the next keys arrive a tile earlier
+  auto k_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bars + 8u * (1 + kFaStages + s); };
+  auto v_full = [&](int s) { return bars + 8u * (1 + 2 * kFaStages + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (1 + 3 * kFaStages + s); };
+  auto s_full = [&](int b) { return bars + 8u * (1 + 4 * kFaStages + b); };
+  auto p_full = [&](int b) { return bars + 8u * (3 + 4 * kFaStages + b); };
+  const uint32_t pv_done = bars + 8u * (5 + 4 * kFaStages);
+  const uint32_t o_final = bars + 8u * (6 + 4 * kFaStages);
+  const uint32_t tmem_slot = bars + 8u * (7 + 4 * kFaStages);
   unsigned char* smem_gen = smem_raw + (base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - base));
 
@@ -95,13 +98,15 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int kt0 = first_key / kFaBN, kt1 = last_pos / kFaBN;
   const int n_tiles = kt1 - kt0 + 1;
   const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
-  constexpr uint32_t kTmemCols = 512;                    // S (two buffers): columns 0..255, O: columns 256..256+D-1
+  constexpr uint32_t kTmemCols = 512;                    // S (two buffers): columns 0..255; O_0, O_1: D columns each from 256
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < kFaStages; ++s) {
-      mbar_init(kv_full(s), 1);
-      mbar_init(kv_empty(s), 1);
+      mbar_init(k_full(s), 1);
+      mbar_init(k_empty(s), 1);
+      mbar_init(v_full(s), 1);
+      mbar_init(v_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(s_full(b), 1);
@@ -140,24 +145,32 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       const int kp = key0 + lane * a.page_size;
       int page = -1;
       if (lane < pages_per_tile && kp <= last_pos && kp + a.page_size > first_key) page = __ldg(table + (kp >> a.page_shift));
+      const bool have = page >= 0 && page < a.num_pages;
+      const uint32_t off = (uint32_t)(lane * a.page_size) * 128u;        // rows of 128 bytes in a sub-tile
       int ok = 1;
       if (lane == 0) {
-        ok = mbar_wait(kv_empty(s), phase ^ 1) ? 1 : 0;
+        ok = mbar_wait(k_empty(s), phase ^ 1) ? 1 : 0;
         if (!ok && a.error_word) atomicExch(a.error_word, 0x7C0021);
-        if (ok) mbar_expect_tx(kv_full(s), 2 * L::kKV);
+        if (ok) mbar_expect_tx(k_full(s), L::kKV);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (lane < pages_per_tile) {
-        const bool have = page >= 0 && page < a.num_pages;
         const int krow = have ? ((page * 2 + 0) * a.kv_heads + kvh) * a.page_size : oob_row;
-        const int vrow = have ? ((page * 2 + 1) * a.kv_heads + kvh) * a.page_size : oob_row;
-        const uint32_t off = (uint32_t)(lane * a.page_size) * 128u;      // rows of 128 bytes in a sub-tile
 #pragma unroll
-        for (int h = 0; h < DH; ++h) {
-          tma_load_2d(k_s(s) + h * kSub + off, &map_kv, h * 64, krow, kv_full(s));
-          tma_load_2d(v_s(s) + h * kSub + off, &map_kv, h * 64, vrow, kv_full(s));
-        }
+        for (int h = 0; h < DH; ++h) tma_load_2d(k_s(s) + h * kSub + off, &map_kv, h * 64, krow, k_full(s));
+      }
+      if (lane == 0) {
+        ok = mbar_wait(v_empty(s), phase ^ 1) ? 1 : 0;
+        if (!ok && a.error_word) atomicExch(a.error_word, 0x7C0028);
+        if (ok) mbar_expect_tx(v_full(s), L::kKV);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < pages_per_tile) {
+        const int vrow = have ? ((page * 2 + 1) * a.kv_heads + kvh) * a.page_size : oob_row;
+#pragma unroll
+        for (int h = 0; h < DH; ++h) tma_load_2d(v_s(s) + h * kSub + off, &map_kv, h * 64, vrow, v_full(s));
       }
       __syncwarp();
     }
@@ -171,19 +184,25 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       // O += P . V of tile `j` (its V in stage j % stages, its P in buffer j & 1)
       auto issue_pv = [&](int j) {
         const int s = j % kFaStages;
+        if (!mbar_wait(v_full(s), (j / kFaStages) & 1)) {
+          if (a.error_word) atomicExch(a.error_word, 0x7C0029);
+          return;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
         for (int kk = 0; kk < kFaBN / 16; ++kk) {
           const uint32_t psub = (kk >> 2) * kSub, pinner = (kk & 3) * 32;
-          umma_f16_idesc(tmem_o, umma_desc_k128(p_s + (j & 1) * L::kP + psub + pinner),
-                         umma_desc_mn128(v_s(s) + kk * 16 * 128, kSub), idesc_o, (j | kk) != 0);
+          // keys 0..63 of the tile go to O_0, keys 64..127 to O_1 (the two halves of a row keep apart)
+          umma_f16_idesc(tmem_o + (kk >> 2) * D, umma_desc_k128(p_s + (j & 1) * L::kP + psub + pinner),
+                         umma_desc_mn128(v_s(s) + kk * 16 * 128, kSub), idesc_o, (j | (kk & 3)) != 0);
         }
-        umma_commit(kv_empty(s));   // the stage goes back to the producer
+        umma_commit(v_empty(s));    // the value stage goes back to the producer
         umma_commit(pv_done);       // O is at rest again
       };
       for (int it = 0; it < n_tiles && ok; ++it) {
         const int s = it % kFaStages;
         const uint32_t phase = (it / kFaStages) & 1;
-        if (!mbar_wait(kv_full(s), phase)) {
+        if (!mbar_wait(k_full(s), phase)) {
           if (a.error_word) atomicExch(a.error_word, 0x7C0023);
           ok = false;
           break;
@@ -197,6 +216,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           umma_f16_idesc(tmem_s + (it & 1) * kFaBN, umma_desc_k128(q_s + sub + inner), umma_desc_k128(k_s(s) + sub + inner),
                          idesc_s, kk != 0);
         }
+        umma_commit(k_empty(s));    // the key stage goes back to the producer
         umma_commit(s_full(it & 1));
         if (it > 0) {
           // P of the tile before (and the rescaled O) are ready: O += P . V
@@ -221,16 +241,18 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       umma_commit(o_final);
     }
   } else {
-    // softmax and epilogue: two threads per row; `half` 0 takes keys (and output dims) 0..63 of a tile,
-    // half 1 the rest.  The halves exchange their row maxima through shared memory once per tile.
+    // softmax and epilogue: two threads per row.  `half` 0 takes keys 0..63 of every tile, half 1 keys
+    // 64..127, each with a running maximum, a sum and an output accumulator (O_half in TMEM) of its own, as
+    // if the keys were split between two workers: nothing passes between the two threads of a row until the
+    // end, where the two partial results are merged exactly.
     const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     const int qpos = r < nrows ? pos0 + r / a.group : last_pos;
     constexpr int HC = kFaBN / 2;                          // score columns per thread
-    constexpr int OC = D / 2;                              // output columns per thread
-    float m = -CUDART_INF_F, l = 0.f;                      // m in log2 units (scaled); l: this half's share of the sum
-    float* xch = reinterpret_cast<float*>(smem_gen + (xch_s - base));   // [2][128]
+    constexpr int OC = D / 2;                              // output columns per thread in the epilogue
+    const uint32_t tmem_mine = tmem_o + half * D;          // O_half
+    float m = -CUDART_INF_F, l = 0.f;                      // of this half's keys; m in log2 units (scaled)
     unsigned char* p_row0 = smem_gen + (p_s - base) + half * kSub + r * 128;
     bool ok = true;                                        // after a timeout the loop keeps its barriers but does no work
     for (int it = 0; it < n_tiles; ++it) {
@@ -242,49 +264,34 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const int key_base = (kt0 + it) * kFaBN + half * HC;
       const bool need_mask = key_base + HC - 1 > pos0 || (a.window > 0 && key_base < last_pos - a.window + 1);
-      float sv[HC];
-      float mx = -CUDART_INF_F;
       if (ok) {
+        uint32_t sv[HC];
+        {
+          uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[0]);
+          uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[32]);
+          tmem_ld32(tmem_s + lane_sel + (it & 1) * kFaBN + half * HC, lo);
+          tmem_ld32(tmem_s + lane_sel + (it & 1) * kFaBN + half * HC + 32, hi);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        }
+        float mx = -CUDART_INF_F;
         // two copies of the loop, so that tiles wholly inside the causal triangle pay nothing for the mask
         if (need_mask) {
 #pragma unroll
-          for (int c = 0; c < HC / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld32(tmem_s + lane_sel + (it & 1) * kFaBN + half * HC + c * 32, v);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int key = key_base + c * 32 + j;
-              const bool allowed = key <= qpos && (a.window <= 0 || key > qpos - a.window);
-              const float x = allowed ? __uint_as_float(v[j]) : -CUDART_INF_F;
-              sv[c * 32 + j] = x;
-              mx = fmaxf(mx, x);
-            }
+          for (int j = 0; j < HC; ++j) {
+            const int key = key_base + j;
+            const bool allowed = key <= qpos && (a.window <= 0 || key > qpos - a.window);
+            if (!allowed) sv[j] = __float_as_uint(-CUDART_INF_F);
+            mx = fmaxf(mx, __uint_as_float(sv[j]));
           }
         } else {
 #pragma unroll
-          for (int c = 0; c < HC / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld32(tmem_s + lane_sel + (it & 1) * kFaBN + half * HC + c * 32, v);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              sv[c * 32 + j] = __uint_as_float(v[j]);
-              mx = fmaxf(mx, sv[c * 32 + j]);
-            }
-          }
+          for (int j = 0; j < HC; ++j) mx = fmaxf(mx, __uint_as_float(sv[j]));
         }
-      }
-      xch[half * 128 + r] = mx;
-      asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kFaSoftmaxWarps) : "memory");
-      mx = fmaxf(mx, xch[(half ^ 1) * 128 + r]);
-      asm volatile("bar.sync 2, %0;\n" ::"n"(32 * kFaSoftmaxWarps) : "memory");   // (the slots may be rewritten next tile)
-      const float m_new = fmaxf(m, mx == -CUDART_INF_F ? -CUDART_INF_F : mx * a.scale_log2);
-      const float basev = m_new == -CUDART_INF_F ? 0.f : m_new;
-      float alpha;
-      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(alpha) : "f"(m - basev));
-      m = m_new;
-      if (ok) {
+        const float m_new = fmaxf(m, mx == -CUDART_INF_F ? -CUDART_INF_F : mx * a.scale_log2);
+        const float basev = m_new == -CUDART_INF_F ? 0.f : m_new;
+        float alpha;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(alpha) : "f"(m - basev));
+        m = m_new;
         float sum = 0.f;
         // P (bf16) into shared memory, in the swizzled K-major layout of an MMA A operand
 #pragma unroll
@@ -294,15 +301,15 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             float e0, e1;
-            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(fmaf(sv[c8 * 8 + 2 * j], a.scale_log2, -basev)));
-            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fmaf(sv[c8 * 8 + 2 * j + 1], a.scale_log2, -basev)));
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(fmaf(__uint_as_float(sv[c8 * 8 + 2 * j]), a.scale_log2, -basev)));
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fmaf(__uint_as_float(sv[c8 * 8 + 2 * j + 1]), a.scale_log2, -basev)));
             sum += e0 + e1;
             p2[j] = __floats2bfloat162_rn(e0, e1);
           }
           *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) << 4)) = packed;
         }
         l = l * alpha + sum;
-        // O of the earlier tiles is scaled to the new maximum, once the P . V of the tile before is done
+        // O_half of the earlier tiles is scaled to the new maximum, once the P . V of the tile before is done
         if (it > 0 && !mbar_wait(pv_done, (it - 1) & 1)) {
           if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C0027);
           ok = false;
@@ -310,13 +317,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (ok && it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-          for (int c = 0; c < OC / 32; ++c) {
+          for (int c = 0; c < D / 32; ++c) {
             uint32_t v[32];
-            tmem_ld32(tmem_o + lane_sel + half * OC + c * 32, v);
+            tmem_ld32(tmem_mine + lane_sel + c * 32, v);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-            tmem_st32(tmem_o + lane_sel + half * OC + c * 32, v);
+            tmem_st32(tmem_mine + lane_sel + c * 32, v);
           }
           asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
         }
@@ -324,6 +331,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int tile_base = (kt0 + it) * kFaBN;
         if (tile_base + kFaBN - 1 > last_pos) {
           const int s = it % kFaStages;
+          if (!mbar_wait(v_full(s), (it / kFaStages) & 1)) {    // the values must have landed before rows of them are cleared
+            if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C002A);
+            ok = false;
+          }
           for (int key = max(last_pos + 1, tile_base) + (warp - 2); key < tile_base + kFaBN; key += kFaSoftmaxWarps) {
             const int kr = key - tile_base;
             for (int cb = lane; cb < D / 8; cb += 32)   // 16-byte chunks of the row (all zero, so the swizzle does not matter)
@@ -339,26 +350,34 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C0026);
       ok = false;
     }
-    // the two halves of a row add their shares of the softmax sum
-    xch[half * 128 + r] = l;
+    // The two halves of a row merge: each passes its (maximum, sum) to the other through the first P buffer,
+    // which no MMA reads any more, and takes half of the output columns.
+    float2* fin = reinterpret_cast<float2*>(smem_gen + (p_s - base));   // [2][128]
+    fin[half * 128 + r] = make_float2(m, l);
     asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kFaSoftmaxWarps) : "memory");
-    l += xch[(half ^ 1) * 128 + r];
+    const float2 other = fin[(half ^ 1) * 128 + r];
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const float inv = 1.f / l;
+      const float mm = fmaxf(m, other.x);                  // finite: every row sees at least one key
+      const float w_mine = exp2f(m - mm), w_other = exp2f(other.x - mm);
+      const float inv = 1.f / (l * w_mine + other.y * w_other);
+      const float w0 = (half == 0 ? w_mine : w_other) * inv, w1 = (half == 0 ? w_other : w_mine) * inv;
       const bool store = r < nrows;
       const int t = r / a.group, g = r - t * a.group;
       __nv_bfloat16* dst = out + (size_t)(row0 + t0 + t) * a.heads * D + (kvh * a.group + g) * D + half * OC;
 #pragma unroll
       for (int c = 0; c < OC / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tmem_o + lane_sel + half * OC + c * 32, v);
+        uint32_t v0[32], v1[32];
+        tmem_ld32(tmem_o + lane_sel + half * OC + c * 32, v0);          // O_0
+        tmem_ld32(tmem_o + D + lane_sel + half * OC + c * 32, v1);      // O_1
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
         if (store) {
           uint4 packed[4];
           __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(packed);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) p2[j] = __floats2bfloat162_rn(__uint_as_float(v[2 * j]) * inv, __uint_as_float(v[2 * j + 1]) * inv);
+          for (int j = 0; j < 16; ++j)
+            p2[j] = __floats2bfloat162_rn(__uint_as_float(v0[2 * j]) * w0 + __uint_as_float(v1[2 * j]) * w1,
+                                          __uint_as_float(v0[2 * j + 1]) * w0 + __uint_as_float(v1[2 * j + 1]) * w1);
 #pragma unroll
           for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst + c * 32)[j] = packed[j];
         }
