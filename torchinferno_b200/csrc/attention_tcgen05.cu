@@ -10,10 +10,10 @@
 //                    `tcgen05.ld` / `tcgen05.st` when the row's maximum moved; merged exactly at the end
 //   O_h += P_h . V_h `tcgen05.mma` (M 128, N = head_dim, K = 64 keys per half); V is used as it lies in
 //                    the cache ([key][head_dim]: an MN-major B operand)
-// Warp 0 (one lane) is the TMA producer: Q by one 3-D tile copy (dims: head_dim, head, token), K and
-// V page by page through a 2-D view of the layer's pages ([page rows, head_dim]); pages past the
-// block's last query are fetched from an out-of-range coordinate, which fills zeros.  Warp 1 (one
-// lane) issues the MMAs.  Every mbarrier wait is bounded; on a timeout a code goes to `error_word`
+// Warp 0 is the TMA producer of Q (one 3-D tile copy; dims: head_dim, head, token) and of K, the last
+// warp that of V, page by page through a 2-D view of the layer's pages ([page rows, head_dim]), each
+// into a ring of its own; pages past the block's last query are fetched from an out-of-range
+// coordinate, which fills zeros.  Warp 1 (one lane) issues the MMAs.  Every mbarrier wait is bounded; on a timeout a code goes to `error_word`
 // and all roles fall through to the common exit.
 //
 // Formula as in attention_mma.cu / attention_simt.cu (src/torchinferno/models/llama3/raw_ops.py:44-51).
@@ -25,7 +25,8 @@ namespace tib {
 
 constexpr int kFaBM = 128, kFaBN = 128;
 constexpr int kFaSoftmaxWarps = 8;                      // two threads per row, each with half the columns
-constexpr int kFaThreads = 64 + 32 * kFaSoftmaxWarps;
+constexpr int kFaThreads = 64 + 32 * kFaSoftmaxWarps + 32;   // key producer, MMA issuer, softmax warps, value producer
+constexpr int kFaValueWarp = 2 + kFaSoftmaxWarps;
 constexpr int kFaStages = 2;
 
 struct FaArgs {
@@ -126,10 +127,14 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const uint32_t tmem_base = *tmem_slot_ptr;
   const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 256;   // S buffer b at tmem_s + 128 b
 
-  if (warp == 0) {
-    // The whole warp produces: lane 0 waits and arms the barrier, then lane pg looks up page pg of the
-    // tile and issues its copies, so the eight table look-ups of a tile cost one latency, not eight.
-    if (lane == 0) {
+  if (warp == 0 || warp == kFaValueWarp) {
+    // Two producer warps, one for the keys (and the queries) and one for the values, each with a ring of its
+    // own: a copy of one page is one TMA instruction per 64-wide half, and at 16-token pages the issue rate of
+    // one warp (about a hundred cycles a box) would otherwise set the pace.  In each, lane 0 waits and arms the
+    // barrier, then lane pg looks up page pg of the tile and issues its copies, so the table look-ups of a
+    // tile cost one latency.
+    const bool values = warp == kFaValueWarp;
+    if (!values && lane == 0) {
       // queries: one 3-D box (64 dims, `group` heads, tok_per_tile tokens) per 64-wide half of head_dim
       mbar_expect_tx(q_full, (uint32_t)(tok_per_tile * a.group * D * 2));
 #pragma unroll
@@ -147,30 +152,20 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       if (lane < pages_per_tile && kp <= last_pos && kp + a.page_size > first_key) page = __ldg(table + (kp >> a.page_shift));
       const bool have = page >= 0 && page < a.num_pages;
       const uint32_t off = (uint32_t)(lane * a.page_size) * 128u;        // rows of 128 bytes in a sub-tile
+      const uint32_t full = values ? v_full(s) : k_full(s);
       int ok = 1;
       if (lane == 0) {
-        ok = mbar_wait(k_empty(s), phase ^ 1) ? 1 : 0;
-        if (!ok && a.error_word) atomicExch(a.error_word, 0x7C0021);
-        if (ok) mbar_expect_tx(k_full(s), L::kKV);
+        ok = mbar_wait(values ? v_empty(s) : k_empty(s), phase ^ 1) ? 1 : 0;
+        if (!ok && a.error_word) atomicExch(a.error_word, values ? 0x7C0028 : 0x7C0021);
+        if (ok) mbar_expect_tx(full, L::kKV);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (lane < pages_per_tile) {
-        const int krow = have ? ((page * 2 + 0) * a.kv_heads + kvh) * a.page_size : oob_row;
+        const int row = have ? ((page * 2 + (values ? 1 : 0)) * a.kv_heads + kvh) * a.page_size : oob_row;
+        const uint32_t dst = (values ? v_s(s) : k_s(s)) + off;
 #pragma unroll
-        for (int h = 0; h < DH; ++h) tma_load_2d(k_s(s) + h * kSub + off, &map_kv, h * 64, krow, k_full(s));
-      }
-      if (lane == 0) {
-        ok = mbar_wait(v_empty(s), phase ^ 1) ? 1 : 0;
-        if (!ok && a.error_word) atomicExch(a.error_word, 0x7C0028);
-        if (ok) mbar_expect_tx(v_full(s), L::kKV);
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      if (lane < pages_per_tile) {
-        const int vrow = have ? ((page * 2 + 1) * a.kv_heads + kvh) * a.page_size : oob_row;
-#pragma unroll
-        for (int h = 0; h < DH; ++h) tma_load_2d(v_s(s) + h * kSub + off, &map_kv, h * 64, vrow, v_full(s));
+        for (int h = 0; h < DH; ++h) tma_load_2d(dst + h * kSub, &map_kv, h * 64, row, full);
       }
       __syncwarp();
     }
