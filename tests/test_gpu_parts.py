@@ -293,3 +293,139 @@ def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped(tmp_p
     finally:
         unregister_part("mixer", "running_mean")
         unregister_architecture("ToyForCausalLM")
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_and_stepped(tmp_path):
+    """Two more parts defined here, neither known to the framework: a feed-forward that routes every token to
+    the best of three small experts (router logits and the softmax weight in 32-bit), and a position encoding
+    that scales queries by g(t) = 1.02^t and keys by 1 / g(s), so that a score is q.k g(t) / g(s).  One layer
+    has the routed feed-forward and the toy encoding, the other the dense feed-forward and no encoding: parts
+    are chosen layer by layer.  Stepped whole, in portions and mixed, against plain arithmetic."""
+    need_gpu()
+    from torchinferno_b200.config.registry import ArchitectureEntry, register_architecture, unregister_architecture
+    from torchinferno_b200.engine.batch import StepEntry
+    from torchinferno_b200.engine.factory import load_model, make_runner
+    from torchinferno_b200.kernels import ops
+    from torchinferno_b200.models.spec import BlockSpec, LayerCall, ModelSpec
+    from torchinferno_b200.parts.base import (FeedForward, PartSpec, PositionEncoding, WeightSpec, register_part,
+                                              unregister_part)
+    from torchinferno_b200.weights.random_init import write_random_model
+    EXPERTS, WIDTH, INTER, HEADS, KV, D, BASE = 3, 24, 16, 2, 1, 16, 1.02
+
+    class RoutedFeedForward(FeedForward):
+        def __init__(self, *, width, inter, experts, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.width, self.inter, self.experts = width, inter, experts
+
+        def weight_specs(self):
+            specs = [WeightSpec("router.weight", (self.experts, self.width), std=0.5)]
+            for e in range(self.experts):
+                specs += [WeightSpec(f"experts.{e}.up.weight", (self.inter, self.width), std=0.2),
+                          WeightSpec(f"experts.{e}.down.weight", (self.width, self.inter), std=0.2)]
+            return specs
+
+        def bind(self, weights):
+            self.router = weights["router.weight"].float()
+            self.up = [weights[f"experts.{e}.up.weight"].float() for e in range(self.experts)]
+            self.down = [weights[f"experts.{e}.down.weight"].float() for e in range(self.experts)]
+
+        def forward(self, x, ctx):
+            xf = x.float()
+            prob = torch.softmax(xf @ self.router.T, dim=-1)
+            weight, choice = prob.max(dim=-1)
+            out = torch.zeros_like(xf)
+            for e in range(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    out[rows] = (torch.relu(xf[rows] @ self.up[e].T) @ self.down[e].T) * weight[rows, None]
+            return out.to(x.dtype)
+
+    class GeometricScaling(PositionEncoding):
+        def __init__(self, *, head_dim, base, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.base = base
+            self.none = torch.zeros(0, dtype=torch.float32, device=device)
+
+        def encode_and_store(self, qkv, q_out, ctx, heads, kv_heads, head_dim):
+            g = torch.pow(torch.tensor(self.base, device=qkv.device), ctx.batch.positions.float())[:, None]
+            scaled = qkv.float().clone()
+            scaled[:, :heads * head_dim] *= g
+            scaled[:, heads * head_dim:(heads + kv_heads) * head_dim] /= g
+            kv = ctx.kv
+            # the framework's own kernel stores k and v in their pages (no rotation: rot_dim 0)
+            return ops.rope_append(scaled.to(qkv.dtype), q_out, kv.pool, ctx.batch.positions, ctx.batch.token_slot, kv.block_table,
+                                   self.none, heads, kv_heads, head_dim, rot_dim=0, write_kv=True, error_word=ctx.error_word)
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyConfig:
+        vocab_size: int
+
+        @classmethod
+        def from_dict(cls, data):
+            return cls(data["vocab_size"])
+
+    def build_toy(cfg):
+        norm = PartSpec("rmsnorm", {"width": WIDTH, "eps": 1e-5})
+        def attention(position):
+            return PartSpec("gqa_attention", {"hidden_size": WIDTH, "heads": HEADS, "kv_heads": KV, "head_dim": D,
+                                              "position": position}, prefix="attn.")
+        norms = {"mixer_norm": dataclasses.replace(norm, prefix="n1."), "feed_forward_norm": dataclasses.replace(norm, prefix="n2.")}
+        routed = PartSpec("prenorm", {"mixer": attention(PartSpec("geometric", {"head_dim": D, "base": BASE})),
+                                      "feed_forward": PartSpec("toy_routed", {"width": WIDTH, "inter": INTER, "experts": EXPERTS}, prefix="moe."),
+                                      **norms})
+        dense = PartSpec("prenorm", {"mixer": attention(PartSpec("none", {"head_dim": D})),
+                                     "feed_forward": PartSpec("swiglu", {"hidden_size": WIDTH, "intermediate_size": INTER}, prefix="ffn."),
+                                     **norms})
+        return ModelSpec(architecture="Toy2ForCausalLM", hidden_size=WIDTH, vocab_size=cfg.vocab_size, max_positions=256,
+                         embedding_name="emb.weight", layers=(BlockSpec(routed, "l0."), BlockSpec(dense, "l1.")),
+                         schedule=(LayerCall(0, 0), LayerCall(1, 1)),
+                         final_norm=dataclasses.replace(norm, prefix="final."), head_name="head.weight")
+
+    register_part("feed_forward", "toy_routed", RoutedFeedForward)
+    register_part("position", "geometric", GeometricScaling)
+    register_architecture(ArchitectureEntry("Toy2ForCausalLM", ToyConfig, build_toy, model_types=("toy2",)))
+    try:
+        write_random_model({"architectures": ["Toy2ForCausalLM"], "model_type": "toy2", "vocab_size": 40}, tmp_path, seed=5)
+        model = load_model(tmp_path, dtype="float32")
+        runner = make_runner(model, page_size=4, max_tokens=96, max_requests=3)
+        reqs = {"a": torch.randint(0, 40, (29,)).tolist(), "b": torch.randint(0, 40, (10,)).tolist()}
+        with torch.inference_mode():
+            whole = {k: runner.step([StepEntry(k + "w", v, list(range(len(v))))]).cpu() for k, v in reqs.items()}
+            runner.end(["aw", "bw"])
+            got = {"a": [], "b": []}
+            got["a"].append(runner.step([StepEntry("a", reqs["a"][:7], list(range(7)))]).cpu())
+            mixed = runner.step([StepEntry("b", reqs["b"][:9], list(range(9))), StepEntry("a", reqs["a"][7:8], [0])]).cpu()
+            got["b"].append(mixed[:9]), got["a"].append(mixed[9:])
+            mixed = runner.step([StepEntry("a", reqs["a"][8:], list(range(21))), StepEntry("b", reqs["b"][9:], [0])]).cpu()
+            got["a"].append(mixed[:21]), got["b"].append(mixed[21:])
+            runner.end(["a", "b"])
+        for k in reqs:
+            assert torch.allclose(torch.cat(got[k]), whole[k], atol=2e-5, rtol=1e-4)
+        _, w = plain_llama.read_model_folder(tmp_path)
+
+        def attention(x, p, g):
+            n, T = plain_llama.rms_norm(x, w[p + "n1.weight"], 1e-5), x.shape[0]
+            q = (n @ w[p + "attn.q_proj.weight"].T).view(T, HEADS, D).transpose(0, 1) * g[None, :, None]
+            k = (n @ w[p + "attn.k_proj.weight"].T).view(T, KV, D).transpose(0, 1) / g[None, :, None]
+            v = (n @ w[p + "attn.v_proj.weight"].T).view(T, KV, D).transpose(0, 1)
+            return x + plain_llama.causal_attention(q, k, v, HEADS // KV).transpose(0, 1).reshape(T, HEADS * D) @ w[p + "attn.o_proj.weight"].T
+
+        x = w["emb.weight"][torch.tensor(reqs["a"])]
+        T = x.shape[0]
+        x = attention(x, "l0.", torch.pow(torch.tensor(BASE, dtype=torch.float64), torch.arange(T, dtype=torch.float64)))
+        n = plain_llama.rms_norm(x, w["l0.n2.weight"], 1e-5)
+        prob = torch.softmax(n @ w["l0.moe.router.weight"].T, dim=-1)
+        weight, choice = prob.max(dim=-1)
+        assert len(set(choice.tolist())) > 1                       # the tokens really go to different experts
+        routed = torch.stack([(torch.relu(n[t] @ w[f"l0.moe.experts.{int(choice[t])}.up.weight"].T)
+                               @ w[f"l0.moe.experts.{int(choice[t])}.down.weight"].T) * weight[t] for t in range(T)])
+        x = x + routed
+        x = attention(x, "l1.", torch.ones(T, dtype=torch.float64))
+        x = x + plain_llama.swiglu_mlp(plain_llama.rms_norm(x, w["l1.n2.weight"], 1e-5), w["l1.ffn.gate_proj.weight"],
+                                       w["l1.ffn.up_proj.weight"], w["l1.ffn.down_proj.weight"])
+        want = plain_llama.rms_norm(x, w["final.weight"], 1e-5) @ w["head.weight"].T
+        assert torch.allclose(whole["a"].double(), want, atol=5e-5, rtol=2e-4), (whole["a"].double() - want).abs().max()
+    finally:
+        unregister_part("feed_forward", "toy_routed")
+        unregister_part("position", "geometric")
+        unregister_architecture("Toy2ForCausalLM")
