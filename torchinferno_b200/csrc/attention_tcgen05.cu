@@ -5,9 +5,9 @@
 //   S = Q . K^T      `tcgen05.mma` (M 128, N 128, K = head_dim), both operands K-major in 128-byte-
 //                    swizzled shared memory, accumulator S in TMEM (128 columns)
 //   softmax          eight warps, two threads per row, each with 64 keys of the tile and a running max / sum
-//                    (fp32) and an output accumulator of its own: `tcgen05.ld` S, mask, P as bf16 into
-//                    shared memory (the A operand of the next product), O_half in TMEM rescaled with
-//                    `tcgen05.ld` / `tcgen05.st` when the row's maximum moved; merged exactly at the end
+//                    (fp32) and an output accumulator of its own: `tcgen05.ld` S, mask, P as bf16 back
+//                    into tensor memory over S (the A operand of the next product), O_half in TMEM rescaled
+//                    with `tcgen05.ld` / `tcgen05.st` when the row's maximum moved; merged exactly at the end
 //   O_h += P_h . V_h `tcgen05.mma` (M 128, N = head_dim, K = 64 keys per half); V is used as it lies in
 //                    the cache ([key][head_dim]: an MN-major B operand)
 // Warp 0 is the TMA producer of Q (one 3-D tile copy; dims: head_dim, head, token) and of K, the last
@@ -27,7 +27,7 @@ constexpr int kFaBM = 128, kFaBN = 128;
 constexpr int kFaSoftmaxWarps = 8;                      // two threads per row, each with half the columns
 constexpr int kFaThreads = 64 + 32 * kFaSoftmaxWarps + 32;   // key producer, MMA issuer, softmax warps, value producer
 constexpr int kFaValueWarp = 2 + kFaSoftmaxWarps;
-constexpr int kFaStages = 2;
+constexpr int kFaStages = 3;
 
 struct FaArgs {
   const int* q_start;
@@ -49,8 +49,7 @@ template <int D>
 struct FaSmem {
   static constexpr uint32_t kQ = kFaBM * D * 2;          // two sub-tiles of [128 rows][64] when D = 128
   static constexpr uint32_t kKV = kFaBN * D * 2;         // one K or V tile
-  static constexpr uint32_t kP = kFaBM * kFaBN * 2;      // two sub-tiles of [128 rows][64 keys]
-  static constexpr uint32_t kTotal = 1024 + kQ + kFaStages * 2 * kKV + 2 * kP + 256;
+  static constexpr uint32_t kTotal = 1024 + kQ + kFaStages * 2 * kKV + 256;
 };
 
 template <int D>
@@ -65,8 +64,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const uint32_t q_s = base;
   auto k_s = [&](int s) { return base + L::kQ + s * 2 * L::kKV; };
   auto v_s = [&](int s) { return base + L::kQ + s * 2 * L::kKV + L::kKV; };
-  const uint32_t p_s = base + L::kQ + kFaStages * 2 * L::kKV;
-  const uint32_t bars = p_s + 2 * L::kP;                   // (two P buffers alternate)
+  const uint32_t bars = base + L::kQ + kFaStages * 2 * L::kKV;
   const uint32_t q_full = bars;
   // keys and values have rings of their own: a key stage is free again once S of its tile is computed,
   // long before the values of that tile are used, so the next keys arrive a tile earlier
@@ -186,10 +184,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
         for (int kk = 0; kk < kFaBN / 16; ++kk) {
-          const uint32_t psub = (kk >> 2) * kSub, pinner = (kk & 3) * 32;
-          // keys 0..63 of the tile go to O_0, keys 64..127 to O_1 (the two halves of a row keep apart)
-          umma_f16_idesc(tmem_o + (kk >> 2) * D, umma_desc_k128(p_s + (j & 1) * L::kP + psub + pinner),
-                         umma_desc_mn128(v_s(s) + kk * 16 * 128, kSub), idesc_o, (j | (kk & 3)) != 0);
+          // keys 0..63 of the tile go to O_0, keys 64..127 to O_1 (the two halves of a row keep apart); P is
+          // read from tensor memory, where each half left it in the first 32 columns of its part of S
+          umma_f16_tmem_a(tmem_o + (kk >> 2) * D, tmem_s + (j & 1) * kFaBN + (kk >> 2) * (kFaBN / 2) + (kk & 3) * 8,
+                          umma_desc_mn128(v_s(s) + kk * 16 * 128, kSub), idesc_o, (j | (kk & 3)) != 0);
         }
         umma_commit(v_empty(s));    // the value stage goes back to the producer
         umma_commit(pv_done);       // O is at rest again
@@ -248,10 +246,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     constexpr int OC = D / 2;                              // output columns per thread in the epilogue
     const uint32_t tmem_mine = tmem_o + half * D;          // O_half
     float m = -CUDART_INF_F, l = 0.f;                      // of this half's keys; m in log2 units (scaled)
-    unsigned char* p_row0 = smem_gen + (p_s - base) + half * kSub + r * 128;
     bool ok = true;                                        // after a timeout the loop keeps its barriers but does no work
     for (int it = 0; it < n_tiles; ++it) {
-      unsigned char* p_row = p_row0 + (it & 1) * L::kP;
       if (ok && !mbar_wait(s_full(it & 1), (it >> 1) & 1)) {
         if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C0025);
         ok = false;
@@ -288,21 +284,19 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(alpha) : "f"(m - basev));
         m = m_new;
         float sum = 0.f;
-        // P (bf16) into shared memory, in the swizzled K-major layout of an MMA A operand
+        // P (bf16, two keys to a column) goes back into tensor memory over this thread's own part of S: it is
+        // the A operand of the next product, and never passes through shared memory
+        uint32_t pk[HC / 2];
 #pragma unroll
-        for (int c8 = 0; c8 < HC / 8; ++c8) {
-          uint4 packed;
-          __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float e0, e1;
-            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(fmaf(__uint_as_float(sv[c8 * 8 + 2 * j]), a.scale_log2, -basev)));
-            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fmaf(__uint_as_float(sv[c8 * 8 + 2 * j + 1]), a.scale_log2, -basev)));
-            sum += e0 + e1;
-            p2[j] = __floats2bfloat162_rn(e0, e1);
-          }
-          *reinterpret_cast<uint4*>(p_row + ((c8 ^ (r & 7)) << 4)) = packed;
+        for (int j = 0; j < HC / 2; ++j) {
+          float e0, e1;
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(fmaf(__uint_as_float(sv[2 * j]), a.scale_log2, -basev)));
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fmaf(__uint_as_float(sv[2 * j + 1]), a.scale_log2, -basev)));
+          sum += e0 + e1;
+          const __nv_bfloat162 pair = __floats2bfloat162_rn(e0, e1);
+          pk[j] = *reinterpret_cast<const uint32_t*>(&pair);
         }
+        tmem_st32(tmem_s + lane_sel + (it & 1) * kFaBN + half * HC, pk);
         l = l * alpha + sum;
         // O_half of the earlier tiles is scaled to the new maximum, once the P . V of the tile before is done
         if (it > 0 && !mbar_wait(pv_done, (it - 1) & 1)) {
@@ -320,8 +314,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
             tmem_st32(tmem_mine + lane_sel + c * 32, v);
           }
-          asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
         }
+        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");   // P (and a rescaled O) are in place
         // values of keys past the block's last query may never have been written: they must not be NaN
         const int tile_base = (kt0 + it) * kFaBN;
         if (tile_base + kFaBN - 1 > last_pos) {
@@ -335,9 +329,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             for (int cb = lane; cb < D / 8; cb += 32)   // 16-byte chunks of the row (all zero, so the swizzle does not matter)
               *reinterpret_cast<uint4*>(smem_gen + (v_s(s) - base) + (cb >> 3) * kSub + kr * 128 + ((cb & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
           }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the zeros, before the MMA reads the stage
         }
       }
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes (P, zeros) before the MMA reads them
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       mbar_arrive(p_full(it & 1));
     }
@@ -345,9 +339,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C0026);
       ok = false;
     }
-    // The two halves of a row merge: each passes its (maximum, sum) to the other through the first P buffer,
+    // The two halves of a row merge: each passes its (maximum, sum) to the other through the first key stage,
     // which no MMA reads any more, and takes half of the output columns.
-    float2* fin = reinterpret_cast<float2*>(smem_gen + (p_s - base));   // [2][128]
+    float2* fin = reinterpret_cast<float2*>(smem_gen + (k_s(0) - base));   // [2][128]
     fin[half * 128 + r] = make_float2(m, l);
     asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kFaSoftmaxWarps) : "memory");
     const float2 other = fin[(half ^ 1) * 128 + r];
