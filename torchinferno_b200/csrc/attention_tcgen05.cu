@@ -81,11 +81,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - base));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int entry = blockIdx.z, kvh = blockIdx.y;
+  const int entry = blockIdx.y, kvh = blockIdx.x;
   const int row0 = a.q_start[entry];
   const int q_len = a.q_start[entry + 1] - row0;
   const int tok_per_tile = kFaBM / a.group;
-  const int tile = gridDim.x - 1 - blockIdx.x;           // the longest tiles start first
+  // blocks are handed out x first, z last: with the row tile in z, the longest row tiles of every kv head and
+  // request start first and the short ones fill the gaps at the end
+  const int tile = gridDim.z - 1 - blockIdx.z;
   const int t0 = tile * tok_per_tile;
   // (uniform exits before any barrier or TMEM use)
   if ((q_len == 1 && a.skip_single) || t0 >= q_len) return;
@@ -283,6 +285,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         float alpha;
         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(alpha) : "f"(m - basev));
         m = m_new;
+        // O is only touched when some row of the warp moved its maximum; only then must P . V of the tile before
+        // be over.  (S of this tile is complete, so every product issued before it is: that of two tiles ago,
+        // which read P from the columns written below, among them.)
+        const bool rescale = it > 0 && __any_sync(0xffffffffu, alpha != 1.f);
         float sum = 0.f;
         // P (bf16, two keys to a column) goes back into tensor memory over this thread's own part of S: it is
         // the A operand of the next product, and never passes through shared memory
@@ -295,16 +301,17 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           sum += e0 + e1;
           const __nv_bfloat162 pair = __floats2bfloat162_rn(e0, e1);
           pk[j] = *reinterpret_cast<const uint32_t*>(&pair);
+          if (j == HC / 4 - 1) tmem_st16(tmem_s + lane_sel + (it & 1) * kFaBN + half * HC, pk);   // the first half is on its way
         }
-        tmem_st32(tmem_s + lane_sel + (it & 1) * kFaBN + half * HC, pk);
+        tmem_st16(tmem_s + lane_sel + (it & 1) * kFaBN + half * HC + HC / 4, pk + HC / 4);
         l = l * alpha + sum;
         // O_half of the earlier tiles is scaled to the new maximum, once the P . V of the tile before is done
-        if (it > 0 && !mbar_wait(pv_done, (it - 1) & 1)) {
+        if (rescale && !mbar_wait(pv_done, (it - 1) & 1)) {
           if (a.error_word && lane == 0) atomicExch(a.error_word, 0x7C0027);
           ok = false;
         }
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        if (ok && it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        if (ok && rescale) {
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
             uint32_t v[32];
@@ -415,7 +422,9 @@ static int launch_fa(const void* q, const void* pool, void* out, FaArgs& a, int 
   auto kern = prefill_attention_tcgen05_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FaSmem<D>::kTotal);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid(ceil_div(max_q_len, tok_per_tile), a.kv_heads, n_entries);
+  const int row_tiles = ceil_div(max_q_len, tok_per_tile);
+  if (row_tiles > 65535) return TIB_E_SIZE;
+  dim3 grid(a.kv_heads, n_entries, row_tiles);
   kern<<<grid, kFaThreads, FaSmem<D>::kTotal, stream>>>(map_q, map_kv, (__nv_bfloat16*)out, a);
   TIB_LAUNCH_CHECK();
   return TIB_OK;
