@@ -9,7 +9,9 @@ Sub-commands and where their option names come from:
 ``generate MODEL --input-ids``   the same on token ids (``--input-ids`` as in ``deepseek-hf-smoke``,
                                  cli.py:1945-1950), prints ``output_ids=[...]``
 ``llama-bench MODEL``            cli.py:1776-1816 (``--dtype --input-len 32 --output-len 128
-                                 --batch-size 8 --num-iters-warmup 1 --num-iters 3 --temperature 1.0 --seed 0``)
+                                 --batch-size 8 --num-iters-warmup 1 --num-iters 3 --num-prompts
+                                 --temperature 1.0 --seed 0``; ``--benchmark latency|throughput`` for its
+                                 ``--benchmarks``)
 ``serve-smoke``                  cli.py:2095-2104 (``--page-size 16 --max-active-requests 2
                                  --new-tokens 2 --vocab-size 128 --temperature 0.0 --seed 0``)
 ``capture-logits`` / ``validate-logits``   cli.py:2330-2350 (``model output --input-ids`` /
@@ -142,32 +144,77 @@ def run_validate_logits(args) -> int:
     return 0 if worst <= 0 else 1
 
 
+def _bench_engine(args):
+    """The engine of a benchmark run: MODEL is a model folder, or with --random-weights a config.json whose
+    model is built with seeded random weights on the device (nothing is written to disk)."""
+    if not args.random_weights:
+        return _engine(args, args.model)
+    from torchinferno_b200.config.engine_config import EngineConfig
+    from torchinferno_b200.engine.engine import InferenceEngine
+    from torchinferno_b200.engine.factory import random_model
+    from torchinferno_b200.kernels import gemm
+    gemm.set_backend(args.gemm_backend)          # decides the layout the weights are bound in
+    path = Path(args.model)
+    config = json.loads((path / "config.json" if path.is_dir() else path).read_text())
+    dtype = "bfloat16" if args.dtype == "auto" else args.dtype
+    model = random_model(config, args.seed, dtype=dtype, device=args.device or "cuda:0")
+    return InferenceEngine(model, EngineConfig(
+        model=str(path), device=args.device, dtype=dtype, max_model_len=args.max_model_len, page_size=args.page_size,
+        max_batch_size=args.max_batch_size, max_num_batched_tokens=args.max_num_batched_tokens,
+        prefill_chunk_size=args.prefill_chunk_size, kv_cache_tokens=args.kv_cache_tokens, seed=args.seed,
+        gemm_backend=args.gemm_backend))
+
+
 def run_llama_bench(args) -> int:
-    """Latency of ``generate`` on random prompts, as src/torchinferno/benchmarks/torchinferno_llama.py:169-194."""
+    """``--benchmark latency``: time of ``generate`` on a batch of random prompts of one length, as
+    src/torchinferno/benchmarks/torchinferno_llama.py:169-194.  ``--benchmark throughput``: ``--num-prompts``
+    requests with prompt lengths uniform in ``--input-len-min .. --input-len`` submitted at once and run by the
+    continuous-batching scheduler (prompt portions beside decoded tokens), as the throughput mode of
+    src/torchinferno/cli.py:1776-1816; reports request, prompt and output tokens per second and the split of
+    the steps."""
     import torch
     from torchinferno_b200.engine.types import GenerateRequest, SamplingConfig
-    args.max_batch_size = max(args.max_batch_size, args.batch_size)
+    throughput = args.benchmark == "throughput"
+    low = args.input_len if args.input_len_min is None else args.input_len_min
+    if not 1 <= low <= args.input_len:
+        raise SystemExit("--input-len-min must lie in 1 .. --input-len")
+    running = min(args.max_batch_size, args.num_prompts) if throughput else args.batch_size
+    args.max_batch_size = max(args.max_batch_size, running) if not throughput else args.max_batch_size
     if args.kv_cache_tokens is None:
-        args.kv_cache_tokens = args.batch_size * (args.input_len + args.output_len + args.page_size)
-    with _engine(args, args.model) as engine:
+        args.kv_cache_tokens = running * (args.input_len + args.output_len + args.page_size)
+    with _bench_engine(args) as engine:
         vocab = engine.model.spec.vocab_size
         g = torch.Generator().manual_seed(args.seed)
-        latencies = []
+        count = args.num_prompts if throughput else args.batch_size
+        latencies, record = [], {}
         for it in range(args.num_iters_warmup + args.num_iters):
-            prompts = torch.randint(0, vocab, (args.batch_size, args.input_len), generator=g).tolist()
+            lengths = torch.randint(low, args.input_len + 1, (count,), generator=g).tolist()
+            prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
             requests = [GenerateRequest(f"bench-{it}-{i}", prompt_token_ids=p, sampling=SamplingConfig(
                 args.output_len, args.temperature, (), args.seed + i)) for i, p in enumerate(prompts)]
+            before = dict(engine.scheduler.stats)
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             outputs = engine.generate_many(requests)
             torch.cuda.synchronize()
             if it >= args.num_iters_warmup:
                 latencies.append(time.perf_counter() - t0)
+                record = {k: engine.scheduler.stats[k] - before[k] for k in before}
+                record["prompt_tokens"] = sum(lengths)
         tokens = sum(len(o.token_ids) for o in outputs)
     mean = sum(latencies) / len(latencies)
-    print(json.dumps({"benchmark": "latency", "model": args.model, "dtype": args.dtype, "batch_size": args.batch_size,
-                      "input_len": args.input_len, "output_len": args.output_len, "latency_s": mean,
-                      "output_tokens_per_s": tokens / mean}))
+    line = {"benchmark": args.benchmark, "model": args.model, "dtype": args.dtype, "input_len": args.input_len,
+            "output_len": args.output_len, "latency_s": round(mean, 4), "output_tokens_per_s": round(tokens / mean, 1)}
+    if throughput:
+        line.update({"num_prompts": count, "input_len_min": low, "max_batch_size": args.max_batch_size,
+                     "requests_per_s": round(count / mean, 2),
+                     "total_tokens_per_s": round((tokens + record["prompt_tokens"]) / mean, 1),
+                     "steps": record["steps"], "ms_per_step": round(1e3 * mean / max(1, record["steps"]), 3),
+                     "prefill_tokens": record["prefill_tokens"], "decode_tokens": record["decode_tokens"],
+                     "preemptions": record["preemptions"]})
+    else:
+        line["batch_size"] = args.batch_size
+    print(json.dumps(line))
     return 0
 
 
@@ -235,6 +282,12 @@ def build_parser() -> argparse.ArgumentParser:
     bench.add_argument("--num-iters", type=int, default=3)
     bench.add_argument("--temperature", type=float, default=1.0)
     bench.add_argument("--seed", type=int, default=0)
+    bench.add_argument("--benchmark", choices=["latency", "throughput"], default="latency")
+    bench.add_argument("--num-prompts", type=int, default=64, help="throughput: requests submitted at once")
+    bench.add_argument("--input-len-min", type=int, default=None,
+                       help="prompt lengths are uniform in this .. --input-len (default: all --input-len)")
+    bench.add_argument("--random-weights", action="store_true",
+                       help="MODEL is a config.json (or a folder with one): build it with seeded random weights")
     _engine_options(bench)
     bench.set_defaults(func=run_llama_bench)
     return parser
