@@ -76,7 +76,9 @@ def _need(t: torch.Tensor, name: str, dtype: torch.dtype | None = None) -> None:
 
 
 def _stream() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    # (the raw handle of the current stream of the current device: a fraction of the cost of
+    # torch.cuda.current_stream(), which is asked for at every launch)
+    return c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 _signatures_set = False
