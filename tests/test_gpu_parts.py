@@ -429,3 +429,38 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_an
         unregister_part("feed_forward", "toy_routed")
         unregister_part("position", "geometric")
         unregister_architecture("Toy2ForCausalLM")
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_the_native_block_call_gives_the_bits_of_the_part_by_part_sequence(model_folders, name, monkeypatch):
+    """A block of the built-in parts in bfloat16 is issued as one call into the CUDA library; it must launch the
+    same kernels with the same choices as the parts do one by one: logits equal bit for bit, for a whole prompt,
+    portions, a mixed step and decoding (captured and not)."""
+    need_gpu()
+    from torchinferno_b200.engine.batch import StepEntry
+    from torchinferno_b200.engine.factory import load_model, make_runner
+    from torchinferno_b200.parts import block as block_module
+    cfg = json.loads((model_folders[name] / "config.json").read_text())
+    g = torch.Generator().manual_seed(3)
+    a, b = (torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in (150, 41))
+
+    def run(native, graphs):
+        monkeypatch.setattr(block_module, "NATIVE_BLOCKS", native)
+        model = load_model(model_folders[name], dtype="bfloat16")
+        runner = make_runner(model, page_size=16, max_tokens=512, max_requests=4)
+        runner.use_cuda_graphs = graphs
+        outs = []
+        with torch.inference_mode():
+            # (a captured step returns the graph's own output buffer: read it before the next step)
+            outs.append(runner.step([StepEntry("a", a[:100], [0, 99])]).cpu())
+            outs.append(runner.step([StepEntry("a", a[100:101], [0]), StepEntry("b", b[:40], [3, 39])]).cpu())
+            for t in range(101, 106):
+                outs.append(runner.step([StepEntry("a", a[t:t + 1], [0]), StepEntry("b", [b[40]] if t == 101 else [7], [0])]).cpu())
+        used = [blk._native is not None and blk._native is not block_module._UNKNOWN for blk in model.blocks]
+        return torch.cat(outs), used
+
+    parts, used_parts = run(False, False)
+    for graphs in (False, True):
+        native, used_native = run(True, graphs)
+        assert all(used_native) and not any(used_parts)
+        assert torch.equal(native, parts), ((native - parts).abs().max(), (native != parts).any(dim=1).tolist())

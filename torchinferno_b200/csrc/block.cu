@@ -1,0 +1,138 @@
+// One pre-norm Llama block as one call: the ten or so launches of a layer issued from here, without a
+// return to the interpreter between them.  Nothing new is computed: the same kernels, in the order and with
+// the choices (which attention kernel, which product) that the Python parts make one by one
+// (parts/block.py, parts/attention.py, parts/mlp.py, kernels/attention.py, kernels/gemm.py); the parts use
+// this call when every part of the block is one of the built-in kinds, and their own sequence otherwise.
+//
+//   n  = rmsnorm(residual += pending)                      add_rmsnorm
+//   qkv = n . Wqkv^T; q, k -> rotary; k, v -> pages        library product, rope_append
+//   a  = attention(q, pages)                               prefill (tcgen05 / mma.sync) and decode (TMA / cp.async)
+//   o  = a . Wo^T                                          swap-AB tcgen05 product at few rows, else library
+//   n  = rmsnorm(residual += o)                            add_rmsnorm
+//   out = (silu(n . Wg^T) * (n . Wu^T)) . Wd^T             library products, swiglu
+// `out` is left pending: the next block's (or the final) norm adds it
+// (src/torchinferno/models/llama3/pipeline.py:190-198; the pending add: tensor_parallel.py:7430-7435).
+#include "common.cuh"
+
+extern "C" {
+int tib_add_rmsnorm(const void*, float*, const int*, const float*, void*, int, int, float, int, cudaStream_t);
+int tib_swiglu(const void*, void*, int, int, int, cudaStream_t);
+int tib_rope_append(const void*, void*, void*, const int*, const int*, const int*, int, const float*, int, int, int, int, int,
+                    int, int, int64_t, int, int, int*, int, cudaStream_t);
+int tib_prefill_attention_tcgen05_supports(int, int, int);
+int tib_prefill_attention_tcgen05(const void*, const void*, void*, const int*, const int*, const int*, const int*, int, int, int,
+                                  int, int, int, int, int, int64_t, int, int, float, int, int*, cudaStream_t);
+int tib_prefill_attention(const void*, const void*, void*, const int*, const int*, const int*, const int*, int, int, int, int,
+                          int, int, int, int64_t, int, int, float, int, cudaStream_t);
+int tib_decode_attention_tma_supports(int, int, int);
+int tib_decode_attention_tma(const void*, const void*, void*, float*, float*, const int*, const int*, const int*, const int*,
+                             int, int, int, int, int, int, int64_t, int, int, float, int, int, int*, int*, cudaStream_t);
+int tib_decode_attention(const void*, const void*, void*, float*, float*, const int*, const int*, const int*, const int*, int,
+                         int, int, int, int, int, int64_t, int, int, float, int, int, cudaStream_t);
+int tib_gemm_tcgen05_swapab_supports(int, int, int);
+int tib_gemm_tcgen05_swapab(const void*, const void*, void*, int, int, int, int64_t, int64_t, int64_t, int, int, int*, cudaStream_t);
+int tib_blas_gemm(const void*, const void*, void*, int, int, int, int64_t, int64_t, int64_t, int, int, cudaStream_t);
+}
+
+// What a block is made of: sizes, constants and weights.  Filled once when the weights are bound.
+struct TibBlockWeights {
+  int hidden, heads, kv_heads, head_dim, intermediate;
+  int rot_dim, interleaved;              // rotary: rotated width (0: none), pairing
+  int qkv_kn, o_kn, gate_up_kn, down_kn; // 1: the matrix is stored [in, out]
+  int o_few_rows;                        // rows up to which the output projection goes to the swap-AB kernel (0: never)
+  float eps_mixer, eps_feed_forward, scale;
+  const float* norm_mixer;               // [hidden]
+  const float* norm_feed_forward;        // [hidden]
+  const float* inv_freq;                 // [rot_dim / 2]
+  const void* qkv;                       // (heads + 2 kv_heads) * head_dim x hidden
+  const void* o;                         // hidden x heads * head_dim
+  const void* gate_up;                   // 2 intermediate x hidden
+  const void* down;                      // hidden x intermediate
+};
+
+// What a step brings: the batch arrays and the buffers the block works in (all of them for n_tokens rows).
+struct TibBlockStep {
+  int n_tokens, n_entries, max_q_len, n_single, n_multi;
+  int decode_splits;
+  const int* positions;
+  const int* token_slot;
+  const int* q_start;
+  const int* kv_start;
+  const int* slots;
+  float* residual;                       // [n_tokens, hidden] fp32
+  void* normed;                          // [n_tokens, hidden]
+  void* qkv;                             // [n_tokens, (heads + 2 kv_heads) * head_dim]
+  void* q;                               // [n_tokens, heads * head_dim]
+  void* attn;                            // [n_tokens, heads * head_dim]
+  void* o_out;                           // [n_tokens, hidden]
+  void* gate_up;                         // [n_tokens, 2 intermediate]
+  void* act;                             // [n_tokens, intermediate]
+  void* out;                             // [n_tokens, hidden]: the block's result, left pending
+  float* split_scratch;                  // decode_splits > 1: n_entries * heads * decode_splits * (head_dim + 2) floats
+  int* split_counters;                   // zeros, n_entries * kv_heads (or null: merge by a second kernel)
+  int* error_word;
+};
+
+#define TIB_TRY(call)        \
+  do {                       \
+    const int rc__ = (call); \
+    if (rc__ != TIB_OK) return rc__; \
+  } while (0)
+
+// pending: the result of the block before (bf16 [n_tokens, hidden]) or null for the first.  pool: this layer's
+// pages [pages, 2, kv_heads, page_size, head_dim] (page_stride elements apart); window 0: every key.
+TIB_API int tib_llama_block(const TibBlockWeights* w, const TibBlockStep* s, const void* pending, void* pool,
+                            const int* block_table, int table_stride, int page_size, int64_t page_stride, int num_pages,
+                            int window, cudaStream_t stream) {
+  if (!w || !s || !pool || !block_table) return TIB_E_ARG;
+  const int n = s->n_tokens;
+  if (n == 0) return TIB_OK;
+  const int h = w->heads, k = w->kv_heads, d = w->head_dim, group = h / k;
+  const int qkv_width = (h + 2 * k) * d, q_width = h * d;
+  const bool packed = page_stride == (int64_t)2 * k * page_size * d;
+
+  TIB_TRY(tib_add_rmsnorm(pending, s->residual, nullptr, w->norm_mixer, s->normed, n, w->hidden, w->eps_mixer, TIB_BF16, stream));
+  TIB_TRY(tib_blas_gemm(s->normed, w->qkv, s->qkv, n, qkv_width, w->hidden, w->hidden, w->qkv_kn ? qkv_width : w->hidden,
+                        qkv_width, w->qkv_kn, TIB_BF16, stream));
+  TIB_TRY(tib_rope_append(s->qkv, s->q, pool, s->positions, s->token_slot, block_table, table_stride, w->inv_freq, n, h, k, d,
+                          w->rot_dim, w->interleaved, page_size, page_stride, num_pages, 1, s->error_word, TIB_BF16, stream));
+  if (s->n_multi) {
+    if (packed && tib_prefill_attention_tcgen05_supports(d, group, page_size))
+      TIB_TRY(tib_prefill_attention_tcgen05(s->q, pool, s->attn, s->q_start, s->kv_start, s->slots, block_table, table_stride,
+                                            s->n_entries, s->max_q_len, n, h, k, d, page_size, page_stride, num_pages, window,
+                                            w->scale, s->n_single > 0, s->error_word, stream));
+    else
+      TIB_TRY(tib_prefill_attention(s->q, pool, s->attn, s->q_start, s->kv_start, s->slots, block_table, table_stride,
+                                    s->n_entries, s->max_q_len, h, k, d, page_size, page_stride, num_pages, window, w->scale,
+                                    s->n_single > 0, stream));
+  }
+  if (s->n_single) {
+    const int splits = s->decode_splits < 1 ? 1 : s->decode_splits;
+    float* scratch_o = splits > 1 ? s->split_scratch : nullptr;
+    float* scratch_ml = splits > 1 ? s->split_scratch + (size_t)s->n_entries * h * splits * d : nullptr;
+    if (splits > 1 && !scratch_o) return TIB_E_ARG;
+    if (packed && tib_decode_attention_tma_supports(d, group, page_size))
+      TIB_TRY(tib_decode_attention_tma(s->q, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots, block_table,
+                                       table_stride, s->n_entries, h, k, d, page_size, page_stride, num_pages, window, w->scale,
+                                       splits, 0, splits > 1 ? s->split_counters : nullptr, s->error_word, stream));
+    else
+      TIB_TRY(tib_decode_attention(s->q, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots, block_table,
+                                   table_stride, s->n_entries, h, k, d, page_size, page_stride, num_pages, window, w->scale,
+                                   splits, 0, stream));
+  }
+  if (w->o_few_rows > 0 && n <= w->o_few_rows && !w->o_kn && tib_gemm_tcgen05_swapab_supports(n, w->hidden, q_width))
+    TIB_TRY(tib_gemm_tcgen05_swapab(s->attn, w->o, s->o_out, n, w->hidden, q_width, q_width, q_width, w->hidden, TIB_BF16, 0,
+                                    s->error_word, stream));
+  else
+    TIB_TRY(tib_blas_gemm(s->attn, w->o, s->o_out, n, w->hidden, q_width, q_width, w->o_kn ? w->hidden : q_width, w->hidden,
+                          w->o_kn, TIB_BF16, stream));
+  TIB_TRY(tib_add_rmsnorm(s->o_out, s->residual, nullptr, w->norm_feed_forward, s->normed, n, w->hidden, w->eps_feed_forward,
+                          TIB_BF16, stream));
+  const int inter = w->intermediate;
+  TIB_TRY(tib_blas_gemm(s->normed, w->gate_up, s->gate_up, n, 2 * inter, w->hidden, w->hidden,
+                        w->gate_up_kn ? 2 * inter : w->hidden, 2 * inter, w->gate_up_kn, TIB_BF16, stream));
+  TIB_TRY(tib_swiglu(s->gate_up, s->act, n, inter, TIB_BF16, stream));
+  TIB_TRY(tib_blas_gemm(s->act, w->down, s->out, n, w->hidden, inter, inter, w->down_kn ? w->hidden : inter, w->hidden,
+                        w->down_kn, TIB_BF16, stream));
+  return TIB_OK;
+}

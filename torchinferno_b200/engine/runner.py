@@ -67,7 +67,9 @@ class ModelRunner:
 
     # --------------------------------------------------------------- step
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Run one batch; returns logits [sum(len(e.want)), vocab] in fp32 on the device."""
+        """Run one batch; returns logits [sum(len(e.want)), vocab] in fp32 on the device.  A pure decode batch
+        that replays a captured graph returns that graph's own output buffer: it holds these logits until the
+        next step of the same batch size."""
         cache, spec = self.cache, self.model.spec
         seen: set[Hashable] = set()
         for entry in entries:

@@ -115,15 +115,9 @@ def _linear_library_kn(x: torch.Tensor, weight_kn: torch.Tensor, out_dtype: torc
     if _backend == "tcgen05":
         raise ops.KernelError("linear: these weights were laid out for the library; bind the model after "
                               "choosing the tcgen05 backend")
-    if out_dtype == torch.bfloat16:
-        if out is None:
-            out = torch.empty((x.shape[0], weight_kn.shape[1]), dtype=torch.bfloat16, device=x.device)
-        return torch.mm(x, weight_kn, out=out)
-    result = torch.mm(x, weight_kn, out_dtype=torch.float32)
-    if out is not None:
-        out.copy_(result)
-        return out
-    return result
+    if out is None or out.dtype != out_dtype:
+        out = torch.empty((x.shape[0], weight_kn.shape[1]), dtype=out_dtype, device=x.device)
+    return ops.library_gemm(x, weight_kn, out, w_kn=True)
 
 
 def _linear_bf16(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
@@ -141,15 +135,8 @@ def _linear_bf16(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
             if out is None or out.dtype != out_dtype:
                 out = torch.empty((m, n), dtype=out_dtype, device=x.device)
             return ops.gemm_tcgen05(x, weight, out, _error_word)
-    if out_dtype == torch.bfloat16:
-        if out is None:
-            out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
-        torch.mm(x, weight.t(), out=out)
-        return out
-    if out_dtype == torch.float32:
-        result = torch.mm(x, weight.t(), out_dtype=torch.float32)
-        if out is not None:
-            out.copy_(result)
-            return out
-        return result
-    raise ops.KernelError(f"linear: unsupported output dtype {out_dtype}")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise ops.KernelError(f"linear: unsupported output dtype {out_dtype}")
+    if out is None or out.dtype != out_dtype:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    return ops.library_gemm(x, weight, out, w_kn=False)

@@ -40,6 +40,11 @@ def set_dependent_launch(on: bool) -> bool:
     return bool(lib().tib_set_dependent_launch(c_int(1 if on else 0)))
 
 
+def count_launches(n: int) -> None:
+    """Launches made by a native call that issues several kernels."""
+    _counter["launches"] += n
+
+
 def launch_count() -> int:
     """How many kernels of this library were launched by this process so far."""
     return _counter["launches"]
@@ -93,6 +98,7 @@ def lib() -> ctypes.CDLL:
                    "tib_attention_mma_supports", "tib_prefill_attention", "tib_decode_attention",
                    "tib_prefill_attention_tcgen05", "tib_prefill_attention_tcgen05_supports",
                    "tib_decode_attention_tma", "tib_decode_attention_tma_supports", "tib_set_dependent_launch",
+                   "tib_blas_init", "tib_blas_gemm",
                    "tib_gemm_skinny", "tib_gemm_skinny_supports", "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
                    "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports"):
             getattr(library, fn).restype = c_int
@@ -413,6 +419,42 @@ def _split_counters(device: torch.device, n: int) -> torch.Tensor | None:
 
 def decode_attention_tma_supports(head_dim: int, group: int, page_size: int) -> bool:
     return bool(lib().tib_decode_attention_tma_supports(c_int(head_dim), c_int(group), c_int(page_size)))
+
+
+_blas_workspace: dict[int, torch.Tensor] = {}
+BLAS_WORKSPACE_BYTES = 32 << 20
+
+
+def library_gemm_ready(device: torch.device) -> None:
+    """Make the cuBLAS handle of ``device`` and give it its workspace (once)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _blas_workspace:
+        buffer = torch.empty(BLAS_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+        with torch.cuda.device(index):
+            status = lib().tib_blas_init(_ptr(buffer), ctypes.c_size_t(buffer.numel()))
+        if status:
+            raise KernelError(f"library_gemm: cuBLAS could not be set up (status {status})")
+        _blas_workspace[index] = buffer
+
+
+def library_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, w_kn: bool) -> torch.Tensor:
+    """out[M, N] (bf16 or fp32) = x[M, K] . w^T by cuBLAS, called from the engine's own library: ``w`` is stored
+    [N, K], or [K, N] when ``w_kn``.  The library's workspace is a buffer of this module, made at the first call on
+    a device (make that call outside a stream capture)."""
+    library_gemm_ready(x.device)
+    m, k = x.shape
+    n = w.shape[1] if w_kn else w.shape[0]
+    if (w.shape[0] if w_kn else w.shape[1]) != k or out.shape != (m, n):
+        raise KernelError(f"library_gemm: shapes {tuple(x.shape)}, {tuple(w.shape)} (kn={w_kn}), {tuple(out.shape)} do not fit")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("library_gemm: bf16 operands with unit inner stride are needed")
+    status = lib().tib_blas_gemm(_ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)),
+                                 c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(1 if w_kn else 0),
+                                 c_int(_code(out.dtype)), _stream())
+    if status:
+        raise KernelError(f"library_gemm: status {status} (20000 + n: cuBLAS status n)")
+    _counter["launches"] += 1
+    return out
 
 
 def gemm_skinny_supports(m: int, n: int, k: int) -> bool:
