@@ -130,5 +130,7 @@ def run_block(w: BlockWeights, stream_state, ctx, window: int | None) -> None:
     if status:
         raise ops.KernelError(f"native block: status {status} (negative: refused arguments; 20000 + n: cuBLAS status n; "
                               f"else a CUDA error at launch)")
-    ops.count_launches(10 + (1 if batch.n_single and batch.n_multi else 0))
+    # this library's own kernels among them: two norms, rotary, SwiGLU, one or two attention kernels, and the
+    # output projection when the swap-AB kernel takes it (the library products are not counted)
+    ops.count_launches(5 + (1 if batch.n_single and batch.n_multi else 0) + (1 if 0 < batch.n_tokens <= w.o_few_rows else 0))
     stream_state.pending = ws.buffers["out"]
