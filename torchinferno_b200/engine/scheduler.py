@@ -37,7 +37,7 @@ from torchinferno_b200.cache.manager import CacheManager
 UNKNOWN_TOKEN = -1   # input token of a step planned ahead: the token the running step is still drawing
 
 
-@dataclass
+@dataclass(eq=False)     # (a request is itself: membership tests and removals go by identity, not by comparing fields)
 class SchedulerRequest:
     request_id: Hashable
     prompt: list[int]
@@ -275,9 +275,10 @@ class Scheduler:
             return None
         need = [0] * len(self.cache.free_pages())
         entries = []
+        live = {id(r) for r in self.running}
         for entry in running.entries:
             request = self._by_id.get(entry.request_id)
-            if (request is None or request not in self.running or not entry.samples
+            if (request is None or id(request) not in live or not entry.samples
                     or len(request.generated) + 2 > request.max_new_tokens
                     or entry.request_id not in self.cache
                     or self.cache.length(entry.request_id) != entry.start + len(entry.tokens)):
