@@ -233,7 +233,7 @@ def drive_ahead(cache, sched, max_steps=500):
                 outputs.setdefault(event.request_id, []).append(event.token)
             if event.finished:
                 outputs.setdefault(event.request_id, []).append(event.finish_reason)
-        if launched is not None and not any(e.request_id in sched._by_id for e in launched[0].entries):
+        if launched is not None and not any(sched.request(e.request_id) is not None for e in launched[0].entries):
             launched = None
         cache.audit()
     assert not sched.has_work(), "the scheduler did not finish"

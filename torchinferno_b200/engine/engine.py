@@ -141,7 +141,7 @@ class InferenceEngine:
         if current is not None:
             # requests that ended while the step ran (a stop token, a cancellation) drop out of it
             live = tuple(e for e, r in zip(current.plan.entries, current.requests)
-                         if self.scheduler._by_id.get(e.request_id) is r)
+                         if self.scheduler.request(e.request_id) is r)
             if not live:
                 current = None
             elif len(live) < len(current.plan.entries):
@@ -171,12 +171,12 @@ class InferenceEngine:
             self.stats["steps"] += 1
             self.stats["h2d_bytes"] += self.runner.last_batch.h2d_bytes
             drawing = [e for e in plan.entries if e.samples]
-            requests = [self.scheduler._by_id[e.request_id] for e in plan.entries]
+            requests = [self.scheduler.request(e.request_id) for e in plan.entries]
             if not drawing:
                 return _Launched(plan, requests, [], None)
             params, positions = [], []
             for e in drawing:
-                request = self.scheduler._by_id[e.request_id]
+                request = self.scheduler.request(e.request_id)
                 params.append(SamplingParams(request.temperature, request.seed))
                 positions.append(e.start + len(e.tokens))  # position of the token being drawn
             tokens = self.sampler.sample(logits, params, positions)
@@ -187,7 +187,7 @@ class InferenceEngine:
     def generate_stream(self, request: GenerateRequest) -> Iterator[TokenOutput]:
         """Yield one ``TokenOutput`` per token, then a final one with ``finished`` and ``usage``."""
         self.submit(request)
-        prompt_tokens = len(self.scheduler._by_id[request.request_id].prompt)
+        prompt_tokens = len(self.scheduler.request(request.request_id).prompt)
         emitted: list[int] = []
         reason = None
         while reason is None:
@@ -223,7 +223,7 @@ class InferenceEngine:
         requests = list(requests)
         for request in requests:
             self.submit(request)
-        prompts = {r.request_id: len(self.scheduler._by_id[r.request_id].prompt) for r in requests}
+        prompts = {r.request_id: len(self.scheduler.request(r.request_id).prompt) for r in requests}
         tokens: dict[Hashable, list[int]] = {r.request_id: [] for r in requests}
         reasons: dict[Hashable, str] = {}
         while len(reasons) < len(requests) and self.scheduler.has_work():

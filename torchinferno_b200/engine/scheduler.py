@@ -128,6 +128,10 @@ class Scheduler:
         self._by_id[request.request_id] = request
         self.waiting.append(request)
 
+    def request(self, request_id: Hashable) -> SchedulerRequest | None:
+        """The live request of this id (waiting or running), or None once it has finished."""
+        return self._by_id.get(request_id)
+
     def has_work(self) -> bool:
         return bool(self.waiting) or bool(self.running)
 
