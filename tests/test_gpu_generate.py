@@ -92,6 +92,23 @@ def test_async_scheduling_gives_the_same_tokens(model_folders):
     assert results[True][2] == results[True][0][0][:6] and results[True][4] == list(results[True][0][0][:12])
 
 
+def test_the_engine_sees_an_error_word_that_a_kernel_set(model_folders):
+    """The kernels report a page id outside its pool or a bounded wait that ran out in one device word; the
+    engine reads it with the step's tokens.  Here the word is set from the host (no kernel is made to fail)."""
+    need_gpu()
+    from torchinferno_b200.engine.runner import StepError
+    config, seed = TINY["A"]
+    prompt = list(requests_for(config, seed, [9]).values())[0]
+    with engine_for(model_folders["A"], "float32", page_size=4, max_batch_size=2) as engine:
+        engine.submit(requests([prompt], 6)[0])
+        engine.step()
+        engine.runner.cache.error_word.fill_(0x7C0031)
+        with pytest.raises(StepError, match="0x7c0031"):
+            for _ in range(3):
+                engine.step()
+        engine.runner.cache.error_word.zero_()
+
+
 def test_seeded_temperature_generation_fp32(model_folders):
     """Tiny B: five prompts (1, 5, 17, 40, 96 tokens), pages of 16, portions of 32, twelve tokens at
     temperature 0.8.  Each token must be the Gumbel-max choice of the plain logits for the engine's own

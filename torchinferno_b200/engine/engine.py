@@ -19,6 +19,7 @@ import torch
 from torchinferno_b200.config.engine_config import EngineConfig
 from torchinferno_b200.engine.batch import StepEntry
 from torchinferno_b200.engine.factory import load_model, make_runner
+from torchinferno_b200.engine.runner import StepError
 from torchinferno_b200.engine.scheduler import Scheduler, SchedulerRequest, StepPlan, TokenEvent, UNKNOWN_TOKEN
 from torchinferno_b200.kernels import gemm
 from torchinferno_b200.engine.types import GenerateOutput, GenerateRequest, SamplingConfig, TokenOutput, Usage
@@ -28,13 +29,17 @@ from torchinferno_b200.sampling.sampler import Sampler, SamplingParams
 class _Launched:
     """A step that runs on the device: its plan, the drawn tokens there and on their way to the host."""
 
-    def __init__(self, plan: StepPlan, requests: list, drawing: list, device_tokens: torch.Tensor | None) -> None:
+    def __init__(self, plan: StepPlan, requests: list, drawing: list, device_tokens: torch.Tensor | None,
+                 error_word: torch.Tensor) -> None:
         self.plan, self.requests, self.drawing, self.device_tokens = plan, requests, drawing, device_tokens
         self.host_tokens: torch.Tensor | None = None
         self.arrived: torch.cuda.Event | None = None
         if device_tokens is not None and device_tokens.numel():
-            self.host_tokens = torch.empty(device_tokens.shape, dtype=device_tokens.dtype, pin_memory=True)
-            self.host_tokens.copy_(device_tokens, non_blocking=True)
+            # the tokens and, behind them, the kernels' error word (a page id outside its pool, a bounded wait
+            # that ran out): one more small copy instead of a synchronising read after every step
+            self.host_tokens = torch.empty(device_tokens.numel() + 1, dtype=torch.int32, pin_memory=True)
+            self.host_tokens[:-1].copy_(device_tokens.reshape(-1), non_blocking=True)
+            self.host_tokens[-1:].copy_(error_word.reshape(-1)[:1], non_blocking=True)
             self.arrived = torch.cuda.Event()
             self.arrived.record()
 
@@ -43,7 +48,10 @@ class _Launched:
         if self.host_tokens is None:
             return {}
         self.arrived.synchronize()
-        return {e.request_id: int(t) for e, t in zip(self.drawing, self.host_tokens.tolist())}
+        *tokens, error = self.host_tokens.tolist()
+        if error:
+            raise StepError(f"a kernel reported an error during the step (code {error:#x}); its tokens are invalid")
+        return {e.request_id: int(t) for e, t in zip(self.drawing, tokens)}
 
 
 class InferenceEngine:
@@ -173,15 +181,15 @@ class InferenceEngine:
             drawing = [e for e in plan.entries if e.samples]
             requests = [self.scheduler.request(e.request_id) for e in plan.entries]
             if not drawing:
-                return _Launched(plan, requests, [], None)
+                return _Launched(plan, requests, [], None, self.runner.cache.error_word)
             params, positions = [], []
             for e in drawing:
                 request = self.scheduler.request(e.request_id)
                 params.append(SamplingParams(request.temperature, request.seed))
                 positions.append(e.start + len(e.tokens))  # position of the token being drawn
             tokens = self.sampler.sample(logits, params, positions)
-            self.stats["d2h_bytes"] += tokens.numel() * tokens.element_size()
-            return _Launched(plan, requests, drawing, tokens)
+            self.stats["d2h_bytes"] += tokens.numel() * tokens.element_size() + 4    # (and the error word)
+            return _Launched(plan, requests, drawing, tokens, self.runner.cache.error_word)
 
     # ------------------------------------------------------------ generate
     def generate_stream(self, request: GenerateRequest) -> Iterator[TokenOutput]:
