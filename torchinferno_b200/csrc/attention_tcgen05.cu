@@ -101,6 +101,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
   constexpr uint32_t kTmemCols = 512;                    // S (two buffers): columns 0..255; O_0, O_1: D columns each from 256
 
+  if (threadIdx.x == 32) {   // (the descriptors are fetched while the barriers are set up)
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_kv) : "memory");
+  }
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < kFaStages; ++s) {
