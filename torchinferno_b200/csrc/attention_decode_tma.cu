@@ -316,18 +316,56 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
   // The parts of one (request, kv head) count themselves in; the one that arrives last merges them all, so
   // no second kernel is needed.  The counter is left at zero for the next launch.
   if (a.num_splits == 1 || a.counters == nullptr) return;
-  __threadfence();
-  __syncthreads();
+  __syncthreads();                       // every thread's part of the partial result is written ...
   int* counter = a.counters + (size_t)entry * a.kv_heads + kvh;
-  if (threadIdx.x == 0) ticket_s = atomicAdd(counter, 1);
+  if (threadIdx.x == 0) {
+    __threadfence();                     // ... and visible to the device before this block counts itself in
+    ticket_s = atomicAdd(counter, 1);
+  }
   __syncthreads();
   if (ticket_s != a.num_splits - 1) return;
   __threadfence();
+  const int ns = a.num_splits;
+  const size_t slot0 = ((size_t)entry * a.heads + head0) * ns;       // (row r, part sp) is slot0 + r * ns + sp
+  if (ns <= 16) {
+    // few parts: every thread asks for all it needs at once (its row's maxima and sums and its four output
+    // columns of every part), so the merge costs one trip to the L2, not one per dependent step
+    for (int idx = threadIdx.x; idx < nrows * (D / 4); idx += kDtThreads) {
+      const int r = idx / (D / 4), d4 = idx - r * (D / 4);
+      const float2* pm = reinterpret_cast<const float2*>(partial_ml) + slot0 + r * ns;
+      const float4* po = reinterpret_cast<const float4*>(partial_o + (slot0 + r * ns) * D) + d4;
+      float2 ml[16];
+      float4 ov[16];
+#pragma unroll
+      for (int sp = 0; sp < 16; ++sp) {
+        const bool have = sp < ns;
+        ml[sp] = have ? __ldcg(pm + sp) : make_float2(-CUDART_INF_F, 0.f);
+        ov[sp] = have ? __ldcg(po + (size_t)sp * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      float mm = -CUDART_INF_F;
+#pragma unroll
+      for (int sp = 0; sp < 16; ++sp) mm = fmaxf(mm, ml[sp].x);
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      float sum = 0.f;
+#pragma unroll
+      for (int sp = 0; sp < 16; ++sp) {
+        if (ml[sp].x == -CUDART_INF_F) continue;   // an empty part wrote no output (what was read may be anything)
+        const float w = exp2f(ml[sp].x - mm);
+        sum += w * ml[sp].y;
+        acc.x += w * ov[sp].x; acc.y += w * ov[sp].y; acc.z += w * ov[sp].z; acc.w += w * ov[sp].w;
+      }
+      const float inv = 1.f / sum;
+      uint2 packed;
+      packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+      packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2*>(out + (size_t)row0 * a.heads * D + (head0 + r) * D + d4 * 4) = packed;
+    }
+    if (threadIdx.x == 0) *counter = 0;
+    return;
+  }
   // weights of the parts first (one load per (row, part), all in flight together), then the sums with the
   // loads of several parts in flight: nothing here waits for one load after another
   float* wgt_s = reinterpret_cast<float*>(smem_gen);                 // [nrows][num_splits] weights, then [nrows] 1 / sum
-  const int ns = a.num_splits;
-  const size_t slot0 = ((size_t)entry * a.heads + head0) * ns;       // (row r, part sp) is slot0 + r * ns + sp
   for (int r = warp; r < nrows; r += kDtThreads / 32) {
     float mm = -CUDART_INF_F;
     for (int sp = lane; sp < ns; sp += 32) mm = fmaxf(mm, __ldcg(partial_ml + (slot0 + r * ns + sp) * 2));
