@@ -92,6 +92,24 @@ def test_async_scheduling_gives_the_same_tokens(model_folders):
     assert results[True][2] == results[True][0][0][:6] and results[True][4] == list(results[True][0][0][:12])
 
 
+def test_programmatic_dependent_launch_changes_no_token(model_folders):
+    """Tiny D in bfloat16 (TMA decode attention, tcgen05 prefill attention, swap-AB output projection, all launched
+    so that they may start while the kernel before drains): the same requests with that switched off."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    config, seed = TINY["D"]
+    prompts = list(requests_for(config, seed, [70, 9, 33]).values())
+    got = {}
+    try:
+        for on in (True, False):
+            ops.set_dependent_launch(on)
+            with engine_for(model_folders["D"], "bfloat16", page_size=16, max_batch_size=4, prefill_chunk_size=32) as engine:
+                got[on] = [o.token_ids for o in engine.generate_many(requests(prompts, 24))]
+    finally:
+        ops.set_dependent_launch(True)
+    assert got[True] == got[False]
+
+
 def test_the_engine_sees_an_error_word_that_a_kernel_set(model_folders):
     """The kernels report a page id outside its pool or a bounded wait that ran out in one device word; the
     engine reads it with the step's tokens.  Here the word is set from the host (no kernel is made to fail)."""
