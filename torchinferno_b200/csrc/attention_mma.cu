@@ -6,7 +6,7 @@
 //   decode_attention_kernel    single tokens: the context of one (request, kv head) is split over
 //                              blocks ("split-K"); each block streams its keys once for all query heads
 //                              of the group and leaves (max, sum, unnormalised output) in scratch
-//   decode_merge_kernel        combines the partial results exactly (fp32)
+//   decode_merge_kernel        (mma.cuh) combines the partial results exactly (fp32)
 //
 // Formula as in attention_simt.cu (src/torchinferno/models/llama3/raw_ops.py:44-51; streaming form
 // src/torchinferno/kernels/triton_ops.py:2555-2574, whose grid is (batch, kv_heads) with no split

@@ -5,8 +5,11 @@ rows q_start[e] .. q_start[e+1]-1, its first query token stands at position
 kv_start[e] of the request, and its pages are row slots[e] of the block table.
 A kernel that does not take a shape is passed over: portions of prompts go to the
 tcgen05 kernel (head size 64 or 128, pages of 8 .. 128 tokens), else to the
-mma.sync kernel (head size 64 or 128, any page size), else to the CUDA-core
-kernel, which takes every shape and is the only one used in 32-bit.
+mma.sync kernel (head size 64 or 128, any page size); single tokens to the TMA
+decode kernel (groups up to 16, pages of 8 .. 64), else to the cp.async one; and
+what none of them takes to the CUDA-core kernel, which takes every shape and is
+the only one used in 32-bit.  (A block of the built-in parts makes the same
+choices in csrc/block.cu.)
 """
 from __future__ import annotations
 

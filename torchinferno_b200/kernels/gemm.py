@@ -1,9 +1,10 @@
 """Matrix products of the projections: out = x . w^T with w stored [out, in].
 
 32-bit operands go to the engine's own CUDA-core kernel (true fp32, fixed k
-order).  bfloat16 operands go to the hand-written tensor-core kernels where one
-takes the shape and otherwise to cuBLAS, which is where the reference sends
-every projection (``F.linear``: src/torchinferno/models/llama3/pipeline.py:206-208,
+order).  bfloat16 operands go to the hand-written tensor-core kernels where they
+were measured faster (or everywhere, on request) and otherwise to cuBLAS, called
+from the engine's library (csrc/library_gemm.cu), which is where the reference
+sends every projection (``F.linear``: src/torchinferno/models/llama3/pipeline.py:206-208,
 src/torchinferno/models/llama3/tensor_parallel.py:11176-11198).
 """
 from __future__ import annotations
