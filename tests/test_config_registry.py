@@ -126,3 +126,15 @@ def test_model_spec_is_data_and_checks_its_schedule():
         dataclasses.replace(spec, schedule=(LayerCall(0, 0), LayerCall(1, 0)))
     with pytest.raises(ValueError, match="names layer"):
         dataclasses.replace(spec, schedule=(LayerCall(7, 0),))
+
+
+def test_engine_config_keeps_the_reference_names_and_checks_its_values():
+    """Names and defaults of src/torchinferno/engine/config.py:40-61 where the reference has them."""
+    from torchinferno_b200.config.engine_config import EngineConfig
+    c = EngineConfig(model="m")
+    assert (c.model_kind, c.dtype, c.cache_backend, c.page_size, c.max_batch_size) == ("auto", "auto", "paged", 16, 64)
+    assert c.async_scheduling and c.use_cuda_graphs and c.gemm_backend == "auto" and c.cache_memory_fraction == 0.9
+    for bad in (dict(cache_backend="dense"), dict(page_size=0), dict(max_batch_size=0), dict(max_num_batched_tokens=0),
+                dict(cache_memory_fraction=0.0), dict(cache_memory_fraction=1.5)):
+        with pytest.raises(ValueError):
+            EngineConfig(model="m", **bad)

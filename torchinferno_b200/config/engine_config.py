@@ -27,7 +27,8 @@ class EngineConfig:
     max_num_batched_tokens: int = 8192      # token budget of one step
     prefill_chunk_size: int | None = 2048   # longest prompt portion in one step
     num_pages: int | None = None            # pages per cache group; default from kv_cache_tokens
-    kv_cache_tokens: int | None = None      # pool size in tokens; default max_batch_size * max_model_len
+    kv_cache_tokens: int | None = None      # pool size in tokens; default max_batch_size * max_model_len, capped by memory
+    cache_memory_fraction: float = 0.9      # of the free device memory, the most the default pool may take
     seed: int = 0
     use_cuda_graphs: bool = True
     async_scheduling: bool = True           # launch the next decode step before the host has read this one's tokens
@@ -36,5 +37,7 @@ class EngineConfig:
     def __post_init__(self) -> None:
         if self.cache_backend != "paged":
             raise ValueError(f"cache_backend={self.cache_backend!r}: only 'paged' exists in this engine")
+        if not 0.0 < self.cache_memory_fraction <= 1.0:
+            raise ValueError("cache_memory_fraction must lie in (0, 1]")
         if self.page_size < 1 or self.max_batch_size < 1 or self.max_num_batched_tokens < 1:
             raise ValueError("page_size, max_batch_size and max_num_batched_tokens must be positive")

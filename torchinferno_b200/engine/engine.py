@@ -63,7 +63,7 @@ class InferenceEngine:
         if config.num_pages is not None:
             num_pages = config.num_pages
         else:
-            tokens = config.kv_cache_tokens or config.max_batch_size * limit
+            tokens = config.kv_cache_tokens or _default_cache_tokens(model, config, limit)
             num_pages = -(-tokens // config.page_size) + config.max_batch_size
         self.runner = make_runner(model, page_size=config.page_size, num_pages=num_pages,
                                   max_requests=config.max_batch_size, max_request_tokens=limit, check_errors=False)
@@ -249,6 +249,22 @@ class InferenceEngine:
             outputs.append(GenerateOutput(r.request_id, tuple(ids), self._decode(ids),
                                           reasons.get(r.request_id, "cancelled"), Usage(prompts[r.request_id], len(ids))))
         return outputs
+
+
+def _default_cache_tokens(model, config: EngineConfig, limit: int) -> int:
+    """The pool when no size is given: room for every request at its longest, but no more than
+    ``cache_memory_fraction`` of the device memory that is free once the weights are loaded (the reference sizes
+    its pool as max_active x ceil(max_seq / page) + 8 pages whatever that costs:
+    src/torchinferno/runtime/paged_serving.py:749-752)."""
+    wanted = config.max_batch_size * limit
+    if model.device.type != "cuda":
+        return wanted
+    per_token = sum(2 * spec.kv_heads * spec.head_dim for spec in model.cache_requirements()) * torch.empty((), dtype=model.dtype).element_size()
+    free, _ = torch.cuda.mem_get_info(model.device)
+    fits = int(free * config.cache_memory_fraction) // max(1, per_token)
+    if fits < config.page_size:
+        raise RuntimeError(f"no room for a cache: {free / 2**30:.1f} GiB are free and a token takes {per_token} bytes")
+    return min(wanted, fits)
 
 
 def _load_tokenizer(config: EngineConfig):
