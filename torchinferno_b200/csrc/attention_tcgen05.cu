@@ -131,6 +131,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const uint32_t tmem_base = *tmem_slot_ptr;
   const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 256;   // S buffer b at tmem_s + 128 b
 
+  // Placed early (programmatic dependent launch), the block has set itself up by now; what the kernel before
+  // writes (the queries, the newest keys and values) is only touched from here on.
+  if (warp != 1) pdl_wait();
   if (warp == 0 || warp == kFaValueWarp) {
     // Two producer warps, one for the keys (and the queries) and one for the values, each with a ring of its
     // own: a copy of one page is one TMA instruction per 64-wide half, and at 16-token pages the issue rate of
@@ -429,7 +432,7 @@ static int launch_fa(const void* q, const void* pool, void* out, FaArgs& a, int 
   const int row_tiles = ceil_div(max_q_len, tok_per_tile);
   if (row_tiles > 65535) return TIB_E_SIZE;
   dim3 grid(a.kv_heads, n_entries, row_tiles);
-  kern<<<grid, kFaThreads, FaSmem<D>::kTotal, stream>>>(map_q, map_kv, (__nv_bfloat16*)out, a);
+  TIB_LAUNCH_DEPENDENT(kern, grid, kFaThreads, FaSmem<D>::kTotal, stream, map_q, map_kv, (__nv_bfloat16*)out, a);
   TIB_LAUNCH_CHECK();
   return TIB_OK;
 }
