@@ -110,6 +110,47 @@ def test_programmatic_dependent_launch_changes_no_token(model_folders):
     assert got[True] == got[False]
 
 
+def test_many_requests_on_a_tight_pool_do_not_depend_on_how_they_are_scheduled(model_folders):
+    """Tiny B, fp32: forty requests of random lengths (1..90 prompt tokens, 1..40 new tokens, some at a temperature,
+    some with a stop token that really occurs), more than the slots and pages hold at once, so that requests wait,
+    are cut into portions, are preempted and recomputed.  Every way of running them (async scheduling on and off,
+    large and small token budgets and portions, pools of two sizes) must give each request the tokens it gets when
+    it runs alone."""
+    need_gpu()
+    import random
+    config, seed = TINY["B"]
+    rng = random.Random(7)
+    lengths = [rng.randint(1, 90) for _ in range(40)]
+    prompts = list(requests_for(config, seed, lengths).values())
+    budgets = [rng.randint(1, 40) for _ in prompts]
+    temps = [0.0 if rng.random() < 0.6 else 0.9 for _ in prompts]
+
+    def make(stops):
+        from torchinferno_b200.engine.types import GenerateRequest, SamplingConfig
+        return [GenerateRequest(f"q{i}", prompt_token_ids=p, sampling=SamplingConfig(budgets[i], temps[i], stops[i], 100 + i))
+                for i, p in enumerate(prompts)]
+
+    with engine_for(model_folders["B"], "float32", page_size=16, max_batch_size=2, kv_cache_tokens=512) as engine:
+        alone = [engine.generate(r) for r in make([()] * len(prompts))]
+        # a stop token that occurs: the token in the middle of what the request generates alone
+        stops = [(o.token_ids[len(o.token_ids) // 2],) if i % 3 == 0 and len(o.token_ids) > 2 else () for i, o in enumerate(alone)]
+        want = [engine.generate(r) for r in make(stops)]
+    assert any(o.finish_reason == "stop" for o in want) and any(o.finish_reason == "length" for o in want)
+    ways = [dict(async_scheduling=True, max_batch_size=8, kv_cache_tokens=400, max_num_batched_tokens=64, prefill_chunk_size=24),
+            dict(async_scheduling=False, max_batch_size=8, kv_cache_tokens=400, max_num_batched_tokens=64, prefill_chunk_size=24),
+            dict(async_scheduling=True, max_batch_size=5, kv_cache_tokens=260, max_num_batched_tokens=33, prefill_chunk_size=7),
+            dict(async_scheduling=True, max_batch_size=16, kv_cache_tokens=2000, max_num_batched_tokens=4096, prefill_chunk_size=2048)]
+    preempted = 0
+    for options in ways:
+        with engine_for(model_folders["B"], "float32", page_size=16, **options) as engine:
+            got = engine.generate_many(make(stops))
+            preempted += engine.scheduler.stats["preemptions"]
+            engine.runner.cache.audit()
+            assert engine.runner.cache.free_pages() == [engine.runner.cache.num_pages]
+        assert [(o.token_ids, o.finish_reason) for o in got] == [(o.token_ids, o.finish_reason) for o in want], options
+    assert preempted > 0                                   # the tight pools really ran out
+
+
 def test_the_engine_sees_an_error_word_that_a_kernel_set(model_folders):
     """The kernels report a page id outside its pool or a bounded wait that ran out in one device word; the
     engine reads it with the step's tokens.  Here the word is set from the host (no kernel is made to fail)."""
