@@ -150,6 +150,26 @@ def test_gemm_tcgen05(m, n, k, out_dtype):
         ops.gemm_tcgen05(dev(rnd(4, 96, dtype=torch.bfloat16)), dev(rnd(8, 96, dtype=torch.bfloat16)), torch.empty(4, 8, dtype=out_dtype, device="cuda"))
 
 
+@pytest.mark.parametrize("m, n, k", [(256, 256, 64), (1, 8, 64), (200, 520, 192), (77, 1000, 4096), (600, 264, 1024), (2048, 512, 14336),
+                                     (515, 1288, 512)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05_on_pairs_of_sms(m, n, k, out_dtype):
+    """The `cta_group::2` product (two blocks per 256 x 256 tile) against float64: one tile, rows and columns that
+    do not fill the tiles (among them tiles whose second block has no rows at all), a long K, more tiles than
+    pairs of SMs take in one round, and both output types."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    x, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, scale=0.05, seed=3)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.gemm_tcgen05_2cta(dev(x), dev(w), torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda"), err)
+    assert int(err) == 0                                   # no bounded wait ran out
+    want = (x.cuda().double() @ w.cuda().double().T).cpu()
+    bound = (1e-2 if out_dtype == torch.bfloat16 else 2e-5) * want.abs().max() + 1e-6
+    assert (as_ref(out) - want).abs().max() <= bound
+    with pytest.raises(ops.KernelError, match="size"):     # K must be a multiple of 64
+        ops.gemm_tcgen05_2cta(dev(rnd(4, 96, dtype=torch.bfloat16)), dev(rnd(8, 96, dtype=torch.bfloat16)), torch.empty(4, 8, dtype=out_dtype, device="cuda"))
+
+
 # -------------------------------------------------------------- RoPE + KV
 def paged_layout(n_requests, lengths, page_size, kv_heads, d, dtype, spare_pages=3, seed=0):
     """A pool with NaN everywhere, shuffled page ids, and block tables for the given lengths."""

@@ -134,6 +134,8 @@ def run_gemm(args) -> None:
             report(f"gemm_tcgen05_swapab[{name}]", timer(lambda: ops.gemm_tcgen05_swapab(x, w, out)), **common)
         elif ops.gemm_tcgen05_supports(args.rows, n, k):
             report(f"gemm_tcgen05[{name}]", timer(lambda: ops.gemm_tcgen05(x, w, out)), **common)
+            if args.rows >= 128 and ops.gemm_tcgen05_2cta_supports(args.rows, n, k):
+                report(f"gemm_tcgen05_2cta[{name}]", timer(lambda: ops.gemm_tcgen05_2cta(x, w, out)), **common)
         report(f"library_gemm[{name}]", timer(lambda: torch.mm(x, w.t(), out=out)), **common)
 
 

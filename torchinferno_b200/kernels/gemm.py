@@ -21,11 +21,13 @@ from torchinferno_b200.kernels import ops
 #              (LinearWeight(few_rows_tcgen05=True): the attention output projection does); everything
 #              else goes to cuBLAS (SWAPAB_AUTO_ROWS = 0).  All hand-written kernels: "tcgen05"
 #   "tcgen05"  the hand-written kernels wherever they take the shape (swap-AB up to 64 rows, the
-#              128 x 256-tile kernel above)
+#              128 x 256-tile kernel above, and from 256 rows the two-SM kernel on 256 x 256 tiles)
 #   "library"  cuBLAS everywhere
 _backend = "auto"
 _error_word: torch.Tensor | None = None
 SWAPAB_AUTO_ROWS = 0
+TWO_CTA_ROWS = 256
+TWO_CTA_MAX_N = 65536
 
 
 def set_backend(name: str) -> None:
@@ -135,6 +137,10 @@ def _linear_bf16(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
         if aligned and _backend == "tcgen05" and ops.gemm_tcgen05_supports(m, n, k):
             if out is None or out.dtype != out_dtype:
                 out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+            # from 256 rows on, pairs of SMs on 256 x 256 tiles (7 to 14 % ahead of one block per 128 x 256 tile on
+            # the layers' shapes at 2,048 rows; the one-block kernel keeps the widest shape, the head)
+            if m >= TWO_CTA_ROWS and n <= TWO_CTA_MAX_N and ops.gemm_tcgen05_2cta_supports(m, n, k):
+                return ops.gemm_tcgen05_2cta(x, weight, out, _error_word)
             return ops.gemm_tcgen05(x, weight, out, _error_word)
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise ops.KernelError(f"linear: unsupported output dtype {out_dtype}")

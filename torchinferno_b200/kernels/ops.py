@@ -98,7 +98,7 @@ def lib() -> ctypes.CDLL:
                    "tib_attention_mma_supports", "tib_prefill_attention", "tib_decode_attention",
                    "tib_prefill_attention_tcgen05", "tib_prefill_attention_tcgen05_supports",
                    "tib_decode_attention_tma", "tib_decode_attention_tma_supports", "tib_set_dependent_launch",
-                   "tib_blas_init", "tib_blas_gemm",
+                   "tib_blas_init", "tib_blas_gemm", "tib_gemm_tcgen05_2cta", "tib_gemm_tcgen05_2cta_supports",
                    "tib_gemm_skinny", "tib_gemm_skinny_supports", "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
                    "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports"):
             getattr(library, fn).restype = c_int
@@ -491,6 +491,25 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, error_word
     _check("gemm_tcgen05", lib().tib_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k),
                                                   c_int64(x.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)),
                                                   c_int(_code(out.dtype)), _ptr(error_word), _stream()))
+    return out
+
+
+def gemm_tcgen05_2cta_supports(m: int, n: int, k: int) -> bool:
+    return bool(lib().tib_gemm_tcgen05_2cta_supports(c_int(m), c_int(n), c_int(k)))
+
+
+def gemm_tcgen05_2cta(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, error_word: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, N] (bf16 or fp32) = x[M, K] . w[N, K]^T on pairs of SMs (`tcgen05.mma.cta_group::2`, 256 x 256 tiles)."""
+    for name, t in (("x", x), ("w", w)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gemm_tcgen05_2cta: {name} must be a 2-D bf16 CUDA tensor with unit inner stride")
+    _need(out, "out")
+    (m, k), (n, k2) = x.shape, w.shape
+    if k != k2 or out.shape != (m, n):
+        raise KernelError(f"gemm_tcgen05_2cta: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    _check("gemm_tcgen05_2cta", lib().tib_gemm_tcgen05_2cta(_ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k),
+                                                            c_int64(x.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)),
+                                                            c_int(_code(out.dtype)), _ptr(error_word), _stream()))
     return out
 
 
