@@ -21,14 +21,19 @@
 
 namespace tib {
 
-constexpr int kT2BM = 256, kT2BN = 256, kT2BK = 64, kT2Stages = 6;
+// The tile is 256 rows by BN columns, BN = 256 or 224: with 74 pairs of SMs a shape whose tiles do not fill the
+// last round runs that round nearly empty, and the narrower tile can make the rounds come out even (the gate/up
+// projection at 2,048 rows: 896 tiles = 12.1 rounds of 256 columns, or 1,024 tiles = 13.8 rounds of 224).
+constexpr int kT2BM = 256, kT2BK = 64, kT2Stages = 6;
 constexpr int kT2Threads = 192;
 constexpr uint32_t kT2ABytes = 128 * kT2BK * 2;                   // this block's rows of x: 16 KB
-constexpr uint32_t kT2BBytes = 128 * kT2BK * 2;                   // this block's rows of w: 16 KB
-constexpr uint32_t kT2StageBytes = kT2ABytes + kT2BBytes;
+constexpr uint32_t kT2StageBytes = kT2ABytes + 128 * kT2BK * 2;   // and at most 128 rows of w
 constexpr uint32_t kT2SmemBytes = kT2Stages * kT2StageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int kT2AccStride = 256;                                 // TMEM columns between the two accumulators
 // D fp32, A and B bf16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24 (M = 256 over the pair)
-constexpr uint32_t kT2Idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kT2BN >> 3) << 17) | ((uint32_t)(kT2BM >> 4) << 24);
+constexpr uint32_t t2_idesc(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kT2BM >> 4) << 24);
+}
 
 __device__ __forceinline__ uint32_t t2_cluster_rank() {
   uint32_t r;
@@ -49,10 +54,10 @@ __device__ __forceinline__ void t2_tma_load(uint32_t dst, const CUtensorMap* map
   asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(cluster_bar) : "memory");
 }
-__device__ __forceinline__ void t2_umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void t2_umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
                "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kT2Idesc), "r"(accumulate) : "memory");
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // Arrive, once the MMAs issued so far are done, on the barrier at this offset in both blocks of the pair.
 __device__ __forceinline__ void t2_commit_both(uint32_t bar) {
@@ -74,7 +79,7 @@ __device__ __forceinline__ bool t2_wait_cluster(uint32_t bar, uint32_t parity) {
 
 // Persistent: pair p walks the tiles t = p, p + pairs, ...; tile t is row tile t % m_tiles of column tile
 // t / m_tiles, so pairs that run together share slices of w through the L2.
-template <typename TOut>
+template <int BN, typename TOut>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kT2Threads, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                          TOut* __restrict__ out, int M, int N, int K, int64_t ldo, int* __restrict__ error_word) {
@@ -92,7 +97,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   const uint32_t rank = t2_cluster_rank();                 // 0: the even block of the pair, which issues the MMAs
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
   const int k_blocks = K / kT2BK;
-  const int m_tiles = (M + kT2BM - 1) / kT2BM, n_tiles = (N + kT2BN - 1) / kT2BN;
+  constexpr uint32_t kBBytes = (BN / 2) * kT2BK * 2;       // this block's rows of w
+  const int m_tiles = (M + kT2BM - 1) / kT2BM, n_tiles = (N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
 
   if (threadIdx.x == 0) {
@@ -107,7 +113,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tmem_slot), "r"(2u * kT2BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tmem_slot), "r"(2u * kT2AccStride) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -121,7 +127,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       uint32_t it = 0;
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += pairs) {
-        const int m0 = (t % m_tiles) * kT2BM + (int)rank * 128, n0 = (t / m_tiles) * kT2BN + (int)rank * 128;
+        const int m0 = (t % m_tiles) * kT2BM + (int)rank * 128, n0 = (t / m_tiles) * BN + (int)rank * (BN / 2);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kT2Stages;
           const uint32_t phase = (it / kT2Stages) & 1;
@@ -130,7 +136,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             ok = false;
             break;
           }
-          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * kT2StageBytes);
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * (kT2ABytes + kBBytes));
           const uint32_t a_dst = base + s * kT2StageBytes, b_dst = a_dst + kT2ABytes;
           const uint32_t bar0 = t2_map(full_bar(s), 0);
           t2_tma_load(a_dst, &map_x, kb * kT2BK, m0, bar0);
@@ -145,7 +151,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       int j = 0;
       for (int t = pair; t < num_tiles && ok; t += pairs, ++j) {
         const int b = j & 1;
-        const uint32_t tmem_acc = tmem_base + b * kT2BN;
+        const uint32_t tmem_acc = tmem_base + b * kT2AccStride;
         if (!t2_wait_cluster(acc_empty_bar(b), ((j >> 1) & 1) ^ 1)) {   // both epilogues have drained this accumulator
           if (error_word) atomicExch(error_word, 0x7C0044);
           ok = false;
@@ -164,7 +170,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
           const uint32_t a_src = base + s * kT2StageBytes, b_src = a_src + kT2ABytes;
 #pragma unroll
           for (int k = 0; k < kT2BK / 16; ++k)
-            t2_umma(tmem_acc, umma_desc_k128(a_src + k * 32), umma_desc_k128(b_src + k * 32), (kb | k) != 0);
+            t2_umma(tmem_acc, umma_desc_k128(a_src + k * 32), umma_desc_k128(b_src + k * 32), t2_idesc(BN), (kb | k) != 0);
           t2_commit_both(empty_bar(s));   // the stage is free in both blocks once these MMAs have read it
         }
         t2_commit_both(acc_full_bar(b));  // (also on failure, so that the epilogues do not wait in vain)
@@ -174,7 +180,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     const int quarter = warp & 3;
     int j = 0;
     for (int t = pair; t < num_tiles; t += pairs, ++j) {
-      const int m0 = (t % m_tiles) * kT2BM + (int)rank * 128, n0 = (t / m_tiles) * kT2BN;
+      const int m0 = (t % m_tiles) * kT2BM + (int)rank * 128, n0 = (t / m_tiles) * BN;
       const int b = j & 1;
       const int row = m0 + quarter * 32 + lane;
       if (!mbar_wait(acc_full_bar(b), (j >> 1) & 1)) {
@@ -183,9 +189,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll 1
-      for (int c = 0; c < kT2BN / 32; ++c) {
+      for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + b * kT2BN + c * 32, v);
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + b * kT2AccStride + c * 32, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
         const int col = n0 + c * 32;
         if (row < M && col < N) {
@@ -219,16 +225,16 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   t2_cluster_sync();   // neither block leaves (or frees tensor memory) while its partner may still signal it
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2u * kT2BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2u * kT2AccStride) : "memory");
   }
 }
 
-static int make_map_2cta(CUtensorMap* map, const void* ptr, int rows, int K, int64_t ld) {
+static int make_map_2cta(CUtensorMap* map, const void* ptr, int rows, int K, int64_t ld, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return TIB_E_ARG;
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)kT2BK, 128u};
+  const cuuint32_t box[2] = {(cuuint32_t)kT2BK, (cuuint32_t)box_rows};
   const cuuint32_t elem[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -236,24 +242,51 @@ static int make_map_2cta(CUtensorMap* map, const void* ptr, int rows, int K, int
   return r == CUDA_SUCCESS ? TIB_OK : TIB_E_ARG;
 }
 
-template <typename TOut>
-static int launch_2cta(const CUtensorMap& map_x, const CUtensorMap& map_w, void* out, int M, int N, int K, int64_t ldo,
+static int t2_pairs() {
+  static int pairs = 0;
+  if (pairs == 0) {
+    int device = 0, sms = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    pairs = sms / 2 > 0 ? sms / 2 : 1;
+  }
+  return pairs;
+}
+
+// The tile width whose rounds over the pairs of SMs cost least: rounds x (width + a little for each tile's start).
+static int t2_tile_width(int M, int N) {
+  const int pairs = t2_pairs(), m_tiles = ceil_div(M, kT2BM);
+  const int widths[2] = {256, 224};
+  int best = 256;
+  long best_cost = -1;
+  for (int bn : widths) {
+    const long rounds = ceil_div(m_tiles * ceil_div(N, bn), pairs);
+    const long cost = rounds * (bn + 16);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+template <int BN, typename TOut>
+static int launch_2cta(const void* x, const void* w, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo,
                        int* error_word, cudaStream_t stream) {
-  auto kern = gemm_tcgen05_2cta_kernel<TOut>;
+  CUtensorMap map_x, map_w;
+  int rc = make_map_2cta(&map_x, x, M, K, ldx, 128);
+  if (rc != TIB_OK) return rc;
+  rc = make_map_2cta(&map_w, w, N, K, ldw, BN / 2);
+  if (rc != TIB_OK) return rc;
+  auto kern = gemm_tcgen05_2cta_kernel<BN, TOut>;
   static bool configured = false;
-  static int sms = 0;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kT2SmemBytes);
     if (e != cudaSuccess) return (int)e;
-    int device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     configured = true;
   }
-  const int tiles = ceil_div(M, kT2BM) * ceil_div(N, kT2BN);
-  int pairs = sms / 2;
-  if (pairs > tiles) pairs = tiles;
-  if (pairs < 1) pairs = 1;
+  const int tiles = ceil_div(M, kT2BM) * ceil_div(N, BN);
+  const int pairs = tiles < t2_pairs() ? tiles : t2_pairs();
   kern<<<2 * pairs, kT2Threads, kT2SmemBytes, stream>>>(map_x, map_w, (TOut*)out, M, N, K, ldo, error_word);
   TIB_LAUNCH_CHECK();
   return TIB_OK;
@@ -278,11 +311,10 @@ TIB_API int tib_gemm_tcgen05_2cta(const void* x, const void* w, void* out, int M
   if (out_dtype == TIB_BF16 && ((((uintptr_t)out) & 15) || ldo % 8)) return TIB_E_ALIGN;
   if (out_dtype == TIB_F32 && ((((uintptr_t)out) & 15) || ldo % 4)) return TIB_E_ALIGN;
   if (out_dtype != TIB_BF16 && out_dtype != TIB_F32) return TIB_E_DTYPE;
-  CUtensorMap map_x, map_w;
-  int rc = make_map_2cta(&map_x, x, M, K, ldx);
-  if (rc != TIB_OK) return rc;
-  rc = make_map_2cta(&map_w, w, N, K, ldw);
-  if (rc != TIB_OK) return rc;
-  return out_dtype == TIB_BF16 ? launch_2cta<__nv_bfloat16>(map_x, map_w, out, M, N, K, ldo, error_word, stream)
-                               : launch_2cta<float>(map_x, map_w, out, M, N, K, ldo, error_word, stream);
+  const bool wide = t2_tile_width(M, N) == 256;
+  if (out_dtype == TIB_BF16)
+    return wide ? launch_2cta<256, __nv_bfloat16>(x, w, out, M, N, K, ldx, ldw, ldo, error_word, stream)
+                : launch_2cta<224, __nv_bfloat16>(x, w, out, M, N, K, ldx, ldw, ldo, error_word, stream);
+  return wide ? launch_2cta<256, float>(x, w, out, M, N, K, ldx, ldw, ldo, error_word, stream)
+              : launch_2cta<224, float>(x, w, out, M, N, K, ldx, ldw, ldo, error_word, stream);
 }
