@@ -60,3 +60,36 @@ def test_large_layer_sizes_under_every_cut(large_folder, large_reference, dtype)
                 assert err <= bound, f"{maker.__name__} {name}@{pos} ({dtype}): {err:.3e} > {bound:.3e}"
         del replayer
         torch.cuda.empty_cache()
+
+
+def test_long_decoding_at_these_sizes_is_the_same_with_and_without_dependent_launch(large_folder):
+    """At the 8B layer sizes kernels really overlap when they are launched as dependents (the decode attention
+    fetches old keys while the rotary kernel runs, the output projection its weights while the attention drains).
+    300 decoded tokens for 1 and for 8 requests at contexts of 600 to 1,200 tokens must come out the same with
+    that switched off, and the same when run again."""
+    need_gpu()
+    from torchinferno_b200.engine.batch import StepEntry
+    from torchinferno_b200.engine.factory import load_model, make_runner
+    from torchinferno_b200.kernels import ops
+    model = load_model(large_folder, dtype="bfloat16")
+    histories = {}
+    try:
+        with torch.inference_mode():
+            for on in (True, False, True):
+                ops.set_dependent_launch(on)
+                for batch in (1, 8):
+                    runner = make_runner(model, page_size=16, max_tokens=batch * 1300, max_requests=batch)
+                    g = torch.Generator().manual_seed(batch)
+                    firsts = []
+                    for i in range(batch):
+                        prompt = torch.randint(0, LARGE["vocab_size"], (600 + 37 * i,), generator=g).tolist()
+                        firsts.append(int(runner.step([StepEntry(i, prompt, [len(prompt) - 1])]).argmax()))
+                    history = runner.decode_loop(list(range(batch)), firsts, 300).cpu()
+                    runner.raise_on_device_error()
+                    if (batch, on) in histories:
+                        assert torch.equal(histories[(batch, on)], history)
+                    histories[(batch, on)] = history
+    finally:
+        ops.set_dependent_launch(True)
+    for batch in (1, 8):
+        assert torch.equal(histories[(batch, True)], histories[(batch, False)])
