@@ -101,18 +101,19 @@ rope_append_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
                           __nv_bfloat16* __restrict__ pool, const int* __restrict__ positions,
                           const int* __restrict__ token_slot, const int* __restrict__ block_table,
                           int table_stride, const float* __restrict__ inv_freq, int heads, int kv_heads,
-                          int head_dim, int page_size, int64_t page_stride, int num_pages, int write_kv,
+                          int head_dim, int chunk_shift, int page_size, int64_t page_stride, int num_pages, int write_kv,
                           int* __restrict__ error_word) {
   pdl_wait();
   pdl_trigger();
-  extern __shared__ float cs[];  // cos[d/2], sin[d/2]
+  extern __shared__ __align__(16) float cs[];  // cos[d/2], sin[d/2]
   const int tok = blockIdx.x;
   const int pos = positions[tok];
   const int half = head_dim >> 1;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    const float ang = (float)pos * inv_freq[i];
-    cs[i] = cosf(ang);
-    cs[half + i] = sinf(ang);
+    float sn, cn;
+    sincosf((float)pos * inv_freq[i], &sn, &cn);   // (the accurate one: angles reach 10^5 radians)
+    cs[i] = cn;
+    cs[half + i] = sn;
   }
   __syncthreads();
   const int q_width = heads * head_dim, kv_width = kv_heads * head_dim;
@@ -132,7 +133,8 @@ rope_append_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
   }
   const int rot_heads = heads + (write_kv ? kv_heads : 0);
   for (int w = threadIdx.x; w < rot_heads * chunks; w += blockDim.x) {
-    const int hh = w / chunks, c = (w - hh * chunks) << 3;
+    // (chunk_shift: log2 of the work items per head when that is a power of two, else -1)
+    const int hh = chunk_shift >= 0 ? w >> chunk_shift : w / chunks, c = (w - hh * chunks) << 3;
     const __nv_bfloat16* src = row + hh * head_dim;   // q heads then k heads are contiguous in qkv
     __nv_bfloat16* dst = hh < heads ? q_out + (size_t)tok * q_width + hh * head_dim
                                     : kpage + ((size_t)(hh - heads) * page_size + off) * head_dim;
@@ -142,10 +144,15 @@ rope_append_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
     uint4 lo_out, hi_out;
     __nv_bfloat162* lo2 = reinterpret_cast<__nv_bfloat162*>(&lo_out);
     __nv_bfloat162* hi2 = reinterpret_cast<__nv_bfloat162*>(&hi_out);
+    float cv[8], sv[8];                                // cos and sin of this item's eight dims: four 16-byte loads
+    *reinterpret_cast<float4*>(cv) = *reinterpret_cast<const float4*>(cs + c);
+    *reinterpret_cast<float4*>(cv + 4) = *reinterpret_cast<const float4*>(cs + c + 4);
+    *reinterpret_cast<float4*>(sv) = *reinterpret_cast<const float4*>(cs + half + c);
+    *reinterpret_cast<float4*>(sv + 4) = *reinterpret_cast<const float4*>(cs + half + c + 4);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float2 lo = __bfloat1622float2(l2[k]), hi = __bfloat1622float2(h2[k]);
-      const float c0 = cs[c + 2 * k], c1 = cs[c + 2 * k + 1], s0 = cs[half + c + 2 * k], s1 = cs[half + c + 2 * k + 1];
+      const float c0 = cv[2 * k], c1 = cv[2 * k + 1], s0 = sv[2 * k], s1 = sv[2 * k + 1];
       lo2[k] = __floats2bfloat162_rn(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
       hi2[k] = __floats2bfloat162_rn(hi.x * c0 + lo.x * s0, hi.y * c1 + lo.y * s1);
     }
@@ -157,7 +164,7 @@ rope_append_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
   const __nv_bfloat16* vsrc = row + q_width + kv_width;
   const int vchunks = head_dim >> 3;
   for (int w = threadIdx.x; w < kv_heads * vchunks; w += blockDim.x) {
-    const int hh = w / vchunks, c = (w - hh * vchunks) << 3;
+    const int hh = chunk_shift >= 0 ? w >> (chunk_shift + 1) : w / vchunks, c = (w - hh * vchunks) << 3;
     *reinterpret_cast<uint4*>(vpage + ((size_t)hh * page_size + off) * head_dim + c) =
         *reinterpret_cast<const uint4*>(vsrc + hh * head_dim + c);
   }
@@ -184,6 +191,9 @@ TIB_API int tib_rope_append(const void* qkv, void* q_out, void* pool, const int*
   const int threads = 256;
   const size_t smem = (size_t)rot_dim * sizeof(float);
   if (smem > 48 * 1024) return TIB_E_SMEM;
+  int chunk_shift = -1;                                  // log2(head_dim / 16) when that is a power of two
+  for (int sft = 0; sft < 16; ++sft)
+    if ((16 << sft) == head_dim) chunk_shift = sft;
   if (dtype == TIB_F32)
     TIB_LAUNCH_DEPENDENT(rope_append_kernel<float>, n_tokens, threads, smem, stream,
         (const float*)qkv, (float*)q_out, (float*)pool, positions, token_slot, block_table,
@@ -193,7 +203,7 @@ TIB_API int tib_rope_append(const void* qkv, void* q_out, void* pool, const int*
            (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pool) & 15) == 0 && (page_stride % 8 == 0 || !write_kv))
     TIB_LAUNCH_DEPENDENT(rope_append_bf16x8_kernel, n_tokens, threads, smem, stream,
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, positions, token_slot, block_table,
-        table_stride, inv_freq, heads, kv_heads, head_dim, page_size, page_stride, num_pages, write_kv, error_word);
+        table_stride, inv_freq, heads, kv_heads, head_dim, chunk_shift, page_size, page_stride, num_pages, write_kv, error_word);
   else if (dtype == TIB_BF16)
     TIB_LAUNCH_DEPENDENT(rope_append_kernel<__nv_bfloat16>, n_tokens, threads, smem, stream,
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, positions,
