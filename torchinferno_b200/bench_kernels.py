@@ -90,7 +90,7 @@ def run_decode_attention(args) -> None:
     kv_bytes = n * args.context * 2 * k * d * 2
     kernels = ["cp_async"] + (["tma"] if ops.decode_attention_tma_supports(d, h // k, args.page_size) else [])
     for forced in (args.splits or [None]):
-        splits, chunk = (ops.decode_num_splits(n, h, k) if forced is None else forced), 0
+        splits, chunk = (ops.decode_num_splits(n, h, k, args.context) if forced is None else forced), 0
         scratch = torch.empty(n * h * splits * (d + 2), dtype=torch.float32, device="cuda")
         for kernel in kernels:
             fn = lambda: ops.decode_attention(q, pool, out, q_start, kv_start, slots, table, n, h, k, d, 1 / math.sqrt(d),

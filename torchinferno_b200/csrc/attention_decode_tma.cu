@@ -23,6 +23,7 @@ namespace tib {
 constexpr int kDtBN = 64;               // keys per tile
 constexpr int kDtConsumers = 4;         // warps; each takes kDtBN / 4 = 16 keys of a tile
 constexpr int kDtThreads = 32 * (1 + kDtConsumers);
+constexpr int kDtMinPart = 192;         // keys: a context is not cut into parts shorter than this (three tiles)
 
 struct DtArgs {
   const int* q_start;
@@ -99,8 +100,16 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
   const int first_key = a.window > 0 ? max(0, pos - a.window + 1) : 0;
   // chunk == 0: this request's own context is cut into num_splits equal parts (multiples of a tile)
   const int first_tile_key = first_key / kDtBN * kDtBN;
+  // ... but into no more parts than it has stretches of kDtMinPart keys: the grid is sized for the longest
+  // context the step may meet, and a short one leaves the blocks past its last part idle.  (Only where the
+  // parts merge themselves: the separate merge kernel reads every part.)
+  int parts = a.num_splits;
+  if (a.chunk == 0 && a.num_splits > 1 && a.counters != nullptr) {
+    parts = min(a.num_splits, max(1, (pos + 1 - first_tile_key + kDtMinPart - 1) / kDtMinPart));
+    if (split >= parts) return;
+  }
   const int chunk = a.chunk > 0 ? a.chunk
-                                : max(kDtBN, ((pos + 1 - first_tile_key + a.num_splits - 1) / a.num_splits + kDtBN - 1) / kDtBN * kDtBN);
+                                : max(kDtBN, ((pos + 1 - first_tile_key + parts - 1) / parts + kDtBN - 1) / kDtBN * kDtBN);
   const int kb = first_tile_key + split * chunk;
   const int ke = min(kb + chunk, pos + 1);               // exclusive
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -109,7 +118,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
   const bool empty_part = kb > pos;   // nothing in this part: an empty partial, which the merge ignores
   if (empty_part) {
     pdl_wait();
-    if (a.num_splits > 1 && threadIdx.x < nrows) {
+    if (parts > 1 && threadIdx.x < nrows) {
       float* ml = partial_ml + (((size_t)entry * a.heads + head0 + threadIdx.x) * a.num_splits + split) * 2;
       ml[0] = -CUDART_INF_F;
       ml[1] = 0.f;
@@ -300,7 +309,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
       acc += red_o[(w * 16 + r) * D + dd] * wgt;
       sum += red_ml[(w * 16 + r) * 2 + 1] * wgt;
     }
-    if (a.num_splits == 1) {
+    if (parts == 1) {
       out[(size_t)row0 * a.heads * D + (head0 + r) * D + dd] = __float2bfloat16_rn(acc / sum);
     } else {
       const size_t slot = ((size_t)entry * a.heads + head0 + r) * a.num_splits + split;
@@ -315,7 +324,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
 
   // The parts of one (request, kv head) count themselves in; the one that arrives last merges them all, so
   // no second kernel is needed.  The counter is left at zero for the next launch.
-  if (a.num_splits == 1 || a.counters == nullptr) return;
+  if (parts == 1 || a.counters == nullptr) return;
   __syncthreads();                       // every thread's part of the partial result is written ...
   int* counter = a.counters + (size_t)entry * a.kv_heads + kvh;
   if (threadIdx.x == 0) {
@@ -323,17 +332,17 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
     ticket_s = atomicAdd(counter, 1);
   }
   __syncthreads();
-  if (ticket_s != a.num_splits - 1) return;
+  if (ticket_s != parts - 1) return;
   __threadfence();
-  const int ns = a.num_splits;
-  const size_t slot0 = ((size_t)entry * a.heads + head0) * ns;       // (row r, part sp) is slot0 + r * ns + sp
+  const int ns = parts, stride = a.num_splits;
+  const size_t slot0 = ((size_t)entry * a.heads + head0) * stride;   // (row r, part sp) is slot0 + r * stride + sp
   if (ns <= 16) {
     // few parts: every thread asks for all it needs at once (its row's maxima and sums and its four output
     // columns of every part), so the merge costs one trip to the L2, not one per dependent step
     for (int idx = threadIdx.x; idx < nrows * (D / 4); idx += kDtThreads) {
       const int r = idx / (D / 4), d4 = idx - r * (D / 4);
-      const float2* pm = reinterpret_cast<const float2*>(partial_ml) + slot0 + r * ns;
-      const float4* po = reinterpret_cast<const float4*>(partial_o + (slot0 + r * ns) * D) + d4;
+      const float2* pm = reinterpret_cast<const float2*>(partial_ml) + slot0 + r * stride;
+      const float4* po = reinterpret_cast<const float4*>(partial_o + (slot0 + r * stride) * D) + d4;
       float2 ml[16];
       float4 ov[16];
 #pragma unroll
@@ -368,14 +377,14 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
   float* wgt_s = reinterpret_cast<float*>(smem_gen);                 // [nrows][num_splits] weights, then [nrows] 1 / sum
   for (int r = warp; r < nrows; r += kDtThreads / 32) {
     float mm = -CUDART_INF_F;
-    for (int sp = lane; sp < ns; sp += 32) mm = fmaxf(mm, __ldcg(partial_ml + (slot0 + r * ns + sp) * 2));
+    for (int sp = lane; sp < ns; sp += 32) mm = fmaxf(mm, __ldcg(partial_ml + (slot0 + r * stride + sp) * 2));
     mm = warp_max(mm);
     float sum = 0.f;
     for (int sp = lane; sp < ns; sp += 32) {
-      const float ms = __ldcg(partial_ml + (slot0 + r * ns + sp) * 2);
+      const float ms = __ldcg(partial_ml + (slot0 + r * stride + sp) * 2);
       const float w = ms == -CUDART_INF_F ? 0.f : exp2f(ms - mm);     // an empty part wrote no output
       wgt_s[r * ns + sp] = w;
-      sum += w == 0.f ? 0.f : w * __ldcg(partial_ml + (slot0 + r * ns + sp) * 2 + 1);
+      sum += w == 0.f ? 0.f : w * __ldcg(partial_ml + (slot0 + r * stride + sp) * 2 + 1);
     }
     sum = warp_sum(sum);
     if (lane == 0) wgt_s[nrows * ns + r] = 1.f / sum;
@@ -383,7 +392,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
   __syncthreads();
   for (int idx = threadIdx.x; idx < nrows * (D / 4); idx += kDtThreads) {   // four output elements per thread
     const int r = idx / (D / 4), d4 = idx - r * (D / 4);
-    const float4* po = reinterpret_cast<const float4*>(partial_o + (slot0 + r * ns) * D) + d4;
+    const float4* po = reinterpret_cast<const float4*>(partial_o + (slot0 + r * stride) * D) + d4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
     for (int sp = 0; sp < ns; ++sp) {

@@ -94,7 +94,7 @@ class StepWorkspace:
         sizes = {"normed": w.hidden, "qkv": q_width + 2 * kv_width, "q": q_width, "attn": q_width, "o_out": w.hidden,
                  "gate_up": 2 * w.intermediate, "act": w.intermediate, "out": w.hidden}
         self.buffers = {name: torch.empty((n, width), dtype=bf16, device=dev) for name, width in sizes.items()}
-        splits = ops.decode_num_splits(batch.n_entries, w.heads, w.kv_heads) if batch.n_single else 1
+        splits = ops.decode_num_splits(batch.n_entries, w.heads, w.kv_heads, batch.max_kv_len) if batch.n_single else 1
         self.scratch = torch.empty(batch.n_entries * w.heads * splits * (w.head_dim + 2), dtype=torch.float32, device=dev) \
             if splits > 1 else None
         counters = ops._split_counters(dev, batch.n_entries * w.kv_heads) if splits > 1 else None

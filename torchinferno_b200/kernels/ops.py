@@ -336,14 +336,19 @@ def decode_split(n_entries: int, heads: int, kv_heads: int, max_kv_len: int, tar
     return -(-tiles // per), per * 64
 
 
-def decode_num_splits(n_entries: int, heads: int, kv_heads: int, target_blocks: int = 256, most: int = 16) -> int:
-    """How many parts each request's context is cut into when the kernel sizes the parts itself.
+def decode_num_splits(n_entries: int, heads: int, kv_heads: int, max_kv_len: int | None = None,
+                      target_blocks: int = 256) -> int:
+    """How many parts the grid provides for each request's context when the kernel sizes the parts itself.
 
     Measured on the B200 at 3,072 tokens of context (32 heads, 8 kv heads of 128): the kernel is fastest
-    with about 256 blocks in all, just under the two per SM that fit (batch 1: 16 splits, 2: 8 to 16, 4: 8,
-    8: 4, 16: 2, 32 and up: 1); more parts than 16 cost more in the merge than they gain."""
+    with about 256 blocks in all, just under the two per SM that fit (batch 1: 16 parts, 2: 8 to 16, 4: 8,
+    8: 4, 16: 2, 32 and up: 1); more than 16 parts cost more in the merge than they gain, except where the
+    context may be long (``max_kv_len`` above 8,192: one request at 32,768 tokens streams at 3.1 TB/s in 16
+    parts, 128 blocks), where up to 32 are provided.  The TMA kernel uses only as many of them as the
+    request's own context has stretches of 192 keys."""
     group = heads // kv_heads
     blocks = max(1, n_entries * kv_heads * ((group + 15) // 16))
+    most = 32 if max_kv_len is not None and max_kv_len > 8192 else 16
     return max(1, min(most, target_blocks // blocks))
 
 
@@ -366,7 +371,7 @@ def decode_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_s
     _check_attention_args(q, pool, out, q_start, kv_start, slots, block_table, n_entries, heads, kv_heads, head_dim)
     if num_splits is None or chunk is None:
         # each request's own context is cut into num_splits equal parts by the kernel (chunk 0)
-        num_splits, chunk = decode_num_splits(n_entries, heads, kv_heads), 0
+        num_splits, chunk = decode_num_splits(n_entries, heads, kv_heads, max_kv_len), 0
     elif chunk != 0 and num_splits * chunk < max_kv_len:
         raise KernelError("decode_attention: num_splits * chunk does not cover the longest context")
     scratch_o = scratch_ml = None
