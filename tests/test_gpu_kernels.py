@@ -170,6 +170,59 @@ def test_gemm_tcgen05_on_pairs_of_sms(m, n, k, out_dtype):
         ops.gemm_tcgen05_2cta(dev(rnd(4, 96, dtype=torch.bfloat16)), dev(rnd(8, 96, dtype=torch.bfloat16)), torch.empty(4, 8, dtype=out_dtype, device="cuda"))
 
 
+@pytest.mark.parametrize("m, n, k, splits", [(8, 128, 64, 0), (1, 8, 64, 1), (8, 6144, 4096, 0), (16, 4096, 4096, 4), (5, 1000, 4096, 0),
+                                             (8, 4096, 14336, 8), (33, 520, 192, 3), (64, 264, 1024, 0), (17, 28672, 512, 0),
+                                             (48, 136, 9472, 5)])
+@pytest.mark.parametrize("w_kn", [False, True])
+def test_gemm_tcgen05_swapab(m, n, k, splits, w_kn):
+    """The few-rows product (weights as the 128-row operand, K split over a cluster) against float64: one tile, a
+    ragged last tile, every padding of the rows, splits chosen and forced, more tiles than clusters, and the weights
+    stored [out, in] (K-major operand) as well as [in, out] (MN-major operand); both output types."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    x, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, scale=0.05, seed=3)
+    want = (x.cuda().double() @ w.cuda().double().T).cpu()
+    wd = dev(w.t().contiguous()) if w_kn else dev(w)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = ops.gemm_tcgen05_swapab(dev(x), wd, torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda"), err,
+                                      splits=splits, w_kn=w_kn)
+        assert int(err) == 0                               # no bounded wait ran out
+        bound = (1e-2 if out_dtype == torch.bfloat16 else 2e-5) * want.abs().max() + 1e-6
+        assert (as_ref(out) - want).abs().max() <= bound
+    with pytest.raises(ops.KernelError, match="size"):     # at most 64 rows
+        ops.gemm_tcgen05_swapab(dev(rnd(65, 64, dtype=torch.bfloat16)), dev(rnd(8, 64, dtype=torch.bfloat16)),
+                                torch.empty(65, 8, dtype=torch.bfloat16, device="cuda"))
+
+
+def test_few_rows_kernel_is_chosen_by_measurement_and_either_choice_is_right():
+    """Weights that leave their few-rows kernel open get it from tune_few_rows: one decision per shape, kept for
+    the process, the same for every weight of the shape; a slice of the weight inherits it; and whichever kernel
+    was chosen, and whichever is forced, the product is right at few and at many rows."""
+    need_gpu()
+    from torchinferno_b200.kernels import gemm
+    from torchinferno_b200.kernels.gemm import LinearWeight, linear
+    n, k = 1160, 2048
+    ws = [rnd(n, k, dtype=torch.bfloat16, scale=0.05, seed=i) for i in range(3)]
+    open_weights = [LinearWeight(dev(w), few_rows_tcgen05=None) for w in ws]
+    assert all(w.few_rows == 0 for w in open_weights)                     # the library until measured
+    decisions = gemm.tune_few_rows()
+    key = (n, k, open_weights[0].tensor.device)
+    assert key in decisions and all(w.few_rows == (LinearWeight.FEW_ROWS if decisions[key] else 0) for w in open_weights)
+    later = LinearWeight(dev(ws[0]), few_rows_tcgen05=None)
+    assert gemm.tune_few_rows()[key] == decisions[key] and later.few_rows == open_weights[0].few_rows
+    forced = [LinearWeight(dev(ws[0]), few_rows_tcgen05=True), LinearWeight(dev(ws[0]), few_rows_tcgen05=False)]
+    assert [w.few_rows for w in forced] == [LinearWeight.FEW_ROWS, 0]
+    for m in (1, 8, 16, 17, 200):
+        x = rnd(m, k, dtype=torch.bfloat16, seed=50 + m)
+        want = x.double() @ ws[0].double().T
+        for weight in (open_weights[0], later, *forced):
+            out = linear(dev(x), weight)
+            assert (as_ref(out) - want).abs().max() <= 1e-2 * want.abs().max() + 1e-6
+            part = linear(dev(x), weight.rows(64, 1096))
+            assert (as_ref(part) - want[:, 64:1096]).abs().max() <= 1e-2 * want.abs().max() + 1e-6
+
+
 # -------------------------------------------------------------- RoPE + KV
 def paged_layout(n_requests, lengths, page_size, kv_heads, d, dtype, spare_pages=3, seed=0):
     """A pool with NaN everywhere, shuffled page ids, and block tables for the given lengths."""

@@ -132,6 +132,10 @@ def run_gemm(args) -> None:
             report(f"gemm_skinny[{name}]", timer(lambda: ops.gemm_skinny(x, w, out)), **common)
         if ops.gemm_tcgen05_swapab_supports(args.rows, n, k):
             report(f"gemm_tcgen05_swapab[{name}]", timer(lambda: ops.gemm_tcgen05_swapab(x, w, out)), **common)
+            w_kn = w.t().contiguous()
+            report(f"gemm_tcgen05_swapab_kn[{name}]", timer(lambda: ops.gemm_tcgen05_swapab(x, w_kn, out, w_kn=True)), **common)
+            report(f"library_gemm_kn[{name}]", timer(lambda: torch.mm(x, w_kn, out=out)), **common)
+            del w_kn
         elif ops.gemm_tcgen05_supports(args.rows, n, k):
             report(f"gemm_tcgen05[{name}]", timer(lambda: ops.gemm_tcgen05(x, w, out)), **common)
             if args.rows >= 128 and ops.gemm_tcgen05_2cta_supports(args.rows, n, k):

@@ -5,11 +5,12 @@
 // this call when every part of the block is one of the built-in kinds, and their own sequence otherwise.
 //
 //   n  = rmsnorm(residual += pending)                      add_rmsnorm
-//   qkv = n . Wqkv^T; q, k -> rotary; k, v -> pages        library product, rope_append
+//   qkv = n . Wqkv^T; q, k -> rotary; k, v -> pages        product, rope_append
 //   a  = attention(q, pages)                               prefill (tcgen05 / mma.sync) and decode (TMA / cp.async)
-//   o  = a . Wo^T                                          swap-AB tcgen05 product at few rows, else library
+//   o  = a . Wo^T                                          product
 //   n  = rmsnorm(residual += o)                            add_rmsnorm
-//   out = (silu(n . Wg^T) * (n . Wu^T)) . Wd^T             library products, swiglu
+//   out = (silu(n . Wg^T) * (n . Wu^T)) . Wd^T             products, swiglu
+// A product is the hand-written swap-AB tcgen05 kernel up to the number of rows its weight asks for, else the library's.
 // `out` is left pending: the next block's (or the final) norm adds it
 // (src/torchinferno/models/llama3/pipeline.py:190-198; the pending add: tensor_parallel.py:7430-7435).
 #include "common.cuh"
@@ -30,7 +31,7 @@ int tib_decode_attention_tma(const void*, const void*, void*, float*, float*, co
 int tib_decode_attention(const void*, const void*, void*, float*, float*, const int*, const int*, const int*, const int*, int,
                          int, int, int, int, int, int64_t, int, int, float, int, int, cudaStream_t);
 int tib_gemm_tcgen05_swapab_supports(int, int, int);
-int tib_gemm_tcgen05_swapab(const void*, const void*, void*, int, int, int, int64_t, int64_t, int64_t, int, int, int*, cudaStream_t);
+int tib_gemm_tcgen05_swapab(const void*, const void*, void*, int, int, int, int64_t, int64_t, int64_t, int, int, int, int*, cudaStream_t);
 int tib_blas_gemm(const void*, const void*, void*, int, int, int, int64_t, int64_t, int64_t, int, int, cudaStream_t);
 }
 
@@ -39,7 +40,7 @@ struct TibBlockWeights {
   int hidden, heads, kv_heads, head_dim, intermediate;
   int rot_dim, interleaved;              // rotary: rotated width (0: none), pairing
   int qkv_kn, o_kn, gate_up_kn, down_kn; // 1: the matrix is stored [in, out]
-  int o_few_rows;                        // rows up to which the output projection goes to the swap-AB kernel (0: never)
+  int qkv_few_rows, o_few_rows, gate_up_few_rows, down_few_rows;   // rows up to which a projection goes to the swap-AB kernel (0: never)
   float eps_mixer, eps_feed_forward, scale;
   const float* norm_mixer;               // [hidden]
   const float* norm_feed_forward;        // [hidden]
@@ -79,6 +80,14 @@ struct TibBlockStep {
     if (rc__ != TIB_OK) return rc__; \
   } while (0)
 
+// out[n, N] = x[n, K] . w^T, w stored [N, K] or (kn) [K, N]: the hand-written swap-AB kernel up to few_rows rows, else the library.
+static int project(const void* x, const void* w, void* out, int n, int N, int K, int kn, int few_rows, int* error_word,
+                   cudaStream_t stream) {
+  if (few_rows > 0 && n <= few_rows && tib_gemm_tcgen05_swapab_supports(n, N, K))
+    return tib_gemm_tcgen05_swapab(x, w, out, n, N, K, K, kn ? N : K, N, kn, TIB_BF16, 0, error_word, stream);
+  return tib_blas_gemm(x, w, out, n, N, K, K, kn ? N : K, N, kn, TIB_BF16, stream);
+}
+
 // pending: the result of the block before (bf16 [n_tokens, hidden]) or null for the first.  pool: this layer's
 // pages [pages, 2, kv_heads, page_size, head_dim] (page_stride elements apart); window 0: every key.
 TIB_API int tib_llama_block(const TibBlockWeights* w, const TibBlockStep* s, const void* pending, void* pool,
@@ -92,8 +101,7 @@ TIB_API int tib_llama_block(const TibBlockWeights* w, const TibBlockStep* s, con
   const bool packed = page_stride == (int64_t)2 * k * page_size * d;
 
   TIB_TRY(tib_add_rmsnorm(pending, s->residual, nullptr, w->norm_mixer, s->normed, n, w->hidden, w->eps_mixer, TIB_BF16, stream));
-  TIB_TRY(tib_blas_gemm(s->normed, w->qkv, s->qkv, n, qkv_width, w->hidden, w->hidden, w->qkv_kn ? qkv_width : w->hidden,
-                        qkv_width, w->qkv_kn, TIB_BF16, stream));
+  TIB_TRY(project(s->normed, w->qkv, s->qkv, n, qkv_width, w->hidden, w->qkv_kn, w->qkv_few_rows, s->error_word, stream));
   TIB_TRY(tib_rope_append(s->qkv, s->q, pool, s->positions, s->token_slot, block_table, table_stride, w->inv_freq, n, h, k, d,
                           w->rot_dim, w->interleaved, page_size, page_stride, num_pages, 1, s->error_word, TIB_BF16, stream));
   if (s->n_multi) {
@@ -120,19 +128,13 @@ TIB_API int tib_llama_block(const TibBlockWeights* w, const TibBlockStep* s, con
                                    table_stride, s->n_entries, h, k, d, page_size, page_stride, num_pages, window, w->scale,
                                    splits, 0, stream));
   }
-  if (w->o_few_rows > 0 && n <= w->o_few_rows && !w->o_kn && tib_gemm_tcgen05_swapab_supports(n, w->hidden, q_width))
-    TIB_TRY(tib_gemm_tcgen05_swapab(s->attn, w->o, s->o_out, n, w->hidden, q_width, q_width, q_width, w->hidden, TIB_BF16, 0,
-                                    s->error_word, stream));
-  else
-    TIB_TRY(tib_blas_gemm(s->attn, w->o, s->o_out, n, w->hidden, q_width, q_width, w->o_kn ? w->hidden : q_width, w->hidden,
-                          w->o_kn, TIB_BF16, stream));
+  TIB_TRY(project(s->attn, w->o, s->o_out, n, w->hidden, q_width, w->o_kn, w->o_few_rows, s->error_word, stream));
   TIB_TRY(tib_add_rmsnorm(s->o_out, s->residual, nullptr, w->norm_feed_forward, s->normed, n, w->hidden, w->eps_feed_forward,
                           TIB_BF16, stream));
   const int inter = w->intermediate;
-  TIB_TRY(tib_blas_gemm(s->normed, w->gate_up, s->gate_up, n, 2 * inter, w->hidden, w->hidden,
-                        w->gate_up_kn ? 2 * inter : w->hidden, 2 * inter, w->gate_up_kn, TIB_BF16, stream));
+  TIB_TRY(project(s->normed, w->gate_up, s->gate_up, n, 2 * inter, w->hidden, w->gate_up_kn, w->gate_up_few_rows, s->error_word,
+                  stream));
   TIB_TRY(tib_swiglu(s->gate_up, s->act, n, inter, TIB_BF16, stream));
-  TIB_TRY(tib_blas_gemm(s->act, w->down, s->out, n, w->hidden, inter, inter, w->down_kn ? w->hidden : inter, w->hidden,
-                        w->down_kn, TIB_BF16, stream));
+  TIB_TRY(project(s->act, w->down, s->out, n, w->hidden, inter, w->down_kn, w->down_few_rows, s->error_word, stream));
   return TIB_OK;
 }

@@ -239,8 +239,9 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity)
   return false;
 }
 
-// NPAD: rows of x padded to a multiple of 16 (16, 32, 48 or 64).
-template <int NPAD, typename TOut>
+// NPAD: rows of x padded to a multiple of 16 (16, 32, 48 or 64).  WKN: w is stored [K, N] (the layout the library
+// prefers at few rows), so a slice of it is an MN-major A operand: two boxes of 64 features x 64 k.
+template <int NPAD, typename TOut, bool WKN>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                            TOut* __restrict__ out, int M, int N, int K, int64_t ldo, int* __restrict__ error_word) {
@@ -295,6 +296,14 @@ gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem_base = *tmem_slot_ptr;
   if (splits > 1) cluster_sync_all();   // every block of the cluster runs and has its barriers: peers may touch them
+  auto load_w = [&](uint32_t dst, int t, int kb, uint32_t bar) {
+    if constexpr (WKN) {
+      tma_load_2d(dst, &map_w, t * 128, kb * kTcBK, bar);
+      tma_load_2d(dst + kSwWBytes / 2, &map_w, t * 128 + 64, kb * kTcBK, bar);
+    } else {
+      tma_load_2d(dst, &map_w, kb * kTcBK, t * 128, bar);
+    }
+  };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -305,7 +314,7 @@ gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       for (int t = cluster_id; t < n_tiles && ahead < (uint32_t)kStages; t += clusters)
         for (int kb = kb0; kb < kb1 && ahead < (uint32_t)kStages; ++kb, ++ahead) {
           mbar_expect_tx(full_bar(ahead), kSwWBytes + kXBytes);
-          tma_load_2d(base + ahead * kStage, &map_w, kb * kTcBK, t * 128, full_bar(ahead));
+          load_w(base + ahead * kStage, t, kb, full_bar(ahead));
         }
       pdl_wait();
       for (int t = cluster_id; t < n_tiles && ok; t += clusters) {
@@ -323,14 +332,16 @@ gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             break;
           }
           mbar_expect_tx(full_bar(s), kSwWBytes + kXBytes);
-          tma_load_2d(w_dst, &map_w, kb * kTcBK, t * 128, full_bar(s));
+          load_w(w_dst, t, kb, full_bar(s));
           tma_load_2d(x_dst, &map_x, kb * kTcBK, 0, full_bar(s));
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      // (bit 15: the A operand is MN-major)
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (WKN ? (1u << 15) : 0u) | ((uint32_t)(NPAD >> 3) << 17) |
+                                 ((uint32_t)(128 >> 4) << 24);
       uint32_t it = 0;
       bool ok = true;
       int j = 0;
@@ -352,9 +363,10 @@ gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
           const uint32_t w_src = base + s * kStage, x_src = w_src + kSwWBytes;
 #pragma unroll
-          for (int k = 0; k < kTcBK / 16; ++k)
-            umma_f16_idesc(tmem_base + b * NPAD, umma_desc_k128(w_src + k * 32), umma_desc_k128(x_src + k * 32), idesc,
-                           (kb > kb0) || (k > 0));
+          for (int k = 0; k < kTcBK / 16; ++k) {
+            const uint64_t adesc = WKN ? umma_desc_mn128(w_src + k * 16 * 128, kSwWBytes / 2) : umma_desc_k128(w_src + k * 32);
+            umma_f16_idesc(tmem_base + b * NPAD, adesc, umma_desc_k128(x_src + k * 32), idesc, (kb > kb0) || (k > 0));
+          }
           umma_commit(empty_bar(s));
         }
         umma_commit(acc_full_bar(b));
@@ -466,13 +478,13 @@ TIB_API int tib_gemm_tcgen05_supports(int M, int N, int K) {
   return M >= 1 && N >= 8 && N % 8 == 0 && K >= 64 && K % 64 == 0;
 }
 
-template <int NPAD, typename TOut>
+template <int NPAD, typename TOut, bool WKN>
 static int launch_swapab(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int M, int N, int K, int64_t ldo,
                          int splits, int* error_word, cudaStream_t stream) {
   constexpr uint32_t x_bytes = NPAD * kTcBK * 2;
   constexpr uint32_t stage = kSwWBytes + ((x_bytes + 1023u) & ~1023u);
   constexpr uint32_t smem = 1024 + sw_stages(NPAD) * stage + 2 * kSwRedRows * (NPAD + 4) * 4 + 256;
-  auto kern = gemm_tcgen05_swapab_kernel<NPAD, TOut>;
+  auto kern = gemm_tcgen05_swapab_kernel<NPAD, TOut, WKN>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -534,10 +546,10 @@ TIB_API int tib_gemm_tcgen05_swapab_supports(int M, int N, int K) {
   return M >= 1 && M <= 64 && N >= 8 && N % 8 == 0 && K >= 64 && K % 64 == 0;
 }
 
-// Few rows (decode): x: [M <= 64, K] bf16, w: [N, K] bf16, out: [M, N] bf16 or fp32.  splits: 0 lets the
-// library choose how many blocks share K (1..8), else that many.
+// Few rows (decode): x: [M <= 64, K] bf16, w: [N, K] (w_kn 0) or [K, N] (w_kn 1) bf16, out: [M, N] bf16 or fp32.
+// splits: 0 lets the library choose how many blocks share K (1..8), else that many.
 TIB_API int tib_gemm_tcgen05_swapab(const void* x, const void* w, void* out, int M, int N, int K, int64_t ldx,
-                                    int64_t ldw, int64_t ldo, int out_dtype, int splits, int* error_word,
+                                    int64_t ldw, int64_t ldo, int w_kn, int out_dtype, int splits, int* error_word,
                                     cudaStream_t stream) {
   if (M == 0 || N == 0) return TIB_OK;
   if (!x || !w || !out) return TIB_E_ARG;
@@ -547,13 +559,14 @@ TIB_API int tib_gemm_tcgen05_swapab(const void* x, const void* w, void* out, int
   const int npad = (M + 15) / 16 * 16;
   if (splits > 8 || splits > K / kTcBK) return TIB_E_SIZE;
   CUtensorMap map_w, map_x;
-  int rc = make_map(&map_w, w, N, K, ldw, 128);
+  int rc = w_kn ? make_map(&map_w, w, K, N, ldw, 64) : make_map(&map_w, w, N, K, ldw, 128);
   if (rc != TIB_OK) return rc;
   rc = make_map(&map_x, x, M, K, ldx, npad);
   if (rc != TIB_OK) return rc;
-#define TIB_SWAPAB(NP)                                                                                              \
-  (out_dtype == TIB_BF16 ? launch_swapab<NP, __nv_bfloat16>(map_w, map_x, out, M, N, K, ldo, splits, error_word, stream) \
-                         : launch_swapab<NP, float>(map_w, map_x, out, M, N, K, ldo, splits, error_word, stream))
+#define TIB_SWAPAB_T(NP, T) \
+  (w_kn ? launch_swapab<NP, T, true>(map_w, map_x, out, M, N, K, ldo, splits, error_word, stream) \
+        : launch_swapab<NP, T, false>(map_w, map_x, out, M, N, K, ldo, splits, error_word, stream))
+#define TIB_SWAPAB(NP) (out_dtype == TIB_BF16 ? TIB_SWAPAB_T(NP, __nv_bfloat16) : TIB_SWAPAB_T(NP, float))
   switch (npad) {
     case 16: return TIB_SWAPAB(16);
     case 32: return TIB_SWAPAB(32);
@@ -561,6 +574,7 @@ TIB_API int tib_gemm_tcgen05_swapab(const void* x, const void* w, void* out, int
     default: return TIB_SWAPAB(64);
   }
 #undef TIB_SWAPAB
+#undef TIB_SWAPAB_T
 }
 
 // x: [M, K] bf16 (row stride ldx), w: [N, K] bf16 (row stride ldw), out: [M, N] bf16 or fp32 (row stride ldo).

@@ -9,23 +9,26 @@ src/torchinferno/models/llama3/tensor_parallel.py:11176-11198).
 """
 from __future__ import annotations
 
+import statistics
+import weakref
+
 import torch
 
 from torchinferno_b200.kernels import ops
 
 # Which kernel multiplies bf16 operands:
-#   "auto"     whichever measured faster inside the engine's steps on the B200.  Inside a captured decode
-#              step of the 8B sizes at 8 rows (us, hand-written swap-AB / cuBLAS, time after the kernel
-#              before has ended): qkv 12.5 / 9.9, o 9.2 / 12.1, gate_up 40.7 / 36.3, down 23.3 / 21.9.
-#              So a weight may say that it wants the swap-AB kernel for few rows
-#              (LinearWeight(few_rows_tcgen05=True): the attention output projection does); everything
-#              else goes to cuBLAS (SWAPAB_AUTO_ROWS = 0).  All hand-written kernels: "tcgen05"
+#   "auto"     whichever is faster on this GPU.  Many rows go to cuBLAS.  At few rows (decode steps) neither the
+#              hand-written swap-AB kernel nor cuBLAS wins everywhere: inside a captured decode step of the 8B
+#              sizes at 8 rows (us, swap-AB / cuBLAS, time after the kernel before has ended) qkv 12.5 / 9.9,
+#              o 9.2 / 12.1, gate_up 40.7 / 36.3, down 23.3 / 21.9, while at the 1B and 3B sizes cuBLAS takes
+#              13 and 18 us for down projections that stream in 5 and 8.  So a weight is given to the swap-AB
+#              kernel for few rows if it says so (few_rows_tcgen05=True) or, left open (None), if that
+#              measured faster for its shape when the model was bound (tune_few_rows)
 #   "tcgen05"  the hand-written kernels wherever they take the shape (swap-AB up to 64 rows, the
 #              128 x 256-tile kernel above, and from 256 rows the two-SM kernel on 256 x 256 tiles)
 #   "library"  cuBLAS everywhere
 _backend = "auto"
 _error_word: torch.Tensor | None = None
-SWAPAB_AUTO_ROWS = 0
 TWO_CTA_ROWS = 256
 TWO_CTA_MAX_N = 65536
 
@@ -54,17 +57,23 @@ class LinearWeight:
     measurably faster on few rows when the matrix is stored [in, out] (at 8 rows of the 8B sizes: qkv
     14.8 -> 12.5 us, gate/up 42.4 -> 37.8 us, down 26.8 -> 25.3 us; no difference at 2,048 rows), which is
     what the reference's optional pre-transposed copies for M <= 64 are for
-    (src/torchinferno/models/llama3/tensor_parallel.py:11201-11239).  Only one layout is kept.
+    (src/torchinferno/models/llama3/tensor_parallel.py:11201-11239).  Only one layout is kept: [in, out] under
+    "auto" (the swap-AB kernel reads both), [out, in] for the other hand-written kernels.
+
+    ``few_rows_tcgen05``: True gives products of up to FEW_ROWS rows to the swap-AB kernel under "auto", False
+    never does, None leaves it to :func:`tune_few_rows` (the library until that has run).
     """
 
-    FEW_ROWS = 16      # up to this many rows a weight with few_rows_tcgen05 goes to the swap-AB kernel under "auto"
+    FEW_ROWS = 16      # up to this many rows a weight may go to the swap-AB kernel under "auto"
 
-    def __init__(self, weight: torch.Tensor, *, allow_transpose: bool = True, few_rows_tcgen05: bool = False) -> None:
+    def __init__(self, weight: torch.Tensor, *, allow_transpose: bool = True, few_rows_tcgen05: bool | None = False) -> None:
         self.out_features, self.in_features = weight.shape
-        self.few_rows_tcgen05 = bool(few_rows_tcgen05 and weight.dtype == torch.bfloat16 and weight.is_cuda)
-        self.transposed = bool(allow_transpose and not self.few_rows_tcgen05 and weight.dtype == torch.bfloat16
-                               and weight.is_cuda and _backend != "tcgen05")
+        on_gpu = weight.dtype == torch.bfloat16 and weight.is_cuda
+        self.few_rows = LinearWeight.FEW_ROWS if few_rows_tcgen05 and on_gpu else 0
+        self.transposed = bool(allow_transpose and on_gpu and _backend != "tcgen05")
         self.tensor = weight.t().contiguous() if self.transposed else weight.contiguous()
+        if few_rows_tcgen05 is None and on_gpu and _backend == "auto":
+            _undecided.add(self)
 
     @property
     def dtype(self) -> torch.dtype:
@@ -74,7 +83,7 @@ class LinearWeight:
         """The projection onto output features start .. stop-1 (a view, nothing is copied)."""
         view = object.__new__(LinearWeight)
         view.out_features, view.in_features, view.transposed = stop - start, self.in_features, self.transposed
-        view.few_rows_tcgen05 = self.few_rows_tcgen05
+        view.few_rows = self.few_rows
         view.tensor = self.tensor[:, start:stop] if self.transposed else self.tensor[start:stop]
         return view
 
@@ -88,8 +97,8 @@ def linear(x: torch.Tensor, weight: "torch.Tensor | LinearWeight", *, out_dtype:
     few_rows = 0
     if isinstance(weight, LinearWeight):
         if weight.transposed:
-            return _linear_library_kn(x, weight.tensor, out_dtype or x.dtype, out)
-        few_rows = LinearWeight.FEW_ROWS if weight.few_rows_tcgen05 else 0
+            return _linear_kn(x, weight.tensor, out_dtype or x.dtype, out, weight.few_rows)
+        few_rows = weight.few_rows
         weight = weight.tensor
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
         raise ops.KernelError(f"linear: shapes {tuple(x.shape)} and {tuple(weight.shape)} do not fit")
@@ -110,17 +119,109 @@ def linear(x: torch.Tensor, weight: "torch.Tensor | LinearWeight", *, out_dtype:
     return _linear_bf16(x, weight, out_dtype, out, few_rows)
 
 
-def _linear_library_kn(x: torch.Tensor, weight_kn: torch.Tensor, out_dtype: torch.dtype,
-                       out: torch.Tensor | None) -> torch.Tensor:
-    """cuBLAS on a matrix stored [in, out]."""
+def _swapab_takes_kn(x: torch.Tensor, weight_kn: torch.Tensor) -> bool:
+    k, n = weight_kn.shape
+    return (x.stride(1) == 1 and weight_kn.stride(1) == 1 and x.stride(0) % 8 == 0 and weight_kn.stride(0) % 8 == 0
+            and weight_kn.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0 and ops.gemm_tcgen05_swapab_supports(x.shape[0], n, k))
+
+
+def _linear_kn(x: torch.Tensor, weight_kn: torch.Tensor, out_dtype: torch.dtype, out: torch.Tensor | None,
+               few_rows: int = 0) -> torch.Tensor:
+    """A matrix stored [in, out]: the swap-AB kernel up to ``few_rows`` rows, else cuBLAS."""
     if x.dim() != 2 or x.shape[1] != weight_kn.shape[0]:
         raise ops.KernelError(f"linear: shapes {tuple(x.shape)} and [in, out] = {tuple(weight_kn.shape)} do not fit")
     if _backend == "tcgen05":
         raise ops.KernelError("linear: these weights were laid out for the library; bind the model after "
                               "choosing the tcgen05 backend")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise ops.KernelError(f"linear: unsupported output dtype {out_dtype}")
     if out is None or out.dtype != out_dtype:
         out = torch.empty((x.shape[0], weight_kn.shape[1]), dtype=out_dtype, device=x.device)
+    if _backend == "auto" and 0 < x.shape[0] <= few_rows and _swapab_takes_kn(x, weight_kn):
+        return ops.gemm_tcgen05_swapab(x, weight_kn, out, _error_word, w_kn=True)
     return ops.library_gemm(x, weight_kn, out, w_kn=True)
+
+
+# ---------------------------------------------------------------------------
+# Which kernel takes a weight's few-row products, by measurement.
+_undecided: "weakref.WeakSet[LinearWeight]" = weakref.WeakSet()
+_tuned: dict[tuple, bool] = {}          # (out, in, device) -> the swap-AB kernel measured faster
+tuning_times: dict[tuple, dict[str, float]] = {}   # the same keys -> milliseconds of the timed walk with either kernel
+TUNE_ROWS = 8
+# The swap-AB kernel must take under this share of the library's time.  The walk repeats within 1 %, but near
+# ties fall differently from one process to the next, and a choice that changes with the process changes the
+# rounding of a model's logits with it: at the 8B, 3B and 1B sizes the measured shares are 0.75-0.82 (o at 8B,
+# down at 3B and 1B), 0.96 (down at 8B) and 0.99-1.26 (the rest), so the line is drawn where no shape is near it.
+TUNE_MARGIN = 0.93
+TUNE_MEMBERS = 32
+
+
+def tune_few_rows() -> dict[tuple, bool]:
+    """Decide, for every weight bound with ``few_rows_tcgen05=None`` since the last call, which kernel takes its
+    products of few rows, and return the decisions made so far by (out, in, device).
+
+    Weights of one shape are measured together, once per shape and process, the way a decode step runs them:
+    a CUDA graph walks over them (different weights one after the other, so nothing comes from L2), each
+    product behind a small kernel, as in a layer (under programmatic dependent launch the swap-AB kernel
+    fetches its first weights while that kernel runs, and a measurement of the product alone would not
+    show it).  The graph is timed with either kernel; the swap-AB kernel gets the shape if it takes less
+    than TUNE_MARGIN of the library's time."""
+    groups: dict[tuple, list[LinearWeight]] = {}
+    for w in list(_undecided):
+        groups.setdefault((w.out_features, w.in_features, w.tensor.device), []).append(w)
+    _undecided.clear()
+    for key, group in groups.items():
+        if key not in _tuned:
+            _tuned[key] = _swapab_is_faster(group[:TUNE_MEMBERS])
+        for w in group:
+            w.few_rows = LinearWeight.FEW_ROWS if _tuned[key] else 0
+    return dict(_tuned)
+
+
+def _swapab_is_faster(group: "list[LinearWeight]") -> bool:
+    first = group[0]
+    n, k, device = first.out_features, first.in_features, first.tensor.device
+    if not first.transposed or not ops.gemm_tcgen05_swapab_supports(TUNE_ROWS, n, k):
+        return False
+    ops.library_gemm_ready(device)
+    with torch.cuda.device(device):
+        x = torch.zeros((TUNE_ROWS, k), dtype=torch.bfloat16, device=device)
+        if not all(_swapab_takes_kn(x, w.tensor) for w in group):
+            return False
+        # the small kernel before each product: a norm of TUNE_ROWS rows of a usual width (a few microseconds)
+        width = min(k, 4096)
+        delta = torch.zeros((TUNE_ROWS, width), dtype=torch.bfloat16, device=device)
+        residual, normed = torch.randn((TUNE_ROWS, width), dtype=torch.float32, device=device), torch.empty_like(delta)
+        norm_weight = torch.ones(width, dtype=torch.float32, device=device)
+        out = torch.empty((TUNE_ROWS, n), dtype=torch.bfloat16, device=device)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)      # larger than the L2
+        products = {"library": lambda w: ops.library_gemm(x, w.tensor, out, w_kn=True),
+                    "swapab": lambda w: ops.gemm_tcgen05_swapab(x, w.tensor, out, None, w_kn=True)}
+        times = {}
+        for name, product in products.items():
+            def walk() -> None:
+                for w in group:
+                    ops.add_rmsnorm(delta, residual, norm_weight, 1e-5, normed)
+                    product(w)
+            walk()                                                            # (first launches: attributes, handles)
+            torch.cuda.synchronize(device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                walk()
+            samples = []
+            for i in range(7):
+                flush.zero_()
+                begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                begin.record()
+                graph.replay()
+                end.record()
+                end.synchronize()
+                if i >= 2:
+                    samples.append(begin.elapsed_time(end))
+            times[name] = statistics.median(samples)
+            del graph
+    tuning_times[(n, k, device)] = times
+    return times["swapab"] < TUNE_MARGIN * times["library"]
 
 
 def _linear_bf16(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
@@ -128,7 +229,7 @@ def _linear_bf16(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
     m, n = x.shape[0], weight.shape[0]
     k = x.shape[1]
     if _backend != "library" and out_dtype in (torch.bfloat16, torch.float32):
-        rows = max(SWAPAB_AUTO_ROWS, few_rows) if _backend == "auto" else 64
+        rows = few_rows if _backend == "auto" else 64
         aligned = x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
         if aligned and m <= rows and ops.gemm_tcgen05_swapab_supports(m, n, k):
             if out is None or out.dtype != out_dtype:

@@ -20,7 +20,8 @@ from torchinferno_b200.kernels.gemm import LinearWeight
 
 class BlockWeights(Structure):
     _fields_ = [(name, c_int) for name in ("hidden", "heads", "kv_heads", "head_dim", "intermediate", "rot_dim", "interleaved",
-                                           "qkv_kn", "o_kn", "gate_up_kn", "down_kn", "o_few_rows")] + \
+                                           "qkv_kn", "o_kn", "gate_up_kn", "down_kn",
+                                           "qkv_few_rows", "o_few_rows", "gate_up_few_rows", "down_few_rows")] + \
                [(name, c_float) for name in ("eps_mixer", "eps_feed_forward", "scale")] + \
                [(name, c_void_p) for name in ("norm_mixer", "norm_feed_forward", "inv_freq", "qkv", "o", "gate_up", "down")]
 
@@ -77,7 +78,9 @@ def block_weights(block) -> BlockWeights | None:
     w.inv_freq = position.inv_freq.data_ptr() if rotary else None
     (w.qkv, w.qkv_kn), (w.o, w.o_kn) = _matrix(mixer.qkv_weight), _matrix(mixer.o_weight)
     (w.gate_up, w.gate_up_kn), (w.down, w.down_kn) = _matrix(ffn.gate_up_weight), _matrix(ffn.down_weight)
-    w.o_few_rows = LinearWeight.FEW_ROWS if mixer.o_weight.few_rows_tcgen05 and gemm.get_backend() == "auto" else 0
+    auto = gemm.get_backend() == "auto"
+    w.qkv_few_rows, w.o_few_rows = (m.few_rows if auto else 0 for m in (mixer.qkv_weight, mixer.o_weight))
+    w.gate_up_few_rows, w.down_few_rows = (m.few_rows if auto else 0 for m in (ffn.gate_up_weight, ffn.down_weight))
     w.eps_mixer, w.eps_feed_forward, w.scale = n1.eps, n2.eps, mixer.scale
     w.norm_mixer, w.norm_feed_forward = n1.weight.data_ptr(), n2.weight.data_ptr()
     return w
@@ -131,6 +134,7 @@ def run_block(w: BlockWeights, stream_state, ctx, window: int | None) -> None:
         raise ops.KernelError(f"native block: status {status} (negative: refused arguments; 20000 + n: cuBLAS status n; "
                               f"else a CUDA error at launch)")
     # this library's own kernels among them: two norms, rotary, SwiGLU, one or two attention kernels, and the
-    # output projection when the swap-AB kernel takes it (the library products are not counted)
-    ops.count_launches(5 + (1 if batch.n_single and batch.n_multi else 0) + (1 if 0 < batch.n_tokens <= w.o_few_rows else 0))
+    # projections that the swap-AB kernel takes (the library products are not counted)
+    own_products = sum(1 for rows in (w.qkv_few_rows, w.o_few_rows, w.gate_up_few_rows, w.down_few_rows) if 0 < batch.n_tokens <= rows)
+    ops.count_launches(5 + (1 if batch.n_single and batch.n_multi else 0) + own_products)
     stream_state.pending = ws.buffers["out"]

@@ -523,20 +523,21 @@ def gemm_tcgen05_swapab_supports(m: int, n: int, k: int) -> bool:
 
 
 def gemm_tcgen05_swapab(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, error_word: torch.Tensor | None = None,
-                        splits: int = 0) -> torch.Tensor:
-    """out[M, N] = x[M, K] . w[N, K]^T for M <= 64 on tcgen05 tensor cores with the operands swapped: w is
-    streamed by TMA as the 128-row operand, K is split over a thread-block cluster (``splits`` = 0: chosen
-    by the library) and the partial tiles are summed through distributed shared memory."""
+                        splits: int = 0, w_kn: bool = False) -> torch.Tensor:
+    """out[M, N] = x[M, K] . w^T for M <= 64 on tcgen05 tensor cores with the operands swapped: w ([N, K], or
+    [K, N] with ``w_kn``) is streamed by TMA as the 128-row operand, K is split over a thread-block cluster
+    (``splits`` = 0: chosen by the library) and the partial tiles are summed through distributed shared memory."""
     for name, t in (("x", x), ("w", w)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
             raise KernelError(f"gemm_tcgen05_swapab: {name} must be a 2-D bf16 CUDA tensor with unit inner stride")
     _need(out, "out")
-    (m, k), (n, k2) = x.shape, w.shape
+    m, k = x.shape
+    k2, n = w.shape if w_kn else (w.shape[1], w.shape[0])
     if k != k2 or out.shape != (m, n):
         raise KernelError(f"gemm_tcgen05_swapab: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
     _check("gemm_tcgen05_swapab", lib().tib_gemm_tcgen05_swapab(
         _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)), c_int64(w.stride(0)),
-        c_int64(out.stride(0)), c_int(_code(out.dtype)), c_int(splits), _ptr(error_word), _stream()))
+        c_int64(out.stride(0)), c_int(int(w_kn)), c_int(_code(out.dtype)), c_int(splits), _ptr(error_word), _stream()))
     return out
 
 

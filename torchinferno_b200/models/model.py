@@ -12,7 +12,7 @@ from typing import Mapping
 
 import torch
 
-from torchinferno_b200.kernels import ops
+from torchinferno_b200.kernels import gemm, ops
 from torchinferno_b200.kernels.gemm import linear
 from torchinferno_b200.models.spec import ModelSpec
 from torchinferno_b200.parts.base import (Block, CacheSpec, KVBinding, LayerContext, ResidualStream,
@@ -65,6 +65,8 @@ class CausalLM:
                            if full + ws.name in tensors})
         self.final_norm.bind({ws.name: tensors[spec.final_norm.prefix + ws.name]
                               for ws in self.final_norm.weight_specs()})
+        if self.device.type == "cuda":
+            gemm.tune_few_rows()      # weights that left the choice of their few-rows kernel open get it now
 
     def weight_bytes(self) -> int:
         """Bytes of distinct weight storage one step reads (a tied head counts once)."""

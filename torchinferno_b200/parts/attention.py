@@ -51,10 +51,9 @@ class GQAAttention(Mixer):
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         q, k, v, o = self.names
-        self.qkv_weight = LinearWeight(torch.cat([weights[q], weights[k], weights[v]], dim=0))
-        # (at few rows the hand-written swap-AB kernel is ahead of cuBLAS on this shape, and starts to fetch the
-        # weights while the attention kernel drains)
-        self.o_weight = LinearWeight(weights[o], few_rows_tcgen05=True)
+        self.qkv_weight = LinearWeight(torch.cat([weights[q], weights[k], weights[v]], dim=0), few_rows_tcgen05=None)
+        # (which kernel takes the products of few rows is measured per shape once the whole model is bound)
+        self.o_weight = LinearWeight(weights[o], few_rows_tcgen05=None)
 
     def cache_spec(self) -> CacheSpec:
         return CacheSpec(self.kv_heads, self.head_dim, self.window)

@@ -35,8 +35,8 @@ class SwiGLUFeedForward(FeedForward):
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         g, u, d = self.names
-        self.gate_up_weight = LinearWeight(torch.cat([weights[g], weights[u]], dim=0))
-        self.down_weight = LinearWeight(weights[d])
+        self.gate_up_weight = LinearWeight(torch.cat([weights[g], weights[u]], dim=0), few_rows_tcgen05=None)
+        self.down_weight = LinearWeight(weights[d], few_rows_tcgen05=None)
 
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         gate_up = linear(x, self.gate_up_weight)
