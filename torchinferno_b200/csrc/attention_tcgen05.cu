@@ -28,6 +28,7 @@ constexpr int kFaSoftmaxWarps = 8;                      // two threads per row, 
 constexpr int kFaThreads = 64 + 32 * kFaSoftmaxWarps + 32;   // key producer, MMA issuer, softmax warps, value producer
 constexpr int kFaValueWarp = 2 + kFaSoftmaxWarps;
 constexpr int kFaStages = 3;
+constexpr float kFaSlack = 8.f;
 
 struct FaArgs {
   const int* q_start;
@@ -287,7 +288,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
           for (int j = 0; j < HC; ++j) mx = fmaxf(mx, __uint_as_float(sv[j]));
         }
-        const float m_new = fmaxf(m, mx == -CUDART_INF_F ? -CUDART_INF_F : mx * a.scale_log2);
+        // The running maximum only has to bound the scores loosely: it is moved when a tile exceeds it by more than
+        // kFaSlack (in log2 units), so P stays below 2^kFaSlack (fine for bf16 and for the fp32 sums) and the
+        // rescaling of O below, with its wait for the product before, becomes rare.  The result is the same
+        // quotient either way.  (From -inf any finite maximum is a move; -inf - -inf is NaN and moves nothing.)
+        float m_new = fmaxf(m, mx == -CUDART_INF_F ? -CUDART_INF_F : mx * a.scale_log2);
+        if (m_new - m <= kFaSlack) m_new = m;
         const float basev = m_new == -CUDART_INF_F ? 0.f : m_new;
         float alpha;
         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(alpha) : "f"(m - basev));
