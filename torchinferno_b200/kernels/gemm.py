@@ -145,9 +145,12 @@ def _linear_kn(x: torch.Tensor, weight_kn: torch.Tensor, out_dtype: torch.dtype,
 # ---------------------------------------------------------------------------
 # Which kernel takes a weight's few-row products, by measurement.
 _undecided: "weakref.WeakSet[LinearWeight]" = weakref.WeakSet()
-_tuned: dict[tuple, bool] = {}          # (out, in, device) -> the swap-AB kernel measured faster
-tuning_times: dict[tuple, dict[str, float]] = {}   # the same keys -> milliseconds of the timed walk with either kernel
-TUNE_ROWS = 8
+_tuned: dict[tuple, int] = {}           # (out, in, device) -> rows up to which the swap-AB kernel measured faster
+tuning_times: dict[tuple, dict[str, float]] = {}   # (out, in, device, rows) -> milliseconds of the timed walk with either kernel
+# cuBLAS changes kernels between 8 and 16 rows (at the 8B sizes its output projection takes 16.2 us at 8 rows and
+# 10.8 at 16, the swap-AB kernel 12.4 and 12.9), so both are measured: a shape may go to the swap-AB kernel up
+# to 8 rows, up to 16, or not at all.
+TUNE_ROWS = (8, 16)
 # The swap-AB kernel must take under this share of the library's time.  The walk repeats within 1 %, but near
 # ties fall differently from one process to the next, and a choice that changes with the process changes the
 # rounding of a model's logits with it: at the 8B, 3B and 1B sizes the measured shares are 0.75-0.82 (o at 8B,
@@ -156,9 +159,9 @@ TUNE_MARGIN = 0.93
 TUNE_MEMBERS = 32
 
 
-def tune_few_rows() -> dict[tuple, bool]:
-    """Decide, for every weight bound with ``few_rows_tcgen05=None`` since the last call, which kernel takes its
-    products of few rows, and return the decisions made so far by (out, in, device).
+def tune_few_rows() -> dict[tuple, int]:
+    """Decide, for every weight bound with ``few_rows_tcgen05=None`` since the last call, up to how many rows the
+    swap-AB kernel takes its products (0, 8 or 16), and return the decisions made so far by (out, in, device).
 
     Weights of one shape are measured together, once per shape and process, the way a decode step runs them:
     a CUDA graph walks over them (different weights one after the other, so nothing comes from L2), each
@@ -172,28 +175,33 @@ def tune_few_rows() -> dict[tuple, bool]:
     _undecided.clear()
     for key, group in groups.items():
         if key not in _tuned:
-            _tuned[key] = _swapab_is_faster(group[:TUNE_MEMBERS])
+            rows_taken = 0
+            for rows in TUNE_ROWS:          # (rising: the first row count at which the library wins ends it)
+                if not _swapab_is_faster(group[:TUNE_MEMBERS], rows):
+                    break
+                rows_taken = rows
+            _tuned[key] = min(rows_taken, LinearWeight.FEW_ROWS)
         for w in group:
-            w.few_rows = LinearWeight.FEW_ROWS if _tuned[key] else 0
+            w.few_rows = _tuned[key]
     return dict(_tuned)
 
 
-def _swapab_is_faster(group: "list[LinearWeight]") -> bool:
+def _swapab_is_faster(group: "list[LinearWeight]", rows: int) -> bool:
     first = group[0]
     n, k, device = first.out_features, first.in_features, first.tensor.device
-    if not first.transposed or not ops.gemm_tcgen05_swapab_supports(TUNE_ROWS, n, k):
+    if not first.transposed or not ops.gemm_tcgen05_swapab_supports(rows, n, k):
         return False
     ops.library_gemm_ready(device)
     with torch.cuda.device(device):
-        x = torch.zeros((TUNE_ROWS, k), dtype=torch.bfloat16, device=device)
+        x = torch.zeros((rows, k), dtype=torch.bfloat16, device=device)
         if not all(_swapab_takes_kn(x, w.tensor) for w in group):
             return False
-        # the small kernel before each product: a norm of TUNE_ROWS rows of a usual width (a few microseconds)
+        # the small kernel before each product: a norm of as many rows of a usual width (a few microseconds)
         width = min(k, 4096)
-        delta = torch.zeros((TUNE_ROWS, width), dtype=torch.bfloat16, device=device)
-        residual, normed = torch.randn((TUNE_ROWS, width), dtype=torch.float32, device=device), torch.empty_like(delta)
+        delta = torch.zeros((rows, width), dtype=torch.bfloat16, device=device)
+        residual, normed = torch.randn((rows, width), dtype=torch.float32, device=device), torch.empty_like(delta)
         norm_weight = torch.ones(width, dtype=torch.float32, device=device)
-        out = torch.empty((TUNE_ROWS, n), dtype=torch.bfloat16, device=device)
+        out = torch.empty((rows, n), dtype=torch.bfloat16, device=device)
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)      # larger than the L2
         products = {"library": lambda w: ops.library_gemm(x, w.tensor, out, w_kn=True),
                     "swapab": lambda w: ops.gemm_tcgen05_swapab(x, w.tensor, out, None, w_kn=True)}
@@ -220,7 +228,7 @@ def _swapab_is_faster(group: "list[LinearWeight]") -> bool:
                     samples.append(begin.elapsed_time(end))
             times[name] = statistics.median(samples)
             del graph
-    tuning_times[(n, k, device)] = times
+    tuning_times[(n, k, device, rows)] = times
     return times["swapab"] < TUNE_MARGIN * times["library"]
 
 
