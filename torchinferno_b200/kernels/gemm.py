@@ -9,7 +9,6 @@ src/torchinferno/models/llama3/tensor_parallel.py:11176-11198).
 """
 from __future__ import annotations
 
-import statistics
 import weakref
 
 import torch
@@ -147,21 +146,24 @@ def _linear_kn(x: torch.Tensor, weight_kn: torch.Tensor, out_dtype: torch.dtype,
 _undecided: "weakref.WeakSet[LinearWeight]" = weakref.WeakSet()
 _tuned: dict[tuple, int] = {}           # (out, in, device) -> rows up to which the swap-AB kernel measured faster
 tuning_times: dict[tuple, dict[str, float]] = {}   # (out, in, device, rows) -> milliseconds of the timed walk with either kernel
-# cuBLAS changes kernels between 8 and 16 rows (at the 8B sizes its output projection takes 16.2 us at 8 rows and
-# 10.8 at 16, the swap-AB kernel 12.4 and 12.9), so both are measured: a shape may go to the swap-AB kernel up
-# to 8 rows, up to 16, or not at all.
-TUNE_ROWS = (8, 16)
-# The swap-AB kernel must take under this share of the library's time.  The walk repeats within 1 %, but near
-# ties fall differently from one process to the next, and a choice that changes with the process changes the
-# rounding of a model's logits with it: at the 8B, 3B and 1B sizes the measured shares are 0.75-0.82 (o at 8B,
-# down at 3B and 1B), 0.96 (down at 8B) and 0.99-1.26 (the rest), so the line is drawn where no shape is near it.
-TUNE_MARGIN = 0.93
+# cuBLAS changes kernels with the row count (at the 8B sizes its output projection takes 16.2 us at 8 rows and
+# 10.8 at 16, the swap-AB kernel 12.4 and 12.9; its down projection is 9 % behind the swap-AB kernel at 1 row
+# and 4 % at 8), so three row counts are measured, each standing for the counts up to it: a shape may go to
+# the swap-AB kernel up to 4 rows, up to 8, up to 16, or not at all.
+TUNE_ROWS = ((1, 4), (8, 8), (16, 16))      # (rows measured, rows it stands for)
+# The swap-AB kernel must take under this share of the library's time.  The measurement repeats within about half
+# a per cent.  The line is drawn in a gap of the shares measured at the 8B and 3B sizes (1, 8 and 16 rows): 0.73-0.95
+# on one side (o and, at few rows, down at 8B; down, o and gate/up at 3B), 0.997 and more on the other.  A shape
+# whose share is within a per cent of the line (qkv and gate/up of the 1B sizes at 1 row: 0.97-0.99) may fall on
+# either side from one process to the next; that costs under a per cent of a step either way, but it changes the
+# rounding of the logits, so a run that must be repeatable to the bit fixes the kernels with the "library" backend.
+TUNE_MARGIN = 0.965
 TUNE_MEMBERS = 32
 
 
 def tune_few_rows() -> dict[tuple, int]:
     """Decide, for every weight bound with ``few_rows_tcgen05=None`` since the last call, up to how many rows the
-    swap-AB kernel takes its products (0, 8 or 16), and return the decisions made so far by (out, in, device).
+    swap-AB kernel takes its products (0, 4, 8 or 16), and return the decisions made so far by (out, in, device).
 
     Weights of one shape are measured together, once per shape and process, the way a decode step runs them:
     a CUDA graph walks over them (different weights one after the other, so nothing comes from L2), each
@@ -176,10 +178,10 @@ def tune_few_rows() -> dict[tuple, int]:
     for key, group in groups.items():
         if key not in _tuned:
             rows_taken = 0
-            for rows in TUNE_ROWS:          # (rising: the first row count at which the library wins ends it)
+            for rows, stands_for in TUNE_ROWS:      # (rising: the first row count at which the library wins ends it)
                 if not _swapab_is_faster(group[:TUNE_MEMBERS], rows):
                     break
-                rows_taken = rows
+                rows_taken = stands_for
             _tuned[key] = min(rows_taken, LinearWeight.FEW_ROWS)
         for w in group:
             w.few_rows = _tuned[key]
@@ -205,7 +207,7 @@ def _swapab_is_faster(group: "list[LinearWeight]", rows: int) -> bool:
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)      # larger than the L2
         products = {"library": lambda w: ops.library_gemm(x, w.tensor, out, w_kn=True),
                     "swapab": lambda w: ops.gemm_tcgen05_swapab(x, w.tensor, out, None, w_kn=True)}
-        times = {}
+        graphs = {}
         for name, product in products.items():
             def walk() -> None:
                 for w in group:
@@ -213,11 +215,14 @@ def _swapab_is_faster(group: "list[LinearWeight]", rows: int) -> bool:
                     product(w)
             walk()                                                            # (first launches: attributes, handles)
             torch.cuda.synchronize(device)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            graphs[name] = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graphs[name]):
                 walk()
-            samples = []
-            for i in range(7):
+        # the two graphs take turns, and the fastest replay of each counts: what slows a replay down (clocks on
+        # their way up, another process's traffic) only ever adds time
+        times = {name: float("inf") for name in graphs}
+        for i in range(8):
+            for name, graph in graphs.items():
                 flush.zero_()
                 begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 begin.record()
@@ -225,9 +230,8 @@ def _swapab_is_faster(group: "list[LinearWeight]", rows: int) -> bool:
                 end.record()
                 end.synchronize()
                 if i >= 2:
-                    samples.append(begin.elapsed_time(end))
-            times[name] = statistics.median(samples)
-            del graph
+                    times[name] = min(times[name], begin.elapsed_time(end))
+        del graphs
     tuning_times[(n, k, device, rows)] = times
     return times["swapab"] < TUNE_MARGIN * times["library"]
 
