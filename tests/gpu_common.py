@@ -1,7 +1,6 @@
 """Shared by the GPU tests: tolerances (set once), plain-reference logits, request sets."""
 from __future__ import annotations
 
-import functools
 
 import numpy as np
 import pytest

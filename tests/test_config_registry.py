@@ -112,7 +112,7 @@ def test_registry_rejects_conflicts_and_duplicates():
 
 def test_model_spec_is_data_and_checks_its_schedule():
     from torchinferno_b200.models.llama import build_llama
-    from torchinferno_b200.models.spec import LayerCall, ModelSpec
+    from torchinferno_b200.models.spec import LayerCall
     import dataclasses
     spec = build_llama(LlamaConfig.from_dict(TINY_B))
     assert len(spec.layers) == 3 and [c.cache for c in spec.schedule] == [0, 1, 2] and spec.cache_layers == 3

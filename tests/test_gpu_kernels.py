@@ -3,7 +3,6 @@ than the engine's tiny models: widths that are no power of two, head sizes in st
 group sizes, page sizes from 1 up, windows, ragged batches."""
 import math
 
-import numpy as np
 import pytest
 import torch
 

@@ -3,7 +3,6 @@ call read another call's cache, and a toy mixer with state of its own that is re
 stepped without a change to the framework's files."""
 import dataclasses
 import json
-import math
 
 import pytest
 import torch

@@ -29,7 +29,7 @@ from __future__ import annotations
 
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Hashable, Sequence
+from typing import Hashable
 
 from torchinferno_b200.cache.manager import CacheManager
 

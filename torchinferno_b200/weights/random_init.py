@@ -15,7 +15,6 @@ from typing import Any, Mapping
 
 import torch
 
-from torchinferno_b200.config.model_config import read_config_json  # noqa: F401  (re-export for callers)
 from torchinferno_b200.config.registry import resolve_architecture
 from torchinferno_b200.weights.loader import SINGLE_FILE, place
 
