@@ -62,6 +62,13 @@ TINY_E = {
 TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
 
 
+@pytest.fixture(autouse=True)
+def same_random_data_every_run():
+    """Data drawn from torch's global generator is the same for a test whatever ran before it."""
+    import torch
+    torch.manual_seed(20240607)
+
+
 @pytest.fixture(scope="session")
 def model_folders(tmp_path_factory):
     """name -> folder with config.json + model.safetensors (bf16 storage, seeded)."""

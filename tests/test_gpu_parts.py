@@ -71,9 +71,19 @@ def test_swiglu_part(dtype):
     ffn.bind({k: v.to(dtype).cuda() for k, v in ws.items()})
     x = torch.randn(11, 72).to(dtype)
     got = ffn.forward(x.cuda(), LayerContext(batch=None))
-    want = plain_llama.swiglu_mlp(x.double(), *(ws[k].double() for k in ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
-    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=5e-2, rtol=3e-2)
-    assert torch.allclose(got.cpu().double(), want, **tol)
+    gate_w, up_w, down_w = (ws[k].double() for k in ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
+    if dtype == torch.float32:
+        want, tol = plain_llama.swiglu_mlp(x.double(), gate_w, up_w, down_w), dict(atol=1e-5, rtol=1e-5)
+    else:
+        # The part stores gate / up and their product in bfloat16 between its kernels.  With these weights an output is
+        # a sum of 200 terms of size 1, so those roundings move it by up to 0.1 in absolute terms, whatever its own
+        # size: the plain formula is therefore rounded at the same two places, and what is left to compare is the
+        # arithmetic (fp32 sums in another order, the fast exponential) and the rounding of the result itself.
+        as_stored = lambda t: t.to(torch.bfloat16).double()
+        gate, up = as_stored(x.double() @ gate_w.T), as_stored(x.double() @ up_w.T)
+        want = as_stored((gate / (1 + torch.exp(-gate))) * up) @ down_w.T
+        tol = dict(atol=2e-2, rtol=8e-3)
+    assert torch.allclose(got.cpu().double(), want, **tol), (got.cpu().double() - want).abs().max()
 
 
 def _attention_weights(hidden, heads, kv, d, seed=0):
