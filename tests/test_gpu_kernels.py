@@ -406,7 +406,9 @@ def test_paged_attention_rows_do_not_depend_on_the_batch():
 
 
 BF16_ATTN = dict(atol=2e-2, rtol=2e-2)
-MMA_SHAPES = [(4, 2, 64, 16), (8, 2, 128, 16), (32, 8, 128, 16), (3, 1, 64, 4), (6, 6, 128, 1), (40, 2, 64, 5), (7, 1, 128, 64)]
+MMA_SHAPES = [(4, 2, 64, 16), (8, 2, 128, 16), (32, 8, 128, 16), (3, 1, 64, 4), (6, 6, 128, 1), (40, 2, 64, 5), (7, 1, 128, 64),
+              # head sizes that do not fill the 64- or 128-wide tiles
+              (5, 1, 48, 16), (4, 2, 80, 8), (6, 2, 96, 16), (3, 3, 112, 4), (4, 4, 16, 16), (8, 2, 32, 3)]
 
 
 @pytest.mark.parametrize("heads, kv_heads, d, page", MMA_SHAPES)
@@ -545,11 +547,12 @@ def test_attention_refuses_what_it_cannot_do():
         call(5, 2, 32)                                              # heads not a multiple of kv heads
     with pytest.raises(ops.KernelError, match="CUDA tensor"):
         ops.swiglu(torch.zeros(2, 4), torch.zeros(2, 2))            # no CPU path
-    assert ops.attention_mma_supports(128, 4) and not ops.attention_mma_supports(48, 4)
-    q = torch.zeros(4, 4 * 48, device="cuda", dtype=torch.bfloat16)
-    pool = torch.zeros(2, 2, 2, 16, 48, device="cuda", dtype=torch.bfloat16)
-    with pytest.raises(ops.KernelError, match="size"):              # the tensor-core kernels take 64 and 128 only
-        ops.prefill_attention(q, pool, torch.empty_like(q), i32([0, 4]), i32([0]), i32([0]), i32([[0, 1]]), 1, 4, 4, 2, 48, 1.0)
+    assert ops.attention_mma_supports(128, 4) and ops.attention_mma_supports(48, 4)
+    assert not ops.attention_mma_supports(40, 4) and not ops.attention_mma_supports(144, 4)
+    q = torch.zeros(4, 4 * 144, device="cuda", dtype=torch.bfloat16)
+    pool = torch.zeros(2, 2, 2, 16, 144, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="size"):              # the tensor-core kernels take steps of 16 up to 128
+        ops.prefill_attention(q, pool, torch.empty_like(q), i32([0, 4]), i32([0]), i32([0]), i32([[0, 1]]), 1, 4, 4, 2, 144, 1.0)
 
 
 # --------------------------------------------------------------- sampling

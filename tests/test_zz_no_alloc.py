@@ -97,5 +97,5 @@ def test_noalloc_decode_attention_refuses_what_does_not_fit():
     rc, out = _call_noalloc(fn, q, pool, table, q_start, kv_start, slots, n, heads, kv_heads, d, splits, 64)
     torch.cuda.synchronize()
     assert rc == -7 and torch.isnan(out).all()            # refused, nothing was launched
-    rc, _ = _call_noalloc(fn, q, pool, table, q_start, kv_start, slots, n, heads, kv_heads, 48, 1, 64)
-    assert rc == -2                                        # a head size the kernel is not built for
+    rc, _ = _call_noalloc(fn, q, pool, table, q_start, kv_start, slots, n, heads, kv_heads, 144, 1, 64)
+    assert rc == -2                                        # a head size the kernel is not built for (steps of 16 up to 128)

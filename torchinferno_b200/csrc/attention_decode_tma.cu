@@ -437,7 +437,7 @@ static int launch_decode_tma(const void* q, const void* pool, float* partial_o, 
   if (a.num_splits > 1 && a.counters == nullptr) {
     dim3 mgrid(a.heads, n_entries);
     TIB_LAUNCH_DEPENDENT(decode_merge_kernel<D>, mgrid, D, (a.num_splits + 1) * sizeof(float), stream, (const float*)partial_o, (const float*)partial_ml,
-                         (__nv_bfloat16*)out, a.q_start, a.heads, a.num_splits);
+                         (__nv_bfloat16*)out, a.q_start, a.heads, a.num_splits, D);
     TIB_LAUNCH_CHECK();
   }
   return TIB_OK;

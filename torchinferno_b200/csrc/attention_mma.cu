@@ -1,5 +1,6 @@
-// Paged attention on tensor cores (bf16 in, fp32 softmax and accumulation), for head sizes that
-// are multiples of 64 up to 128:
+// Paged attention on tensor cores (bf16 in, fp32 softmax and accumulation), for head sizes in steps
+// of 16 up to 128 (the tiles in shared memory are 64 or 128 wide; columns past the head's width are
+// zeros, which add nothing to a score and are not stored):
 //
 //   prefill_attention_kernel   portions of prompts: a block owns 64 rows (token, query head) of one
 //                              kv head and walks the keys up to the causal edge, flash-attention style
@@ -28,6 +29,7 @@ struct MmaAttnArgs {
   const int* block_table;
   int table_stride;
   int heads, kv_heads, group;
+  int head_dim;          // width of a head in memory: a multiple of 16, at most the kernels' D (tiles are padded with zeros)
   int page_size;
   int page_shift;        // log2(page_size) when it is a power of two, else -1
   int64_t page_stride;
@@ -55,8 +57,10 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_tile, __nv_bfloat1
   constexpr int CPR = D / 8;                       // 16-byte chunks per key row
   constexpr int ROWS = kMmaThreads / CPR;          // rows fetched by one pass of the block
   constexpr int PASSES = kBN / ROWS;
-  const int64_t v_off = (int64_t)a.kv_heads * a.page_size * D;
+  const int hd = a.head_dim;
+  const int64_t v_off = (int64_t)a.kv_heads * a.page_size * hd;
   const int c = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
+  const bool in_head = c * 8 < hd;                 // chunks past the head's width stay zero
   // first all page ids (independent loads, one latency), then all copies
   int page[PASSES], within[PASSES];
 #pragma unroll
@@ -77,8 +81,8 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_tile, __nv_bfloat1
 #pragma unroll
   for (int i = 0; i < PASSES; ++i) {
     const int r = r0 + i * ROWS;
-    const bool valid = page[i] >= 0 && page[i] < a.num_pages;
-    const __nv_bfloat16* src = valid ? pool + (int64_t)page[i] * a.page_stride + ((int64_t)kvh * a.page_size + within[i]) * D + c * 8 : pool;
+    const bool valid = in_head && page[i] >= 0 && page[i] < a.num_pages;
+    const __nv_bfloat16* src = valid ? pool + (int64_t)page[i] * a.page_stride + ((int64_t)kvh * a.page_size + within[i]) * hd + c * 8 : pool;
     const int off = r * D + ((c ^ (r & 7)) << 3);
     cp_async16(k_tile + off, src, valid);
     cp_async16(v_tile + off, valid ? src + v_off : pool, valid);
@@ -179,15 +183,16 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   const int first_key = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
   const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int q_width = a.heads * D;
+  const int hd = a.head_dim;
+  const int q_width = a.heads * hd;
 
-  // queries of the tile -> shared memory (rows beyond nrows are zero)
+  // queries of the tile -> shared memory (rows beyond nrows, and columns beyond the head's width, are zero)
   constexpr int CPR = D / 8;
   for (int idx = threadIdx.x; idx < BM * CPR; idx += kMmaThreads) {
     const int r = idx / CPR, c = idx - r * CPR;
-    const bool valid = r < nrows;
+    const bool valid = r < nrows && c * 8 < hd;
     const int t = r / a.group, g = r - t * a.group;
-    const __nv_bfloat16* src = valid ? q + (size_t)(row0 + t0 + t) * q_width + (kvh * a.group + g) * D + c * 8 : q;
+    const __nv_bfloat16* src = valid ? q + (size_t)(row0 + t0 + t) * q_width + (kvh * a.group + g) * hd + c * 8 : q;
     cp_async16(q_s + r * D + ((c ^ (r & 7)) << 3), src, valid);
   }
   cp_async_commit();
@@ -276,11 +281,11 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     if (r >= nrows) continue;
     const float inv = 1.f / sum;
     const int t = r / a.group, g = r - t * a.group;
-    __nv_bfloat16* dst = out + (size_t)(row0 + t0 + t) * q_width + (kvh * a.group + g) * D;
+    __nv_bfloat16* dst = out + (size_t)(row0 + t0 + t) * q_width + (kvh * a.group + g) * hd;
 #pragma unroll
     for (int n = 0; n < D / 8; ++n) {
       const uint32_t v = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
-      *reinterpret_cast<uint32_t*>(dst + n * 8 + tig * 2) = v;
+      if (n * 8 < hd) *reinterpret_cast<uint32_t*>(dst + n * 8 + tig * 2) = v;
     }
   }
 }
@@ -328,11 +333,12 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   }
   const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
 
+  const int hd = a.head_dim;
   constexpr int CPR = D / 8;
   for (int idx = threadIdx.x; idx < 16 * CPR; idx += kMmaThreads) {
     const int r = idx / CPR, c = idx - r * CPR;
-    const bool valid = r < nrows;
-    const __nv_bfloat16* src = valid ? q + (size_t)row0 * a.heads * D + (head0 + r) * D + c * 8 : q;
+    const bool valid = r < nrows && c * 8 < hd;
+    const __nv_bfloat16* src = valid ? q + ((size_t)row0 * a.heads + head0 + r) * hd + c * 8 : q;
     cp_async16(q_s + r * D + ((c ^ (r & 7)) << 3), src, valid);
   }
   cp_async_commit();
@@ -415,6 +421,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   __syncthreads();
   for (int idx = threadIdx.x; idx < nrows * D; idx += kMmaThreads) {
     const int r = idx / D, dd = idx - r * D;
+    if (dd >= hd) continue;
     float mm = -CUDART_INF_F;
 #pragma unroll
     for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red_ml[(w * 16 + r) * 2]);
@@ -427,10 +434,10 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       sum += red_ml[(w * 16 + r) * 2 + 1] * wgt;
     }
     if (a.num_splits == 1) {
-      out[(size_t)row0 * a.heads * D + (head0 + r) * D + dd] = __float2bfloat16_rn(acc / sum);
+      out[((size_t)row0 * a.heads + head0 + r) * hd + dd] = __float2bfloat16_rn(acc / sum);
     } else {
       const size_t slot = ((size_t)entry * a.heads + head0 + r) * a.num_splits + split;
-      partial_o[slot * D + dd] = acc;
+      partial_o[slot * hd + dd] = acc;
       if (dd == 0) {
         partial_ml[slot * 2] = mm;
         partial_ml[slot * 2 + 1] = sum;
@@ -471,7 +478,7 @@ static int launch_decode(const void* q, const void* pool, float* partial_o, floa
   TIB_LAUNCH_CHECK();
   if (a.num_splits > 1) {
     dim3 mgrid(a.heads, n_entries);
-    decode_merge_kernel<D><<<mgrid, D, (a.num_splits + 1) * sizeof(float), stream>>>(partial_o, partial_ml, (__nv_bfloat16*)out, a.q_start, a.heads, a.num_splits);
+    decode_merge_kernel<D><<<mgrid, D, (a.num_splits + 1) * sizeof(float), stream>>>(partial_o, partial_ml, (__nv_bfloat16*)out, a.q_start, a.heads, a.num_splits, a.head_dim);
     TIB_LAUNCH_CHECK();
   }
   return TIB_OK;
@@ -482,10 +489,11 @@ static int fill_args(MmaAttnArgs& a, const int* q_start, const int* kv_start, co
                      int num_pages, int window, float scale) {
   if (!q_start || !kv_start || !slots || !block_table) return TIB_E_ARG;
   if (heads < 1 || kv_heads < 1 || heads % kv_heads != 0 || page_size < 1) return TIB_E_SIZE;
-  if (head_dim != 64 && head_dim != 128) return TIB_E_SIZE;
+  if (head_dim < 16 || head_dim > 128 || head_dim % 16 != 0) return TIB_E_SIZE;
   if (page_stride % 8 != 0) return TIB_E_ALIGN;  // 16-byte copies of key rows
   a.q_start = q_start; a.kv_start = kv_start; a.slots = slots; a.block_table = block_table;
   a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads; a.group = heads / kv_heads;
+  a.head_dim = head_dim;
   a.page_size = page_size; a.page_shift = -1;
   for (int sft = 0; sft < 31; ++sft) if ((1 << sft) == page_size) a.page_shift = sft;
   a.page_stride = page_stride; a.num_pages = num_pages; a.window = window;
@@ -500,7 +508,7 @@ using namespace tib;
 
 // Which head sizes the tensor-core attention kernels are built for.
 TIB_API int tib_attention_mma_supports(int head_dim, int group) {
-  return (head_dim == 64 || head_dim == 128) && group >= 1 && group <= 64;
+  return head_dim >= 16 && head_dim <= 128 && head_dim % 16 == 0 && group >= 1 && group <= 64;
 }
 
 // Portions of prompts (and, unless skip_single, single tokens too).  bf16 only.
@@ -517,7 +525,7 @@ TIB_API int tib_prefill_attention(const void* q, const void* pool, void* out, co
   if (rc != TIB_OK) return rc;
   if (a.group > 64 || n_entries > 65535 || kv_heads > 65535) return TIB_E_SIZE;
   a.skip_single = skip_single;
-  return head_dim == 64 ? launch_prefill<64>(q, pool, out, a, n_entries, max_q_len, stream)
+  return head_dim <= 64 ? launch_prefill<64>(q, pool, out, a, n_entries, max_q_len, stream)
                         : launch_prefill<128>(q, pool, out, a, n_entries, max_q_len, stream);
 }
 
@@ -542,7 +550,7 @@ TIB_API int tib_decode_attention(const void* q, const void* pool, void* out, flo
   if (n_entries > 65535 || (int64_t)kv_heads * row_tiles > 65535) return TIB_E_SIZE;
   a.num_splits = num_splits;
   a.chunk = chunk;
-  return head_dim == 64 ? launch_decode<64>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream)
+  return head_dim <= 64 ? launch_decode<64>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream)
                         : launch_decode<128>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream);
 }
 
@@ -624,6 +632,6 @@ TIB_API int tib_decode_attention_noalloc(const void* q, const void* pool, void* 
   }
   a.num_splits = num_splits;
   a.chunk = chunk;
-  return head_dim == 64 ? launch_decode<64>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream)
+  return head_dim <= 64 ? launch_decode<64>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream)
                         : launch_decode<128>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream);
 }

@@ -84,7 +84,9 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], f
 template <int D>
 __global__ void __launch_bounds__(D)
 decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
-                    __nv_bfloat16* __restrict__ out, const int* __restrict__ q_start, int heads, int num_splits) {
+                    __nv_bfloat16* __restrict__ out, const int* __restrict__ q_start, int heads, int num_splits,
+                    int head_dim) {
+  // (D threads; head_dim <= D is the width of a head in memory)
   pdl_wait();   // (returns at once when the launch was an ordinary one)
   pdl_trigger();
   extern __shared__ float merge_w[];     // [num_splits] weights, then 1 / sum
@@ -108,14 +110,15 @@ decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict
     if (lane == 0) merge_w[num_splits] = 1.f / sum;
   }
   __syncthreads();
-  const float* po = partial_o + base_slot * D + threadIdx.x;
+  if ((int)threadIdx.x >= head_dim) return;
+  const float* po = partial_o + base_slot * head_dim + threadIdx.x;
   float acc = 0.f;
 #pragma unroll 8
   for (int s = 0; s < num_splits; ++s) {
     const float w = merge_w[s];
-    acc += w == 0.f ? 0.f : w * po[(size_t)s * D];
+    acc += w == 0.f ? 0.f : w * po[(size_t)s * head_dim];
   }
-  out[(size_t)row0 * heads * D + head * D + threadIdx.x] = __float2bfloat16_rn(acc * merge_w[num_splits]);
+  out[((size_t)row0 * heads + head) * head_dim + threadIdx.x] = __float2bfloat16_rn(acc * merge_w[num_splits]);
 }
 
 }  // namespace tib

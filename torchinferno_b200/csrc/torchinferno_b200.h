@@ -14,7 +14,7 @@
 extern "C" {
 #endif
 
-/* Paged decode attention (bf16, head_dim 64 or 128) that allocates nothing.
+/* Paged decode attention (bf16, head_dim a multiple of 16 up to 128) that allocates nothing.
  *
  * This entry point has no counterpart in the reference project.  It exists for hosts that cannot
  * allocate device memory when they call: code running under another framework's fixed memory plan,
