@@ -167,10 +167,11 @@ def run_elementwise(args) -> None:
 
 
 def run_step_timeline(args) -> None:
-    """Which kernels a captured decode step spends its time in: every kernel of one step with its start and
-    duration as the driver's activity records (CUPTI, through torch.profiler) give them, summed by kernel,
-    and one layer listed launch by launch (a negative gap: the kernel was placed before the one before it
-    had ended, by programmatic dependent launch, and its duration includes the wait)."""
+    """Which kernels a captured decode step (or, with --prompt, the step of one whole prompt of --context tokens)
+    spends its time in: every kernel of one step with its start and duration as the driver's activity records
+    (CUPTI, through torch.profiler) give them, summed by kernel, and one layer listed launch by launch (a
+    negative gap: the kernel was placed before the one before it had ended, by programmatic dependent launch,
+    and its duration includes the wait)."""
     import collections
     from torch.profiler import ProfilerActivity, profile
     from torchinferno_b200.engine.batch import StepEntry
@@ -183,11 +184,20 @@ def run_step_timeline(args) -> None:
               "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False}
     model = random_model(config, seed=0, dtype="bfloat16")
     n, ctx = args.batch, args.context
-    runner = make_runner(model, page_size=args.page_size, max_tokens=n * (ctx + 64), max_requests=n, check_errors=False)
     prompts = torch.randint(0, args.vocab, (n, ctx), generator=torch.Generator().manual_seed(0)).tolist()
-    for i, prompt in enumerate(prompts):
-        runner.step([StepEntry(i, prompt, [ctx - 1])])
-    step = lambda: runner.step([StepEntry(i, [5], [0]) for i in range(n)])
+    if args.prompt:
+        runner = make_runner(model, page_size=args.page_size, max_tokens=2 * (ctx + 64), max_requests=2, check_errors=False)
+        turn = [0]
+
+        def step() -> None:      # a new request's whole prompt, alone in its step
+            turn[0] += 1
+            runner.step([StepEntry(turn[0], prompts[0], [ctx - 1])])
+            runner.end([turn[0]])
+    else:
+        runner = make_runner(model, page_size=args.page_size, max_tokens=n * (ctx + 64), max_requests=n, check_errors=False)
+        for i, prompt in enumerate(prompts):
+            runner.step([StepEntry(i, prompt, [ctx - 1])])
+        step = lambda: runner.step([StepEntry(i, [5], [0]) for i in range(n)])
     for _ in range(5):
         step()
     torch.cuda.synchronize()
@@ -209,8 +219,8 @@ def run_step_timeline(args) -> None:
     for e in last:
         total[e.name[:64]][0] += 1
         total[e.name[:64]][1] += e.time_range.end - e.time_range.start
-    print(json.dumps({"step_us": round(t1 - t0, 1), "kernels": len(last), "batch": n, "context": ctx, "layers": args.layers,
-                      "gemm_backend": args.gemm_backend}))
+    print(json.dumps({"step_us": round(t1 - t0, 1), "kernels": len(last), "step": "prompt" if args.prompt else "decode",
+                      "batch": 1 if args.prompt else n, "context": ctx, "layers": args.layers, "gemm_backend": args.gemm_backend}))
     for name, (count, us) in sorted(total.items(), key=lambda kv: -kv[1][1]):
         print(f"{us:9.1f} us  x{count:4d}  avg {us / count:7.2f}  {name}")
     print("one layer, launch by launch (gap to the end of the kernel before, duration):")
@@ -265,6 +275,7 @@ def main(argv=None) -> int:
     p.add_argument("--vocab", type=int, default=128256)
     p.add_argument("--gemm-backend", choices=["auto", "tcgen05", "library"], default="auto")
     p.add_argument("--plain", action="store_true", help="run the steps without the activity profiler (for ncu)")
+    p.add_argument("--prompt", action="store_true", help="the step of one whole prompt of --context tokens instead of a decode step")
     common(p)
     p.set_defaults(func=run_step_timeline, iters=3)
     args = parser.parse_args(argv)
