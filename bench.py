@@ -55,7 +55,9 @@ def load_peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (every 200 ms), and once
+    more through NVML at a moment the caller chooses (``snap``: while the timed steps are still running on the GPU),
+    so that a region shorter than the sampling period has a sample too.  Reading only: nothing is set."""
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
@@ -63,6 +65,13 @@ class ClockSampler:
     def __init__(self, index: int = 0) -> None:
         self.lines: list[str] = []
         self.proc = None
+        self.nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = (pynvml, pynvml.nvmlDeviceGetHandleByIndex(index))
+        except Exception:      # (no NVML binding: the periodic samples remain)
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
@@ -78,6 +87,24 @@ class ClockSampler:
 
     def mark(self) -> int:
         return len(self.lines)
+
+    def snap(self) -> None:
+        """One sample now, in the format of the periodic ones."""
+        if self.nvml is None:
+            return
+        nv, handle = self.nvml
+        try:
+            sm = nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)
+            top = nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM)
+            watts = nv.nvmlDeviceGetPowerUsage(handle) / 1e3
+            bits = nv.nvmlDeviceGetCurrentClocksEventReasons(handle)
+            flag = lambda bit: "Active" if bits & bit else "Not Active"
+            self.lines.append(", ".join([str(sm), str(top), f"{watts:.2f}", flag(nv.nvmlClocksEventReasonHwSlowdown),
+                                         flag(nv.nvmlClocksEventReasonHwThermalSlowdown),
+                                         flag(nv.nvmlClocksEventReasonSwThermalSlowdown),
+                                         flag(nv.nvmlClocksEventReasonSwPowerCap)]))
+        except Exception:
+            pass
 
     def stop(self) -> None:
         if self.proc is not None:
@@ -147,6 +174,7 @@ def timed_decode(runner, batch: int, steps: int, warmup: int, numbers: dict, sam
     begin.record()
     runner.decode_loop(ids, last, steps, temperature=temps, seeds=seeds)
     end.record()
+    sampler.snap()                   # (the steps are launched, not finished: the GPU is at work on them)
     torch.cuda.synchronize()
     ms = begin.elapsed_time(end)
     clocks = sampler.summary(mark, sampler.mark())
