@@ -222,6 +222,40 @@ def test_few_rows_kernel_is_chosen_by_measurement_and_either_choice_is_right():
             assert (as_ref(part) - want[:, 64:1096]).abs().max() <= 1e-2 * want.abs().max() + 1e-6
 
 
+def test_advance_decode_moves_tokens_and_positions_on():
+    """The kernel between two captured decode steps: the drawn tokens become the next inputs, positions (and the
+    positions the sampler draws at) move on by one, and the history row takes the tokens; longer buffers keep their tails."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    i32 = lambda xs: dev(torch.tensor(xs, dtype=torch.int32))
+    tokens, sampled = i32([7, 8, 9]), i32([100, 200, 300, 999])
+    positions, draws, history = i32([4, 0, 511, 77]), i32([5, 1, 512]), i32([-1, -1, -1, -1, -1])
+    ops.advance_decode(tokens, sampled, positions, draws, history)
+    assert tokens.tolist() == [100, 200, 300] and positions.tolist() == [5, 1, 512, 77]
+    assert draws.tolist() == [6, 2, 513] and history.tolist() == [100, 200, 300, -1, -1]
+    ops.advance_decode(tokens, sampled, positions)                   # the optional buffers may be left out
+    assert positions.tolist() == [6, 2, 513, 77]
+    with pytest.raises(ops.KernelError, match="shorter"):
+        ops.advance_decode(tokens, i32([1]), positions)
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 72, 40), (8, 4096, 4096), (17, 1000, 264), (300, 136, 2048)])
+@pytest.mark.parametrize("w_kn", [False, True])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_library_gemm_both_layouts(m, n, k, w_kn, out_dtype):
+    """cuBLAS called from the engine's library (its own handle and workspace): weights stored [out, in] and
+    [in, out], bf16 and fp32 results, against float64."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    x, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, scale=0.05, seed=3)
+    ops.library_gemm_ready(torch.device("cuda", torch.cuda.current_device()))
+    out = ops.library_gemm(dev(x), dev(w.t().contiguous()) if w_kn else dev(w),
+                           torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda"), w_kn=w_kn)
+    want = x.double() @ w.double().T
+    bound = (1e-2 if out_dtype == torch.bfloat16 else 2e-5) * want.abs().max() + 1e-6
+    assert (as_ref(out) - want).abs().max() <= bound
+
+
 # -------------------------------------------------------------- RoPE + KV
 def paged_layout(n_requests, lengths, page_size, kv_heads, d, dtype, spare_pages=3, seed=0):
     """A pool with NaN everywhere, shuffled page ids, and block tables for the given lengths."""
