@@ -96,7 +96,9 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
 
 // bf16, full rotate-half rotation, head size a multiple of 16: every work item is eight dims of
 // the lower half and their partners in the upper half (two 16-byte loads and stores).
-__global__ void __launch_bounds__(256)
+// (MAXT: the most threads a block is launched with; the registers a thread may use follow from it)
+template <int MAXT>
+__global__ void __launch_bounds__(MAXT)
 rope_append_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
                           __nv_bfloat16* __restrict__ pool, const int* __restrict__ positions,
                           const int* __restrict__ token_slot, const int* __restrict__ block_table,
@@ -200,11 +202,22 @@ TIB_API int tib_rope_append(const void* qkv, void* q_out, void* pool, const int*
         table_stride, inv_freq, heads, kv_heads, head_dim, rot_dim, interleaved, page_size,
         page_stride, num_pages, write_kv, error_word);
   else if (dtype == TIB_BF16 && rot_dim == head_dim && !interleaved && head_dim % 16 == 0 &&
-           (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pool) & 15) == 0 && (page_stride % 8 == 0 || !write_kv))
-    TIB_LAUNCH_DEPENDENT(rope_append_bf16x8_kernel, n_tokens, threads, smem, stream,
-        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, positions, token_slot, block_table,
-        table_stride, inv_freq, heads, kv_heads, head_dim, chunk_shift, page_size, page_stride, num_pages, write_kv, error_word);
-  else if (dtype == TIB_BF16)
+           (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pool) & 15) == 0 && (page_stride % 8 == 0 || !write_kv)) {
+    // With few tokens (a decode step) a block is all there is on its SM and its latency is the kernel's: it gets as
+    // many threads as a token has work items (eight dims of a q or k head and their partners; 32 + 8 heads of 128
+    // are 320), so that they are done in one pass (5.8 -> 4.9 us at 8 tokens).  With many tokens blocks of 256
+    // share the SMs better (14.8 us at 2,048 tokens against 19.4).
+    const int items = (heads + (write_kv ? kv_heads : 0)) * (head_dim / 16);
+    const int item_threads = n_tokens <= 128 && items <= 1024 ? (items + 31) / 32 * 32 : 256;
+    if (item_threads <= 256)
+      TIB_LAUNCH_DEPENDENT(rope_append_bf16x8_kernel<256>, n_tokens, item_threads < 64 ? 64 : item_threads, smem, stream,
+          (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, positions, token_slot, block_table,
+          table_stride, inv_freq, heads, kv_heads, head_dim, chunk_shift, page_size, page_stride, num_pages, write_kv, error_word);
+    else
+      TIB_LAUNCH_DEPENDENT(rope_append_bf16x8_kernel<1024>, n_tokens, item_threads, smem, stream,
+          (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, positions, token_slot, block_table,
+          table_stride, inv_freq, heads, kv_heads, head_dim, chunk_shift, page_size, page_stride, num_pages, write_kv, error_word);
+  } else if (dtype == TIB_BF16)
     TIB_LAUNCH_DEPENDENT(rope_append_kernel<__nv_bfloat16>, n_tokens, threads, smem, stream,
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, positions,
         token_slot, block_table, table_stride, inv_freq, heads, kv_heads, head_dim, rot_dim,
