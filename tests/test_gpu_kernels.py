@@ -195,8 +195,8 @@ def test_gemm_tcgen05_swapab(m, n, k, splits, w_kn):
 
 
 def test_few_rows_kernel_is_chosen_by_measurement_and_either_choice_is_right():
-    """Weights that leave their few-rows kernel open get it from tune_few_rows (the swap-AB kernel up to 0, 4, 8 or 16
-    rows): one decision per shape, kept for the process, the same for every weight of the shape; a slice of the weight inherits it; and whichever kernel
+    """Weights that leave their few-rows kernel open get it from tune_few_rows (the swap-AB kernel up to 0, 4, 8, 16, 32
+    or 64 rows): one decision per shape, kept for the process, the same for every weight of the shape; a slice of the weight inherits it; and whichever kernel
     was chosen, and whichever is forced, the product is right at few and at many rows."""
     need_gpu()
     from torchinferno_b200.kernels import gemm
@@ -207,12 +207,12 @@ def test_few_rows_kernel_is_chosen_by_measurement_and_either_choice_is_right():
     assert all(w.few_rows == 0 for w in open_weights)                     # the library until measured
     decisions = gemm.tune_few_rows()
     key = (n, k, open_weights[0].tensor.device)
-    assert decisions[key] in (0, 4, 8, 16) and all(w.few_rows == decisions[key] for w in open_weights)
+    assert decisions[key] in (0, 4, 8, 16, 32, 64) and all(w.few_rows == decisions[key] for w in open_weights)
     later = LinearWeight(dev(ws[0]), few_rows_tcgen05=None)
     assert gemm.tune_few_rows()[key] == decisions[key] and later.few_rows == open_weights[0].few_rows
     forced = [LinearWeight(dev(ws[0]), few_rows_tcgen05=True), LinearWeight(dev(ws[0]), few_rows_tcgen05=False)]
-    assert [w.few_rows for w in forced] == [LinearWeight.FEW_ROWS, 0]
-    for m in (1, 4, 5, 8, 9, 16, 17, 200):
+    assert [w.few_rows for w in forced] == [LinearWeight.FEW_ROWS, 0] and LinearWeight.FEW_ROWS == 64
+    for m in (1, 4, 5, 8, 9, 16, 17, 33, 64, 65, 200):
         x = rnd(m, k, dtype=torch.bfloat16, seed=50 + m)
         want = x.double() @ ws[0].double().T
         for weight in (open_weights[0], later, *forced):

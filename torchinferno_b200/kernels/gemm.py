@@ -63,7 +63,7 @@ class LinearWeight:
     never does, None leaves it to :func:`tune_few_rows` (the library until that has run).
     """
 
-    FEW_ROWS = 16      # up to this many rows a weight may go to the swap-AB kernel under "auto"
+    FEW_ROWS = 64      # up to this many rows a weight may go to the swap-AB kernel under "auto" (the most it takes)
 
     def __init__(self, weight: torch.Tensor, *, allow_transpose: bool = True, few_rows_tcgen05: bool | None = False) -> None:
         self.out_features, self.in_features = weight.shape
@@ -148,9 +148,9 @@ _tuned: dict[tuple, int] = {}           # (out, in, device) -> rows up to which 
 tuning_times: dict[tuple, dict[str, float]] = {}   # (out, in, device, rows) -> milliseconds of the timed walk with either kernel
 # cuBLAS changes kernels with the row count (at the 8B sizes its output projection takes 16.2 us at 8 rows and
 # 10.8 at 16, the swap-AB kernel 12.4 and 12.9; its down projection is 9 % behind the swap-AB kernel at 1 row
-# and 4 % at 8), so three row counts are measured, each standing for the counts up to it: a shape may go to
-# the swap-AB kernel up to 4 rows, up to 8, up to 16, or not at all.
-TUNE_ROWS = ((1, 4), (8, 8), (16, 16))      # (rows measured, rows it stands for)
+# and 4 % at 8), so several row counts are measured, each standing for the counts up to it: a shape may go to
+# the swap-AB kernel up to 4 rows, up to 8, 16, 32 or 64, or not at all.
+TUNE_ROWS = ((1, 4), (8, 8), (16, 16), (32, 32), (64, 64))      # (rows measured, rows it stands for)
 # The swap-AB kernel must take under this share of the library's time.  The measurement repeats within about half
 # a per cent.  The line is drawn in a gap of the shares measured at the 8B and 3B sizes (1, 8 and 16 rows): 0.73-0.95
 # on one side (o and, at few rows, down at 8B; down, o and gate/up at 3B), 0.997 and more on the other.  A shape
@@ -163,7 +163,7 @@ TUNE_MEMBERS = 32
 
 def tune_few_rows() -> dict[tuple, int]:
     """Decide, for every weight bound with ``few_rows_tcgen05=None`` since the last call, up to how many rows the
-    swap-AB kernel takes its products (0, 4, 8 or 16), and return the decisions made so far by (out, in, device).
+    swap-AB kernel takes its products (0, 4, 8, 16, 32 or 64), and return the decisions made so far by (out, in, device).
 
     Weights of one shape are measured together, once per shape and process, the way a decode step runs them:
     a CUDA graph walks over them (different weights one after the other, so nothing comes from L2), each
