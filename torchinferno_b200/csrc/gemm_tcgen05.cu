@@ -197,9 +197,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 // no second kernel.
 constexpr uint32_t kSwWBytes = 128 * kTcBK * 2;   // 16 KB of w per stage
 constexpr int kSwRedRows = 136;                   // splits * ceil(128 / splits) <= 135 for up to 8 splits
-// Stages of the w / x ring: what fits beside two reduction buffers (a block has an SM to itself, and the
-// bytes in flight are what hide the memory latency).
-constexpr int sw_stages(int npad) { return npad <= 16 ? 9 : npad <= 32 ? 8 : npad <= 48 ? 6 : 5; }
+// Stages of the w / x ring.  More bytes in flight are not better: with every SM streaming, about 16 to 20 MB on
+// their way (6 to 8 stages of 18 KB on each of 135 to 148 SMs) stream fastest; with 11 stages the same loop was
+// 5 % slower, with 3 stages 15 %.  (At more rows a stage is larger and fewer fit.)
+constexpr int sw_stages(int npad) { return npad <= 16 ? 7 : npad <= 32 ? 8 : npad <= 48 ? 6 : 5; }
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
