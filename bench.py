@@ -377,7 +377,7 @@ def run_reference(args) -> dict:
                         "value": round(args.batch * PROMPT_LEN / (short / 1e3), 1)}}
 
 
-def main() -> int:
+def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=2032)
@@ -389,7 +389,7 @@ def main() -> int:
     parser.add_argument("--point-steps", type=int, default=None, help="decode steps of the other batch sizes (default: --steps)")
     parser.add_argument("--e2e-steps", type=int, default=None, help="steps of the end-to-end run (default: --steps, the same contexts)")
     parser.add_argument("--gemm-backend", choices=["auto", "tcgen05", "library"], default="auto")
-    args = parser.parse_args()
+    args = parser.parse_args(argv)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps({"metric": METRIC, "unsupported": f"this engine runs on one GPU; --gpus {args.gpus} is not supported",
