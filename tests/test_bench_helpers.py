@@ -60,3 +60,14 @@ def test_more_than_one_gpu_is_refused_with_one_line_and_exit_code_2(bench, capsy
     assert bench.main(["--gpus", "2"]) == 2
     out = capsys.readouterr().out.strip().splitlines()
     assert len(out) == 1 and '"n_gpus": 2' in out[0] and "unsupported" in out[0]
+
+
+def test_parts_provided_for_split_decode_attention():
+    """The grid of the decode attention kernel: about 256 blocks in all, at most 16 parts a request, 32 where
+    contexts may be long, one when the batch fills the GPU by itself."""
+    from torchinferno_b200.kernels.ops import decode_num_splits
+    parts = {b: decode_num_splits(b, 32, 8) for b in (1, 2, 4, 8, 16, 32, 64, 200)}
+    assert parts == {1: 16, 2: 16, 4: 8, 8: 4, 16: 2, 32: 1, 64: 1, 200: 1}
+    assert decode_num_splits(1, 32, 8, max_kv_len=8192) == 16 and decode_num_splits(1, 32, 8, max_kv_len=8193) == 32
+    assert decode_num_splits(2, 32, 8, max_kv_len=100000) == 16          # 16 blocks of kv heads x 16 parts are 256
+    assert decode_num_splits(1, 64, 2) == 16 and decode_num_splits(3, 40, 40) == 2   # groups above 16 take more row tiles
