@@ -235,6 +235,9 @@ def run_step_timeline(args) -> None:
 
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="python -m torchinferno_b200.bench_kernels", description=__doc__.splitlines()[0])
+    parser.add_argument("--ordinary-launches", action="store_true",
+                        help="launch the kernels without programmatic dependent launch (a profiler that lists kernels "
+                             "by name does not see dependent launches)")
     sub = parser.add_subparsers(dest="command", required=True)
 
     def common(p):
@@ -281,6 +284,8 @@ def main(argv=None) -> int:
     args = parser.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("bench_kernels needs a CUDA device")
+    if args.ordinary_launches:
+        ops.set_dependent_launch(False)
     with torch.inference_mode():
         args.func(args)
     return 0
