@@ -115,22 +115,6 @@ def test_gemm_f32_is_true_fp32_and_row_independent(m, n, k, wdtype):
     assert torch.equal(one[0], out[m // 2])               # a row does not depend on the rows beside it
 
 
-@pytest.mark.parametrize("m, n, k", [(1, 64, 64), (8, 4096, 4096), (16, 1000, 512), (33, 129 * 8, 96 * 2 + 64), (64, 6144, 4096)])
-@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_gemm_skinny(m, n, k, out_dtype):
-    need_gpu()
-    from torchinferno_b200.kernels import ops
-    x, w = rnd(m, k, dtype=torch.bfloat16), rnd(n, k, dtype=torch.bfloat16, scale=0.05, seed=3)
-    out = ops.gemm_skinny(dev(x), dev(w), torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda"))
-    want = x.double() @ w.double().T
-    bound = (1e-2 if out_dtype == torch.bfloat16 else 1e-4) * want.abs().max() + 1e-6
-    assert (as_ref(out) - want).abs().max() <= bound
-    with pytest.raises(ops.KernelError, match="size"):
-        ops.gemm_skinny(dev(rnd(65, 64, dtype=torch.bfloat16)), dev(rnd(8, 64, dtype=torch.bfloat16)), torch.empty(65, 8, dtype=out_dtype, device="cuda"))
-    with pytest.raises(ops.KernelError, match="size"):
-        ops.gemm_skinny(dev(rnd(4, 48, dtype=torch.bfloat16)), dev(rnd(8, 48, dtype=torch.bfloat16)), torch.empty(4, 8, dtype=out_dtype, device="cuda"))
-
-
 @pytest.mark.parametrize("m, n, k", [(128, 256, 64), (1, 8, 64), (200, 520, 192), (77, 1000, 4096), (300, 264, 1024), (2048, 512, 14336)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05(m, n, k, out_dtype):

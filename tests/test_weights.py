@@ -59,8 +59,12 @@ def test_tied_head_is_not_stored_and_is_shared(tmp_path):
     assert model.head is model.embedding
     # a tied checkpoint that also stores the head is accepted (the head is optional when tied)
     tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)
     save_file(tensors, str(tmp_path / "model.safetensors"))
-    load_weights(_model(TINY_B), tmp_path)
+    model = _model(TINY_B)
+    report = load_weights(model, tmp_path)
+    assert model.head is model.embedding and report["not_read"] == ["lm_head.weight"]
+    assert report["ignored"] == ["model.layers.0.self_attn.rotary_emb.inv_freq"]
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
@@ -68,14 +72,15 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     tensors = load_file(str(tmp_path / "model.safetensors"))
     del tensors["model.layers.0.self_attn.k_proj.weight"]
     del tensors["model.norm.weight"]
-    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)      # a known harmless buffer: ignored
+    tensors["model.layers.0.self_attn.q_norm.weight"] = torch.zeros(8)
     tensors["model.layers.1.mlp.up_proj.weight"] = torch.zeros(64, 128, dtype=torch.bfloat16)
     save_file(tensors, str(tmp_path / "model.safetensors"))
     with pytest.raises(WeightError) as err:
         load_weights(_model(TINY_A), tmp_path)
     text = str(err.value)
     assert "missing (2)" in text and "model.layers.0.self_attn.k_proj.weight" in text and "model.norm.weight" in text
-    assert "unexpected (1)" in text and "rotary_emb.inv_freq" in text
+    assert "unexpected (1)" in text and "q_norm.weight" in text and "inv_freq" not in text
     assert "wrong shape (1)" in text and "model.layers.1.mlp.up_proj.weight: file [64, 128] vs model [128, 64]" in text
 
 

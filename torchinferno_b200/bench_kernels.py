@@ -128,8 +128,6 @@ def run_gemm(args) -> None:
         x = torch.randn(args.rows, k, device="cuda").to(torch.bfloat16)
         out = torch.empty(args.rows, n, dtype=torch.bfloat16, device="cuda")
         common = dict(bytes_moved=n * k * 2, flops=2 * args.rows * n * k, rows=args.rows, n=n, k=k)
-        if ops.gemm_skinny_supports(args.rows, n, k):
-            report(f"gemm_skinny[{name}]", timer(lambda: ops.gemm_skinny(x, w, out)), **common)
         if ops.gemm_tcgen05_swapab_supports(args.rows, n, k):
             report(f"gemm_tcgen05_swapab[{name}]", timer(lambda: ops.gemm_tcgen05_swapab(x, w, out)), **common)
             w_kn = w.t().contiguous()

@@ -16,7 +16,8 @@ What is different here:
   with a window gives pages back as soon as the window has passed them
   (:meth:`CacheManager.release_behind_window`), all others when the request ends;
 * one layer's pages are laid out ``[pages, 2, kv_heads, page_size, head_dim]``
-  so that the keys of one head in one page are contiguous;
+  so that the keys of one head in one page are contiguous (keys and values may
+  differ in width: a page then holds all its keys, then all its values);
 * beside the pages there are **state slots**: one fixed-size record per live
   request for every layer call whose mixer asks for one, zeroed when the
   request is opened.
@@ -93,6 +94,8 @@ class GroupBinding:
     block_table: torch.Tensor
     page_size: int
     window: int | None
+    keys: torch.Tensor | None = None
+    values: torch.Tensor | None = None
 
 
 @dataclass
@@ -100,7 +103,8 @@ class CacheGroup:
     spec: CacheSpec
     cache_layers: list[int]
     allocator: PageAllocator
-    pool: torch.Tensor | None             # [layers_in_group, pages, 2, kv_heads, page_size, head_dim]
+    pool: torch.Tensor | None             # [layers_in_group, pages, elements of a page]: in a page all keys
+                                          # [kv_heads, page_size, head_dim], then all values [kv_heads, page_size, value width]
     table_device: torch.Tensor | None     # [max_slots, max_pages] int32
     pending: dict[int, int] = field(default_factory=dict)    # flat index into table_device -> page id;
                                                              # the last change to an entry wins
@@ -140,7 +144,7 @@ class CacheManager:
             group.cache_layers.append(layer)
         for group in self.groups:
             if allocate_tensors:
-                shape = (len(group.cache_layers), num_pages, 2, group.spec.kv_heads, page_size, group.spec.head_dim)
+                shape = (len(group.cache_layers), num_pages, page_size * group.spec.elements_per_token)
                 group.pool = torch.zeros(shape, dtype=dtype, device=self.device)
                 group.table_device = torch.full((max_requests, self.max_pages_per_request), -1,
                                                 dtype=torch.int32, device=self.device)
@@ -288,7 +292,13 @@ class CacheManager:
     def kv_binding(self, cache_layer: int) -> GroupBinding:
         gi, li = self._group_of_layer[cache_layer]
         group = self.groups[gi]
-        return GroupBinding(group.pool[li], group.table_device, self.page_size, group.spec.window)
+        spec, pages, page = group.spec, group.pool[li], self.page_size
+        key_elems = spec.kv_heads * page * spec.head_dim
+        keys = pages[:, :key_elems].unflatten(1, (spec.kv_heads, page, spec.head_dim))
+        values = pages[:, key_elems:].unflatten(1, (spec.kv_heads, page, spec.value_width)) if spec.value_width else None
+        if spec.value_width == spec.head_dim:
+            pages = pages.view(self.num_pages, 2, spec.kv_heads, page, spec.head_dim)
+        return GroupBinding(pages, group.table_device, page, spec.window, keys, values)
 
     def group_of_layer(self, cache_layer: int) -> int:
         return self._group_of_layer[cache_layer][0]
@@ -298,7 +308,7 @@ class CacheManager:
 
     def kv_bytes_per_token(self) -> int:
         element = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.cache_layers) * 2 * g.spec.kv_heads * g.spec.head_dim * element for g in self.groups)
+        return sum(len(g.cache_layers) * g.spec.elements_per_token * element for g in self.groups)
 
     # --------------------------------------------------------------- audit
     def audit(self) -> None:

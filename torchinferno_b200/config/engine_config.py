@@ -6,7 +6,8 @@ Names and defaults the reference has are kept as they are
 ``max_batch_size=64``, ``cache_backend`` (only "paged" exists here).  Options
 for several GPUs, disaggregation and servers are not carried.  Added: the
 per-step token budget, the prompt portion size, the size of the page pool and
-the default sampling seed, and ``async_scheduling``.
+the default sampling seed, ``async_scheduling``, and which kernels multiply
+(``gemm_backend``, ``few_rows_choice``).
 """
 from __future__ import annotations
 
@@ -33,6 +34,8 @@ class EngineConfig:
     use_cuda_graphs: bool = True
     async_scheduling: bool = True           # launch the next decode step before the host has read this one's tokens
     gemm_backend: str = "auto"              # auto | tcgen05 | library (bf16 projections)
+    few_rows_choice: str = "measured"       # under "auto", which kernel multiplies few rows (decode steps): measured
+                                            # once per GPU model and shape and kept on disk | swapab | library
 
     def __post_init__(self) -> None:
         if self.cache_backend != "paged":

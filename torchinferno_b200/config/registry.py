@@ -66,6 +66,18 @@ def registered_architectures() -> tuple[str, ...]:
     return tuple(sorted({entry.name for entry in _BY_ARCHITECTURE.values()}))
 
 
+def entry_for_kind(kind: str) -> ArchitectureEntry | None:
+    """The entry a user's ``model_kind`` names (an architecture name, an alias or a ``model_type``), or None."""
+    _ensure_builtin()
+    key = str(kind).strip().lower()
+    return _BY_ARCHITECTURE.get(key) or _BY_MODEL_TYPE.get(key)
+
+
+def known_kinds() -> tuple[str, ...]:
+    _ensure_builtin()
+    return tuple(sorted(set(_BY_ARCHITECTURE) | set(_BY_MODEL_TYPE)))
+
+
 def resolve_architecture(config: Mapping[str, Any]) -> ArchitectureEntry:
     """Pick the registered entry that ``config.json`` names, or raise."""
     _ensure_builtin()

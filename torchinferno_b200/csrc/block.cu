@@ -1,4 +1,4 @@
-// One pre-norm Llama block as one call: the ten or so launches of a layer issued from here, without a
+// One pre-norm block of grouped-query attention and a gated (SwiGLU) feed-forward as one call: the ten or so launches of a layer issued from here, without a
 // return to the interpreter between them.  Nothing new is computed: the same kernels, in the order and with
 // the choices (which attention kernel, which product) that the Python parts make one by one
 // (parts/block.py, parts/attention.py, parts/mlp.py, kernels/attention.py, kernels/gemm.py); the parts use
@@ -36,7 +36,7 @@ int tib_blas_gemm(const void*, const void*, void*, int, int, int, int64_t, int64
 }
 
 // What a block is made of: sizes, constants and weights.  Filled once when the weights are bound.
-struct TibBlockWeights {
+struct TibPrenormBlockWeights {
   int hidden, heads, kv_heads, head_dim, intermediate;
   int rot_dim, interleaved;              // rotary: rotated width (0: none), pairing
   int qkv_kn, o_kn, gate_up_kn, down_kn; // 1: the matrix is stored [in, out]
@@ -52,7 +52,7 @@ struct TibBlockWeights {
 };
 
 // What a step brings: the batch arrays and the buffers the block works in (all of them for n_tokens rows).
-struct TibBlockStep {
+struct TibPrenormBlockStep {
   int n_tokens, n_entries, max_q_len, n_single, n_multi;
   int decode_splits;
   const int* positions;
@@ -90,7 +90,7 @@ static int project(const void* x, const void* w, void* out, int n, int N, int K,
 
 // pending: the result of the block before (bf16 [n_tokens, hidden]) or null for the first.  pool: this layer's
 // pages [pages, 2, kv_heads, page_size, head_dim] (page_stride elements apart); window 0: every key.
-TIB_API int tib_llama_block(const TibBlockWeights* w, const TibBlockStep* s, const void* pending, void* pool,
+TIB_API int tib_prenorm_gqa_glu_block(const TibPrenormBlockWeights* w, const TibPrenormBlockStep* s, const void* pending, void* pool,
                             const int* block_table, int table_stride, int page_size, int64_t page_stride, int num_pages,
                             int window, cudaStream_t stream) {
   if (!w || !s || !pool || !block_table) return TIB_E_ARG;

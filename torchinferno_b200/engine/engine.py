@@ -16,7 +16,9 @@ from typing import Hashable, Iterable, Iterator, Sequence
 
 import torch
 
+from torchinferno_b200.config import registry
 from torchinferno_b200.config.engine_config import EngineConfig
+from torchinferno_b200.config.model_config import read_config_json
 from torchinferno_b200.engine.batch import StepEntry
 from torchinferno_b200.engine.factory import load_model, make_runner
 from torchinferno_b200.engine.runner import StepError
@@ -82,9 +84,17 @@ class InferenceEngine:
     # -------------------------------------------------------- construction
     @classmethod
     def from_config(cls, config: EngineConfig) -> "InferenceEngine":
-        if config.model_kind not in ("auto", "llama3", "llama"):
-            raise ValueError(f"model_kind={config.model_kind!r} is not known; use 'auto'")
+        wanted = None
+        if config.model_kind != "auto":
+            wanted = registry.entry_for_kind(config.model_kind)
+            if wanted is None:
+                raise ValueError(f"model_kind={config.model_kind!r} is not registered; 'auto' or one of {list(registry.known_kinds())}")
         gemm.set_backend(config.gemm_backend)   # decides the layout the weights are bound in
+        gemm.set_few_rows_choice(config.few_rows_choice)
+        if wanted is not None:
+            named = registry.resolve_architecture(read_config_json(config.model))
+            if named is not wanted:
+                raise ValueError(f"model_kind={config.model_kind!r} names {wanted.name}, but {config.model}/config.json names {named.name}")
         model = load_model(config.model, dtype=config.dtype, device=config.device or "cuda:0")
         return cls(model, config, _load_tokenizer(config))
 
@@ -259,7 +269,7 @@ def _default_cache_tokens(model, config: EngineConfig, limit: int) -> int:
     wanted = config.max_batch_size * limit
     if model.device.type != "cuda":
         return wanted
-    per_token = sum(2 * spec.kv_heads * spec.head_dim for spec in model.cache_requirements()) * torch.empty((), dtype=model.dtype).element_size()
+    per_token = sum(spec.elements_per_token for spec in model.cache_requirements()) * torch.empty((), dtype=model.dtype).element_size()
     free, _ = torch.cuda.mem_get_info(model.device)
     fits = int(free * config.cache_memory_fraction) // max(1, per_token)
     if fits < config.page_size:

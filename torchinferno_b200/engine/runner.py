@@ -62,6 +62,7 @@ class ModelRunner:
         self.use_cuda_graphs = use_cuda_graphs
         self._graph_ok = all(spec is None for spec in model.state_requirements())
         self._graphs: dict[int, _DecodeGraph] = {}
+        self._graph_generation = gemm.generation()
         gemm.set_error_word(cache.error_word)   # bounded waits of the tcgen05 kernels report here
         self.graph_replays = 0
 
@@ -144,6 +145,10 @@ class ModelRunner:
         return copied
 
     def _graph_for(self, n: int) -> _DecodeGraph:
+        if self._graph_generation != gemm.generation():
+            # a weight was bound or a kernel choice changed: captured passes hold what was chosen before
+            self._graphs.clear()
+            self._graph_generation = gemm.generation()
         if n not in self._graphs:
             self._graphs[n] = _DecodeGraph(n, self.cache.device, self.cache.max_request_tokens)
         return self._graphs[n]

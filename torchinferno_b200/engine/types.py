@@ -1,11 +1,12 @@
 """Request and result types of the Python entry point.
 
-Names and meanings follow src/torchinferno/engine/types.py:10-77 of the
-reference: ``SamplingConfig(max_tokens, temperature, stop_token_ids)``,
-``GenerateRequest`` with exactly one prompt source, ``TokenOutput`` per
-streamed token, ``GenerateOutput`` with ``finish_reason`` in
-{"length", "stop", "cancelled"} and ``Usage``.  ``seed`` is added for the
-seeded sampler.
+The classes, their field names, order and defaults are the public request /
+result schema of the reference (src/torchinferno/engine/types.py:10-77), kept so
+that code written against it runs here: ``SamplingConfig(max_tokens, temperature,
+stop_token_ids)``, ``GenerateRequest`` with one prompt source, ``TokenOutput`` per
+streamed token, ``GenerateOutput`` with ``finish_reason`` in {"length", "stop",
+"cancelled"} and ``Usage``.  ``seed`` is added for the seeded sampler.  The
+checks below are this engine's own.
 """
 from __future__ import annotations
 
@@ -13,6 +14,16 @@ from collections.abc import Mapping, Sequence
 from dataclasses import dataclass, field
 
 ChatMessage = Mapping[str, object]
+
+
+def _token_tuple(ids, what: str) -> tuple[int, ...]:
+    """Token ids as a tuple of plain ints; refuses what is no integer or is negative."""
+    out = []
+    for t in ids:
+        if isinstance(t, bool) or int(t) != t or int(t) < 0:
+            raise ValueError(f"{what}: {t!r} is not a token id")
+        out.append(int(t))
+    return tuple(out)
 
 
 @dataclass(frozen=True)
@@ -23,11 +34,10 @@ class SamplingConfig:
     seed: int = 0
 
     def __post_init__(self) -> None:
-        if self.max_tokens < 0:
-            raise ValueError("max_tokens must be non-negative")
-        if self.temperature < 0:
-            raise ValueError("temperature must be non-negative")
-        object.__setattr__(self, "stop_token_ids", tuple(int(t) for t in self.stop_token_ids))
+        for name in ("max_tokens", "temperature"):
+            if getattr(self, name) < 0:
+                raise ValueError(f"SamplingConfig.{name} = {getattr(self, name)!r}: a negative value has no meaning")
+        object.__setattr__(self, "stop_token_ids", _token_tuple(self.stop_token_ids, "stop_token_ids"))
 
 
 @dataclass(frozen=True)
@@ -39,15 +49,22 @@ class GenerateRequest:
     sampling: SamplingConfig = field(default_factory=SamplingConfig)
     stream: bool = False
 
+    def _prompt_sources(self) -> list[str]:
+        """Names of the prompt fields that were given."""
+        given = {"prompt": self.prompt is not None, "messages": len(self.messages) > 0,
+                 "prompt_token_ids": self.prompt_token_ids is not None}
+        return [name for name, present in given.items() if present]
+
     def __post_init__(self) -> None:
-        if not self.request_id:
-            raise ValueError("request_id must be non-empty")
-        sources = sum([self.prompt is not None, bool(self.messages), self.prompt_token_ids is not None])
-        if sources != 1:
-            raise ValueError("exactly one of prompt, messages, or prompt_token_ids must be provided")
-        object.__setattr__(self, "messages", tuple(dict(m) for m in self.messages))
-        if self.prompt_token_ids is not None:
-            object.__setattr__(self, "prompt_token_ids", tuple(int(t) for t in self.prompt_token_ids))
+        if self.request_id in ("", None):
+            raise ValueError("a request needs a request_id (it names the request in results and in cancel())")
+        sources = self._prompt_sources()
+        if len(sources) != 1:
+            raise ValueError("a request takes its prompt from one of prompt, messages and prompt_token_ids; "
+                             f"given: {', '.join(sources) or 'none'}")
+        object.__setattr__(self, "messages", tuple({**m} for m in self.messages))
+        if sources == ["prompt_token_ids"]:
+            object.__setattr__(self, "prompt_token_ids", _token_tuple(self.prompt_token_ids, "prompt_token_ids"))
 
 
 @dataclass(frozen=True)

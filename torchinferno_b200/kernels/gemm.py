@@ -30,13 +30,41 @@ _backend = "auto"
 _error_word: torch.Tensor | None = None
 TWO_CTA_ROWS = 256
 TWO_CTA_MAX_N = 65536
+# Under "auto", how a weight left open (few_rows_tcgen05=None) gets its few-rows kernel:
+#   "measured"  by timing, once per (GPU model, shape): the outcome is written beside the built library and read
+#               back by later processes, so the same checkpoint runs the same kernels from one process to the next
+#   "swapab"    always the hand-written kernel (up to FEW_ROWS rows), "library" never: nothing is timed
+_few_rows_choice = "measured"
+_generation = 0       # rises whenever a weight is bound or a choice changes: holders of raw pointers compare it
+
+
+def generation() -> int:
+    return _generation
+
+
+def _changed() -> None:
+    global _generation
+    _generation += 1
 
 
 def set_backend(name: str) -> None:
     global _backend
     if name not in ("auto", "tcgen05", "library"):
         raise ValueError(f"unknown GEMM backend {name!r}: auto, tcgen05 or library")
+    if name != _backend:
+        _changed()
     _backend = name
+
+
+def set_few_rows_choice(mode: str) -> None:
+    global _few_rows_choice
+    if mode not in ("measured", "swapab", "library"):
+        raise ValueError(f"unknown few-rows choice {mode!r}: measured, swapab or library")
+    _few_rows_choice = mode
+
+
+def get_few_rows_choice() -> str:
+    return _few_rows_choice
 
 
 def get_backend() -> str:
@@ -73,6 +101,7 @@ class LinearWeight:
         self.tensor = weight.t().contiguous() if self.transposed else weight.contiguous()
         if few_rows_tcgen05 is None and on_gpu and _backend == "auto":
             _undecided.add(self)
+        _changed()
 
     @property
     def dtype(self) -> torch.dtype:
@@ -152,39 +181,105 @@ tuning_times: dict[tuple, dict[str, float]] = {}   # (out, in, device, rows) -> 
 # the swap-AB kernel up to 4 rows, up to 8, 16, 32 or 64, or not at all.
 TUNE_ROWS = ((1, 4), (8, 8), (16, 16), (32, 32), (64, 64))      # (rows measured, rows it stands for)
 # The swap-AB kernel must take under this share of the library's time.  The measurement repeats within about half
-# a per cent.  The line is drawn in a gap of the shares measured at the 8B and 3B sizes (1, 8 and 16 rows): 0.73-0.95
-# on one side (o and, at few rows, down at 8B; down, o and gate/up at 3B), 0.997 and more on the other.  A shape
-# whose share is within a per cent of the line (qkv and gate/up of the 1B sizes at 1 row: 0.97-0.99) may fall on
-# either side from one process to the next; that costs under a per cent of a step either way, but it changes the
-# rounding of the logits, so a run that must be repeatable to the bit fixes the kernels with the "library" backend.
-TUNE_MARGIN = 0.965
+# a per cent; the line leaves a dead band of several per cent below parity, so a shape near parity stays with the
+# library whatever the noise of one run, and what is decided is kept (see _stored_choices): the kernels a
+# checkpoint runs on a GPU model do not change from one process to the next.
+TUNE_MARGIN = 0.93
 TUNE_MEMBERS = 32
+_flush: dict[torch.device, torch.Tensor] = {}     # larger than the L2; made once per tuning pass
+
+
+def _choice_file():
+    """The file of decisions beside the built library (which a changed kernel source replaces: its stamp is part of
+    every key), or None when that folder cannot be written."""
+    from pathlib import Path
+    from torchinferno_b200.kernels.library import library_path
+    path = library_path()
+    return None if path is None else Path(path).parent / "gemm_choice.json"
+
+
+def _choice_key(n: int, k: int, device: torch.device, members: int) -> str:
+    """What a stored decision holds for: the GPU model, the build of the kernels, the line, the shape, and whether
+    the measured weights together exceed the L2 (a model of two layers is timed out of the L2, one of thirty-two
+    out of memory, and the two may well decide differently)."""
+    from pathlib import Path
+    from torchinferno_b200.kernels.library import library_path
+    stamp = Path(library_path()).parent / "stamp.txt"
+    mark = stamp.read_text().strip()[:16] if stamp.is_file() else "?"
+    measured = min(members, TUNE_MEMBERS)
+    where = "from memory" if measured * n * k * 2 > (256 << 20) else f"{measured} weights"
+    return f"{torch.cuda.get_device_name(device)}|{mark}|margin {TUNE_MARGIN}|{n}x{k}|{where}"
+
+
+def _stored_choices() -> dict[str, int]:
+    import json
+    path = _choice_file()
+    try:
+        return {str(k): int(v) for k, v in json.loads(path.read_text()).items()} if path and path.is_file() else {}
+    except (OSError, ValueError):
+        return {}
+
+
+def _store_choice(key: str, rows: int) -> None:
+    import json
+    import os
+    path = _choice_file()
+    if path is None:
+        return
+    choices = _stored_choices()
+    choices[key] = rows
+    try:
+        tmp = path.with_suffix(f".tmp{os.getpid()}")
+        tmp.write_text(json.dumps(choices, indent=0, sort_keys=True))
+        os.replace(tmp, path)
+    except OSError:
+        pass          # (a read-only folder: the choice is measured again by the next process)
+
+
+def decisions() -> dict[tuple, int]:
+    """(out, in, device) -> rows up to which the swap-AB kernel takes that shape's products, as decided so far."""
+    return dict(_tuned)
 
 
 def tune_few_rows() -> dict[tuple, int]:
     """Decide, for every weight bound with ``few_rows_tcgen05=None`` since the last call, up to how many rows the
     swap-AB kernel takes its products (0, 4, 8, 16, 32 or 64), and return the decisions made so far by (out, in, device).
 
-    Weights of one shape are measured together, once per shape and process, the way a decode step runs them:
-    a CUDA graph walks over them (different weights one after the other, so nothing comes from L2), each
-    product behind a small kernel, as in a layer (under programmatic dependent launch the swap-AB kernel
-    fetches its first weights while that kernel runs, and a measurement of the product alone would not
-    show it).  The graph is timed with either kernel; the swap-AB kernel gets the shape if it takes less
-    than TUNE_MARGIN of the library's time."""
+    Under the "measured" choice, weights of one shape are measured together, once per shape and GPU model, the way
+    a decode step runs them: a CUDA graph walks over them (different weights one after the other, so nothing
+    comes from L2), each product behind a small kernel, as in a layer (under programmatic dependent launch the
+    swap-AB kernel fetches its first weights while that kernel runs, and a measurement of the product alone
+    would not show it).  The graph is timed with either kernel; the swap-AB kernel gets the shape if it takes
+    less than TUNE_MARGIN of the library's time.  The outcome is stored and later processes read it."""
     groups: dict[tuple, list[LinearWeight]] = {}
     for w in list(_undecided):
         groups.setdefault((w.out_features, w.in_features, w.tensor.device), []).append(w)
     _undecided.clear()
-    for key, group in groups.items():
-        if key not in _tuned:
-            rows_taken = 0
-            for rows, stands_for in TUNE_ROWS:      # (rising: the first row count at which the library wins ends it)
-                if not _swapab_is_faster(group[:TUNE_MEMBERS], rows):
-                    break
-                rows_taken = stands_for
-            _tuned[key] = min(rows_taken, LinearWeight.FEW_ROWS)
-        for w in group:
-            w.few_rows = _tuned[key]
+    try:
+        for key, group in groups.items():
+            if key not in _tuned:
+                n, k, device = key
+                if _few_rows_choice != "measured":
+                    takes = _few_rows_choice == "swapab" and group[0].transposed and ops.gemm_tcgen05_swapab_supports(1, n, k)
+                    _tuned[key] = LinearWeight.FEW_ROWS if takes else 0
+                else:
+                    name, stored = _choice_key(n, k, device, len(group)), _stored_choices()
+                    if name in stored:
+                        _tuned[key] = stored[name]
+                    else:
+                        rows_taken = 0
+                        for rows, stands_for in TUNE_ROWS:      # (rising: the first row count at which the library wins ends it)
+                            if not _swapab_is_faster(group[:TUNE_MEMBERS], rows):
+                                break
+                            rows_taken = stands_for
+                        _tuned[key] = min(rows_taken, LinearWeight.FEW_ROWS)
+                        _store_choice(name, _tuned[key])
+            for w in group:
+                w.few_rows = _tuned[key]
+    finally:
+        _flush.clear()
+    if groups:
+        _changed()
     return dict(_tuned)
 
 
@@ -204,7 +299,9 @@ def _swapab_is_faster(group: "list[LinearWeight]", rows: int) -> bool:
         residual, normed = torch.randn((rows, width), dtype=torch.float32, device=device), torch.empty_like(delta)
         norm_weight = torch.ones(width, dtype=torch.float32, device=device)
         out = torch.empty((rows, n), dtype=torch.bfloat16, device=device)
-        flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)      # larger than the L2
+        flush = _flush.get(device)
+        if flush is None:
+            flush = _flush[device] = torch.empty(256 << 20, dtype=torch.uint8, device=device)      # larger than the L2
         products = {"library": lambda w: ops.library_gemm(x, w.tensor, out, w_kn=True),
                     "swapab": lambda w: ops.gemm_tcgen05_swapab(x, w.tensor, out, None, w_kn=True)}
         graphs = {}

@@ -2,7 +2,7 @@
 
 The parts stay what they are (each with its weights and its own forward); when a block is made only of
 the built-in kinds (RMSNorm, grouped-query attention with rotary or no position encoding, SwiGLU) in
-bfloat16, `PreNormBlock` hands the whole sequence of launches to ``tib_llama_block``, which issues the
+bfloat16, `PreNormBlock` hands the whole sequence of launches to ``tib_prenorm_gqa_glu_block``, which issues the
 same kernels with the same choices without returning to the interpreter between them: an eager step of
 32 layers costs the host about a third of what the part-by-part sequence does.  Any other composition,
 the float32 path and the ``tcgen05`` GEMM backend keep the part-by-part sequence.
@@ -38,7 +38,7 @@ _configured = False
 
 def _function():
     global _configured
-    fn = ops.lib().tib_llama_block
+    fn = ops.lib().tib_prenorm_gqa_glu_block
     if not _configured:
         fn.restype = c_int
         fn.argtypes = [POINTER(BlockWeights), POINTER(BlockStep), c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int,

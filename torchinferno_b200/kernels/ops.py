@@ -99,7 +99,7 @@ def lib() -> ctypes.CDLL:
                    "tib_prefill_attention_tcgen05", "tib_prefill_attention_tcgen05_supports",
                    "tib_decode_attention_tma", "tib_decode_attention_tma_supports", "tib_set_dependent_launch",
                    "tib_blas_init", "tib_blas_gemm", "tib_gemm_tcgen05_2cta", "tib_gemm_tcgen05_2cta_supports",
-                   "tib_gemm_skinny", "tib_gemm_skinny_supports", "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
+                   "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
                    "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
@@ -459,25 +459,6 @@ def library_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, w_kn: bool
     if status:
         raise KernelError(f"library_gemm: status {status} (20000 + n: cuBLAS status n)")
     return out        # (a library kernel: not counted among this library's launches)
-
-
-def gemm_skinny_supports(m: int, n: int, k: int) -> bool:
-    return bool(lib().tib_gemm_skinny_supports(c_int(m), c_int(n), c_int(k)))
-
-
-def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[M, N] (bf16 or fp32) = x[M, K] . w[N, K]^T for M <= 64: one pass over the weights."""
-    for name, t in (("x", x), ("w", w)):
-        if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
-            raise KernelError(f"gemm_skinny: {name} must be a 2-D bf16 CUDA tensor with unit inner stride")
-    _need(out, "out")
-    (m, k), (n, k2) = x.shape, w.shape
-    if k != k2 or out.shape != (m, n):
-        raise KernelError(f"gemm_skinny: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
-    _check("gemm_skinny", lib().tib_gemm_skinny(_ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k),
-                                                c_int64(x.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)),
-                                                c_int(_code(out.dtype)), _stream()))
-    return out
 
 
 def gemm_tcgen05_supports(m: int, n: int, k: int) -> bool:

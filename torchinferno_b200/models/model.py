@@ -51,17 +51,30 @@ class CausalLM:
                 spec.head_name, (spec.vocab_size, spec.hidden_size), optional=spec.tie_head_to_embedding)
         return expected
 
-    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+    def unused_optional_tensors(self) -> list[str]:
+        """Optional tensors that are not read even when the file has them (a head tied to the embedding)."""
         spec = self.spec
-        self.embedding = tensors[spec.embedding_name]
+        return [spec.head_name] if spec.tie_head_to_embedding and spec.head_name is not None else []
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], consume: bool = False) -> None:
+        """Give every part its tensors.  ``consume``: ``tensors`` is a dict of the caller's that is emptied part
+        by part, so that a part which repacks its weights (fused projections) does not leave the sources alive
+        beside the packed copy until the whole model is bound."""
+        spec = self.spec
+        take = tensors.pop if consume else tensors.__getitem__
+        self.embedding = take(spec.embedding_name)
         if spec.tie_head_to_embedding or spec.head_name is None:
             self.head = self.embedding
+        elif spec.head_name in tensors:
+            self.head = take(spec.head_name)
         else:
-            self.head = tensors[spec.head_name]
+            # An untied model whose file has no head is refused on purpose: guessing that the embedding
+            # doubles as the head would turn a truncated checkpoint into silently wrong logits.
+            raise KeyError(f"{spec.head_name}: the model does not tie its head to the embedding, and no head was given")
         for layer, block in zip(spec.layers, self.blocks):
             for prefix, part in block.named_parts():
                 full = layer.prefix + prefix
-                part.bind({ws.name: tensors[full + ws.name] for ws in part.weight_specs()
+                part.bind({ws.name: take(full + ws.name) for ws in part.weight_specs()
                            if full + ws.name in tensors})
         self.final_norm.bind({ws.name: tensors[spec.final_norm.prefix + ws.name]
                               for ws in self.final_norm.weight_specs()})
@@ -114,7 +127,7 @@ class CausalLM:
             kv = None
             if call.cache is not None:
                 kv = cache.kv_binding(call.cache)
-                kv = KVBinding(kv.pool, kv.block_table, kv.page_size, kv.window, call.writes_cache)
+                kv = KVBinding(kv.pool, kv.block_table, kv.page_size, kv.window, call.writes_cache, kv.keys, kv.values)
             ctx = LayerContext(batch=batch, kv=kv, state=cache.state(index),
                                error_word=cache.error_word, layer_index=index)
             self.blocks[call.layer].forward(stream, ctx)

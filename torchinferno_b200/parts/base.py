@@ -49,7 +49,8 @@ class WeightSpec:
 
 @dataclass(frozen=True)
 class CacheSpec:
-    """What a mixer keeps per token: ``kv_heads`` x ``head_dim`` keys and values.
+    """What a mixer keeps per token: for each of ``kv_heads`` heads a key of ``head_dim`` elements and a
+    value of ``value_dim`` elements (None: as wide as the key; 0: keys only, e.g. one latent vector).
 
     ``window``: None keeps every token; w > 0 means a query at position p reads
     keys p-w+1 .. p only, so pages wholly behind the window may be given back.
@@ -57,6 +58,15 @@ class CacheSpec:
     kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None
+
+    @property
+    def value_width(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
+
+    @property
+    def elements_per_token(self) -> int:
+        return self.kv_heads * (self.head_dim + self.value_width)
 
 
 @dataclass(frozen=True)
@@ -69,11 +79,14 @@ class StateSpec:
 @dataclass
 class KVBinding:
     """The cache one layer call reads and, unless ``writes`` is False, writes."""
-    pool: torch.Tensor          # [pages, 2, kv_heads, page_size, head_dim] of this cache layer
+    pool: torch.Tensor          # this cache layer's pages: [pages, 2, kv_heads, page_size, head_dim] when keys and
+                                # values are equally wide, else the flat pages [pages, elements of a page]
     block_table: torch.Tensor   # [slots, max_pages] int32, on the device
     page_size: int
     window: int | None
     writes: bool = True
+    keys: torch.Tensor | None = None     # [pages, kv_heads, page_size, head_dim], a view of the pages
+    values: torch.Tensor | None = None   # [pages, kv_heads, page_size, value width], a view of the pages
 
 
 @dataclass

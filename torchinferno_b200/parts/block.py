@@ -12,7 +12,7 @@ from typing import Mapping
 
 import torch
 
-from torchinferno_b200.kernels import native_block
+from torchinferno_b200.kernels import gemm, native_block
 from torchinferno_b200.parts.base import (Block, LayerContext, Part, PartSpec, ResidualStream,
                                           build_part, register_part)
 
@@ -36,6 +36,7 @@ class PreNormBlock(Block):
         self.mixer_norm = build_part("norm", self.specs["mixer_norm"], dtype=dtype, device=device)
         self.feed_forward_norm = build_part("norm", self.specs["feed_forward_norm"], dtype=dtype, device=device)
         self._native = _UNKNOWN
+        self._native_generation = -1
 
     def named_parts(self) -> list[tuple[str, Part]]:
         return [(self.specs["mixer_norm"].prefix, self.mixer_norm),
@@ -44,10 +45,12 @@ class PreNormBlock(Block):
                 (self.specs["feed_forward"].prefix, self.feed_forward)]
 
     def forward(self, stream: ResidualStream, ctx: LayerContext) -> None:
-        if self._native is _UNKNOWN:
-            # (decided at the first use, when the weights are bound: a block of the built-in parts in
-            # bfloat16 is issued as one call into the CUDA library, the same kernels in the same order)
+        if self._native is _UNKNOWN or self._native_generation != gemm.generation():
+            # (decided at the first use, when the weights are bound, and again whenever a weight was bound or a
+            # kernel choice changed since: a block of the built-in parts in bfloat16 is issued as one call into
+            # the CUDA library, the same kernels in the same order)
             self._native = native_block.block_weights(self) if NATIVE_BLOCKS else None
+            self._native_generation = gemm.generation()
         if self._native is not None and ctx.kv is not None and ctx.kv.writes and ctx.batch is not None:
             window = self.mixer.window if self.mixer.window is not None else ctx.kv.window
             native_block.run_block(self._native, stream, ctx, window)

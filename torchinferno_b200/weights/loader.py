@@ -29,6 +29,11 @@ class WeightError(ValueError):
     """The checkpoint does not hold what the model needs."""
 
 
+# Buffers some exporters store beside the weights; they are recomputed from the configuration and never read.
+# Anything else the model does not expect is an error.
+IGNORED_SUFFIXES = ("rotary_emb.inv_freq", "self_attn.rotary_emb.inv_freq", "attn.masked_bias", "attn.bias")
+
+
 _DTYPES = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16, "F64": torch.float64,
            "I32": torch.int32, "I64": torch.int64, "I16": torch.int16, "I8": torch.int8, "U8": torch.uint8,
            "BOOL": torch.bool}
@@ -84,7 +89,10 @@ def load_weights(model, folder: str | Path) -> dict[str, object]:
 
     try:
         missing = [n for n, ws in expected.items() if n not in files and not ws.optional]
-        unexpected = [n for n in files if n not in expected]
+        ignored = sorted(n for n in files if n not in expected and n.endswith(IGNORED_SUFFIXES))
+        unexpected = [n for n in files if n not in expected and n not in ignored]
+        # a head that the model ties to its embedding is not read even if the file stores a copy
+        unused = set(model.unused_optional_tensors()) if hasattr(model, "unused_optional_tensors") else set()
         wrong: list[str] = []
         for name, ws in expected.items():
             if name not in files:
@@ -106,7 +114,7 @@ def load_weights(model, folder: str | Path) -> dict[str, object]:
         tensors: dict[str, torch.Tensor] = {}
         stored: dict[str, str] = {}
         for name, ws in expected.items():
-            if name not in files:
+            if name not in files or name in unused:
                 continue
             tensor = handle_of(files[name]).get_tensor(name)
             stored[name] = str(tensor.dtype).replace("torch.", "")
@@ -114,8 +122,10 @@ def load_weights(model, folder: str | Path) -> dict[str, object]:
     finally:
         for handle in handles.values():
             handle.__exit__(None, None, None)
-    model.bind(tensors)
-    return {"tensors": len(tensors), "stored_dtypes": sorted(set(stored.values()))}
+    count = len(tensors)
+    model.bind(tensors, consume=True)      # (each part's source tensors are dropped as it binds them)
+    return {"tensors": count, "stored_dtypes": sorted(set(stored.values())), "ignored": ignored,
+            "not_read": sorted(unused & set(files))}
 
 
 def place(tensor: torch.Tensor, role: str, compute_dtype: torch.dtype, device: torch.device) -> torch.Tensor:

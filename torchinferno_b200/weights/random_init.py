@@ -74,4 +74,4 @@ def init_random_weights(model, seed: int, storage_dtype: torch.dtype = torch.bfl
             continue
         raw = random_tensor(spec, seed, device=model.device, dtype=storage_dtype)
         tensors[name] = place(raw, spec.role, model.dtype, model.device)
-    model.bind(tensors)
+    model.bind(tensors, consume=True)
