@@ -170,3 +170,41 @@ def test_a_slot_reused_between_two_steps_queues_each_table_entry_once():
     (index, value), = m.drain_table_updates()
     assert sorted(index) == [0, 1] and len(set(index)) == len(index)
     assert dict(zip(index, value)) == {0: m.block_table("b")[0], 1: -1}
+
+
+def test_a_request_record_is_written_whole_when_the_slot_is_opened():
+    """Every word of the slot's record is queued at open (nothing of the last holder stays), later changes replace
+    queued ones word by word, and the queue empties when it is drained."""
+    import struct
+    from torchinferno_b200.cache.manager import (REC_DRAWN, REC_LAST_TOKEN, REC_LENGTH, REC_SEED_HI, REC_SEED_LO,
+                                                  REC_TEMPERATURE, RECORD_WORDS)
+    m = manager()
+    slot = m.open("a", seed=(7 << 32) + 0xFFFFFFFE, temperature=0.75)
+    index, value = m.drain_record_updates()
+    assert sorted(index) == list(range(slot * RECORD_WORDS, (slot + 1) * RECORD_WORDS))
+    words = dict(zip((i - slot * RECORD_WORDS for i in index), value))
+    assert words[REC_LENGTH] == 0 and words[REC_LAST_TOKEN] == -1 and words[REC_DRAWN] == 0
+    assert words[REC_SEED_LO] == -2 and words[REC_SEED_HI] == 7          # two signed halves
+    assert struct.unpack("<f", struct.pack("<i", words[REC_TEMPERATURE]))[0] == 0.75
+    assert m.drain_record_updates() == ([], [])
+    m.set_record("a", REC_LENGTH, 5), m.set_record("a", REC_LENGTH, 9), m.set_record("a", REC_LAST_TOKEN, 3)
+    assert m.drain_record_updates() == ([slot * RECORD_WORDS + REC_LENGTH, slot * RECORD_WORDS + REC_LAST_TOKEN], [9, 3])
+    m.close("a")
+    assert m.open("b", seed=1) == slot and len(m.drain_record_updates()[0]) == RECORD_WORDS
+    with pytest.raises(CacheError):
+        m.set_record("a", REC_LENGTH, 1)
+    with pytest.raises(CacheError):
+        m.set_record("b", RECORD_WORDS, 1)
+
+
+def test_keys_and_values_of_different_widths_share_a_page():
+    m = manager(specs=[CacheSpec(2, 16, value_dim=8), CacheSpec(2, 16), CacheSpec(1, 24, value_dim=0)], tensors=True)
+    assert len(m.groups) == 3 and [g.pool.shape[-1] for g in m.groups] == [4 * 2 * 24, 4 * 2 * 32, 4 * 24]
+    unequal, equal, keys_only = (m.kv_binding(i) for i in range(3))
+    assert unequal.keys.shape == (8, 2, 4, 16) and unequal.values.shape == (8, 2, 4, 8) and unequal.pool.shape == (8, 4 * 2 * 24)
+    assert equal.pool.shape == (8, 2, 2, 4, 16) and equal.keys.data_ptr() == equal.pool[:, 0].data_ptr()
+    assert equal.values.data_ptr() == equal.pool[:, 1].data_ptr()
+    assert keys_only.values is None and keys_only.keys.shape == (8, 1, 4, 24)
+    unequal.keys.fill_(1.0), unequal.values.fill_(2.0)
+    assert m.groups[0].pool[0].sum().item() == 8 * 4 * 2 * (16 * 1 + 8 * 2)     # the views cover the pages, once
+    assert m.kv_bytes_per_token() == 4 * (2 * 24 + 2 * 32 + 24)

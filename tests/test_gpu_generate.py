@@ -151,13 +151,16 @@ def test_many_requests_on_a_tight_pool_do_not_depend_on_how_they_are_scheduled(m
     assert preempted > 0                                   # the tight pools really ran out
 
 
-def test_the_engine_sees_an_error_word_that_a_kernel_set(model_folders):
+def test_the_engine_sees_an_error_word_that_a_kernel_set_and_goes_on_without_the_failed_requests(model_folders):
     """The kernels report a page id outside its pool or a bounded wait that ran out in one device word; the
-    engine reads it with the step's tokens.  Here the word is set from the host (no kernel is made to fail)."""
+    engine reads it with the step's tokens.  Here the word is set from the host (no kernel is made to fail).
+    The step's requests are cancelled and give their pages back, the word is cleared, and the next request
+    generates what it should."""
     need_gpu()
     from torchinferno_b200.engine.runner import StepError
     config, seed = TINY["A"]
     prompt = list(requests_for(config, seed, [9]).values())[0]
+    cfg, weights = plain_llama.read_model_folder(model_folders["A"])
     with engine_for(model_folders["A"], "float32", page_size=4, max_batch_size=2) as engine:
         engine.submit(requests([prompt], 6)[0])
         engine.step()
@@ -165,7 +168,68 @@ def test_the_engine_sees_an_error_word_that_a_kernel_set(model_folders):
         with pytest.raises(StepError, match="0x7c0031"):
             for _ in range(3):
                 engine.step()
-        engine.runner.cache.error_word.zero_()
+        cache = engine.runner.cache
+        assert int(cache.error_word.item()) == 0 and not engine.scheduler.has_work()
+        assert cache.free_pages() == [cache.num_pages] and not cache.live_requests
+        again = engine.generate(requests([prompt], 6)[0])
+        assert list(again.token_ids) == plain_llama.generate_greedy(cfg, weights, prompt, 6)
+
+
+@pytest.mark.parametrize("ahead", [True, False])
+def test_a_sampled_decode_step_copies_only_new_block_table_entries_to_the_device(model_folders, ahead):
+    """Seed, temperature, position and the last drawn token of every request live in its record on the device:
+    a decode step at a temperature takes its inputs and the sampler its parameters from there.  Over decode
+    steps that need no new page nothing at all goes from the host to the device; a step in which a request
+    crosses into a new page brings that one block-table entry (index and page id)."""
+    need_gpu()
+    config, seed = TINY["B"]
+    prompts = list(requests_for(config, seed, [20, 37, 5]).values())
+    with engine_for(model_folders["B"], "float32", page_size=16, max_batch_size=4, async_scheduling=ahead) as engine:
+        for r in requests(prompts, 40, 0.7, [5, 6, 7]):
+            engine.submit(r)
+        while any(r.prefilling for r in engine.scheduler.running) or engine.scheduler.waiting:
+            engine.step()
+        engine.step()                                        # (the first decode step brings the slots of its requests)
+        per_step = []
+        for _ in range(30):
+            lengths = {r.request_id: engine.runner.cache.length(r.request_id) for r in engine.scheduler.running}
+            before = engine.stats["h2d_bytes"]
+            engine.step()
+            new_pages = sum(1 for rid, n in lengths.items() if engine.runner.cache.length(rid) > n and n % 16 == 0)
+            per_step.append((engine.stats["h2d_bytes"] - before, new_pages))
+        assert all(copied == 8 * pages for copied, pages in per_step), per_step
+        assert any(pages for _, pages in per_step) and any(not pages for _, pages in per_step)
+
+
+def test_a_slot_used_again_carries_nothing_over(tmp_path, model_folders):
+    """A request that takes the slot of one that has ended starts from a whole new record (length, token, seed,
+    temperature, count of drawn tokens) and zeroed mixer state: its tokens are those it draws in a fresh engine."""
+    need_gpu()
+    from torchinferno_b200.cache.manager import REC_DRAWN, REC_LENGTH, REC_SEED_LO
+    config, seed = TINY["B"]
+    first, second = list(requests_for(config, seed, [33, 12]).values())
+    with engine_for(model_folders["B"], "float32", page_size=16, max_batch_size=1) as engine:
+        engine.generate(requests([first], 9, 0.9, [1234])[0])
+        cache = engine.runner.cache
+        torch.cuda.synchronize()
+        left = cache.request_records[0].tolist()              # (one slot: the record the first request leaves behind)
+        assert left[REC_LENGTH] >= 33 + 8 and left[REC_DRAWN] == 9 and left[REC_SEED_LO] == 1234
+        reused = engine.generate(requests([second], 9, 0.6, [77])[0])
+        torch.cuda.synchronize()
+        now = cache.request_records[0].tolist()
+        assert now[REC_SEED_LO] == 77 and now[REC_DRAWN] == 9 and now[REC_LENGTH] in (12 + 8, 12 + 9)
+    with engine_for(model_folders["B"], "float32", page_size=16, max_batch_size=1) as engine:
+        fresh = engine.generate(requests([second], 9, 0.6, [77])[0])
+    assert reused.token_ids == fresh.token_ids
+    # and the state tensors of a mixer that keeps some: the cache manager zeroes the slot when it is opened
+    from torchinferno_b200.cache.manager import CacheManager
+    from torchinferno_b200.parts.base import CacheSpec, StateSpec
+    manager = CacheManager([CacheSpec(1, 16)], [StateSpec((5,)), None], page_size=4, num_pages=8, max_requests=2,
+                           max_request_tokens=32, dtype=torch.float32, device="cuda")
+    slot = manager.open("a")
+    manager.states[0][slot] = 3.0
+    manager.close("a")
+    assert manager.open("b") == slot and manager.states[0][slot].abs().sum().item() == 0.0
 
 
 def test_seeded_temperature_generation_fp32(model_folders):

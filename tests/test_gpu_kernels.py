@@ -206,21 +206,61 @@ def test_few_rows_kernel_is_chosen_by_measurement_and_either_choice_is_right():
             assert (as_ref(part) - want[:, 64:1096]).abs().max() <= 1e-2 * want.abs().max() + 1e-6
 
 
-def test_advance_decode_moves_tokens_and_positions_on():
-    """The kernel between two captured decode steps: the drawn tokens become the next inputs, positions (and the
-    positions the sampler draws at) move on by one, and the history row takes the tokens; longer buffers keep their tails."""
+def _records(rows):
+    """A record table [slots, 8] from {slot: (length, last token, seed, temperature, drawn)}."""
+    import struct
+    table = torch.zeros(max(rows) + 1, 8, dtype=torch.int32)
+    for slot, (length, last, seed, temperature, drawn) in rows.items():
+        seed &= 0xFFFFFFFFFFFFFFFF
+        words = [length, last, seed & 0xFFFFFFFF, seed >> 32, struct.unpack("<I", struct.pack("<f", temperature))[0], drawn]
+        table[slot, :6] = torch.tensor([w - (1 << 32) if w >= (1 << 31) else w for w in words], dtype=torch.int64).to(torch.int32)
+    return table
+
+
+def test_decode_inputs_come_from_the_requests_records_which_move_on():
+    """The first kernel of a captured decode step: request i of the step sits in slot slots[i]; its next token and
+    its position come from its record, whose length moves one on.  Records of other slots, the other words of a
+    record and the tails of longer buffers stay as they are; a slot outside the table yields token -1."""
     need_gpu()
     from torchinferno_b200.kernels import ops
     i32 = lambda xs: dev(torch.tensor(xs, dtype=torch.int32))
-    tokens, sampled = i32([7, 8, 9]), i32([100, 200, 300, 999])
-    positions, draws, history = i32([4, 0, 511, 77]), i32([5, 1, 512]), i32([-1, -1, -1, -1, -1])
-    ops.advance_decode(tokens, sampled, positions, draws, history)
-    assert tokens.tolist() == [100, 200, 300] and positions.tolist() == [5, 1, 512, 77]
-    assert draws.tolist() == [6, 2, 513] and history.tolist() == [100, 200, 300, -1, -1]
-    ops.advance_decode(tokens, sampled, positions)                   # the optional buffers may be left out
-    assert positions.tolist() == [6, 2, 513, 77]
+    table = _records({0: (4, 100, 7, 0.5, 1), 1: (9, 9, 9, 0.0, 9), 2: (511, 300, -3, 1.5, 2), 5: (0, 200, 1 << 40, 0.0, 0)})
+    before, records = table.clone(), dev(table)
+    tokens, positions = i32([7, 8, 9, 77]), i32([-1, -1, -1, 55])
+    ops.decode_inputs(records, i32([2, 5, 0]), tokens, positions)
+    assert tokens.tolist() == [300, 200, 100, 77] and positions.tolist() == [511, 0, 4, 55]
+    after = records.cpu()
+    assert after[:, 0].tolist() == [5, 9, 512, 0, 0, 1]
+    assert torch.equal(after[:, 1:], before[:, 1:])
+    ops.decode_inputs(records, i32([6, 1]), tokens, positions)           # slot 6 is outside the table
+    assert tokens.tolist()[:2] == [-1, 9] and positions.tolist()[:2] == [0, 9]
     with pytest.raises(ops.KernelError, match="shorter"):
-        ops.advance_decode(tokens, i32([1]), positions)
+        ops.decode_inputs(records, i32([0, 1, 2]), i32([1]), positions)
+
+
+def test_sampling_from_records_is_sampling_with_the_same_parameters_given_by_hand():
+    """The sampler reads temperature, seed and the position of the drawn token (the request's length) from the
+    record of each row's request, draws what the explicit form draws, and leaves the token in the record."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    g = torch.Generator().manual_seed(5)
+    logits = dev(torch.randn(4, 1000, generator=g) * 3)
+    rows = {3: (17, -1, 12345678901234567, 0.8, 0), 1: (40, 5, -99, 1.3, 7), 0: (5, 5, 3, 0.0, 2), 6: (1, 1, 1, 0.7, 0)}
+    records = dev(_records(rows))
+    slots = dev(torch.tensor([3, 0, 1, 6], dtype=torch.int32))
+    out, history = torch.empty(4, dtype=torch.int32, device="cuda"), torch.full((6,), -1, dtype=torch.int32, device="cuda")
+    ops.sample_records(logits, out, records, slots, history)
+    order = [3, 0, 1, 6]
+    as_i64 = lambda s: ((s & 0xFFFFFFFFFFFFFFFF) ^ (1 << 63)) - (1 << 63)
+    want = ops.sample(logits, torch.empty(4, dtype=torch.int32, device="cuda"),
+                      dev(torch.tensor([rows[s][3] for s in order])), dev(torch.tensor([as_i64(rows[s][2]) for s in order])),
+                      dev(torch.tensor([rows[s][0] for s in order], dtype=torch.int32)))
+    assert out.tolist() == want.tolist() and history.tolist() == want.tolist() + [-1, -1]
+    assert out.tolist()[1] == int(logits[1].argmax())                    # temperature 0 is greedy
+    after = records.cpu()
+    for row, slot in enumerate(order):
+        assert after[slot, 1].item() == want[row].item() and after[slot, 5].item() == rows[slot][4] + 1
+        assert after[slot, 0].item() == rows[slot][0]                    # the length is the decode step's to move
 
 
 @pytest.mark.parametrize("m, n, k", [(1, 72, 40), (8, 4096, 4096), (17, 1000, 264), (300, 136, 2048)])

@@ -440,6 +440,130 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_an
         unregister_architecture("Toy2ForCausalLM")
 
 
+def test_a_toy_mixer_with_keys_narrower_than_values_and_a_stage_after_the_embedding(tmp_path):
+    """Two more parts defined here.  A mixer that caches a key of 8 and a value of 24 elements per token (the
+    cache manager gives it pages that hold keys and values of different widths, as views) and reads them back
+    through the block table; it walks the step's entries on the host, so it declares itself not capturable and
+    the model's decode steps run uncaptured.  And a stage between the embedding and the first block that adds a
+    learned absolute position table and multiplies by a constant.  Registered, given random weights, loaded and
+    stepped whole, in portions and token by token, against plain arithmetic; nothing of the package is edited."""
+    need_gpu()
+    from torchinferno_b200.config.registry import ArchitectureEntry, register_architecture, unregister_architecture
+    from torchinferno_b200.engine.batch import StepEntry
+    from torchinferno_b200.engine.factory import load_model, make_runner
+    from torchinferno_b200.models.spec import BlockSpec, LayerCall, ModelSpec
+    from torchinferno_b200.parts.base import (CacheSpec, Mixer, PartSpec, StreamStage, WeightSpec, register_part,
+                                              unregister_part)
+    from torchinferno_b200.weights.random_init import write_random_model
+    WIDTH, KEY, POSITIONS, SCALE = 24, 8, 64, 1.7
+
+    class WideValueMixer(Mixer):
+        capturable = False                                           # (it reads ctx.batch.entries on the host)
+
+        def __init__(self, *, width, key_dim, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.width, self.key_dim = width, key_dim
+
+        def weight_specs(self):
+            return [WeightSpec("q.weight", (self.key_dim, self.width), std=0.4), WeightSpec("k.weight", (self.key_dim, self.width), std=0.4),
+                    WeightSpec("o.weight", (self.width, self.width), std=0.2)]
+
+        def bind(self, weights):
+            self.wq, self.wk, self.wo = (weights[n].float() for n in ("q.weight", "k.weight", "o.weight"))
+
+        def cache_spec(self):
+            return CacheSpec(1, self.key_dim, value_dim=self.width)
+
+        def forward(self, x, ctx):
+            kv, page = ctx.kv, ctx.kv.page_size
+            assert kv.keys.shape[1:] == (1, page, self.key_dim) and kv.values.shape[1:] == (1, page, self.width)
+            out = torch.empty_like(x)
+            for e in ctx.batch.entries:
+                rows = x[e.q_start:e.q_start + e.q_len].float()
+                positions = torch.arange(e.kv_start, e.kv_start + e.q_len, device=x.device)
+                table = kv.block_table[e.slot]
+                pages, offsets = table[positions // page].long(), positions % page
+                kv.keys[pages, 0, offsets] = (rows @ self.wk.T).to(kv.keys.dtype)
+                kv.values[pages, 0, offsets] = rows.to(kv.values.dtype)
+                every = torch.arange(0, e.kv_start + e.q_len, device=x.device)
+                keys = kv.keys[table[every // page].long(), 0, every % page].float()
+                values = kv.values[table[every // page].long(), 0, every % page].float()
+                scores = (rows @ self.wq.T) @ keys.T / self.key_dim ** 0.5
+                scores = scores.masked_fill(every[None, :] > positions[:, None], float("-inf"))
+                out[e.q_start:e.q_start + e.q_len] = ((torch.softmax(scores, -1) @ values) @ self.wo.T).to(x.dtype)
+            return out
+
+    class LearnedPositions(StreamStage):
+        def __init__(self, *, width, positions, scale, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.width, self.positions, self.scale = width, positions, scale
+
+        def weight_specs(self):
+            return [WeightSpec("table.weight", (self.positions, self.width), std=0.3)]
+
+        def bind(self, weights):
+            self.table = weights["table.weight"].float()
+
+        def forward(self, stream, ctx):
+            stream.residual.add_(self.table[ctx.batch.positions.long()]).mul_(self.scale)
+
+    @dataclasses.dataclass(frozen=True)
+    class Toy3Config:
+        vocab_size: int
+
+        @classmethod
+        def from_dict(cls, data):
+            return cls(data["vocab_size"])
+
+    def build_toy3(cfg):
+        norm = PartSpec("rmsnorm", {"width": WIDTH, "eps": 1e-5})
+        block = PartSpec("prenorm", {
+            "mixer": PartSpec("wide_value", {"width": WIDTH, "key_dim": KEY}, prefix="mix."),
+            "feed_forward": PartSpec("swiglu", {"hidden_size": WIDTH, "intermediate_size": 40}, prefix="ffn."),
+            "mixer_norm": dataclasses.replace(norm, prefix="n1."), "feed_forward_norm": dataclasses.replace(norm, prefix="n2.")})
+        return ModelSpec(architecture="Toy3ForCausalLM", hidden_size=WIDTH, vocab_size=cfg.vocab_size, max_positions=POSITIONS,
+                         embedding_name="emb.weight", layers=(BlockSpec(block, "l0."), BlockSpec(block, "l1.")),
+                         schedule=(LayerCall(0, 0), LayerCall(1, 1)), final_norm=dataclasses.replace(norm, prefix="final."),
+                         head_name="head.weight",
+                         after_embedding=PartSpec("learned_positions", {"width": WIDTH, "positions": POSITIONS, "scale": SCALE}, prefix="pos."))
+
+    register_part("mixer", "wide_value", WideValueMixer)
+    register_part("stream_stage", "learned_positions", LearnedPositions)
+    register_architecture(ArchitectureEntry("Toy3ForCausalLM", Toy3Config, build_toy3, model_types=("toy3",)))
+    try:
+        write_random_model({"architectures": ["Toy3ForCausalLM"], "model_type": "toy3", "vocab_size": 40}, tmp_path, seed=3)
+        model = load_model(tmp_path, dtype="float32")
+        assert not model.capturable() and [c.value_width for c in model.cache_requirements()] == [WIDTH, WIDTH]
+        runner = make_runner(model, page_size=4, max_tokens=96, max_requests=2)
+        assert runner.cache.groups[0].pool.shape == (2, 24, 4 * (KEY + WIDTH)) and not runner._graph_ok
+        tokens = torch.randint(0, 40, (29,)).tolist()
+        with torch.inference_mode():
+            whole = runner.step([StepEntry("w", tokens, list(range(29)))]).cpu()
+            runner.end(["w"])
+            cut = [runner.step([StepEntry("c", tokens[:7], list(range(7)))]).cpu(),
+                   runner.step([StepEntry("c", tokens[7:20], list(range(13)))]).cpu()]
+            cut += [runner.step([StepEntry("c", [t], [0])]).cpu() for t in tokens[20:]]          # single tokens, uncaptured
+            runner.end(["c"])
+        assert runner.graph_replays == 0 and runner.cache.free_pages() == [24]
+        assert torch.allclose(torch.cat(cut), whole, atol=1e-5, rtol=1e-4)
+        _, w = plain_llama.read_model_folder(tmp_path)
+        T = len(tokens)
+        x = (w["emb.weight"][torch.tensor(tokens)] + w["pos.table.weight"][:T]) * SCALE
+        for p in ("l0.", "l1."):
+            n = plain_llama.rms_norm(x, w[p + "n1.weight"], 1e-5)
+            scores = (n @ w[p + "mix.q.weight"].T) @ (n @ w[p + "mix.k.weight"].T).T / KEY ** 0.5
+            scores = scores.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+            x = x + (torch.softmax(scores, -1) @ n) @ w[p + "mix.o.weight"].T
+            x = x + plain_llama.swiglu_mlp(plain_llama.rms_norm(x, w[p + "n2.weight"], 1e-5), w[p + "ffn.gate_proj.weight"],
+                                           w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
+        want = plain_llama.rms_norm(x, w["final.weight"], 1e-5) @ w["head.weight"].T
+        assert torch.allclose(whole.double(), want, atol=5e-5, rtol=2e-4), (whole.double() - want).abs().max()
+    finally:
+        unregister_part("mixer", "wide_value")
+        unregister_part("stream_stage", "learned_positions")
+        unregister_architecture("Toy3ForCausalLM")
+
+
 @pytest.mark.parametrize("name", ["D", "E"])
 def test_the_native_block_call_gives_the_bits_of_the_part_by_part_sequence(model_folders, name, monkeypatch):
     """A block of the built-in parts in bfloat16 is issued as one call into the CUDA library; it must launch the

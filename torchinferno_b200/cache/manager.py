@@ -18,8 +18,12 @@ What is different here:
 * one layer's pages are laid out ``[pages, 2, kv_heads, page_size, head_dim]``
   so that the keys of one head in one page are contiguous (keys and values may
   differ in width: a page then holds all its keys, then all its values);
-* beside the pages there are **state slots**: one fixed-size record per live
-  request for every layer call whose mixer asks for one, zeroed when the
+* beside the pages there are **state slots**: every live request has a slot,
+  and in it a fixed-size record on the device (``request_records``: length,
+  next input token, sampling seed and temperature, count of drawn tokens),
+  written whole when the request is opened, read by the decode step for its
+  inputs and by the sampler for its parameters; and, for every layer call
+  whose mixer asks for one, a fixed-size state tensor that is zeroed when the
   request is opened.
 
 The manager is plain host code apart from the tensors it owns; block-table
@@ -27,12 +31,24 @@ changes are queued and applied on the device in one go before a step runs.
 """
 from __future__ import annotations
 
+import struct
 from dataclasses import dataclass, field
 from typing import Hashable, Sequence
 
 import torch
 
 from torchinferno_b200.parts.base import CacheSpec, StateSpec
+
+
+# A request's record: int32 words (the kernels' side: csrc/common.cuh TibRequestRecord).
+RECORD_WORDS = 8
+REC_LENGTH, REC_LAST_TOKEN, REC_SEED_LO, REC_SEED_HI, REC_TEMPERATURE, REC_DRAWN = range(6)
+
+
+def _i32(value: int) -> int:
+    """The low 32 bits of ``value`` as a signed integer."""
+    value &= 0xFFFFFFFF
+    return value - (1 << 32) if value >= (1 << 31) else value
 
 
 class OutOfPages(RuntimeError):
@@ -156,6 +172,10 @@ class CacheManager:
             else:
                 self.states.append(torch.zeros((max_requests, *spec.shape), dtype=spec.dtype, device=self.device))
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device) if allocate_tensors else None
+        # one record per slot; changes are queued like block-table changes (flat index -> word, the last wins)
+        self.request_records = torch.zeros((max_requests, RECORD_WORDS), dtype=torch.int32, device=self.device) \
+            if allocate_tensors else None
+        self.pending_records: dict[int, int] = {}
         self._free_slots = list(reversed(range(max_requests)))
         self._requests: dict[Hashable, _Request] = {}
 
@@ -170,8 +190,10 @@ class CacheManager:
     def free_slots(self) -> int:
         return len(self._free_slots)
 
-    def open(self, request_id: Hashable) -> int:
-        """Give the request a state slot and empty block tables; returns the slot."""
+    def open(self, request_id: Hashable, *, seed: int = 0, temperature: float = 0.0) -> int:
+        """Give the request a state slot and empty block tables; returns the slot.  Its record is written whole
+        (length 0, no token, the sampling parameters given, nothing drawn) and its mixer states are zeroed:
+        nothing of the slot's last holder is left."""
         if request_id in self._requests:
             raise CacheError(f"request {request_id!r} is already open")
         if not self._free_slots:
@@ -181,7 +203,32 @@ class CacheManager:
         for state in self.states:
             if state is not None:
                 state[slot].zero_()
+        seed &= 0xFFFFFFFFFFFFFFFF
+        temperature_bits = struct.unpack("<i", struct.pack("<f", float(temperature)))[0]
+        words = {REC_LENGTH: 0, REC_LAST_TOKEN: -1, REC_SEED_LO: _i32(seed), REC_SEED_HI: _i32(seed >> 32),
+                 REC_TEMPERATURE: temperature_bits, REC_DRAWN: 0}
+        for word in range(RECORD_WORDS):
+            self.pending_records[slot * RECORD_WORDS + word] = words.get(word, 0)
         return slot
+
+    def set_record(self, request_id: Hashable, word: int, value: int) -> None:
+        """Queue a change of one word of the request's record (applied on the device before the next step)."""
+        if not 0 <= word < RECORD_WORDS:
+            raise CacheError(f"a record has words 0..{RECORD_WORDS - 1}")
+        self.pending_records[self._get(request_id).slot * RECORD_WORDS + word] = _i32(int(value))
+
+    def set_sampling(self, request_id: Hashable, *, seed: int, temperature: float) -> None:
+        """Queue new sampling parameters for the request's record."""
+        seed &= 0xFFFFFFFFFFFFFFFF
+        self.set_record(request_id, REC_SEED_LO, seed)
+        self.set_record(request_id, REC_SEED_HI, seed >> 32)
+        self.set_record(request_id, REC_TEMPERATURE, struct.unpack("<i", struct.pack("<f", float(temperature)))[0])
+
+    def drain_record_updates(self) -> tuple[list[int], list[int]]:
+        """Queued (flat index, word) changes of ``request_records``; clears the queue."""
+        out = (list(self.pending_records.keys()), list(self.pending_records.values()))
+        self.pending_records = {}
+        return out
 
     def slot(self, request_id: Hashable) -> int:
         return self._get(request_id).slot

@@ -27,6 +27,19 @@ enum TibError : int {
   TIB_E_SCRATCH = -7,    // needs more scratch than the library's built-in array holds
 };
 
+// The fixed-size record every live request has on the device, one row of int32 words per request slot.
+// The host writes a whole record when a request is opened; after that a decode step reads its inputs from it and
+// the sampler reads its parameters from it and leaves the drawn token in it, with no host copy in between.
+enum TibRequestRecord : int {
+  TIB_REC_LENGTH = 0,       // tokens of the request in the cache = position of its next input token
+  TIB_REC_LAST_TOKEN = 1,   // its next input token (the one drawn last)
+  TIB_REC_SEED_LO = 2,      // sampling seed, low and high half
+  TIB_REC_SEED_HI = 3,
+  TIB_REC_TEMPERATURE = 4,  // bits of a float; <= 0: greedy
+  TIB_REC_DRAWN = 5,        // tokens drawn for the request so far
+  TIB_REC_WORDS = 8,        // (two words spare)
+};
+
 // kernel<<<grid, block, smem, stream>>>(args) as a programmatic dependent launch (see launch_dependent below)
 #define TIB_LAUNCH_DEPENDENT(kernel, grid, block, smem, stream, ...)                                              \
   do {                                                                                                            \

@@ -197,18 +197,23 @@ __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict_
   }
 }
 
-__global__ void advance_decode_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
-                                      int* __restrict__ positions, int* __restrict__ draw_positions,
-                                      int* __restrict__ history, int n) {
+__global__ void decode_inputs_kernel(int* __restrict__ records, const int* __restrict__ slots, int max_slots,
+                                     int* __restrict__ token_ids, int* __restrict__ positions, int n) {
   pdl_wait();
   pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
-    const int t = sampled[i];
-    token_ids[i] = t;
-    positions[i] += 1;
-    if (draw_positions) draw_positions[i] += 1;
-    if (history) history[i] = t;
+    const int slot = slots[i];
+    if (slot < 0 || slot >= max_slots) {       // (the embedding then writes NaN: it must show)
+      token_ids[i] = -1;
+      positions[i] = 0;
+      return;
+    }
+    int* record = records + (size_t)slot * TIB_REC_WORDS;
+    const int length = record[TIB_REC_LENGTH];
+    token_ids[i] = record[TIB_REC_LAST_TOKEN];
+    positions[i] = length;
+    record[TIB_REC_LENGTH] = length + 1;
   }
 }
 
@@ -323,13 +328,14 @@ TIB_API int tib_scatter_i32(int* dst, const int* index, const int* value, int n,
   return TIB_OK;
 }
 
-// After a decode step on the device: the drawn tokens become the next inputs and every
-// request moves one position on.  history (optional) receives the drawn tokens.
-TIB_API int tib_advance_decode(int* token_ids, const int* sampled, int* positions, int* draw_positions,
-                               int* history, int n, cudaStream_t stream) {
+// The inputs of a decode step from the requests' own records (common.cuh: TibRequestRecord): request i of the step
+// sits in slot slots[i]; its next token and its position are read from its record, and the record moves one
+// position on.  A request appears at most once in slots.
+TIB_API int tib_decode_inputs(int* records, const int* slots, int max_slots, int* token_ids, int* positions, int n,
+                              cudaStream_t stream) {
   if (n == 0) return TIB_OK;
-  if (!token_ids || !sampled || !positions || n < 0) return TIB_E_ARG;
-  TIB_LAUNCH_DEPENDENT(advance_decode_kernel, ceil_div(n, 128), 128, 0, stream, token_ids, sampled, positions, draw_positions, history, n);
+  if (!records || !slots || !token_ids || !positions || n < 0 || max_slots < 1) return TIB_E_ARG;
+  TIB_LAUNCH_DEPENDENT(decode_inputs_kernel, ceil_div(n, 128), 128, 0, stream, records, slots, max_slots, token_ids, positions, n);
   TIB_LAUNCH_CHECK();
   return TIB_OK;
 }

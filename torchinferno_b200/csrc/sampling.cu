@@ -43,17 +43,29 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, int64_t row_stride, const float* __restrict__ temperature,
               const int64_t* __restrict__ seeds, const int* __restrict__ positions,
-              int* __restrict__ out, int vocab) {
+              int* __restrict__ out, int vocab, int* __restrict__ records, const int* __restrict__ record_slots,
+              int max_slots, int* __restrict__ history) {
   pdl_wait();
   pdl_trigger();
   __shared__ float sv[32];
   __shared__ int si[32];
   const int row = blockIdx.x;
   const float* lg = logits + (size_t)row * row_stride;
-  const float temp = temperature ? temperature[row] : 0.f;
+  float temp = temperature ? temperature[row] : 0.f;
+  uint64_t seed = seeds ? (uint64_t)seeds[row] : 0ull;
+  uint32_t pos = positions ? (uint32_t)positions[row] : 0u;
+  int* record = nullptr;
+  if (records) {
+    // parameters from the request's own record: its length after this step is the position of the token drawn now
+    const int slot = record_slots[row];
+    if (slot >= 0 && slot < max_slots) {
+      record = records + (size_t)slot * TIB_REC_WORDS;
+      temp = __int_as_float(record[TIB_REC_TEMPERATURE]);
+      seed = ((uint64_t)(uint32_t)record[TIB_REC_SEED_HI] << 32) | (uint32_t)record[TIB_REC_SEED_LO];
+      pos = (uint32_t)record[TIB_REC_LENGTH];
+    }
+  }
   const bool greedy = !(temp > 0.f);
-  const uint64_t seed = seeds ? (uint64_t)seeds[row] : 0ull;
-  const uint32_t pos = positions ? (uint32_t)positions[row] : 0u;
   float bv = -CUDART_INF_F;
   int bi = 0x7fffffff;
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
@@ -84,7 +96,14 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, const float*
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
     }
-    if (lane == 0) out[row] = bi;
+    if (lane == 0) {
+      out[row] = bi;
+      if (history) history[row] = bi;
+      if (record) {
+        record[TIB_REC_LAST_TOKEN] = bi;
+        record[TIB_REC_DRAWN] += 1;
+      }
+    }
   }
 }
 
@@ -101,7 +120,24 @@ TIB_API int tib_sample(const float* logits, int64_t row_stride, const float* tem
   if (!logits || !out || n_rows < 0 || vocab < 1) return TIB_E_ARG;
   int threads = 1024;
   while (threads > 32 && threads / 2 >= vocab) threads /= 2;
-  TIB_LAUNCH_DEPENDENT(sample_kernel, n_rows, threads, 0, stream, logits, row_stride, temperature, seeds, positions, out, vocab);
+  TIB_LAUNCH_DEPENDENT(sample_kernel, n_rows, threads, 0, stream, logits, row_stride, temperature, seeds, positions, out, vocab,
+                       (int*)nullptr, (const int*)nullptr, 0, (int*)nullptr);
+  TIB_LAUNCH_CHECK();
+  return TIB_OK;
+}
+
+// The same with every row's parameters taken from its request's record (common.cuh: TibRequestRecord):
+// records [max_slots][TIB_REC_WORDS], record_slots [n_rows] the slot of each row's request.  The drawn token is
+// written to out[row], to the record (next input token; count of drawn tokens) and, when given, to history[row].
+// A slot outside the table is drawn greedily and writes no record.
+TIB_API int tib_sample_records(const float* logits, int64_t row_stride, int* records, const int* record_slots, int max_slots,
+                               int* out, int* history, int n_rows, int vocab, cudaStream_t stream) {
+  if (n_rows == 0) return TIB_OK;
+  if (!logits || !out || !records || !record_slots || n_rows < 0 || vocab < 1 || max_slots < 1) return TIB_E_ARG;
+  int threads = 1024;
+  while (threads > 32 && threads / 2 >= vocab) threads /= 2;
+  TIB_LAUNCH_DEPENDENT(sample_kernel, n_rows, threads, 0, stream, logits, row_stride, (const float*)nullptr,
+                       (const int64_t*)nullptr, (const int*)nullptr, out, vocab, records, record_slots, max_slots, history);
   TIB_LAUNCH_CHECK();
   return TIB_OK;
 }

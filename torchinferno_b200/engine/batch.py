@@ -9,7 +9,7 @@ a range of it.
 Device arrays (int32, views into one uploaded buffer):
   token_ids[t], positions[t], token_slot[t]     per token
   q_start[e] (n_entries + 1), kv_start[e], slots[e]   per entry
-  logit_rows[i]                                 token rows whose logits are wanted
+  logit_rows[i], logit_slots[i]                 token rows whose logits are wanted, and the slot of their request
 """
 from __future__ import annotations
 
@@ -25,6 +25,8 @@ class StepEntry:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()      # indices into ``tokens``
+    seed: int = 0                 # sampling parameters, written into the request's record when this step opens it
+    temperature: float = 0.0
 
 
 @dataclass
@@ -45,6 +47,7 @@ class StepBatch:
     kv_start: torch.Tensor
     slots: torch.Tensor
     logit_rows: torch.Tensor
+    logit_slots: torch.Tensor
     n_tokens: int
     n_entries: int
     n_logits: int
@@ -67,6 +70,7 @@ def build_batch(placements: list[EntryPlacement], tokens: list[Sequence[int]], w
     kv_start: list[int] = []
     slots: list[int] = []
     logit_rows: list[int] = []
+    logit_slots: list[int] = []
     for place, toks, want in zip(placements, tokens, wants):
         token_ids.extend(int(t) for t in toks)
         positions.extend(range(place.kv_start, place.kv_start + place.q_len))
@@ -75,7 +79,8 @@ def build_batch(placements: list[EntryPlacement], tokens: list[Sequence[int]], w
         kv_start.append(place.kv_start)
         slots.append(place.slot)
         logit_rows.extend(place.q_start + int(w) for w in want)
-    sections = [token_ids, positions, token_slot, q_start, kv_start, slots, logit_rows]
+        logit_slots.extend([place.slot] * len(want))
+    sections = [token_ids, positions, token_slot, q_start, kv_start, slots, logit_rows, logit_slots]
     for index, value in table_updates:
         sections.extend((index, value))
     total = sum(len(s) for s in sections)
@@ -94,10 +99,10 @@ def build_batch(placements: list[EntryPlacement], tokens: list[Sequence[int]], w
         offset += len(section)
     batch = StepBatch(
         token_ids=views[0], positions=views[1], token_slot=views[2], q_start=views[3], kv_start=views[4],
-        slots=views[5], logit_rows=views[6], n_tokens=len(token_ids), n_entries=len(placements),
+        slots=views[5], logit_rows=views[6], logit_slots=views[7], n_tokens=len(token_ids), n_entries=len(placements),
         n_logits=len(logit_rows), max_q_len=max((p.q_len for p in placements), default=0),
         max_kv_len=max((p.kv_start + p.q_len for p in placements), default=0),
         n_single=sum(1 for p in placements if p.q_len == 1), n_multi=sum(1 for p in placements if p.q_len > 1),
         entries=placements, h2d_bytes=total * 4)
-    updates = [(views[7 + 2 * i], views[8 + 2 * i]) for i in range(len(table_updates))]
+    updates = [(views[8 + 2 * i], views[9 + 2 * i]) for i in range(len(table_updates))]
     return batch, updates

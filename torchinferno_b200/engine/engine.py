@@ -79,7 +79,7 @@ class InferenceEngine:
         self._cancelled: set[Hashable] = set()
         self._closed = False
         self._ahead: _Launched | None = None      # a step launched before the one before it was committed
-        self.stats = {"steps": 0, "steps_ahead": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+        self.stats = {"steps": 0, "steps_ahead": 0, "tokens": 0, "h2d_bytes": 0, "d2h_bytes": 0}
 
     # -------------------------------------------------------- construction
     @classmethod
@@ -168,38 +168,69 @@ class InferenceEngine:
             plan = self.scheduler.plan()
             if not plan.entries:
                 return []
-            current = self._launch(plan, None)
+            current = self._launch(plan, False)
         if self.config.async_scheduling and current.device_tokens is not None and self.runner.use_cuda_graphs:
             ahead = self.scheduler.plan_ahead(current.plan)
             if ahead is not None and len(current.drawing) == len(ahead.entries):
-                self._ahead = self._launch(ahead, current.device_tokens)
+                self._ahead = self._launch(ahead, True)
                 self.stats["steps_ahead"] += 1
-        return self.scheduler.commit(current.plan, current.tokens())
+        try:
+            tokens = current.tokens()
+        except StepError:
+            self._abandon(current.plan)
+            raise
+        return self.scheduler.commit(current.plan, tokens)
 
-    def _launch(self, plan: StepPlan, fed: torch.Tensor | None) -> _Launched:
-        """Start a step on the device.  ``fed``: the tokens drawn by the step before, when the
-        plan was made ahead of them."""
+    def _launch(self, plan: StepPlan, ahead: bool) -> _Launched:
+        """Start a step on the device.  ``ahead``: the plan was made before the tokens of the step before it
+        were read; they are on the device, in the requests' records."""
+        runner, cache = self.runner, self.runner.cache
         with torch.inference_mode():
-            if fed is not None:
-                logits = self.runner.decode_ahead([e.request_id for e in plan.entries], fed)
-            else:
-                assert all(t != UNKNOWN_TOKEN for e in plan.entries for t in e.tokens)
-                logits = self.runner.step([StepEntry(e.request_id, e.tokens, (len(e.tokens) - 1,) if e.samples else ())
-                                           for e in plan.entries])
+            # a step of decoded tokens only takes its inputs from the requests' records on the device, where the
+            # sampler left them: nothing but new block-table entries is copied
+            fed_by_device = ahead or (runner.use_cuda_graphs and runner._graph_ok
+                                      and all(e.kind == "decode" and e.request_id in cache for e in plan.entries))
+            try:
+                if fed_by_device:
+                    logits = runner.decode_ahead([e.request_id for e in plan.entries])
+                else:
+                    assert all(t != UNKNOWN_TOKEN for e in plan.entries for t in e.tokens)
+                    entries = []
+                    for e in plan.entries:
+                        request = self.scheduler.request(e.request_id)
+                        entries.append(StepEntry(e.request_id, e.tokens, (len(e.tokens) - 1,) if e.samples else (),
+                                                 seed=request.seed, temperature=request.temperature))
+                    logits = runner.step(entries)
+            except StepError:
+                self._abandon(plan)
+                raise
+            batch = runner.last_batch
+            for planned, placed in zip(plan.entries, batch.entries):
+                if placed.kv_start != planned.start:
+                    self._abandon(plan)
+                    raise StepError(f"request {planned.request_id!r} was planned at position {planned.start} "
+                                    f"but its cache stands at {placed.kv_start}")
             self.stats["steps"] += 1
-            self.stats["h2d_bytes"] += self.runner.last_batch.h2d_bytes
+            self.stats["h2d_bytes"] += batch.h2d_bytes
+            self.stats["tokens"] += batch.n_tokens
             drawing = [e for e in plan.entries if e.samples]
             requests = [self.scheduler.request(e.request_id) for e in plan.entries]
             if not drawing:
-                return _Launched(plan, requests, [], None, self.runner.cache.error_word)
-            params, positions = [], []
-            for e in drawing:
-                request = self.scheduler.request(e.request_id)
-                params.append(SamplingParams(request.temperature, request.seed))
-                positions.append(e.start + len(e.tokens))  # position of the token being drawn
-            tokens = self.sampler.sample(logits, params, positions)
+                return _Launched(plan, requests, [], None, cache.error_word)
+            tokens = self.sampler.sample_records(logits, cache.request_records, batch.logit_slots)
             self.stats["d2h_bytes"] += tokens.numel() * tokens.element_size() + 4    # (and the error word)
-            return _Launched(plan, requests, drawing, tokens, self.runner.cache.error_word)
+            return _Launched(plan, requests, drawing, tokens, cache.error_word)
+
+    def _abandon(self, plan: StepPlan | None) -> None:
+        """A step failed: its requests (and those of a step launched ahead) are cancelled and give back what
+        they hold, and the device's error word is cleared, so that the engine can go on with the rest."""
+        ahead, self._ahead = self._ahead, None
+        for p in (plan, None if ahead is None else ahead.plan):
+            for entry in (() if p is None else p.entries):
+                self.scheduler.cancel(entry.request_id)
+                self._requests.pop(entry.request_id, None)
+        if self.runner.cache.error_word is not None:
+            self.runner.cache.error_word.zero_()
 
     # ------------------------------------------------------------ generate
     def generate_stream(self, request: GenerateRequest) -> Iterator[TokenOutput]:

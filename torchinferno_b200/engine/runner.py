@@ -14,7 +14,7 @@ from typing import Hashable, Iterable, Sequence
 
 import torch
 
-from torchinferno_b200.cache.manager import CacheManager, OutOfPages
+from torchinferno_b200.cache.manager import REC_LAST_TOKEN, REC_LENGTH, CacheManager, OutOfPages
 from torchinferno_b200.engine.batch import EntryPlacement, StepBatch, StepEntry, build_batch
 from torchinferno_b200.kernels import gemm, ops
 
@@ -31,7 +31,9 @@ class _DecodeGraph:
     row; here a graph is captured per exact batch size, so no padded row ever touches the cache.
     The static integers are: token ids, positions (also the number of cached tokens, since each
     request brings one token), slots (also the slot of each token), and the fixed ranges
-    q_start = 0..n and logit_rows = 0..n-1.
+    q_start = 0..n and logit_rows = 0..n-1.  Only the slots come from the host, and only when the set of
+    requests changes: the pass begins with a kernel that reads every request's next token and position from
+    its record on the device and moves the record on (``ops.decode_inputs``).
     """
 
     def __init__(self, n: int, device: torch.device, max_kv_len: int) -> None:
@@ -44,11 +46,12 @@ class _DecodeGraph:
         self.logit_rows.copy_(torch.arange(n, dtype=torch.int32))
         self.batch = StepBatch(
             token_ids=self.token_ids, positions=self.positions, token_slot=self.slots, q_start=self.q_start,
-            kv_start=self.positions, slots=self.slots, logit_rows=self.logit_rows, n_tokens=n, n_entries=n,
+            kv_start=self.positions, slots=self.slots, logit_rows=self.logit_rows, logit_slots=self.slots, n_tokens=n, n_entries=n,
             n_logits=n, max_q_len=1, max_kv_len=max_kv_len, n_single=n, n_multi=0, entries=[])
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits: torch.Tensor | None = None
         self.launches = 0          # kernels of this library inside the graph
+        self.host_slots: list[int] | None = None     # what self.slots holds
 
 
 class ModelRunner:
@@ -58,9 +61,9 @@ class ModelRunner:
         self.check_errors = check_errors
         self.last_batch: StepBatch | None = None
         self.steps = 0
-        # a mixer with per-request state walks the entries on the host: no graph for such a model
+        # a part that walks the step's entries on the host cannot be captured: no graph for such a model
         self.use_cuda_graphs = use_cuda_graphs
-        self._graph_ok = all(spec is None for spec in model.state_requirements())
+        self._graph_ok = model.capturable()
         self._graphs: dict[int, _DecodeGraph] = {}
         self._graph_generation = gemm.generation()
         gemm.set_error_word(cache.error_word)   # bounded waits of the tcgen05 kernels report here
@@ -113,15 +116,18 @@ class ModelRunner:
         row = 0
         for entry in entries:
             if entry.request_id not in cache:
-                cache.open(entry.request_id)
+                cache.open(entry.request_id, seed=entry.seed, temperature=entry.temperature)
             start = cache.extend(entry.request_id, len(entry.tokens))
+            # (the record's length after the step is the position of the token a sampler would draw from it)
+            cache.set_record(entry.request_id, REC_LENGTH, start + len(entry.tokens))
             placements.append(EntryPlacement(entry.request_id, cache.slot(entry.request_id), row, len(entry.tokens), start))
             row += len(entry.tokens)
         batch, updates = build_batch(placements, [e.tokens for e in entries], [e.want for e in entries],
-                                     cache.drain_table_updates(), cache.device)
-        for group, (index, value) in zip(cache.groups, updates):
+                                     cache.drain_table_updates() + [cache.drain_record_updates()], cache.device)
+        targets = [group.table_device for group in cache.groups] + [cache.request_records]
+        for target, (index, value) in zip(targets, updates):
             if index.numel():
-                ops.scatter_i32(group.table_device, index, value)
+                ops.scatter_i32(target, index, value)
         self.last_batch = batch
         logits = self.model.forward(batch, cache)
         for entry in entries:
@@ -133,16 +139,26 @@ class ModelRunner:
 
     # ------------------------------------------------------- decode graphs
     def _apply_table_updates(self) -> int:
-        """Upload and apply queued block-table changes; returns the bytes copied to the device."""
+        """Upload and apply queued changes of the block tables and of the requests' records; returns the bytes
+        copied to the device."""
         copied = 0
-        for group, (index, value) in zip(self.cache.groups, self.cache.drain_table_updates()):
+        targets = [group.table_device for group in self.cache.groups] + [self.cache.request_records]
+        for target, (index, value) in zip(targets, self.cache.drain_table_updates() + [self.cache.drain_record_updates()]):
             if not index:
                 continue
             host = torch.tensor([index, value], dtype=torch.int32).pin_memory()
             dev = host.to(self.cache.device, non_blocking=True)
-            ops.scatter_i32(group.table_device, dev[0], dev[1])
+            ops.scatter_i32(target, dev[0], dev[1])
             copied += host.numel() * 4
         return copied
+
+    def _set_slots(self, g: _DecodeGraph, slots: list[int]) -> int:
+        """Make ``g`` run the requests in these slots; returns the bytes copied (none while the set stays)."""
+        if g.host_slots == slots:
+            return 0
+        g.slots.copy_(torch.tensor(slots, dtype=torch.int32).pin_memory(), non_blocking=True)
+        g.host_slots = list(slots)
+        return 4 * len(slots)
 
     def _graph_for(self, n: int) -> _DecodeGraph:
         if self._graph_generation != gemm.generation():
@@ -155,14 +171,17 @@ class ModelRunner:
 
     def _run_decode_graph(self, g: _DecodeGraph) -> torch.Tensor:
         """Logits [n, vocab] for the decode batch described by ``g``'s static buffers."""
+        records = self.cache.request_records
         if g.graph is None:
             # First use at this batch size: run once outside a graph (this also does every lazy
             # set-up of libraries and kernels), then capture the same pass for later steps.
+            ops.decode_inputs(records, g.slots, g.token_ids, g.positions)
             logits = self.model.forward(g.batch, self.cache)
             torch.cuda.synchronize(self.cache.device)
             before = ops.launch_count()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
+                ops.decode_inputs(records, g.slots, g.token_ids, g.positions)
                 g.logits = self.model.forward(g.batch, self.cache)
             g.launches = ops.launch_count() - before
             g.graph = graph
@@ -171,18 +190,15 @@ class ModelRunner:
         self.graph_replays += 1
         return g.logits
 
-    def decode_ahead(self, request_ids: Sequence[Hashable], device_tokens: torch.Tensor) -> torch.Tensor:
-        """One decode step whose input tokens are still being drawn on the device.
-
-        ``device_tokens`` [n] int32 holds, in stream order, the token each open request drew in
-        the step before; the host need not have read it yet.  Otherwise as :meth:`step` with one
-        token and ``want=(0,)`` per request.
-        """
+    def decode_ahead(self, request_ids: Sequence[Hashable]) -> torch.Tensor:
+        """One decode step fed from the device: every request's input token is the one the sampler last drew for
+        it (``ops.sample_records`` left it in the request's record); the host need not have read it yet.
+        Otherwise as :meth:`step` with one token and ``want=(0,)`` per request."""
         cache = self.cache
         if not (self.use_cuda_graphs and self._graph_ok and cache.device.type == "cuda"):
             raise StepError("decode_ahead needs the captured decode pass (a CUDA device, graphs on, no per-request host state)")
-        if device_tokens.dtype != torch.int32 or device_tokens.numel() != len(request_ids) or len(set(request_ids)) != len(request_ids):
-            raise StepError("decode_ahead takes one int32 device token per distinct request")
+        if len(set(request_ids)) != len(request_ids):
+            raise StepError("decode_ahead takes distinct requests")
         need = [0] * len(cache.groups)
         for request_id in request_ids:
             if request_id not in cache:
@@ -194,27 +210,22 @@ class ModelRunner:
         for g, (n, f) in enumerate(zip(need, cache.free_pages())):
             if n > f:
                 raise OutOfPages(f"the step needs {n} new pages of cache group {g}, {f} are free")
-        return self._decode_step([StepEntry(r, (0,), (0,)) for r in request_ids], device_tokens)
+        return self._decode_step([StepEntry(r, (0,), (0,)) for r in request_ids], fed_by_device=True)
 
-    def _decode_step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
+    def _decode_step(self, entries: Sequence[StepEntry], fed_by_device: bool = False) -> torch.Tensor:
         cache = self.cache
         n = len(entries)
         g = self._graph_for(n)
         starts = []
         for entry in entries:
             if entry.request_id not in cache:
-                cache.open(entry.request_id)
+                cache.open(entry.request_id, seed=entry.seed, temperature=entry.temperature)
             starts.append(cache.extend(entry.request_id, 1))
+            if not fed_by_device:       # the host names the token (and, for good measure, where it stands)
+                cache.set_record(entry.request_id, REC_LAST_TOKEN, int(entry.tokens[0]))
+                cache.set_record(entry.request_id, REC_LENGTH, starts[-1])
         slots = [cache.slot(e.request_id) for e in entries]
-        if device_tokens is None:
-            host = torch.tensor([int(e.tokens[0]) for e in entries] + starts + slots, dtype=torch.int32).pin_memory()
-            g.buffer[:3 * n].copy_(host, non_blocking=True)
-        else:
-            host = torch.tensor(starts + slots, dtype=torch.int32).pin_memory()
-            g.buffer[n:3 * n].copy_(host, non_blocking=True)
-            g.token_ids.copy_(device_tokens.reshape(n), non_blocking=True)
-        copied = host.numel() * 4 + self._apply_table_updates()
-        g.batch.h2d_bytes = copied
+        g.batch.h2d_bytes = self._set_slots(g, slots) + self._apply_table_updates()
         g.batch.entries = [EntryPlacement(e.request_id, s, i, 1, st) for i, (e, s, st) in enumerate(zip(entries, slots, starts))]
         self.last_batch = g.batch
         logits = self._run_decode_graph(g)
@@ -230,32 +241,32 @@ class ModelRunner:
         """Decode ``steps`` tokens for each request without a host round trip per token.
 
         Every request must be open; ``tokens[i]`` is its next input token (the last one drawn, not
-        yet in the cache).  Each step runs the captured decode pass, draws the next tokens on the
-        device and feeds them back; the host only runs ahead with page bookkeeping.  Returns the
-        drawn tokens [steps, n] (int32, on the device).  Nothing stops a request early.
+        yet in the cache).  Each step runs the captured decode pass, which takes its inputs from the
+        requests' records, and draws the next tokens into those records; the host only runs ahead with
+        page bookkeeping.  ``temperature`` / ``seeds`` replace the sampling parameters the requests
+        were opened with.  Returns the drawn tokens [steps, n] (int32, on the device).  Nothing stops a
+        request early.
         """
         cache = self.cache
         n = len(request_ids)
         if not (self._graph_ok and cache.device.type == "cuda"):
             raise StepError("decode_loop needs a CUDA device and a model without per-request host state")
         g = self._graph_for(n)
-        lengths = [cache.length(r) for r in request_ids]
-        slots = [cache.slot(r) for r in request_ids]
-        dev = cache.device
-        g.buffer[:3 * n].copy_(torch.tensor(list(map(int, tokens)) + lengths + slots, dtype=torch.int32).pin_memory(),
-                               non_blocking=True)
-        draw_positions = torch.tensor([l + 1 for l in lengths], dtype=torch.int32).to(dev)
-        temps = None if temperature is None else torch.tensor(list(temperature), dtype=torch.float32).to(dev)
-        seed_t = None if seeds is None else torch.tensor(list(seeds), dtype=torch.int64).to(dev)
-        history = torch.empty((steps, n), dtype=torch.int32, device=dev)
-        sampled = torch.empty(n, dtype=torch.int32, device=dev)
+        for i, request_id in enumerate(request_ids):
+            cache.set_record(request_id, REC_LAST_TOKEN, int(tokens[i]))
+            cache.set_record(request_id, REC_LENGTH, cache.length(request_id))
+            if temperature is not None or seeds is not None:
+                cache.set_sampling(request_id, seed=0 if seeds is None else int(seeds[i]),
+                                   temperature=0.0 if temperature is None else float(temperature[i]))
+        self._set_slots(g, [cache.slot(r) for r in request_ids])
+        history = torch.empty((steps, n), dtype=torch.int32, device=cache.device)
+        sampled = torch.empty(n, dtype=torch.int32, device=cache.device)
         for step in range(steps):
             for request_id in request_ids:
                 cache.extend(request_id, 1)
             self._apply_table_updates()
             logits = self._run_decode_graph(g)
-            ops.sample(logits, sampled, temps, seed_t, draw_positions)
-            ops.advance_decode(g.token_ids, sampled, g.positions, draw_positions, history[step])
+            ops.sample_records(logits, sampled, cache.request_records, g.slots, history[step])
             for request_id in request_ids:
                 cache.release_behind_window(request_id)
             self.steps += 1

@@ -94,7 +94,7 @@ def lib() -> ctypes.CDLL:
     library = load_library()
     if not _signatures_set:
         for fn in ("tib_embedding", "tib_add_rmsnorm", "tib_rmsnorm", "tib_swiglu", "tib_cast",
-                   "tib_scatter_i32", "tib_advance_decode", "tib_rope_append", "tib_paged_attention_simt", "tib_gemm_f32", "tib_sample",
+                   "tib_scatter_i32", "tib_decode_inputs", "tib_sample_records", "tib_rope_append", "tib_paged_attention_simt", "tib_gemm_f32", "tib_sample",
                    "tib_attention_mma_supports", "tib_prefill_attention", "tib_decode_attention",
                    "tib_prefill_attention_tcgen05", "tib_prefill_attention_tcgen05_supports",
                    "tib_decode_attention_tma", "tib_decode_attention_tma_supports", "tib_set_dependent_launch",
@@ -281,18 +281,43 @@ def scatter_i32(dst: torch.Tensor, index: torch.Tensor, value: torch.Tensor) -> 
     return dst
 
 
-def advance_decode(token_ids: torch.Tensor, sampled: torch.Tensor, positions: torch.Tensor,
-                   draw_positions: torch.Tensor | None = None, history: torch.Tensor | None = None) -> None:
-    """token_ids = sampled; positions += 1; draw_positions += 1; history = sampled (all int32, length n)."""
-    n = token_ids.numel()
-    for name, t in (("token_ids", token_ids), ("sampled", sampled), ("positions", positions),
-                    ("draw_positions", draw_positions), ("history", history)):
-        if t is not None:
-            _need(t, name, torch.int32)
-            if t.numel() < n:
-                raise KernelError(f"advance_decode: {name} is shorter than token_ids")
-    _check("advance_decode", lib().tib_advance_decode(_ptr(token_ids), _ptr(sampled), _ptr(positions),
-                                                      _ptr(draw_positions), _ptr(history), c_int(n), _stream()))
+RECORD_WORDS = 8          # int32 words of a request's record (csrc/common.cuh: TibRequestRecord)
+REC_LENGTH, REC_LAST_TOKEN, REC_SEED_LO, REC_SEED_HI, REC_TEMPERATURE, REC_DRAWN = range(6)
+
+
+def _need_records(records: torch.Tensor) -> None:
+    _need(records, "records", torch.int32)
+    if records.dim() != 2 or records.shape[1] != RECORD_WORDS:
+        raise KernelError(f"records must be [slots, {RECORD_WORDS}] int32")
+
+
+def sample_records(logits: torch.Tensor, out: torch.Tensor, records: torch.Tensor, record_slots: torch.Tensor,
+                   history: torch.Tensor | None = None) -> torch.Tensor:
+    """As :func:`sample`, every row's temperature, seed and position taken from the record of its request
+    (``record_slots[row]``); the drawn token also goes into that record as the request's next input token."""
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be a 2-D fp32 CUDA tensor with unit inner stride")
+    _need(out, "out", torch.int32), _need_records(records), _need(record_slots, "record_slots", torch.int32)
+    n, vocab = logits.shape
+    if history is not None:
+        _need(history, "history", torch.int32)
+    if out.numel() < n or record_slots.numel() < n or (history is not None and history.numel() < n):
+        raise KernelError("sample: a per-row array is shorter than the number of rows")
+    _check("sample", lib().tib_sample_records(_ptr(logits), c_int64(logits.stride(0)), _ptr(records), _ptr(record_slots),
+                                              c_int(records.shape[0]), _ptr(out), _ptr(history), c_int(n), c_int(vocab), _stream()))
+    return out
+
+
+def decode_inputs(records: torch.Tensor, slots: torch.Tensor, token_ids: torch.Tensor, positions: torch.Tensor) -> None:
+    """token_ids[i], positions[i] = next token and position of the request in slot slots[i]; its record moves on by one."""
+    n = slots.numel()
+    _need_records(records)
+    for name, t in (("slots", slots), ("token_ids", token_ids), ("positions", positions)):
+        _need(t, name, torch.int32)
+        if t.numel() < n:
+            raise KernelError(f"decode_inputs: {name} is shorter than slots")
+    _check("decode_inputs", lib().tib_decode_inputs(_ptr(records), _ptr(slots), c_int(records.shape[0]), _ptr(token_ids),
+                                                    _ptr(positions), c_int(n), _stream()))
 
 
 def attention_mma_supports(head_dim: int, group: int) -> bool:

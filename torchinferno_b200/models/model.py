@@ -29,6 +29,8 @@ class CausalLM:
         self.blocks: list[Block] = [
             build_part("block", layer.block, dtype=dtype, device=self.device) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, dtype=dtype, device=self.device)
+        self.after_embedding = None if spec.after_embedding is None else \
+            build_part("stream_stage", spec.after_embedding, dtype=dtype, device=self.device)
         self.embedding: torch.Tensor | None = None
         self.head: torch.Tensor | None = None
 
@@ -43,9 +45,10 @@ class CausalLM:
                 for ws in part.weight_specs():
                     name = layer.prefix + prefix + ws.name
                     expected[name] = WeightSpec(name, ws.shape, ws.init, ws.std, ws.role, ws.optional)
-        for ws in self.final_norm.weight_specs():
-            name = spec.final_norm.prefix + ws.name
-            expected[name] = WeightSpec(name, ws.shape, ws.init, ws.std, ws.role, ws.optional)
+        for part, part_spec in ((self.final_norm, spec.final_norm), (self.after_embedding, spec.after_embedding)):
+            for ws in (part.weight_specs() if part is not None else ()):
+                name = part_spec.prefix + ws.name
+                expected[name] = WeightSpec(name, ws.shape, ws.init, ws.std, ws.role, ws.optional)
         if spec.head_name is not None:
             expected[spec.head_name] = WeightSpec(
                 spec.head_name, (spec.vocab_size, spec.hidden_size), optional=spec.tie_head_to_embedding)
@@ -76,8 +79,12 @@ class CausalLM:
                 full = layer.prefix + prefix
                 part.bind({ws.name: take(full + ws.name) for ws in part.weight_specs()
                            if full + ws.name in tensors})
-        self.final_norm.bind({ws.name: tensors[spec.final_norm.prefix + ws.name]
+        self.final_norm.bind({ws.name: take(spec.final_norm.prefix + ws.name)
                               for ws in self.final_norm.weight_specs()})
+        if self.after_embedding is not None:
+            self.after_embedding.bind({ws.name: take(spec.after_embedding.prefix + ws.name)
+                                       for ws in self.after_embedding.weight_specs()
+                                       if spec.after_embedding.prefix + ws.name in tensors})
         if self.device.type == "cuda":
             gemm.tune_few_rows()      # weights that left the choice of their few-rows kernel open get it now
 
@@ -112,6 +119,11 @@ class CausalLM:
             needs.setdefault(call.cache, cs)
         return [needs[i] for i in range(self.spec.cache_layers)]
 
+    def capturable(self) -> bool:
+        """Whether a decode step of this model may be captured in a CUDA graph (see ``Mixer.capturable``)."""
+        parts = [block.mixer for block in self.blocks] + ([self.after_embedding] if self.after_embedding is not None else [])
+        return all(getattr(part, "capturable", getattr(part, "state_spec", lambda: None)() is None) for part in parts)
+
     def state_requirements(self) -> list[StateSpec | None]:
         """StateSpec of every layer call of the schedule (None where the mixer has none)."""
         return [self.blocks[call.layer].mixer.state_spec() for call in self.spec.schedule]
@@ -123,6 +135,8 @@ class CausalLM:
         residual = torch.empty((n, self.spec.hidden_size), dtype=torch.float32, device=self.device)
         ops.embedding(batch.token_ids, self.embedding, residual)
         stream = ResidualStream(residual, self.dtype)
+        if self.after_embedding is not None:
+            self.after_embedding.forward(stream, LayerContext(batch=batch, error_word=cache.error_word, layer_index=-1))
         for index, call in enumerate(self.spec.schedule):
             kv = None
             if call.cache is not None:

@@ -39,6 +39,7 @@ class ModelSpec:
     final_norm: PartSpec            # prefix holds its full name prefix
     head_name: str | None           # tensor name of the [vocab, hidden] output matrix
     tie_head_to_embedding: bool = False
+    after_embedding: PartSpec | None = None   # category "stream_stage"; prefix holds its full name prefix
     config: Mapping[str, Any] = field(default_factory=dict)  # the config.json this came from
 
     def __post_init__(self) -> None:

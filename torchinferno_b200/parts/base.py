@@ -17,6 +17,7 @@ Interfaces
 ``Mixer``          ``cache_spec()``, ``state_spec()``, ``forward(x, ctx) -> y``
 ``FeedForward``    ``forward(x, ctx) -> y``
 ``Block``          ``forward(stream, ctx)`` on a :class:`ResidualStream`
+``StreamStage``    ``forward(stream, ctx)`` between the embedding and the first block
 """
 from __future__ import annotations
 
@@ -161,6 +162,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # ``capturable``: the forward only launches kernels on the current stream and reads the batch through its
+    # device arrays, so a decode step that contains it may be captured in a CUDA graph.  Left unset, a mixer
+    # without a StateSpec counts as capturable and one with a StateSpec does not (it is taken to walk
+    # ``ctx.batch.entries`` on the host); a model with any mixer that is not runs its decode steps uncaptured.
     def cache_spec(self) -> CacheSpec | None:
         return None
 
@@ -187,8 +192,16 @@ class Block(Part):
         raise NotImplementedError
 
 
+class StreamStage(Part):
+    """Something done to the residual stream once, after the embedding and before the first block: a learned
+    absolute position table added to it, a multiplier, a norm.  ``ctx`` carries the batch (positions, slots)."""
+
+    def forward(self, stream: ResidualStream, ctx: LayerContext) -> None:
+        raise NotImplementedError
+
+
 # ----------------------------------------------------------------- registry
-_KINDS = ("mixer", "feed_forward", "norm", "position", "block")
+_KINDS = ("mixer", "feed_forward", "norm", "position", "block", "stream_stage")
 _REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {kind: {} for kind in _KINDS}
 
 

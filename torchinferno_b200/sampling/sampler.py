@@ -10,8 +10,16 @@ top_p other than 1, top-k and penalties are not offered there
 (src/torchinferno/server/openai_protocol.py:34-38) nor here.
 
 Here the Gumbel-max form runs in one kernel with counter-based noise keyed by
-(request seed, position of the token being drawn, vocabulary index): a request's
-tokens do not depend on what else is in the batch, nor on how its prompt was cut.
+(request seed, position of the token being drawn, vocabulary index): given the
+same logits, a request's token does not depend on what else is in the batch,
+nor on how its prompt was cut.  (In bfloat16 the logits themselves may differ in
+their last bits with the number of rows of a step, because products of few and
+of many rows run different kernels; in float32 they do not.)
+
+The engine keeps every live request's seed and temperature in its record on the
+device (``CacheManager.request_records``); :meth:`Sampler.sample_records` reads
+them there by slot and leaves the drawn token in the record, so a sampled step
+copies nothing from the host.
 """
 from __future__ import annotations
 
@@ -54,6 +62,17 @@ class Sampler:
         seeds = torch.tensor([_as_int64(p.seed) for p in params], dtype=torch.int64).to(self.device)
         pos = torch.tensor(list(positions), dtype=torch.int32).to(self.device)
         return ops.sample(logits, out, temperature, seeds, pos)
+
+
+    def sample_records(self, logits: torch.Tensor, records: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+        """Token ids (int32, on the device) for fp32 ``logits`` [n, vocab] whose row i belongs to the request in
+        slot ``slots[i]``: temperature, seed and the position of the token being drawn (the request's length)
+        come from ``records``; the token is also written there as the request's next input."""
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+        if logits.shape[0] == 0:
+            return out
+        return ops.sample_records(logits, out, records, slots)
+
 
 
 def _as_int64(seed: int) -> int:
