@@ -79,3 +79,21 @@ def model_folders(tmp_path_factory):
         write_random_model(config, folder, seed)
         folders[name] = folder
     return folders
+
+
+def pytest_terminal_summary(terminalreporter):
+    """The largest error each comparison with the plain implementation saw, as a share of its tolerance."""
+    try:
+        from gpu_common import WORST
+    except Exception:
+        return
+    if not WORST:
+        return
+    terminalreporter.section("largest error / tolerance")
+    by_dtype: dict[str, float] = {}
+    for what, share in sorted(WORST.items(), key=lambda kv: -kv[1])[:12]:
+        terminalreporter.write_line(f"{share:6.3f}  {what}")
+    for what, share in WORST.items():
+        kind = "bfloat16" if "bfloat16" in what else "float32"
+        by_dtype[kind] = max(by_dtype.get(kind, 0.0), share)
+    terminalreporter.write_line("worst by dtype: " + ", ".join(f"{k} {v:.3f}" for k, v in sorted(by_dtype.items())))

@@ -16,6 +16,15 @@ F32_ATOL, F32_RTOL = 2e-5, 1e-4
 BF16_REL = 0.015
 
 
+# The largest error a test saw, as a share of its bound (printed at the end of the run, so that it shows how much
+# room a tolerance leaves).
+WORST: dict[str, float] = {}
+
+
+def note_worst(what: str, share: float) -> None:
+    WORST[what] = max(WORST.get(what, 0.0), float(share))
+
+
 def need_gpu():
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
@@ -39,9 +48,12 @@ def plain_logits(folder, tokens):
     return _plain_cache[key]
 
 
-def check_rows(rows, folder, requests, dtype):
-    """Every (request, position) row against the plain implementation."""
+def check_rows(rows, folder, requests, dtype, what: str | None = None):
+    """Every (request, position) row against the plain implementation.  Returns, and notes under ``what`` (by
+    default the running test's name), the largest error as a share of its bound."""
+    import os
     assert rows, "nothing was compared"
+    what = what or os.environ.get("PYTEST_CURRENT_TEST", "?").split("::")[-1].split(" (")[0]
     worst = 0.0
     for (name, pos), got_list in rows.items():
         ref = plain_logits(folder, requests[name])
@@ -55,4 +67,5 @@ def check_rows(rows, folder, requests, dtype):
                 bound = BF16_REL * np.abs(ref).max()
             worst = max(worst, err / bound)
             assert err <= bound, f"{name}@{pos} ({dtype}): max error {err:.3e} exceeds {bound:.3e}"
+    note_worst(f"{what} [{dtype}]", worst)
     return worst

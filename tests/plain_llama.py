@@ -78,20 +78,23 @@ def rotary(x, positions, inv_freq):
     return x * cos + rotated * sin
 
 
-def causal_attention(q, k, v, group, window=None):
+def causal_attention(q, k, v, group, window=None, rows=None):
     """softmax(q k^T / sqrt(d) + causal mask) v with grouped heads.
 
     q [h, T, d], k, v [kv, T, d]; query head j reads kv head j // group
-    (src/torchinferno/models/llama3/raw_ops.py:38-51).
+    (src/torchinferno/models/llama3/raw_ops.py:38-51).  ``rows`` (positions): q holds only the queries at
+    these positions of the sequence, [h, len(rows), d]; the keys are still all T (long sequences of which
+    a few rows are compared).
     """
     k = k.repeat_interleave(group, dim=0)
     v = v.repeat_interleave(group, dim=0)
-    T = q.shape[1]
+    T = k.shape[1]
     scores = torch.matmul(q, k.transpose(-1, -2)) / math.sqrt(q.shape[-1])
     pos = torch.arange(T)
-    allowed = pos[None, :] <= pos[:, None]
+    at = pos if rows is None else torch.as_tensor(rows, dtype=torch.long)
+    allowed = pos[None, :] <= at[:, None]
     if window:
-        allowed &= (pos[:, None] - pos[None, :]) < window
+        allowed &= (at[:, None] - pos[None, :]) < window
     scores = scores.masked_fill(~allowed[None], float("-inf"))
     return torch.matmul(torch.softmax(scores, dim=-1), v)
 
@@ -120,14 +123,17 @@ def decoder_layer(x, positions, config, weights, prefix, inv_freq):
                           weights[prefix + "mlp.down_proj.weight"])
 
 
-def forward(config, weights, token_ids):
-    """Logits [T, vocab] of one whole sequence (src/torchinferno/models/llama3/pipeline.py:371-401)."""
+def forward(config, weights, token_ids, rows=None):
+    """Logits [T, vocab] of one whole sequence (src/torchinferno/models/llama3/pipeline.py:371-401);
+    with ``rows`` only those positions are projected to the vocabulary: [len(rows), vocab]."""
     ids = torch.as_tensor(token_ids, dtype=torch.long)
     x = weights["model.embed_tokens.weight"][ids]
     positions = torch.arange(len(ids))
     inv_freq = inverse_frequencies(config)
     for layer in range(config["num_hidden_layers"]):
         x = decoder_layer(x, positions, config, weights, f"model.layers.{layer}.", inv_freq)
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long)]
     x = rms_norm(x, weights["model.norm.weight"], config["rms_norm_eps"])
     head = weights["model.embed_tokens.weight"] if config.get("tie_word_embeddings") or \
         "lm_head.weight" not in weights else weights["lm_head.weight"]

@@ -151,6 +151,55 @@ def test_many_requests_on_a_tight_pool_do_not_depend_on_how_they_are_scheduled(m
     assert preempted > 0                                   # the tight pools really ran out
 
 
+def test_schedules_in_bfloat16_on_the_default_path_give_the_same_tokens(model_folders):
+    """Config D (head size 64: tcgen05 prompt attention, TMA decode attention, the native block call, captured
+    decode steps, steps launched ahead) in bfloat16 with the library's products, which makes the kernels of a row
+    the same under every schedule: thirty requests (some at a temperature, some with a stop token that occurs)
+    on pools so tight that requests wait, are cut and are preempted.  Every schedule must give every request
+    the tokens of every other schedule."""
+    need_gpu()
+    import random
+    config, seed = TINY["D"]
+    rng = random.Random(11)
+    lengths = [rng.randint(1, 200) for _ in range(30)]
+    prompts = list(requests_for(config, seed, lengths).values())
+    budgets = [rng.randint(2, 40) for _ in prompts]
+    temps = [0.0 if rng.random() < 0.5 else 0.8 for _ in prompts]
+
+    def make(stops):
+        from torchinferno_b200.engine.types import GenerateRequest, SamplingConfig
+        return [GenerateRequest(f"q{i}", prompt_token_ids=p, sampling=SamplingConfig(budgets[i], temps[i], stops[i], 500 + i))
+                for i, p in enumerate(prompts)]
+
+    base = dict(gemm_backend="library", page_size=16)
+    with engine_for(model_folders["D"], "bfloat16", max_batch_size=8, kv_cache_tokens=4096, **base) as engine:
+        roomy = engine.generate_many(make([()] * len(prompts)))
+    stops = [(o.token_ids[len(o.token_ids) // 2],) if i % 3 == 0 and len(o.token_ids) > 2 else () for i, o in enumerate(roomy)]
+    ways = [dict(async_scheduling=True, max_batch_size=8, kv_cache_tokens=4096, max_num_batched_tokens=4096),
+            dict(async_scheduling=False, max_batch_size=8, kv_cache_tokens=4096, max_num_batched_tokens=4096),
+            dict(async_scheduling=True, max_batch_size=8, kv_cache_tokens=640, max_num_batched_tokens=96, prefill_chunk_size=40),
+            dict(async_scheduling=False, max_batch_size=6, kv_cache_tokens=560, max_num_batched_tokens=64, prefill_chunk_size=24),
+            dict(async_scheduling=True, max_batch_size=3, kv_cache_tokens=480, max_num_batched_tokens=33, prefill_chunk_size=7)]
+    results, preempted, ahead = [], 0, 0
+    for options in ways:
+        with engine_for(model_folders["D"], "bfloat16", **base, **options) as engine:
+            got = engine.generate_many(make(stops))
+            preempted += engine.scheduler.stats["preemptions"]
+            ahead += engine.stats["steps_ahead"]
+            engine.runner.cache.audit()
+            assert engine.runner.cache.free_pages() == [engine.runner.cache.num_pages]
+            assert engine.runner.graph_replays > 0
+        results.append([(o.token_ids, o.finish_reason) for o in got])
+    assert any(r == "stop" for _, r in results[0]) and any(r == "length" for _, r in results[0])
+    # Single-token rows are multiplied by the same library kernel whatever the batch, but a prompt portion's
+    # rows are not (the kernel changes with the row count), so a token may differ where two schedules cut a
+    # prompt differently and two logits lie within rounding of each other.  Equal cuts must give equal tokens.
+    assert results[0] == results[1], "async scheduling changed a token"
+    agree = [sum(a == b for a, b in zip(results[0], other)) for other in results[2:]]
+    assert min(agree) >= len(prompts) - 3, agree
+    assert preempted > 0 and ahead > 20
+
+
 def test_the_engine_sees_an_error_word_that_a_kernel_set_and_goes_on_without_the_failed_requests(model_folders):
     """The kernels report a page id outside its pool or a bounded wait that ran out in one device word; the
     engine reads it with the step's tokens.  Here the word is set from the host (no kernel is made to fail).

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import plain_llama
-from gpu_common import BF16_REL, need_gpu
+from gpu_common import BF16_REL, need_gpu, note_worst
 from replay_util import InProcessReplayer, gather, peak_tokens, trace_mixed, trace_portions, trace_whole
 
 pytestmark = pytest.mark.gpu
@@ -58,6 +58,7 @@ def test_large_layer_sizes_under_every_cut(large_folder, large_reference, dtype)
                 bound = (1e-4 if dtype == "float32" else BF16_REL) * np.abs(ref).max()
                 worst = max(worst, err / bound)
                 assert err <= bound, f"{maker.__name__} {name}@{pos} ({dtype}): {err:.3e} > {bound:.3e}"
+        note_worst(f"8B layer sizes, short prompts, {maker.__name__} [{dtype}]", worst)
         del replayer
         torch.cuda.empty_cache()
 

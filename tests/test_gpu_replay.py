@@ -97,6 +97,44 @@ def test_peaky_attention_shows_a_lost_key(model_folders, tmp_path):
         check_rows(gather(replayer.run(steps), index), folder, requests, "float32")
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_peaky_attention_in_bfloat16_on_the_tensor_core_kernels(model_folders, tmp_path, name):
+    """The same in bfloat16 at head sizes 64 and 128, where prompt portions run on the tcgen05 kernel and single
+    tokens on the TMA decode kernel, through the engine's own dispatch, block tables and context splits, whole,
+    in portions and mixed on a tight pool.  With nearly flat attention a lost key moves a logit by less than the
+    bfloat16 tolerance; with the scores spread it does not."""
+    need_gpu()
+    from safetensors.torch import load_file, save_file
+    import shutil
+    folder = tmp_path / "peaky"
+    shutil.copytree(model_folders[name], folder)
+    tensors = load_file(str(folder / "model.safetensors"))
+    for key in tensors:
+        if key.endswith("q_proj.weight") or key.endswith("k_proj.weight"):
+            tensors[key] = (tensors[key].float() * 8).to(torch.bfloat16)
+    save_file(tensors, str(folder / "model.safetensors"))
+    config, seed = TINY[name]
+    requests = requests_for(config, seed + 7, [300, 77, 130, 610, 64, 1000])
+    for maker in (trace_whole, trace_portions, trace_mixed):
+        steps, index = maker(requests)
+        replayer = InProcessReplayer(folder, "bfloat16", max_tokens=peak_tokens(steps))
+        check_rows(gather(replayer.run(steps), index), folder, requests, "bfloat16")
+
+
+def test_two_processes_write_the_same_bits(model_folders, tmp_path):
+    """bin/trace_run twice, in two processes, on the same trace in bfloat16 with the default choice of kernels:
+    the files are equal byte for byte (which kernel multiplies few rows is decided once per GPU model and shape
+    and kept beside the built library, not timed anew by every process)."""
+    need_gpu()
+    folder, requests = model_folders["D"], _requests("D")
+    steps, _ = trace_mixed(requests, seed=5)
+    first = run_trace_program(folder, "bfloat16", peak_tokens(steps), steps, tmp_path / "one")
+    second = run_trace_program(folder, "bfloat16", peak_tokens(steps), steps, tmp_path / "two")
+    assert first.keys() == second.keys() and len(first) > 10
+    for step in first:
+        assert np.array_equal(first[step], second[step]), f"step {step} differs between two processes"
+
+
 @pytest.mark.parametrize("backend", ["tcgen05", "library"])
 def test_bf16_projections_on_either_gemm_backend(model_folders, backend):
     """The hand-written tcgen05 products (swap-AB for few rows, 128 x 256 tiles for many) and cuBLAS

@@ -21,7 +21,7 @@ def _symbol():
     lib = load_library()
     fn = lib.tib_decode_attention_noalloc
     fn.restype = c_int
-    fn.argtypes = [c_void_p] * 7 + [c_int] * 6 + [c_int64, c_int, c_int, c_float, c_int, c_int, c_void_p]
+    fn.argtypes = [c_void_p] * 7 + [c_int] * 6 + [c_int64, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p]
     lib.tib_decode_attention_noalloc_need.restype = c_longlong
     lib.tib_decode_attention_noalloc_need.argtypes = [c_int] * 4
     lib.tib_decode_attention_noalloc_capacity.restype = c_longlong
@@ -53,10 +53,11 @@ def _call_noalloc(fn, q, pool, table, q_start, kv_start, slots, n, heads, kv_hea
     return rc, out
 
 
-def _raw_call(fn, q, pool, out, table, q_start, kv_start, slots, n, heads, kv_heads, d, splits, chunk):
+def _raw_call(fn, q, pool, out, table, q_start, kv_start, slots, n, heads, kv_heads, d, splits, chunk, longest=None):
+    longest = int(kv_start.max().item()) + 1 if longest is None else longest
     return fn(q.data_ptr(), pool.data_ptr(), out.data_ptr(), q_start.data_ptr(), kv_start.data_ptr(), slots.data_ptr(),
             table.data_ptr(), table.stride(0), n, heads, kv_heads, d, pool.shape[3], pool.stride(0), pool.shape[0], 0,
-            1.0 / math.sqrt(d), splits, chunk, torch.cuda.current_stream().cuda_stream)
+            1.0 / math.sqrt(d), splits, chunk, longest, torch.cuda.current_stream().cuda_stream)
 
 
 def test_noalloc_decode_attention_matches_the_ordinary_entry_point_twice_in_a_row():
@@ -97,5 +98,10 @@ def test_noalloc_decode_attention_refuses_what_does_not_fit():
     rc, out = _call_noalloc(fn, q, pool, table, q_start, kv_start, slots, n, heads, kv_heads, d, splits, 64)
     torch.cuda.synchronize()
     assert rc == -7 and torch.isnan(out).all()            # refused, nothing was launched
-    rc, _ = _call_noalloc(fn, q, pool, table, q_start, kv_start, slots, n, heads, kv_heads, 144, 1, 64)
+    rc, _ = _call_noalloc(fn, q, pool, table, q_start, kv_start, slots, n, heads, kv_heads, 144, 1, 128)
     assert rc == -2                                        # a head size the kernel is not built for (steps of 16 up to 128)
+    # parts that do not cover the longest context (70 keys in one part of 64) are refused, not run with keys left out
+    rc, out = _call_noalloc(fn, q, pool, table, q_start, kv_start, slots, n, heads, kv_heads, d, 1, 64)
+    assert rc == -2 and torch.isnan(out).all()
+    out = torch.full_like(q, float("nan"))
+    assert _raw_call(fn, q, pool, out, table, q_start, kv_start, slots, -1, heads, kv_heads, d, 2, 64) == -5

@@ -37,6 +37,9 @@ class EngineConfig:
     few_rows_choice: str = "measured"       # under "auto", which kernel multiplies few rows (decode steps): measured
                                             # once per GPU model and shape and kept on disk | swapab | library
 
+    profile_kernels: bool = False           # CUDA-event timers per kernel class around the layers' launches
+                                            # (InferenceEngine.kernel_times()); steps then run uncaptured
+
     def __post_init__(self) -> None:
         if self.cache_backend != "paged":
             raise ValueError(f"cache_backend={self.cache_backend!r}: only 'paged' exists in this engine")

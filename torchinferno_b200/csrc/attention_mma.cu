@@ -16,6 +16,7 @@
 // fetched by its own address.  Keys past a block's last query position are never read from memory
 // (they may be unwritten): their shared-memory rows are zero-filled, and they are masked.
 #include "mma.cuh"
+#include <mutex>
 
 namespace tib {
 
@@ -582,6 +583,8 @@ static float* noalloc_scratch_address(int* status) {
   // the device address must be asked for, once per device, with that device current.
   constexpr int kMaxDevices = 64;
   static float* address[kMaxDevices] = {nullptr};
+  static std::mutex guard;                 // (first calls from two host threads would otherwise race on the table)
+  std::lock_guard<std::mutex> lock(guard);
   int device = -1;
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) { *status = (int)e; return nullptr; }
@@ -605,15 +608,18 @@ TIB_API long long tib_decode_attention_noalloc_need(int n_entries, int heads, in
 TIB_API long long tib_decode_attention_noalloc_capacity(void) { return TIB_NOALLOC_SCRATCH_FLOATS; }
 
 // Same contract as tib_decode_attention, minus the two scratch pointers.  The caller passes inputs
-// and outputs; the partial results live in the library's own array (see above).
+// and outputs; the partial results live in the library's own array (see above).  max_kv_len is the
+// longest context of the batch (the largest kv_start + 1): a split that does not cover it is refused.
 TIB_API int tib_decode_attention_noalloc(const void* q, const void* pool, void* out, const int* q_start,
                                          const int* kv_start, const int* slots, const int* block_table,
                                          int table_stride, int n_entries, int heads, int kv_heads, int head_dim,
                                          int page_size, int64_t page_stride, int num_pages, int window, float scale,
-                                         int num_splits, int chunk, cudaStream_t stream) {
+                                         int num_splits, int chunk, int max_kv_len, cudaStream_t stream) {
   if (n_entries == 0) return TIB_OK;
-  if (!q || !pool || !out) return TIB_E_ARG;
+  if (!q || !pool || !out || n_entries < 0 || max_kv_len < 1) return TIB_E_ARG;
   if (num_splits < 1 || num_splits > 4096 || chunk < kBN || chunk % kBN != 0) return TIB_E_SIZE;
+  // the parts must cover the longest context: keys beyond num_splits * chunk would be left out without a sign
+  if ((long long)num_splits * chunk < (long long)max_kv_len) return TIB_E_SIZE;
   MmaAttnArgs a;
   int rc = fill_args(a, q_start, kv_start, slots, block_table, table_stride, heads, kv_heads, head_dim, page_size,
                      page_stride, num_pages, window, scale);

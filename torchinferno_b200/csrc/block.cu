@@ -14,6 +14,8 @@
 // `out` is left pending: the next block's (or the final) norm adds it
 // (src/torchinferno/models/llama3/pipeline.py:190-198; the pending add: tensor_parallel.py:7430-7435).
 #include "common.cuh"
+#include <mutex>
+#include <vector>
 
 extern "C" {
 int tib_add_rmsnorm(const void*, float*, const int*, const float*, void*, int, int, float, int, cudaStream_t);
@@ -80,6 +82,92 @@ struct TibPrenormBlockStep {
     if (rc__ != TIB_OK) return rc__; \
   } while (0)
 
+// --- optional timers per kernel class -------------------------------------------------------------------------
+// Off by default and free when off.  When on (tib_kernel_timers(1)), every launch of the block is bracketed by two
+// CUDA events on the launching stream; tib_kernel_timers_read() waits for the events recorded so far and adds
+// their elapsed times up by class (the reference keeps such per-class timers around its layer's launches:
+// src/torchinferno/models/llama3/tensor_parallel.py:4058-4069, 4462-4480).  Nothing is recorded while the
+// stream is being captured into a graph: a captured step has no per-kernel times, run it uncaptured to time it.
+namespace {
+enum KernelClass { KC_NORM, KC_QKV, KC_ROPE_APPEND, KC_ATTENTION_PREFILL, KC_ATTENTION_DECODE, KC_O, KC_GATE_UP, KC_SWIGLU, KC_DOWN, KC_COUNT };
+struct PendingTime { int kind; cudaEvent_t begin, end; };
+struct KernelTimers {
+  bool on = false;
+  std::mutex guard;
+  std::vector<PendingTime> pending;
+  std::vector<cudaEvent_t> spare;
+  double ms[KC_COUNT] = {0};
+  long long count[KC_COUNT] = {0};
+  cudaEvent_t event() {
+    if (!spare.empty()) { cudaEvent_t e = spare.back(); spare.pop_back(); return e; }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+  }
+};
+KernelTimers& timers() { static KernelTimers t; return t; }
+
+struct TimedScope {
+  int kind; cudaStream_t stream; cudaEvent_t begin = nullptr;
+  TimedScope(int k, cudaStream_t s) : kind(k), stream(s) {
+    KernelTimers& t = timers();
+    if (!t.on) return;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) return;
+    std::lock_guard<std::mutex> lock(t.guard);
+    begin = t.event();
+    if (begin) cudaEventRecord(begin, s);
+  }
+  ~TimedScope() {
+    if (!begin) return;
+    KernelTimers& t = timers();
+    std::lock_guard<std::mutex> lock(t.guard);
+    cudaEvent_t end = t.event();
+    if (end) cudaEventRecord(end, stream);
+    t.pending.push_back({kind, begin, end});
+  }
+};
+}  // namespace
+
+#define TIB_TIMED(kind, call)            \
+  do {                                   \
+    TimedScope scope__(kind, stream);    \
+    TIB_TRY(call);                       \
+  } while (0)
+
+// Switch the per-class timers on (1) or off (0); returns the setting before.
+TIB_API int tib_kernel_timers(int on) {
+  KernelTimers& t = timers();
+  std::lock_guard<std::mutex> lock(t.guard);
+  const int before = t.on ? 1 : 0;
+  t.on = on != 0;
+  return before;
+}
+
+// Waits for every pair of events recorded so far, adds the times up and copies the totals: ms[n], count[n] for the
+// classes in the order of KernelClass (norm, qkv, rope_append, attention_prefill, attention_decode, o, gate_up,
+// swiglu, down).  reset != 0 clears the totals afterwards.  Returns the number of classes.
+TIB_API int tib_kernel_timers_read(double* ms, long long* count, int n, int reset) {
+  KernelTimers& t = timers();
+  std::lock_guard<std::mutex> lock(t.guard);
+  for (const PendingTime& p : t.pending) {
+    float elapsed = 0.f;
+    if (p.end && cudaEventSynchronize(p.end) == cudaSuccess && cudaEventElapsedTime(&elapsed, p.begin, p.end) == cudaSuccess) {
+      t.ms[p.kind] += elapsed;
+      t.count[p.kind] += 1;
+    }
+    t.spare.push_back(p.begin);
+    if (p.end) t.spare.push_back(p.end);
+  }
+  t.pending.clear();
+  for (int i = 0; i < KC_COUNT && i < n; ++i) {
+    if (ms) ms[i] = t.ms[i];
+    if (count) count[i] = t.count[i];
+  }
+  if (reset) for (int i = 0; i < KC_COUNT; ++i) { t.ms[i] = 0; t.count[i] = 0; }
+  return KC_COUNT;
+}
+
 // out[n, N] = x[n, K] . w^T, w stored [N, K] or (kn) [K, N]: the hand-written swap-AB kernel up to few_rows rows, else the library.
 static int project(const void* x, const void* w, void* out, int n, int N, int K, int kn, int few_rows, int* error_word,
                    cudaStream_t stream) {
@@ -100,17 +188,17 @@ TIB_API int tib_prenorm_gqa_glu_block(const TibPrenormBlockWeights* w, const Tib
   const int qkv_width = (h + 2 * k) * d, q_width = h * d;
   const bool packed = page_stride == (int64_t)2 * k * page_size * d;
 
-  TIB_TRY(tib_add_rmsnorm(pending, s->residual, nullptr, w->norm_mixer, s->normed, n, w->hidden, w->eps_mixer, TIB_BF16, stream));
-  TIB_TRY(project(s->normed, w->qkv, s->qkv, n, qkv_width, w->hidden, w->qkv_kn, w->qkv_few_rows, s->error_word, stream));
-  TIB_TRY(tib_rope_append(s->qkv, s->q, pool, s->positions, s->token_slot, block_table, table_stride, w->inv_freq, n, h, k, d,
+  TIB_TIMED(KC_NORM, tib_add_rmsnorm(pending, s->residual, nullptr, w->norm_mixer, s->normed, n, w->hidden, w->eps_mixer, TIB_BF16, stream));
+  TIB_TIMED(KC_QKV, project(s->normed, w->qkv, s->qkv, n, qkv_width, w->hidden, w->qkv_kn, w->qkv_few_rows, s->error_word, stream));
+  TIB_TIMED(KC_ROPE_APPEND, tib_rope_append(s->qkv, s->q, pool, s->positions, s->token_slot, block_table, table_stride, w->inv_freq, n, h, k, d,
                           w->rot_dim, w->interleaved, page_size, page_stride, num_pages, 1, s->error_word, TIB_BF16, stream));
   if (s->n_multi) {
     if (packed && tib_prefill_attention_tcgen05_supports(d, group, page_size))
-      TIB_TRY(tib_prefill_attention_tcgen05(s->q, pool, s->attn, s->q_start, s->kv_start, s->slots, block_table, table_stride,
+      TIB_TIMED(KC_ATTENTION_PREFILL, tib_prefill_attention_tcgen05(s->q, pool, s->attn, s->q_start, s->kv_start, s->slots, block_table, table_stride,
                                             s->n_entries, s->max_q_len, n, h, k, d, page_size, page_stride, num_pages, window,
                                             w->scale, s->n_single > 0, s->error_word, stream));
     else
-      TIB_TRY(tib_prefill_attention(s->q, pool, s->attn, s->q_start, s->kv_start, s->slots, block_table, table_stride,
+      TIB_TIMED(KC_ATTENTION_PREFILL, tib_prefill_attention(s->q, pool, s->attn, s->q_start, s->kv_start, s->slots, block_table, table_stride,
                                     s->n_entries, s->max_q_len, h, k, d, page_size, page_stride, num_pages, window, w->scale,
                                     s->n_single > 0, stream));
   }
@@ -120,21 +208,21 @@ TIB_API int tib_prenorm_gqa_glu_block(const TibPrenormBlockWeights* w, const Tib
     float* scratch_ml = splits > 1 ? s->split_scratch + (size_t)s->n_entries * h * splits * d : nullptr;
     if (splits > 1 && !scratch_o) return TIB_E_ARG;
     if (packed && tib_decode_attention_tma_supports(d, group, page_size))
-      TIB_TRY(tib_decode_attention_tma(s->q, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots, block_table,
+      TIB_TIMED(KC_ATTENTION_DECODE, tib_decode_attention_tma(s->q, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots, block_table,
                                        table_stride, s->n_entries, h, k, d, page_size, page_stride, num_pages, window, w->scale,
                                        splits, 0, splits > 1 ? s->split_counters : nullptr, s->error_word, stream));
     else
-      TIB_TRY(tib_decode_attention(s->q, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots, block_table,
+      TIB_TIMED(KC_ATTENTION_DECODE, tib_decode_attention(s->q, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots, block_table,
                                    table_stride, s->n_entries, h, k, d, page_size, page_stride, num_pages, window, w->scale,
                                    splits, 0, stream));
   }
-  TIB_TRY(project(s->attn, w->o, s->o_out, n, w->hidden, q_width, w->o_kn, w->o_few_rows, s->error_word, stream));
-  TIB_TRY(tib_add_rmsnorm(s->o_out, s->residual, nullptr, w->norm_feed_forward, s->normed, n, w->hidden, w->eps_feed_forward,
+  TIB_TIMED(KC_O, project(s->attn, w->o, s->o_out, n, w->hidden, q_width, w->o_kn, w->o_few_rows, s->error_word, stream));
+  TIB_TIMED(KC_NORM, tib_add_rmsnorm(s->o_out, s->residual, nullptr, w->norm_feed_forward, s->normed, n, w->hidden, w->eps_feed_forward,
                           TIB_BF16, stream));
   const int inter = w->intermediate;
-  TIB_TRY(project(s->normed, w->gate_up, s->gate_up, n, 2 * inter, w->hidden, w->gate_up_kn, w->gate_up_few_rows, s->error_word,
+  TIB_TIMED(KC_GATE_UP, project(s->normed, w->gate_up, s->gate_up, n, 2 * inter, w->hidden, w->gate_up_kn, w->gate_up_few_rows, s->error_word,
                   stream));
-  TIB_TRY(tib_swiglu(s->gate_up, s->act, n, inter, TIB_BF16, stream));
-  TIB_TRY(project(s->act, w->down, s->out, n, w->hidden, inter, w->down_kn, w->down_few_rows, s->error_word, stream));
+  TIB_TIMED(KC_SWIGLU, tib_swiglu(s->gate_up, s->act, n, inter, TIB_BF16, stream));
+  TIB_TIMED(KC_DOWN, project(s->act, w->down, s->out, n, w->hidden, inter, w->down_kn, w->down_few_rows, s->error_word, stream));
   return TIB_OK;
 }

@@ -26,8 +26,9 @@ extern "C" {
  *   pool          one layer's pages [num_pages][2][kv_heads][page_size][head_dim] bf16
  *   q_start       [n_entries + 1] first token row of each entry; kv_start [n_entries] position of that
  *                 token; slots [n_entries] row of block_table; block_table [rows][table_stride] page ids
- *   num_splits, chunk   the context is cut into num_splits parts of chunk keys (a multiple of 64);
- *                 num_splits * chunk must cover the longest context
+ *   num_splits, chunk   the context is cut into num_splits parts of chunk keys (a multiple of 64)
+ *   max_kv_len    the longest context of the batch (the largest kv_start + 1); num_splits * chunk must
+ *                 cover it, or the call is refused with -2 (keys beyond the parts would be left out)
  *
  * A call needs n_entries * heads * num_splits * (head_dim + 2) floats of the array (none when
  * num_splits is 1); more than tib_decode_attention_noalloc_capacity() is refused with -7.
@@ -40,7 +41,7 @@ int tib_decode_attention_noalloc(const void* q, const void* pool, void* out, con
                                  const int* kv_start, const int* slots, const int* block_table,
                                  int table_stride, int n_entries, int heads, int kv_heads, int head_dim,
                                  int page_size, int64_t page_stride, int num_pages, int window, float scale,
-                                 int num_splits, int chunk, cudaStream_t stream);
+                                 int num_splits, int chunk, int max_kv_len, cudaStream_t stream);
 
 /* Floats of the built-in array a call would use, and how many it holds. */
 long long tib_decode_attention_noalloc_need(int n_entries, int heads, int head_dim, int num_splits);

@@ -23,7 +23,7 @@ from torchinferno_b200.engine.batch import StepEntry
 from torchinferno_b200.engine.factory import load_model, make_runner
 from torchinferno_b200.engine.runner import StepError
 from torchinferno_b200.engine.scheduler import Scheduler, SchedulerRequest, StepPlan, TokenEvent, UNKNOWN_TOKEN
-from torchinferno_b200.kernels import gemm
+from torchinferno_b200.kernels import gemm, ops
 from torchinferno_b200.engine.types import GenerateOutput, GenerateRequest, SamplingConfig, TokenOutput, Usage
 from torchinferno_b200.sampling.sampler import Sampler, SamplingParams
 
@@ -69,7 +69,9 @@ class InferenceEngine:
             num_pages = -(-tokens // config.page_size) + config.max_batch_size
         self.runner = make_runner(model, page_size=config.page_size, num_pages=num_pages,
                                   max_requests=config.max_batch_size, max_request_tokens=limit, check_errors=False)
-        self.runner.use_cuda_graphs = config.use_cuda_graphs
+        self.runner.use_cuda_graphs = config.use_cuda_graphs and not config.profile_kernels
+        if config.profile_kernels:
+            ops.set_kernel_timers(True)
         gemm.set_backend(config.gemm_backend)
         self.scheduler = Scheduler(self.runner.cache, max_batch_size=config.max_batch_size,
                                    max_step_tokens=config.max_num_batched_tokens,
@@ -104,9 +106,16 @@ class InferenceEngine:
     def __exit__(self, *exc) -> None:
         self.close()
 
+    def kernel_times(self, reset: bool = False) -> dict[str, dict[str, float]]:
+        """With ``profile_kernels``: milliseconds and launches per kernel class of the layers run so far (norm, qkv,
+        rope_append, attention_prefill, attention_decode, o, gate_up, swiglu, down); and the step counters."""
+        return {**ops.read_kernel_timers(reset), "counters": dict(self.runner.counters)}
+
     def close(self) -> None:
         if self._closed:
             return
+        if self.config.profile_kernels:
+            ops.set_kernel_timers(False)
         for request_id in list(self._requests):
             self.cancel(request_id)
         self._ahead = None

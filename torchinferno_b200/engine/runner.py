@@ -61,6 +61,10 @@ class ModelRunner:
         self.check_errors = check_errors
         self.last_batch: StepBatch | None = None
         self.steps = 0
+        # what the steps so far did, and the last one alone (same keys): tokens run, pages taken from and given
+        # back to the pools, bytes copied to the device, steps that replayed a captured graph
+        self.counters = {"steps": 0, "tokens": 0, "pages_taken": 0, "pages_freed": 0, "h2d_bytes": 0, "graph_steps": 0}
+        self.last_step: dict[str, int] = {}
         # a part that walks the step's entries on the host cannot be captured: no graph for such a model
         self.use_cuda_graphs = use_cuda_graphs
         self._graph_ok = model.capturable()
@@ -114,6 +118,7 @@ class ModelRunner:
 
         placements: list[EntryPlacement] = []
         row = 0
+        free_before = cache.free_pages()
         for entry in entries:
             if entry.request_id not in cache:
                 cache.open(entry.request_id, seed=entry.seed, temperature=entry.temperature)
@@ -129,13 +134,25 @@ class ModelRunner:
             if index.numel():
                 ops.scatter_i32(target, index, value)
         self.last_batch = batch
+        free_mid = cache.free_pages()
         logits = self.model.forward(batch, cache)
         for entry in entries:
             cache.release_behind_window(entry.request_id)
         self.steps += 1
+        self._count(batch, free_before, free_mid, False)
         if self.check_errors:
             self.raise_on_device_error()
         return logits
+
+    def _count(self, batch: StepBatch, free_before: list[int], free_mid: list[int], graph: bool) -> None:
+        """Per-step counters: ``free_before`` / ``free_mid`` are the free pages before the step took its pages and
+        after (before windows gave pages back)."""
+        free_after = self.cache.free_pages()
+        self.last_step = {"steps": 1, "tokens": batch.n_tokens, "pages_taken": sum(b - m for b, m in zip(free_before, free_mid)),
+                          "pages_freed": sum(a - m for a, m in zip(free_after, free_mid)), "h2d_bytes": batch.h2d_bytes,
+                          "graph_steps": int(graph)}
+        for key, value in self.last_step.items():
+            self.counters[key] += value
 
     # ------------------------------------------------------- decode graphs
     def _apply_table_updates(self) -> int:
@@ -217,6 +234,7 @@ class ModelRunner:
         n = len(entries)
         g = self._graph_for(n)
         starts = []
+        free_before = cache.free_pages()
         for entry in entries:
             if entry.request_id not in cache:
                 cache.open(entry.request_id, seed=entry.seed, temperature=entry.temperature)
@@ -228,10 +246,12 @@ class ModelRunner:
         g.batch.h2d_bytes = self._set_slots(g, slots) + self._apply_table_updates()
         g.batch.entries = [EntryPlacement(e.request_id, s, i, 1, st) for i, (e, s, st) in enumerate(zip(entries, slots, starts))]
         self.last_batch = g.batch
+        free_mid = cache.free_pages()
         logits = self._run_decode_graph(g)
         for entry in entries:
             cache.release_behind_window(entry.request_id)
         self.steps += 1
+        self._count(g.batch, free_before, free_mid, True)
         if self.check_errors:
             self.raise_on_device_error()
         return logits

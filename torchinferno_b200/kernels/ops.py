@@ -40,6 +40,23 @@ def set_dependent_launch(on: bool) -> bool:
     return bool(lib().tib_set_dependent_launch(c_int(1 if on else 0)))
 
 
+KERNEL_CLASSES = ("norm", "qkv", "rope_append", "attention_prefill", "attention_decode", "o", "gate_up", "swiglu", "down")
+
+
+def set_kernel_timers(on: bool) -> bool:
+    """CUDA-event timers around every launch of a natively issued block, by kernel class (off by default; a step
+    captured in a graph records nothing).  Returns the setting before."""
+    return bool(lib().tib_kernel_timers(c_int(1 if on else 0)))
+
+
+def read_kernel_timers(reset: bool = False) -> dict[str, dict[str, float]]:
+    """{class: {"ms": total, "launches": n}} of what the timers have recorded; waits for the recorded events."""
+    n = len(KERNEL_CLASSES)
+    ms, counts = (ctypes.c_double * n)(), (ctypes.c_longlong * n)()
+    lib().tib_kernel_timers_read(ms, counts, c_int(n), c_int(1 if reset else 0))
+    return {name: {"ms": float(ms[i]), "launches": int(counts[i])} for i, name in enumerate(KERNEL_CLASSES)}
+
+
 def count_launches(n: int) -> None:
     """Launches made by a native call that issues several kernels."""
     _counter["launches"] += n
@@ -98,6 +115,7 @@ def lib() -> ctypes.CDLL:
                    "tib_attention_mma_supports", "tib_prefill_attention", "tib_decode_attention",
                    "tib_prefill_attention_tcgen05", "tib_prefill_attention_tcgen05_supports",
                    "tib_decode_attention_tma", "tib_decode_attention_tma_supports", "tib_set_dependent_launch",
+                   "tib_kernel_timers", "tib_kernel_timers_read",
                    "tib_blas_init", "tib_blas_gemm", "tib_gemm_tcgen05_2cta", "tib_gemm_tcgen05_2cta_supports",
                    "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
                    "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports"):
