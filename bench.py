@@ -4,10 +4,12 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
 One JSON line on stdout.  ``value`` is decoded tokens a second at batch 8 (device-timed over exactly K
-decode steps after W warm-up steps, prompts of 2,048 random ids, decoding on from there); ``e2e`` is the
-same through the Python entry point with host tokens in and out; ``prefill`` is one 2,048-token prompt;
-``points`` holds decoding at batch 1 and 64; ``roofline`` relates the decode step to the measured HBM
-bandwidth.  Weights are random (N(0, 0.02), norm weights 1) and token ids synthetic: there is no
+decode steps after W warm-up steps, prompts of 2,048 random ids, decoding on from there; when K is small the
+K steps are timed several times over, decoding on, and the median counts); ``e2e`` is the same through the
+Python entry point with host tokens in and out; ``prefill`` is one 2,048-token prompt; ``points`` holds
+decoding at batch 1 and 64 and the two serving workloads of the smaller sizes (64 mixed requests at the
+Llama-3.2-1B sizes, 16 long-context requests at the Llama-3.2-3B sizes) through the Python entry point;
+``roofline`` relates the decode step to the measured HBM bandwidth.  Weights are random (N(0, 0.02), norm weights 1) and token ids synthetic: there is no
 network for checkpoints or datasets.  Several GPUs are not supported: one line says so, exit code 2.
 
 The reference has no single-GPU Llama-3.1-8B number; its own harness times ``generate`` on random
@@ -154,8 +156,14 @@ def prefill_requests(runner, ids, prompts, chunk: int) -> list[int]:
     return first
 
 
+REPEAT_TARGET_STEPS = 240     # a run of fewer timed steps than this is repeated (decoding on) until it has as many
+MAX_REPEATS = 15
+
+
 def timed_decode(runner, batch: int, steps: int, warmup: int, numbers: dict, sampler, seed: int) -> dict:
-    """Prefill ``batch`` prompts, then time exactly ``steps`` device-side decode steps."""
+    """Prefill ``batch`` prompts, then time exactly ``steps`` device-side decode steps; a short run is repeated
+    from where the last repeat ended and the median repeat counts (a region of 70 ms is at the mercy of one
+    clock change)."""
     import torch
     from torchinferno_b200.kernels import ops
     vocab = runner.model.spec.vocab_size
@@ -167,24 +175,31 @@ def timed_decode(runner, batch: int, steps: int, warmup: int, numbers: dict, sam
     drawn = runner.decode_loop(ids, first, warmup, temperature=temps, seeds=seeds)   # captures the graph too
     torch.cuda.synchronize()
     last = drawn[-1].tolist() if warmup else first
+    room = CONTEXT + PAGE_SIZE - 1 - PROMPT_LEN - warmup
+    repeats = max(1, min(MAX_REPEATS, -(-REPEAT_TARGET_STEPS // steps), room // steps))
     start_context = PROMPT_LEN + warmup
-    launches_before, replays_before = ops.launch_count(), runner.graph_replays
     mark = sampler.mark()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    begin.record()
-    runner.decode_loop(ids, last, steps, temperature=temps, seeds=seeds)
-    end.record()
-    sampler.snap()                   # (the steps are launched, not finished: the GPU is at work on them)
-    torch.cuda.synchronize()
-    ms = begin.elapsed_time(end)
+    runs = []
+    for r in range(repeats):
+        launches_before, replays_before = ops.launch_count(), runner.graph_replays
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        drawn = runner.decode_loop(ids, last, steps)
+        end.record()
+        sampler.snap()                   # (the steps are launched, not finished: the GPU is at work on them)
+        torch.cuda.synchronize()
+        last = drawn[-1].tolist()
+        graph = runner._graphs[batch]
+        launches = (ops.launch_count() - launches_before) + (runner.graph_replays - replays_before) * graph.launches
+        runs.append((begin.elapsed_time(end), start_context + r * steps, launches))
     clocks = sampler.summary(mark, sampler.mark())
-    graph = runner._graphs[batch]
-    launches = (ops.launch_count() - launches_before) + (runner.graph_replays - replays_before) * graph.launches
-    mean_context = start_context + (steps + 1) / 2            # cached tokens a step reads, on average
+    ms, context, launches = sorted(runs)[len(runs) // 2]          # the median repeat, with its own contexts
+    mean_context = context + (steps + 1) / 2                      # cached tokens a step reads, on average
     step_bytes = numbers["matmul_params"] * 2 + batch * mean_context * numbers["kv_bytes_per_token"]
     runner.end(ids)
     return {"batch": batch, "steps": steps, "ms": ms, "ms_per_step": ms / steps, "tokens_per_s": batch * steps / (ms / 1e3),
-            "context_from": start_context, "context_to": start_context + steps, "step_bytes": step_bytes,
+            "context_from": context, "context_to": context + steps, "step_bytes": step_bytes, "repeats": repeats,
+            "repeat_ms": [round(m, 3) for m, _, _ in runs],
             "achieved_gbs": step_bytes / (ms / steps / 1e3) / 1e9, "launches": launches, "clocks": clocks}
 
 
@@ -254,6 +269,74 @@ def timed_e2e(model, batch: int, steps: int, warmup: int, seed: int) -> dict:
             "steps_launched_ahead": engine.stats["steps_ahead"] - ahead0}
 
 
+# The two serving workloads of the smaller sizes (the fourth and fifth configurations of BASELINE.json), run
+# through InferenceEngine as a user would: requests in, tokens out, continuous batching in between.
+WORKLOADS = {
+    "mixed_1b": dict(preset="llama-3.2-1b.json", requests=64, prompt_min=16, prompt_max=2048, new_tokens=256, temperature=0.0),
+    "long_3b": dict(preset="llama-3.2-3b.json", requests=16, prompt_min=8192, prompt_max=8192, new_tokens=512, temperature=0.7),
+}
+
+
+def timed_workload(name: str, peaks: dict, gemm_backend: str) -> dict:
+    """Output tokens a second of one workload, the split of its steps (those that carry prompt portions, those
+    that only decode) and, for the decode steps, the bytes they must read (every weight once, the cache of the
+    running requests) over their time.  The harness of the reference for such runs:
+    src/torchinferno/benchmarks/torchinferno_llama.py:58-437."""
+    import torch
+    from torchinferno_b200.config.engine_config import EngineConfig
+    from torchinferno_b200.engine.engine import InferenceEngine
+    from torchinferno_b200.engine.factory import random_model
+    from torchinferno_b200.engine.types import GenerateRequest, SamplingConfig
+    w = WORKLOADS[name]
+    config = json.loads((ROOT / "torchinferno_b200" / "config" / "presets" / w["preset"]).read_text())
+    model = random_model(config, seed=0, dtype="bfloat16")
+    longest = w["prompt_max"] + w["new_tokens"]
+    engine = InferenceEngine(model, EngineConfig(
+        model="<in memory>", dtype="bfloat16", page_size=PAGE_SIZE, max_batch_size=w["requests"], gemm_backend=gemm_backend,
+        max_model_len=longest + PAGE_SIZE, kv_cache_tokens=w["requests"] * (longest + PAGE_SIZE)))
+    g = torch.Generator().manual_seed(17)
+    weight_bytes, kv_bytes = model.weight_bytes(), engine.runner.cache.kv_bytes_per_token()
+    result = {}
+    for it in range(2):                                   # (the first pass warms up: graphs are captured, kernels chosen)
+        lengths = torch.randint(w["prompt_min"], w["prompt_max"] + 1, (w["requests"],), generator=g).tolist()
+        for i, n in enumerate(lengths):
+            engine.submit(GenerateRequest(f"{name}-{it}-{i}", prompt_token_ids=torch.randint(0, model.spec.vocab_size, (n,), generator=g).tolist(),
+                                          sampling=SamplingConfig(w["new_tokens"], w["temperature"], (), 1000 + i)))
+        split = {"prefill": [0, 0.0], "decode": [0, 0.0]}
+        decode_bytes, tokens = 0, 0
+        torch.cuda.synchronize()
+        begin = last = time.perf_counter()
+        while engine.scheduler.has_work():
+            sched, cache = engine.scheduler, engine.runner.cache
+            prefilling = bool(sched.waiting) or any(r.prefilling for r in sched.running)
+            held = sum(cache.length(r.request_id) for r in sched.running if r.request_id in cache)
+            tokens += sum(1 for e in engine.step() if e.token is not None)
+            now = time.perf_counter()
+            kind = "prefill" if prefilling else "decode"
+            split[kind][0] += 1
+            split[kind][1] += now - last
+            if not prefilling:
+                decode_bytes += weight_bytes + held * kv_bytes
+            last = now
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - begin
+        split["decode"][1] += time.perf_counter() - last
+        decode_seconds = max(split["decode"][1], 1e-9)
+        result = {name: round(tokens / seconds, 1), f"{name}_seconds": round(seconds, 3),
+                  f"{name}_prompt_tokens": sum(lengths), f"{name}_output_tokens": tokens,
+                  f"{name}_prefill_steps": split["prefill"][0],
+                  f"{name}_prefill_ms_per_step": round(1e3 * split["prefill"][1] / max(1, split["prefill"][0]), 3),
+                  f"{name}_decode_steps": split["decode"][0],
+                  f"{name}_decode_ms_per_step": round(1e3 * decode_seconds / max(1, split["decode"][0]), 3),
+                  f"{name}_decode_gbs": round(decode_bytes / decode_seconds / 1e9, 1),
+                  f"{name}_decode_hbm_frac": round(decode_bytes / decode_seconds / 1e9 / peaks["hbm_gbs"], 4),
+                  f"{name}_preemptions": engine.scheduler.stats["preemptions"]}
+    engine.close()
+    del engine, model
+    torch.cuda.empty_cache()
+    return result
+
+
 def run_ours(args) -> dict:
     import torch
     from torchinferno_b200.engine.factory import make_runner, random_model
@@ -283,6 +366,10 @@ def run_ours(args) -> dict:
         del runner
         torch.cuda.empty_cache()
         e2e = timed_e2e(model, args.batch, min(args.steps, args.e2e_steps or args.steps), args.warmup, seed=4)
+        del model
+        torch.cuda.empty_cache()
+        for name in args.workloads:
+            points.update(timed_workload(name, peaks, args.gemm_backend))
     sampler.stop()
     peak_flops = peaks["bf16_tflops"] * 1e12
     record = {
@@ -297,6 +384,7 @@ def run_ours(args) -> dict:
             "context_to": main["context_to"], "page_size": PAGE_SIZE, "parallelism": "single GPU",
             "l2": "inputs larger than L2 (weights of a step: %.1f GB)" % (numbers["matmul_params"] * 2 / 1e9),
             "peaks": peaks["source"], "gemm_backend": args.gemm_backend,
+            "repeats": "%d runs of %d steps, decoding on; the median run counts" % (main["repeats"], args.steps),
         },
         "clocks": main["clocks"],
         "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
@@ -358,18 +446,37 @@ def run_reference(args) -> dict:
             e.record()
             torch.cuda.synchronize()
             return b.elapsed_time(e)
+        # end to end, as a caller of generate() meets it: the prompts start in pinned host memory and the
+        # generated ids end in host memory, inside the timed region
+        host_prompts = prompts.cpu().pin_memory()
+        def timed_e2e(new_tokens):
+            torch.cuda.synchronize()
+            b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            b.record()
+            out = model.generate(host_prompts.to("cuda", non_blocking=True), max_new_tokens=new_tokens, temperature=0.0)
+            ids = out[:, PROMPT_LEN:].cpu()
+            e.record()
+            torch.cuda.synchronize()
+            return b.elapsed_time(e), ids.numel() * ids.element_size()
         for _ in range(max(1, min(args.warmup, 3))):
             timed(2)
         mark = sampler.mark()
         short = timed(1)
         long = timed(1 + args.steps)
+        e2e_short, _ = timed_e2e(1)
+        e2e_long, out_bytes = timed_e2e(1 + args.steps)
         clocks = sampler.summary(mark, sampler.mark())
     sampler.stop()
     ms = long - short
+    e2e_ms = e2e_long - e2e_short
     return {"metric": METRIC, "value": round(args.batch * args.steps / (ms / 1e3), 1), "unit": "tok/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights",
             "impl": "reference", "clocks": clocks,
+            "e2e": {"value": round(args.batch * args.steps / (e2e_ms / 1e3), 1), "unit": "tok/s", "ms_per_step": round(e2e_ms / args.steps, 4),
+                    "h2d_bytes_per_step": round(host_prompts.numel() * host_prompts.element_size() / (1 + args.steps), 1),
+                    "d2h_bytes_per_step": round(out_bytes / (1 + args.steps), 1),
+                    "how": "generate() with the prompts in pinned host memory and the new ids read back, (1 + steps) new tokens minus 1"},
             "config": {"model": "Llama-3.1-8B sizes", "layers": args.layers, "layers_of_model": FULL_LAYERS,
                        "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
                        "path": "Llama3PipelineForCausalLM.generate (dense cache, torch ops)"},
@@ -389,6 +496,8 @@ def main(argv=None) -> int:
     parser.add_argument("--point-steps", type=int, default=None, help="decode steps of the other batch sizes (default: --steps)")
     parser.add_argument("--e2e-steps", type=int, default=None, help="steps of the end-to-end run (default: --steps, the same contexts)")
     parser.add_argument("--gemm-backend", choices=["auto", "tcgen05", "library"], default="auto")
+    parser.add_argument("--workloads", nargs="*", default=list(WORKLOADS), choices=list(WORKLOADS),
+                        help="serving workloads of the smaller sizes to add to points")
     args = parser.parse_args(argv)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:

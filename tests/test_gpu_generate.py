@@ -304,22 +304,29 @@ def test_seeded_temperature_generation_fp32(model_folders):
     assert len({o.token_ids for o in together}) == 5
 
 
-@pytest.mark.parametrize("name", ["A", "C"])
+@pytest.mark.parametrize("name", ["A", "C", "D"])
 def test_greedy_generation_bf16_follows_the_plain_logits(model_folders, name):
     """In bfloat16 a near-tie may go the other way, so each generated token is checked against the plain
-    logits of the engine's own prefix: it must be within the bf16 tolerance of the best."""
+    logits of the engine's own prefix: it is the plain implementation's own choice nearly always, and where it
+    is not, it is one of the plain implementation's three best and its logit is within the engine's own
+    error bound (twice the bfloat16 tolerance: one for either logit) of the best."""
     need_gpu()
     config, seed = TINY[name]
     prompts = list(requests_for(config, seed, [7, 13, 1, 60]).values())
     cfg, weights = plain_llama.read_model_folder(model_folders[name])
     with engine_for(model_folders[name], "bfloat16", page_size=16) as engine:
         outs = engine.generate_many(requests(prompts, 10))
+    same = total = 0
     for prompt, out in zip(prompts, outs):
         ids = list(prompt) + list(out.token_ids)
         logits = plain_llama.forward(cfg, weights, ids[:-1]).numpy()
         for i, tok in enumerate(out.token_ids):
             row = logits[len(prompt) + i - 1]
             assert row[tok] >= row.max() - 2 * BF16_REL * np.abs(logits).max()
+            assert tok in np.argsort(row)[-3:], (tok, np.argsort(row)[-3:])
+            same += int(tok == int(row.argmax()))
+            total += 1
+    assert same >= 0.85 * total, f"only {same} of {total} tokens are the plain implementation's choice"
 
 
 def test_preemption_on_a_small_pool_does_not_change_the_tokens(model_folders):

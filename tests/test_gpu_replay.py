@@ -111,10 +111,32 @@ def test_peaky_attention_in_bfloat16_on_the_tensor_core_kernels(model_folders, t
     tensors = load_file(str(folder / "model.safetensors"))
     for key in tensors:
         if key.endswith("q_proj.weight") or key.endswith("k_proj.weight"):
-            tensors[key] = (tensors[key].float() * 8).to(torch.bfloat16)
+            tensors[key] = (tensors[key].float() * 4).to(torch.bfloat16)
     save_file(tensors, str(folder / "model.safetensors"))
     config, seed = TINY[name]
     requests = requests_for(config, seed + 7, [300, 77, 130, 610, 64, 1000])
+    # What a lost key would cost here: the plain logits with one early key hidden from every later query leave the
+    # true ones by many times the tolerance (measured: 20 times; with the unscaled weights it is under one).  The
+    # scale is as large as bfloat16 allows: queries and keys rounded to 8 bits move a score by score / 256, and at
+    # four times the scale of the weights that alone takes 0.4 of the tolerance, at six times more than all of it.
+    import plain_llama
+    from gpu_common import BF16_REL, plain_logits
+    true_attention = plain_llama.causal_attention
+
+    def one_key_lost(q, k, v, group, window=None, rows=None):
+        out = true_attention(q, k, v, group, window, rows)
+        if k.shape[1] > 40:                              # queries after position 5 do not see key 5
+            keep = [i for i in range(k.shape[1]) if i != 5]
+            out[:, 6:] = true_attention(q[:, 6:], k[:, keep], v[:, keep], group, None, rows=range(5, k.shape[1] - 1))
+        return out
+    cfg, weights = plain_llama.read_model_folder(folder)
+    truth = plain_logits(folder, requests["r0"])
+    plain_llama.causal_attention = one_key_lost
+    try:
+        lossy = plain_llama.forward(cfg, weights, requests["r0"]).numpy()
+    finally:
+        plain_llama.causal_attention = true_attention
+    assert np.abs(lossy - truth).max() > 5 * BF16_REL * np.abs(truth).max()
     for maker in (trace_whole, trace_portions, trace_mixed):
         steps, index = maker(requests)
         replayer = InProcessReplayer(folder, "bfloat16", max_tokens=peak_tokens(steps))

@@ -45,9 +45,10 @@ def _case(n, heads, kv_heads, d, page, contexts, seed):
 
 def _call_noalloc(fn, q, pool, table, q_start, kv_start, slots, n, heads, kv_heads, d, splits, chunk):
     out = torch.full_like(q, float("nan"))
+    longest = int(kv_start.max().item()) + 1
     torch.cuda.synchronize()
     allocations = torch.cuda.memory_stats()["allocation.all.allocated"]
-    rc = _raw_call(fn, q, pool, out, table, q_start, kv_start, slots, n, heads, kv_heads, d, splits, chunk)
+    rc = _raw_call(fn, q, pool, out, table, q_start, kv_start, slots, n, heads, kv_heads, d, splits, chunk, longest)
     torch.cuda.synchronize()
     assert torch.cuda.memory_stats()["allocation.all.allocated"] == allocations     # torch's allocator was not entered
     return rc, out

@@ -255,6 +255,8 @@ def tune_few_rows() -> dict[tuple, int]:
     for w in list(_undecided):
         groups.setdefault((w.out_features, w.in_features, w.tensor.device), []).append(w)
     _undecided.clear()
+    if groups:
+        ops.lib()                 # (loads, and at the first call builds, the library the decisions are kept beside)
     try:
         for key, group in groups.items():
             if key not in _tuned:
