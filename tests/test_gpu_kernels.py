@@ -179,31 +179,81 @@ def test_gemm_tcgen05_swapab(m, n, k, splits, w_kn):
 
 
 def test_few_rows_kernel_is_chosen_by_measurement_and_either_choice_is_right():
-    """Weights that leave their few-rows kernel open get it from tune_few_rows (the swap-AB kernel up to 0, 4, 8, 16, 32
-    or 64 rows): one decision per shape, kept for the process, the same for every weight of the shape; a slice of the weight inherits it; and whichever kernel
-    was chosen, and whichever is forced, the product is right at few and at many rows."""
+    """Weights that leave their few-rows kernel open get it from tune_few_rows (the hand-written kernel up to 0, 4, 8,
+    16, 32 or 64 rows, with the tile width and K split that measured fastest): one decision per shape, kept for the
+    process and on disk, the same for every weight of the shape; a slice of the weight inherits it; whichever kernel
+    was chosen, and whichever is forced, the product is right at few and at many rows; and so is silu(gate) * up
+    of a weight bound with the SwiGLU epilogue, fused or not."""
     need_gpu()
     from torchinferno_b200.kernels import gemm
-    from torchinferno_b200.kernels.gemm import LinearWeight, linear
+    from torchinferno_b200.kernels.gemm import LinearWeight, linear, linear_swiglu
     n, k = 1160, 2048
     ws = [rnd(n, k, dtype=torch.bfloat16, scale=0.05, seed=i) for i in range(3)]
     open_weights = [LinearWeight(dev(w), few_rows_tcgen05=None) for w in ws]
     assert all(w.few_rows == 0 for w in open_weights)                     # the library until measured
     decisions = gemm.tune_few_rows()
-    key = (n, k, open_weights[0].tensor.device)
-    assert decisions[key] in (0, 4, 8, 16, 32, 64) and all(w.few_rows == decisions[key] for w in open_weights)
+    key = (n, k, open_weights[0].tensor.device, "none")
+    rows, features, splits = decisions[key]
+    assert rows in (0, 4, 8, 16, 32, 64) and features in (128, 256) and 0 <= splits <= 8
+    assert all((w.few_rows, w.features, w.splits) == decisions[key] for w in open_weights)
     later = LinearWeight(dev(ws[0]), few_rows_tcgen05=None)
     assert gemm.tune_few_rows()[key] == decisions[key] and later.few_rows == open_weights[0].few_rows
+    gemm._tuned.pop(key)                                                   # a new process reads what this one stored
+    again = LinearWeight(dev(ws[0]), few_rows_tcgen05=None)
+    assert gemm.tune_few_rows()[key] == decisions[key] and again.splits == splits
     forced = [LinearWeight(dev(ws[0]), few_rows_tcgen05=True), LinearWeight(dev(ws[0]), few_rows_tcgen05=False)]
     assert [w.few_rows for w in forced] == [LinearWeight.FEW_ROWS, 0] and LinearWeight.FEW_ROWS == 64
+    configured = LinearWeight(dev(ws[0]), few_rows_tcgen05=True)
+    configured.features, configured.splits = 128, 4
+    glu = [LinearWeight(dev(ws[0][:1152]), few_rows_tcgen05=flag, epilogue="swiglu") for flag in (True, False)]
+    glu[0].splits = 1
     for m in (1, 4, 5, 8, 9, 16, 17, 33, 64, 65, 200):
         x = rnd(m, k, dtype=torch.bfloat16, seed=50 + m)
         want = x.double() @ ws[0].double().T
-        for weight in (open_weights[0], later, *forced):
+        for weight in (open_weights[0], later, configured, *forced):
             out = linear(dev(x), weight)
             assert (as_ref(out) - want).abs().max() <= 1e-2 * want.abs().max() + 1e-6
             part = linear(dev(x), weight.rows(64, 1096))
             assert (as_ref(part) - want[:, 64:1096]).abs().max() <= 1e-2 * want.abs().max() + 1e-6
+        gate, up = want[:, 0:1152:2], want[:, 1:1152:2]
+        act = gate / (1 + torch.exp(-gate)) * up
+        for weight in glu:
+            got = linear_swiglu(dev(x), weight)
+            assert got.shape == (m, 576) and (as_ref(got) - act).abs().max() <= 1.5e-2 * act.abs().max() + 1e-6
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 256, 64), (8, 6144, 4096), (16, 28672, 4096), (5, 1000, 4096), (33, 520, 192), (64, 4096, 4096)])
+def test_gemm_decode_every_tile_width_split_and_epilogue(m, n, k):
+    """The few-rows kernel on [in, out] weights: tiles of 128 features with K shared by 1 to 8 blocks of a cluster,
+    tiles of 256 features unsplit, bf16 and fp32 results, and the SwiGLU epilogue on interleaved gate/up columns,
+    against float64; NaN in the output buffer beforehand shows what was not written."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    x, w = rnd(m, k, dtype=torch.bfloat16), rnd(k, n, dtype=torch.bfloat16, scale=0.05, seed=3)
+    want = x.double() @ w.double()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ran = 0
+    for features in (128, 256):
+        for splits in (1, 2, 3, 5, 8):
+            if not ops.gemm_decode_supports(m, n, k, features, splits):
+                continue
+            for out_dtype in (torch.bfloat16, torch.float32):
+                out = ops.gemm_decode(dev(x), dev(w), torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda"),
+                                      features=features, splits=splits, error_word=err)
+                bound = (1e-2 if out_dtype == torch.bfloat16 else 1e-4) * want.abs().max() + 1e-6
+                assert (as_ref(out) - want).abs().max() <= bound, (features, splits, out_dtype)
+                ran += 1
+        if n % 16 == 0:
+            gate, up = want[:, 0::2], want[:, 1::2]
+            act = gate / (1 + torch.exp(-gate)) * up
+            out = ops.gemm_decode(dev(x), dev(w), torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device="cuda"),
+                                  features=features, splits=1, epilogue=ops.DG_SWIGLU, error_word=err)
+            assert (as_ref(out) - act).abs().max() <= 1e-2 * act.abs().max() + 1e-6
+    assert ran >= 4 and int(err) == 0
+    assert not ops.gemm_decode_supports(65, n, k) and not ops.gemm_decode_supports(m, n, k, 256, 2)
+    assert not ops.gemm_decode_supports(m, n, k, 128, 2, ops.DG_SWIGLU) and not ops.gemm_decode_supports(m, n, k + 8)
+    with pytest.raises(ops.KernelError, match="size"):
+        ops.gemm_decode(dev(x), dev(w), torch.empty(m, n, dtype=torch.bfloat16, device="cuda"), features=256, splits=2)
 
 
 def _records(rows):

@@ -31,7 +31,9 @@ def test_random_folder_has_every_tensor_and_loads(tmp_path):
     assert block.mixer.qkv_weight.tensor.shape == ((4 + 2 * 2) * 16, 64) and block.mixer.qkv_weight.dtype == torch.bfloat16
     assert torch.equal(block.mixer.qkv_weight.tensor[:64], tensors["model.layers.0.self_attn.q_proj.weight"])
     assert torch.equal(block.mixer.qkv_weight.tensor[64:96], tensors["model.layers.0.self_attn.k_proj.weight"])
-    assert torch.equal(block.feed_forward.gate_up_weight.tensor[128:], tensors["model.layers.0.mlp.up_proj.weight"])
+    # (gate and up rows are interleaved: row 2i = gate i, row 2i + 1 = up i)
+    assert torch.equal(block.feed_forward.gate_up_weight.tensor[1::2], tensors["model.layers.0.mlp.up_proj.weight"])
+    assert torch.equal(block.feed_forward.gate_up_weight.tensor[0::2], tensors["model.layers.0.mlp.gate_proj.weight"])
     assert block.mixer_norm.weight.dtype == torch.float32          # vectors are widened
     assert model.head is not model.embedding
 

@@ -137,9 +137,11 @@ __global__ void rmsnorm_t_kernel(const T* __restrict__ x, const float* __restric
 }
 
 // ------------------------------------------------------------------- SwiGLU
+// gate_up rows hold either all gates, then all ups (interleaved 0), or gate i and up i side by side (interleaved 1:
+// the layout in which one tile of a fused gate/up product holds both).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter,
-                              int64_t total) {
+                              int64_t total, int interleaved) {
   pdl_wait();
   pdl_trigger();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -147,8 +149,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     const int64_t row = i / inter;
     const int col = (int)(i - row * inter);
     const T* src = gate_up + row * 2 * (int64_t)inter;
-    const float g = to_f32(src[col]);
-    const float u = to_f32(src[inter + col]);
+    const float g = to_f32(interleaved ? src[2 * col] : src[col]);
+    const float u = to_f32(interleaved ? src[2 * col + 1] : src[inter + col]);
     out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
   }
 }
@@ -159,23 +161,34 @@ __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.f +
 
 // bf16, intermediate width a multiple of 8: 16-byte loads and stores.
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
-                                     int inter, int64_t total_vec) {
+                                     int inter, int64_t total_vec, int interleaved) {
   pdl_wait();
   pdl_trigger();
   const int per_row = inter >> 3;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t row = i / per_row;
     const int col = (int)(i - row * per_row) << 3;
-    const __nv_bfloat16* src = gate_up + row * 2 * (int64_t)inter + col;
-    const uint4 graw = *reinterpret_cast<const uint4*>(src), uraw = *reinterpret_cast<const uint4*>(src + inter);
-    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
-    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+    const __nv_bfloat16* src = gate_up + row * 2 * (int64_t)inter + (interleaved ? 2 * col : col);
+    // eight (gate, up) pairs: two vectors of gates and of ups, or two vectors of pairs
+    const uint4 a = *reinterpret_cast<const uint4*>(src), b = *reinterpret_cast<const uint4*>(src + (interleaved ? 8 : inter));
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
     uint4 packed;
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+    if (interleaved) {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-      o2[k] = __floats2bfloat162_rn(silu_fast(g.x) * u.x, silu_fast(g.y) * u.y);
+      for (int k = 0; k < 2; ++k) {
+        const float2 p0 = __bfloat1622float2(a2[2 * k]), p1 = __bfloat1622float2(a2[2 * k + 1]);
+        const float2 q0 = __bfloat1622float2(b2[2 * k]), q1 = __bfloat1622float2(b2[2 * k + 1]);
+        o2[k] = __floats2bfloat162_rn(silu_fast(p0.x) * p0.y, silu_fast(p1.x) * p1.y);
+        o2[2 + k] = __floats2bfloat162_rn(silu_fast(q0.x) * q0.y, silu_fast(q1.x) * q1.y);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 g = __bfloat1622float2(a2[k]), u = __bfloat1622float2(b2[k]);
+        o2[k] = __floats2bfloat162_rn(silu_fast(g.x) * u.x, silu_fast(g.y) * u.y);
+      }
     }
     *reinterpret_cast<uint4*>(out + row * (int64_t)inter + col) = packed;
   }
@@ -279,7 +292,7 @@ TIB_API int tib_rmsnorm(const void* x, const float* weight, void* out, int n_row
   return TIB_OK;
 }
 
-TIB_API int tib_swiglu(const void* gate_up, void* out, int n_rows, int inter, int dtype,
+TIB_API int tib_swiglu(const void* gate_up, void* out, int n_rows, int inter, int dtype, int interleaved,
                        cudaStream_t stream) {
   const int64_t total = (int64_t)n_rows * inter;
   if (total == 0) return TIB_OK;
@@ -287,12 +300,12 @@ TIB_API int tib_swiglu(const void* gate_up, void* out, int n_rows, int inter, in
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == TIB_F32)
-    TIB_LAUNCH_DEPENDENT(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, inter, total);
+    TIB_LAUNCH_DEPENDENT(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, inter, total, interleaved);
   else if (dtype == TIB_BF16 && inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
     const int64_t vec = total / 8, want_v = (vec + threads - 1) / threads;
-    TIB_LAUNCH_DEPENDENT(swiglu_bf16x8_kernel, (int)(want_v < 148 * 16 ? want_v : 148 * 16), threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, vec);
+    TIB_LAUNCH_DEPENDENT(swiglu_bf16x8_kernel, (int)(want_v < 148 * 16 ? want_v : 148 * 16), threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, vec, interleaved);
   } else if (dtype == TIB_BF16)
-    TIB_LAUNCH_DEPENDENT(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+    TIB_LAUNCH_DEPENDENT(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total, interleaved);
   else
     return TIB_E_DTYPE;
   TIB_LAUNCH_CHECK();

@@ -15,6 +15,7 @@
 //
 // The reference sends these products to cuBLAS (src/torchinferno/models/llama3/tensor_parallel.py:11176-11198).
 #include "tcgen05.cuh"
+#include "cluster.cuh"
 
 namespace tib {
 
@@ -201,44 +202,6 @@ constexpr int kSwRedRows = 136;                   // splits * ceil(128 / splits)
 // their way (6 to 8 stages of 18 KB on each of 135 to 148 SMs) stream fastest; with 11 stages the same loop was
 // 5 % slower, with 3 stages 15 %.  (At more rows a stage is larger and fewer fit.)
 constexpr int sw_stages(int npad) { return npad <= 16 ? 7 : npad <= 32 ? 8 : npad <= 48 ? 6 : 5; }
-
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ uint32_t cluster_size() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-// Arrive on an mbarrier of another block of the cluster (address from map_to_cta); what this thread wrote
-// before is visible to whoever then waits with cluster scope.
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-    if (i > 64) __nanosleep(32);
-  }
-  return false;
-}
 
 // NPAD: rows of x padded to a multiple of 16 (16, 32, 48 or 64).  WKN: w is stored [K, N] (the layout the library
 // prefers at few rows), so a slice of it is an MN-major A operand: two boxes of 64 features x 64 k.
@@ -456,20 +419,6 @@ gemm_tcgen05_swapab_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 }
 
 // ------------------------------------------------------------------ host side
-// A [rows, K] bf16 matrix with row stride ld (elements), read in boxes of box_rows x 64 with 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int64_t ld, int box_rows) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return TIB_E_ARG;
-  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)kTcBK, (cuuint32_t)box_rows};
-  const cuuint32_t elem[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? TIB_OK : TIB_E_ARG;
-}
-
 }  // namespace tib
 
 using namespace tib;

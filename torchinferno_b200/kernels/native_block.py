@@ -21,7 +21,9 @@ from torchinferno_b200.kernels.gemm import LinearWeight
 class BlockWeights(Structure):
     _fields_ = [(name, c_int) for name in ("hidden", "heads", "kv_heads", "head_dim", "intermediate", "rot_dim", "interleaved",
                                            "qkv_kn", "o_kn", "gate_up_kn", "down_kn",
-                                           "qkv_few_rows", "o_few_rows", "gate_up_few_rows", "down_few_rows")] + \
+                                           "qkv_few_rows", "o_few_rows", "gate_up_few_rows", "down_few_rows",
+                                           "qkv_features", "o_features", "gate_up_features", "down_features",
+                                           "qkv_splits", "o_splits", "gate_up_splits", "down_splits")] + \
                [(name, c_float) for name in ("eps_mixer", "eps_feed_forward", "scale")] + \
                [(name, c_void_p) for name in ("norm_mixer", "norm_feed_forward", "inv_freq", "qkv", "o", "gate_up", "down")]
 
@@ -81,6 +83,11 @@ def block_weights(block) -> BlockWeights | None:
     auto = gemm.get_backend() == "auto"
     w.qkv_few_rows, w.o_few_rows = (m.few_rows if auto else 0 for m in (mixer.qkv_weight, mixer.o_weight))
     w.gate_up_few_rows, w.down_few_rows = (m.few_rows if auto else 0 for m in (ffn.gate_up_weight, ffn.down_weight))
+    for name, m in (("qkv", mixer.qkv_weight), ("o", mixer.o_weight), ("gate_up", ffn.gate_up_weight), ("down", ffn.down_weight)):
+        setattr(w, name + "_features", m.features)
+        setattr(w, name + "_splits", m.splits)
+    if ffn.gate_up_weight.epilogue != "swiglu":
+        return None
     w.eps_mixer, w.eps_feed_forward, w.scale = n1.eps, n2.eps, mixer.scale
     w.norm_mixer, w.norm_feed_forward = n1.weight.data_ptr(), n2.weight.data_ptr()
     return w
@@ -136,5 +143,6 @@ def run_block(w: BlockWeights, stream_state, ctx, window: int | None) -> None:
     # this library's own kernels among them: two norms, rotary, SwiGLU, one or two attention kernels, and the
     # projections that the swap-AB kernel takes (the library products are not counted)
     own_products = sum(1 for rows in (w.qkv_few_rows, w.o_few_rows, w.gate_up_few_rows, w.down_few_rows) if 0 < batch.n_tokens <= rows)
-    ops.count_launches(5 + (1 if batch.n_single and batch.n_multi else 0) + own_products)
+    fused_swiglu = 0 < batch.n_tokens <= w.gate_up_few_rows and w.gate_up_splits == 1 and w.gate_up_kn
+    ops.count_launches(5 - int(fused_swiglu) + (1 if batch.n_single and batch.n_multi else 0) + own_products)
     stream_state.pending = ws.buffers["out"]

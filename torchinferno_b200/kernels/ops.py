@@ -118,7 +118,7 @@ def lib() -> ctypes.CDLL:
                    "tib_kernel_timers", "tib_kernel_timers_read",
                    "tib_blas_init", "tib_blas_gemm", "tib_gemm_tcgen05_2cta", "tib_gemm_tcgen05_2cta_supports",
                    "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
-                   "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports"):
+                   "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports", "tib_gemm_decode", "tib_gemm_decode_supports"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
     return library
@@ -172,14 +172,15 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out = silu(gate_up[:, :I]) * gate_up[:, I:], silu and product in fp32."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
+    """out = silu(gate) * up, silu and product in fp32; a row of ``gate_up`` holds the I gates, then the I ups,
+    or (``interleaved``) gate i and up i side by side."""
     _need(gate_up, "gate_up"), _need(out, "out", gate_up.dtype)
     n, two_i = gate_up.shape
     if two_i % 2 or out.shape != (n, two_i // 2):
         raise KernelError("swiglu: shapes do not fit")
     _check("swiglu", lib().tib_swiglu(_ptr(gate_up), _ptr(out), c_int(n), c_int(two_i // 2),
-                                      c_int(_code(gate_up.dtype)), _stream()))
+                                      c_int(_code(gate_up.dtype)), c_int(int(interleaved)), _stream()))
     return out
 
 
@@ -562,6 +563,32 @@ def gemm_tcgen05_swapab(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err
     _check("gemm_tcgen05_swapab", lib().tib_gemm_tcgen05_swapab(
         _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)), c_int64(w.stride(0)),
         c_int64(out.stride(0)), c_int(int(w_kn)), c_int(_code(out.dtype)), c_int(splits), _ptr(error_word), _stream()))
+    return out
+
+
+DG_PLAIN, DG_SWIGLU = 0, 1
+
+
+def gemm_decode_supports(m: int, n: int, k: int, features: int = 128, splits: int = 1, epilogue: int = DG_PLAIN) -> bool:
+    return bool(lib().tib_gemm_decode_supports(c_int(m), c_int(n), c_int(k), c_int(features), c_int(splits), c_int(epilogue)))
+
+
+def gemm_decode(x: torch.Tensor, w_kn: torch.Tensor, out: torch.Tensor, *, features: int = 128, splits: int = 1,
+                epilogue: int = DG_PLAIN, error_word: torch.Tensor | None = None) -> torch.Tensor:
+    """The product of a decode step, out[M, N] = x[M, K] . w for M <= 64 with ``w_kn`` stored [K, N]: tiles of
+    ``features`` (128 or 256) features streamed by TMA, K shared by ``splits`` blocks of a cluster.  With the SwiGLU
+    epilogue ``w_kn`` holds gate and up columns interleaved and ``out`` is the activation [M, N / 2]."""
+    for name, t in (("x", x), ("w_kn", w_kn)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gemm_decode: {name} must be a 2-D bf16 CUDA tensor with unit inner stride")
+    _need(out, "out")
+    (m, k), (k2, n) = x.shape, w_kn.shape
+    if k != k2 or out.shape != (m, n // 2 if epilogue == DG_SWIGLU else n):
+        raise KernelError(f"gemm_decode: shapes {tuple(x.shape)} x {tuple(w_kn.shape)} -> {tuple(out.shape)} do not fit")
+    _check("gemm_decode", lib().tib_gemm_decode(
+        _ptr(x), _ptr(w_kn), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)), c_int64(w_kn.stride(0)),
+        c_int64(out.stride(0)), c_int(_code(out.dtype)), c_int(features), c_int(splits), c_int(epilogue), _ptr(error_word),
+        _stream()))
     return out
 
 

@@ -1,7 +1,9 @@
 """SwiGLU feed-forward: down(silu(gate(x)) * up(x)).
 
-gate and up run as one product on cat(Wg, Wu) split at (I, I), gate first
-(src/torchinferno/models/llama3/tensor_parallel.py:4398, 3170);
+gate and up run as one product (src/torchinferno/models/llama3/tensor_parallel.py:4398, 3170 concatenates
+them, gate first); here their rows are interleaved instead (row 2i = gate i, row 2i + 1 = up i), so that one
+tile of the product holds both and the few-rows kernel of a decode step can apply the activation in its
+epilogue;
 silu(g) = g / (1 + exp(-g)) with g in fp32
 (src/torchinferno/kernels/triton_ops.py:29-32); no bias
 (src/torchinferno/models/llama3/pipeline.py:247-250).
@@ -13,7 +15,7 @@ from typing import Mapping
 import torch
 
 from torchinferno_b200.kernels import ops
-from torchinferno_b200.kernels.gemm import LinearWeight, linear
+from torchinferno_b200.kernels.gemm import LinearWeight, linear, linear_swiglu
 from torchinferno_b200.parts.base import FeedForward, LayerContext, WeightSpec, register_part
 
 
@@ -35,14 +37,12 @@ class SwiGLUFeedForward(FeedForward):
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         g, u, d = self.names
-        self.gate_up_weight = LinearWeight(torch.cat([weights[g], weights[u]], dim=0), few_rows_tcgen05=None)
+        pairs = torch.stack([weights[g], weights[u]], dim=1).reshape(2 * self.intermediate_size, self.hidden_size)
+        self.gate_up_weight = LinearWeight(pairs, few_rows_tcgen05=None, epilogue="swiglu")
         self.down_weight = LinearWeight(weights[d], few_rows_tcgen05=None)
 
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
-        gate_up = linear(x, self.gate_up_weight)
-        act = torch.empty((x.shape[0], self.intermediate_size), dtype=gate_up.dtype, device=x.device)
-        ops.swiglu(gate_up, act)
-        return linear(act, self.down_weight)
+        return linear(linear_swiglu(x, self.gate_up_weight), self.down_weight)
 
 
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)
