@@ -199,8 +199,8 @@ def test_few_rows_kernel_is_chosen_by_measurement_and_either_choice_is_right():
     later = LinearWeight(dev(ws[0]), few_rows_tcgen05=None)
     assert gemm.tune_few_rows()[key] == decisions[key] and later.few_rows == open_weights[0].few_rows
     gemm._tuned.pop(key)                                                   # a new process reads what this one stored
-    again = LinearWeight(dev(ws[0]), few_rows_tcgen05=None)
-    assert gemm.tune_few_rows()[key] == decisions[key] and again.splits == splits
+    again = [LinearWeight(dev(w), few_rows_tcgen05=None) for w in ws]      # (as many weights of the shape as were measured)
+    assert gemm.tune_few_rows()[key] == decisions[key] and again[0].splits == splits
     forced = [LinearWeight(dev(ws[0]), few_rows_tcgen05=True), LinearWeight(dev(ws[0]), few_rows_tcgen05=False)]
     assert [w.few_rows for w in forced] == [LinearWeight.FEW_ROWS, 0] and LinearWeight.FEW_ROWS == 64
     configured = LinearWeight(dev(ws[0]), few_rows_tcgen05=True)
@@ -608,6 +608,48 @@ def test_tma_decode_attention_finds_one_far_key(standout):
     out, ref = attention_case(torch.bfloat16, 8, 2, 64, 16, entries, seed=5, standout=standout, kernel="tma")
     assert ref.abs().max() > 3
     assert torch.allclose(out.double(), ref, atol=6e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("heads, kv_heads, d, page, rot, inter", [(8, 2, 128, 16, 128, False), (4, 2, 64, 8, 64, False), (32, 8, 128, 16, 128, False),
+                                                                  (6, 1, 64, 32, 32, True), (4, 4, 128, 64, 0, False), (3, 1, 64, 16, 48, False)])
+def test_tma_decode_attention_that_rotates_and_stores_the_newest_token_itself(heads, kv_heads, d, page, rot, inter):
+    """One kernel from the rows of the qkv product (rotary encoding of q and k, the write of k and v into their pages,
+    attention) gives bit for bit what the rotary kernel followed by the attention kernel gives: the same output and
+    the same pages, with contexts that end at the first and last slot of a page and of a tile, and with 1, 4 and 16
+    context parts."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    contexts = [1, 2, 64, 65, 16, 17, 700, 128, 333, 1000]
+    n = len(contexts)
+    pool, table, slots = paged_layout(n, contexts, page, kv_heads, d, torch.bfloat16, seed=9)
+    for e, c in enumerate(contexts):                                  # older keys and values; the newest slot stays NaN
+        if c > 1:
+            fill_pages(pool, table, slots[e], rnd(kv_heads, c - 1, d, dtype=torch.bfloat16, seed=e), rnd(kv_heads, c - 1, d, dtype=torch.bfloat16, seed=40 + e))
+    qkv = rnd(n, (heads + 2 * kv_heads) * d, dtype=torch.bfloat16, seed=77)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / max(rot, 1)))) if rot else torch.zeros(0)
+    i32 = lambda xs: dev(torch.tensor(xs, dtype=torch.int32))
+    q_start, kv_start, slot_t, table_d = i32(list(range(n + 1))), i32([c - 1 for c in contexts]), i32(slots), dev(table)
+    scale = 1.0 / math.sqrt(d)
+    for splits in (1, 4, 16):
+        pool_a, pool_b = dev(pool), dev(pool)
+        q_rot = torch.empty(n, heads * d, dtype=torch.bfloat16, device="cuda")
+        ops.rope_append(dev(qkv), q_rot, pool_a, kv_start, slot_t, table_d, dev(inv_freq), heads, kv_heads, d, rot_dim=rot, interleaved=inter)
+        want = ops.decode_attention(q_rot, pool_a, torch.empty_like(q_rot), q_start, kv_start, slot_t, table_d, n, heads, kv_heads, d,
+                                    scale, max(contexts), num_splits=splits, chunk=0, kernel="tma")
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        got = ops.decode_attention_rope(dev(qkv), pool_b, torch.full_like(q_rot, float("nan")), q_start, kv_start, slot_t, table_d, n,
+                                        heads, kv_heads, d, scale, max(contexts), dev(inv_freq), rot_dim=rot, interleaved=inter,
+                                        num_splits=splits, error_word=err)
+        torch.cuda.synchronize()
+        assert int(err) == 0 and torch.isfinite(got).all()
+        assert torch.equal(got, want), (splits, (got.float() - want.float()).abs().max())
+        a, b = pool_a.cpu(), pool_b.cpu()
+        assert torch.equal(torch.isnan(a), torch.isnan(b)) and torch.equal(torch.nan_to_num(a), torch.nan_to_num(b))
+    bad = table.clone()
+    bad[slots[6], 699 // page] = pool.shape[0] + 3                    # a page id outside the pool is reported, not written
+    ops.decode_attention_rope(dev(qkv), dev(pool), torch.empty_like(q_rot), q_start, kv_start, slot_t, dev(bad), n, heads, kv_heads, d,
+                              scale, max(contexts), dev(inv_freq), rot_dim=rot, interleaved=inter, error_word=err)
+    assert int(err) != 0
 
 
 def test_tma_decode_attention_refuses_other_shapes():

@@ -39,6 +39,13 @@ struct DtArgs {
   int chunk, num_splits;
   int* counters;         // [entries * kv_heads] zeros: the parts of a split context count themselves in; or null
   int* error_word;
+  // The kernel rotates and stores the newest token itself (ROPE): q points at the unrotated rows of the qkv
+  // product (q_stride elements apart; k at column heads * D, v behind it), which the kernel before wrote.
+  int q_stride;
+  const float* inv_freq;  // [rot_dim / 2]
+  int rot_dim, interleaved;
+  __nv_bfloat16* pool;    // this layer's pages, to write the newest key and value into
+  int64_t page_stride;
 };
 
 template <int D>
@@ -49,7 +56,8 @@ struct DtSmem {
   static constexpr uint32_t kStage = 2 * kKV;
   static constexpr uint32_t kReduce = sizeof(float) * (kDtConsumers * 16 * D + kDtConsumers * 16 * 2);
   static constexpr uint32_t kData = kStages * kStage > kReduce ? kStages * kStage : kReduce;
-  static constexpr uint32_t kTotal = 1024 + kData + 16 * kStages;
+  static constexpr uint32_t kRope = 16 * D * 2 + 2 * D * 4;       // rotated queries [16][D] bf16; cos, sin of the position, twice
+  static constexpr uint32_t kTotal = 1024 + kData + 16 * kStages + kRope;
 };
 
 // Address of element (row, col) of a tile half-by-half in the TMA's 128-byte swizzle: the 16-byte chunk
@@ -68,7 +76,12 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
 
 // grid: (num_splits, kv_heads, n_entries).  partial_o: [entries][heads][splits][D] fp32, partial_ml:
 // [entries][heads][splits][2] fp32 (max in log2 units, sum).
-template <int D>
+// ROPE: q holds the unrotated rows of the qkv product.  The four consumer warps rotate the group's queries into
+// shared memory (each part of a context does: four heads cost less than a trip to memory), and in the block
+// whose part holds the newest position the producer warp rotates that token's key, writes key and value into
+// their page and only then has the tile copied (a proxy fence between its stores and the copy); no kernel
+// between the qkv product and this one.  Same arithmetic as rope_append_kernel (rope_kv.cu).
+template <int D, bool ROPE>
 __global__ void __launch_bounds__(kDtThreads)
 decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bfloat16* __restrict__ q,
                             float* __restrict__ partial_o, float* __restrict__ partial_ml,
@@ -85,6 +98,9 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;     // the swizzle pattern repeats every 1024 bytes
   unsigned char* smem_gen = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bars = base + L::kData;
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_gen + L::kData + 16 * STAGES);   // [16][D]
+  float* cs_s = reinterpret_cast<float*>(q_s + 16 * D);                                        // consumers' cos | sin
+  float* cs_p = cs_s + D;                                                                      // the producer's own
   auto full = [&](int s) { return bars + 8u * s; };
   auto empty = [&](int s) { return bars + 8u * (STAGES + s); };
   auto k_s = [&](int s) { return base + (uint32_t)s * L::kStage; };
@@ -152,6 +168,43 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
       if (!waited && key0 + kDtBN > pos) {   // the tile that holds the newest token
         pdl_wait();
         waited = true;
+        if constexpr (ROPE) {
+          // this part holds the newest position: its key (rotated) and value go into their page first
+          const int page_new = __ldg(table + (pos >> a.page_shift));
+          if (page_new < 0 || page_new >= a.num_pages) {
+            if (a.error_word && lane == 0) atomicExch(a.error_word, 1 + entry);
+          } else {
+            const int half = a.rot_dim >> 1;
+            for (int i = lane; i < half; i += 32) {
+              float sn, cn;
+              sincosf((float)pos * a.inv_freq[i], &sn, &cn);
+              cs_p[i] = cn;
+              cs_p[half + i] = sn;
+            }
+            __syncwarp();
+            const __nv_bfloat16* ksrc = q + (size_t)row0 * a.q_stride + (size_t)(a.heads + kvh) * D;
+            const __nv_bfloat16* vsrc = ksrc + (size_t)a.kv_heads * D;
+            __nv_bfloat16* kdst = a.pool + (size_t)page_new * a.page_stride + ((size_t)kvh * a.page_size + (pos & (a.page_size - 1))) * D;
+            __nv_bfloat16* vdst = kdst + (size_t)a.kv_heads * a.page_size * D;
+            for (int i = lane; i < D / 2; i += 32) {
+              if (i < half) {
+                const int ia = a.interleaved ? 2 * i : i, ib = a.interleaved ? 2 * i + 1 : i + half;
+                const float lo = __bfloat162float(ksrc[ia]), hi = __bfloat162float(ksrc[ib]);
+                kdst[ia] = __float2bfloat16_rn(rope_lo(lo, hi, cs_p[i], cs_p[half + i]));
+                kdst[ib] = __float2bfloat16_rn(rope_hi(lo, hi, cs_p[i], cs_p[half + i]));
+              } else {
+                const int ia = a.rot_dim + 2 * (i - half);
+                kdst[ia] = ksrc[ia];
+                kdst[ia + 1] = ksrc[ia + 1];
+              }
+            }
+            for (int i = lane; i < D / 8; i += 32)
+              reinterpret_cast<uint4*>(vdst)[i] = reinterpret_cast<const uint4*>(vsrc)[i];
+            // the copy below reads these stores through the async proxy
+            asm volatile("fence.proxy.async;\n" ::: "memory");
+            __syncwarp();
+          }
+        }
       }
       int page = -1;
       if (lane < pages_per_tile) {
@@ -186,10 +239,37 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
     const int cw = warp - 1;                    // which 16 keys of every tile
     const int g_row = lane >> 2, tig = lane & 3;
     pdl_wait();
-    // Q fragments straight from global memory: row g_row of the A operand is head head0 + g_row
+    if constexpr (ROPE) {
+      // the group's queries, rotated, into shared memory: 128 threads, a pair of dims each per pass
+      const int ct = threadIdx.x - 32, half = a.rot_dim >> 1;
+      for (int i = ct; i < half; i += 32 * kDtConsumers) {
+        float sn, cn;
+        sincosf((float)pos * a.inv_freq[i], &sn, &cn);
+        cs_s[i] = cn;
+        cs_s[half + i] = sn;
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kDtConsumers) : "memory");
+      for (int w = ct; w < nrows * (D / 2); w += 32 * kDtConsumers) {
+        const int r = w / (D / 2), i = w - r * (D / 2);
+        const __nv_bfloat16* src = q + (size_t)row0 * a.q_stride + (size_t)(head0 + r) * D;
+        __nv_bfloat16* dst = q_s + r * D;
+        if (i < half) {
+          const int ia = a.interleaved ? 2 * i : i, ib = a.interleaved ? 2 * i + 1 : i + half;
+          const float lo = __bfloat162float(src[ia]), hi = __bfloat162float(src[ib]);
+          dst[ia] = __float2bfloat16_rn(rope_lo(lo, hi, cs_s[i], cs_s[half + i]));
+          dst[ib] = __float2bfloat16_rn(rope_hi(lo, hi, cs_s[i], cs_s[half + i]));
+        } else {
+          const int ia = a.rot_dim + 2 * (i - half);
+          dst[ia] = src[ia];
+          dst[ia + 1] = src[ia + 1];
+        }
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kDtConsumers) : "memory");
+    }
+    // Q fragments (from global memory, or rotated from shared memory): row g_row of the A operand is head head0 + g_row
     uint32_t qf[D / 16][4];
     {
-      const __nv_bfloat16* qrow = q + (size_t)row0 * a.heads * D + (size_t)(head0 + g_row) * D;
+      const __nv_bfloat16* qrow = ROPE ? q_s + g_row * D : q + (size_t)row0 * a.q_stride + (size_t)(head0 + g_row) * D;
       const __nv_bfloat16* qrow8 = qrow + 8 * D;
       const bool v0 = g_row < nrows, v8 = g_row + 8 < nrows;
 #pragma unroll
@@ -411,7 +491,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
   if (threadIdx.x == 0) *counter = 0;
 }
 
-template <int D>
+template <int D, bool ROPE>
 static int launch_decode_tma(const void* q, const void* pool, float* partial_o, float* partial_ml, void* out,
                              const DtArgs& a, int n_entries, cudaStream_t stream) {
   EncodeTiledFn fn = encode_tiled_fn();
@@ -427,7 +507,7 @@ static int launch_decode_tma(const void* q, const void* pool, float* partial_o, 
          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return TIB_E_ARG;
-  auto kern = decode_attention_tma_kernel<D>;
+  auto kern = decode_attention_tma_kernel<D, ROPE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DtSmem<D>::kTotal);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(a.num_splits, a.kv_heads, n_entries);
@@ -458,11 +538,12 @@ TIB_API int tib_decode_attention_tma_supports(int head_dim, int group, int page_
 // counters: n_entries * kv_heads ints that are zero (the kernel leaves them zero): with them the parts of a
 // split context are merged by the block that finishes last; without (null) by a second kernel.  Launches
 // that may overlap on the GPU need counters of their own.
-TIB_API int tib_decode_attention_tma(const void* q, const void* pool, void* out, float* scratch_o, float* scratch_ml,
-                                     const int* q_start, const int* kv_start, const int* slots, const int* block_table,
-                                     int table_stride, int n_entries, int heads, int kv_heads, int head_dim,
-                                     int page_size, int64_t page_stride, int num_pages, int window, float scale,
-                                     int num_splits, int chunk, int* counters, int* error_word, cudaStream_t stream) {
+static int decode_attention_tma(const void* q, int q_stride, const void* pool, void* out, float* scratch_o, float* scratch_ml,
+                                const int* q_start, const int* kv_start, const int* slots, const int* block_table,
+                                int table_stride, int n_entries, int heads, int kv_heads, int head_dim,
+                                int page_size, int64_t page_stride, int num_pages, int window, float scale,
+                                int num_splits, int chunk, int* counters, int* error_word, bool rope, const float* inv_freq,
+                                int rot_dim, int interleaved, cudaStream_t stream) {
   if (n_entries == 0) return TIB_OK;
   if (!q || !pool || !out || !q_start || !kv_start || !slots || !block_table) return TIB_E_ARG;
   if (heads < 1 || kv_heads < 1 || heads % kv_heads != 0) return TIB_E_SIZE;
@@ -470,9 +551,10 @@ TIB_API int tib_decode_attention_tma(const void* q, const void* pool, void* out,
   if (num_splits < 1 || num_splits > 1024 || chunk < 0 || chunk % kDtBN != 0) return TIB_E_SIZE;   // (the merge keeps a weight per part in shared memory)
   if (num_splits > 1 && (!scratch_o || !scratch_ml)) return TIB_E_ARG;
   if (page_stride != (int64_t)2 * kv_heads * page_size * head_dim) return TIB_E_ALIGN;
-  if ((((uintptr_t)q | (uintptr_t)pool | (uintptr_t)out) & 15) != 0) return TIB_E_ALIGN;
+  if ((((uintptr_t)q | (uintptr_t)pool | (uintptr_t)out) & 15) != 0 || q_stride % 8 != 0) return TIB_E_ALIGN;
   if (n_entries > 65535 || kv_heads > 65535) return TIB_E_SIZE;
   if ((int64_t)num_pages * 2 * kv_heads * page_size >= ((int64_t)1 << 31)) return TIB_E_SIZE;   // row coordinates are 32-bit
+  if (rope && (rot_dim < 0 || rot_dim > head_dim || (rot_dim & 1) || (rot_dim > 0 && !inv_freq))) return TIB_E_SIZE;
   DtArgs a;
   a.q_start = q_start; a.kv_start = kv_start; a.slots = slots; a.block_table = block_table;
   a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads; a.group = heads / kv_heads;
@@ -480,6 +562,37 @@ TIB_API int tib_decode_attention_tma(const void* q, const void* pool, void* out,
   while ((1 << a.page_shift) < page_size) ++a.page_shift;
   a.num_pages = num_pages; a.window = window; a.scale_log2 = scale * 1.4426950408889634f;
   a.chunk = chunk; a.num_splits = num_splits; a.counters = counters; a.error_word = error_word;
-  return head_dim == 64 ? launch_decode_tma<64>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream)
-                        : launch_decode_tma<128>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream);
+  a.q_stride = q_stride; a.inv_freq = inv_freq; a.rot_dim = rot_dim; a.interleaved = interleaved;
+  a.pool = (__nv_bfloat16*)const_cast<void*>(pool); a.page_stride = page_stride;
+  if (rope)
+    return head_dim == 64 ? launch_decode_tma<64, true>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream)
+                          : launch_decode_tma<128, true>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream);
+  return head_dim == 64 ? launch_decode_tma<64, false>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream)
+                        : launch_decode_tma<128, false>(q, pool, scratch_o, scratch_ml, out, a, n_entries, stream);
+}
+
+TIB_API int tib_decode_attention_tma(const void* q, const void* pool, void* out, float* scratch_o, float* scratch_ml,
+                                     const int* q_start, const int* kv_start, const int* slots, const int* block_table,
+                                     int table_stride, int n_entries, int heads, int kv_heads, int head_dim,
+                                     int page_size, int64_t page_stride, int num_pages, int window, float scale,
+                                     int num_splits, int chunk, int* counters, int* error_word, cudaStream_t stream) {
+  return decode_attention_tma(q, heads * head_dim, pool, out, scratch_o, scratch_ml, q_start, kv_start, slots, block_table,
+                              table_stride, n_entries, heads, kv_heads, head_dim, page_size, page_stride, num_pages, window,
+                              scale, num_splits, chunk, counters, error_word, false, nullptr, 0, 0, stream);
+}
+
+// The same for a step of single tokens whose rotary encoding and cache write have not been done: qkv holds the rows
+// of the qkv product, [tokens][(heads + 2 kv_heads) * head_dim], unrotated.  The kernel rotates the queries (rot_dim
+// leading dims of a head, pairs (i, i + rot_dim / 2) or, interleaved, (2i, 2i + 1); angle = position * inv_freq[i];
+// rot_dim 0: no rotation), and writes each token's rotated key and its value into the token's page before it
+// attends.  Every entry must bring exactly one token (entries with more are skipped, and their keys not written).
+TIB_API int tib_decode_attention_tma_rope(const void* qkv, void* pool, void* out, float* scratch_o, float* scratch_ml,
+                                          const int* q_start, const int* kv_start, const int* slots, const int* block_table,
+                                          int table_stride, int n_entries, int heads, int kv_heads, int head_dim,
+                                          int page_size, int64_t page_stride, int num_pages, int window, float scale,
+                                          int num_splits, int chunk, int* counters, int* error_word, const float* inv_freq,
+                                          int rot_dim, int interleaved, cudaStream_t stream) {
+  return decode_attention_tma(qkv, (heads + 2 * kv_heads) * head_dim, pool, out, scratch_o, scratch_ml, q_start, kv_start, slots,
+                              block_table, table_stride, n_entries, heads, kv_heads, head_dim, page_size, page_stride, num_pages,
+                              window, scale, num_splits, chunk, counters, error_word, true, inv_freq, rot_dim, interleaved, stream);
 }

@@ -30,6 +30,9 @@ int tib_prefill_attention(const void*, const void*, void*, const int*, const int
 int tib_decode_attention_tma_supports(int, int, int);
 int tib_decode_attention_tma(const void*, const void*, void*, float*, float*, const int*, const int*, const int*, const int*,
                              int, int, int, int, int, int, int64_t, int, int, float, int, int, int*, int*, cudaStream_t);
+int tib_decode_attention_tma_rope(const void*, void*, void*, float*, float*, const int*, const int*, const int*, const int*,
+                                  int, int, int, int, int, int, int64_t, int, int, float, int, int, int*, int*, const float*, int, int,
+                                  cudaStream_t);
 int tib_decode_attention(const void*, const void*, void*, float*, float*, const int*, const int*, const int*, const int*, int,
                          int, int, int, int, int, int64_t, int, int, float, int, int, cudaStream_t);
 int tib_gemm_tcgen05_swapab_supports(int, int, int);
@@ -61,6 +64,7 @@ struct TibPrenormBlockWeights {
 struct TibPrenormBlockStep {
   int n_tokens, n_entries, max_q_len, n_single, n_multi;
   int decode_splits;
+  int decode_rotates;                    // 1: a step of single tokens goes to the decode kernel unrotated
   const int* positions;
   const int* token_slot;
   const int* q_start;
@@ -199,8 +203,12 @@ TIB_API int tib_prenorm_gqa_glu_block(const TibPrenormBlockWeights* w, const Tib
 
   TIB_TIMED(KC_NORM, tib_add_rmsnorm(pending, s->residual, nullptr, w->norm_mixer, s->normed, n, w->hidden, w->eps_mixer, TIB_BF16, stream));
   TIB_TIMED(KC_QKV, project(s->normed, w->qkv, s->qkv, n, qkv_width, w->hidden, w->qkv_kn, w->qkv_few_rows, w->qkv_features, w->qkv_splits, s->error_word, stream));
-  TIB_TIMED(KC_ROPE_APPEND, tib_rope_append(s->qkv, s->q, pool, s->positions, s->token_slot, block_table, table_stride, w->inv_freq, n, h, k, d,
-                          w->rot_dim, w->interleaved, page_size, page_stride, num_pages, 1, s->error_word, TIB_BF16, stream));
+  // a step of single tokens only: the decode kernel rotates and stores the newest token itself (no rotary kernel)
+  const bool fused_rope = s->decode_rotates && !s->n_multi && s->n_single == s->n_entries && packed &&
+                          tib_decode_attention_tma_supports(d, group, page_size);
+  if (!fused_rope)
+    TIB_TIMED(KC_ROPE_APPEND, tib_rope_append(s->qkv, s->q, pool, s->positions, s->token_slot, block_table, table_stride, w->inv_freq, n, h, k, d,
+                            w->rot_dim, w->interleaved, page_size, page_stride, num_pages, 1, s->error_word, TIB_BF16, stream));
   if (s->n_multi) {
     if (packed && tib_prefill_attention_tcgen05_supports(d, group, page_size))
       TIB_TIMED(KC_ATTENTION_PREFILL, tib_prefill_attention_tcgen05(s->q, pool, s->attn, s->q_start, s->kv_start, s->slots, block_table, table_stride,
@@ -216,7 +224,12 @@ TIB_API int tib_prenorm_gqa_glu_block(const TibPrenormBlockWeights* w, const Tib
     float* scratch_o = splits > 1 ? s->split_scratch : nullptr;
     float* scratch_ml = splits > 1 ? s->split_scratch + (size_t)s->n_entries * h * splits * d : nullptr;
     if (splits > 1 && !scratch_o) return TIB_E_ARG;
-    if (packed && tib_decode_attention_tma_supports(d, group, page_size))
+    if (fused_rope)
+      TIB_TIMED(KC_ATTENTION_DECODE, tib_decode_attention_tma_rope(s->qkv, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots,
+                                              block_table, table_stride, s->n_entries, h, k, d, page_size, page_stride, num_pages,
+                                              window, w->scale, splits, 0, splits > 1 ? s->split_counters : nullptr, s->error_word,
+                                              w->inv_freq, w->rot_dim, w->interleaved, stream));
+    else if (packed && tib_decode_attention_tma_supports(d, group, page_size))
       TIB_TIMED(KC_ATTENTION_DECODE, tib_decode_attention_tma(s->q, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots, block_table,
                                        table_stride, s->n_entries, h, k, d, page_size, page_stride, num_pages, window, w->scale,
                                        splits, 0, splits > 1 ? s->split_counters : nullptr, s->error_word, stream));

@@ -64,6 +64,11 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
   return __float2bfloat16_rn(v);
 }
 
+// One rotated pair of the rotary encoding, with the roundings spelled out so that every kernel that rotates
+// (the stand-alone one, and the decode attention kernel that rotates the newest token itself) gives the same bits.
+__device__ __forceinline__ float rope_lo(float lo, float hi, float c, float s) { return __fmaf_rn(lo, c, -__fmul_rn(hi, s)); }
+__device__ __forceinline__ float rope_hi(float lo, float hi, float c, float s) { return __fmaf_rn(hi, c, __fmul_rn(lo, s)); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

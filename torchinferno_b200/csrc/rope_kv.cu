@@ -32,9 +32,10 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
   const int pos = positions[tok];
   const int half = rot_dim >> 1;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    const float ang = (float)pos * inv_freq[i];
-    cs[i] = cosf(ang);
-    cs[half + i] = sinf(ang);
+    float sn, cn;
+    sincosf((float)pos * inv_freq[i], &sn, &cn);
+    cs[i] = cn;
+    cs[half + i] = sn;
   }
   __syncthreads();
 
@@ -51,8 +52,8 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
       const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
       const float lo = to_f32(src[a]), hi = to_f32(src[b]);
       const float c = cs[i], s = cs[half + i];
-      dst[a] = from_f32<T>(lo * c - hi * s);
-      dst[b] = from_f32<T>(hi * c + lo * s);
+      dst[a] = from_f32<T>(rope_lo(lo, hi, c, s));
+      dst[b] = from_f32<T>(rope_hi(lo, hi, c, s));
     } else {
       const int a = rot_dim + 2 * (i - half);
       dst[a] = src[a];
@@ -80,8 +81,8 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
       const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
       const float lo = to_f32(src[a]), hi = to_f32(src[b]);
       const float c = cs[i], s = cs[half + i];
-      dst[a] = from_f32<T>(lo * c - hi * s);
-      dst[b] = from_f32<T>(hi * c + lo * s);
+      dst[a] = from_f32<T>(rope_lo(lo, hi, c, s));
+      dst[b] = from_f32<T>(rope_hi(lo, hi, c, s));
     } else {
       const int a = rot_dim + 2 * (i - half);
       dst[a] = src[a];
@@ -155,8 +156,8 @@ rope_append_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
     for (int k = 0; k < 4; ++k) {
       const float2 lo = __bfloat1622float2(l2[k]), hi = __bfloat1622float2(h2[k]);
       const float c0 = cv[2 * k], c1 = cv[2 * k + 1], s0 = sv[2 * k], s1 = sv[2 * k + 1];
-      lo2[k] = __floats2bfloat162_rn(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
-      hi2[k] = __floats2bfloat162_rn(hi.x * c0 + lo.x * s0, hi.y * c1 + lo.y * s1);
+      lo2[k] = __floats2bfloat162_rn(rope_lo(lo.x, hi.x, c0, s0), rope_lo(lo.y, hi.y, c1, s1));
+      hi2[k] = __floats2bfloat162_rn(rope_hi(lo.x, hi.x, c0, s0), rope_hi(lo.y, hi.y, c1, s1));
     }
     *reinterpret_cast<uint4*>(dst + c) = lo_out;
     *reinterpret_cast<uint4*>(dst + half + c) = hi_out;

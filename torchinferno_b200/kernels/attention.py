@@ -45,3 +45,27 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, ctx, heads: int, kv_head
         q, kv.pool, out, batch.q_start, batch.kv_start, batch.slots, kv.block_table,
         batch.n_entries, batch.max_q_len, heads, kv_heads, head_dim, scale,
         window=win, error_word=ctx.error_word)
+
+
+# Single tokens go to the decode kernel unrotated where it can rotate and store them itself (set False to compare
+# with the rotary kernel followed by the attention kernel).
+DECODE_ROTATES = True
+
+
+def decode_takes_unrotated(x: torch.Tensor, ctx, heads: int, kv_heads: int, head_dim: int, position) -> bool:
+    """Whether this step's attention can run as one kernel from the rows of the qkv product: a step of single tokens
+    only, in bfloat16, a shape the TMA decode kernel takes, and a position encoding that is a rotary table."""
+    batch, kv = ctx.batch, ctx.kv
+    return (DECODE_ROTATES and x.dtype == torch.bfloat16 and batch.n_multi == 0 and batch.n_single == batch.n_entries > 0
+            and hasattr(position, "rotary_table") and kv.pool.dim() == 5
+            and kv.pool.stride(0) == 2 * kv_heads * kv.page_size * head_dim
+            and ops.decode_attention_tma_supports(head_dim, heads // kv_heads, kv.page_size))
+
+
+def decode_attention_unrotated(qkv: torch.Tensor, out: torch.Tensor, ctx, heads: int, kv_heads: int, head_dim: int,
+                               scale: float, window: int | None, position) -> torch.Tensor:
+    batch, kv = ctx.batch, ctx.kv
+    inv_freq, rot_dim, interleaved = position.rotary_table()
+    return ops.decode_attention_rope(qkv, kv.pool, out, batch.q_start, batch.kv_start, batch.slots, kv.block_table,
+                                     batch.n_entries, heads, kv_heads, head_dim, scale, batch.max_kv_len, inv_freq,
+                                     rot_dim=rot_dim, interleaved=interleaved, window=int(window or 0), error_word=ctx.error_word)

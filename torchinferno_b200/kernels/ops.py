@@ -114,7 +114,7 @@ def lib() -> ctypes.CDLL:
                    "tib_scatter_i32", "tib_decode_inputs", "tib_sample_records", "tib_rope_append", "tib_paged_attention_simt", "tib_gemm_f32", "tib_sample",
                    "tib_attention_mma_supports", "tib_prefill_attention", "tib_decode_attention",
                    "tib_prefill_attention_tcgen05", "tib_prefill_attention_tcgen05_supports",
-                   "tib_decode_attention_tma", "tib_decode_attention_tma_supports", "tib_set_dependent_launch",
+                   "tib_decode_attention_tma", "tib_decode_attention_tma_rope", "tib_decode_attention_tma_supports", "tib_set_dependent_launch",
                    "tib_kernel_timers", "tib_kernel_timers_read",
                    "tib_blas_init", "tib_blas_gemm", "tib_gemm_tcgen05_2cta", "tib_gemm_tcgen05_2cta_supports",
                    "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
@@ -448,6 +448,52 @@ def decode_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_s
         _ptr(block_table), c_int(block_table.stride(0)), c_int(n_entries), c_int(heads), c_int(kv_heads), c_int(head_dim),
         c_int(pool.shape[3]), c_int64(pool.stride(0)), c_int(pool.shape[0]), c_int(window), c_float(scale),
         c_int(num_splits), c_int(chunk), _stream()))
+    return out
+
+
+def decode_attention_rope(qkv: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor,
+                          kv_start: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, n_entries: int,
+                          heads: int, kv_heads: int, head_dim: int, scale: float, max_kv_len: int, inv_freq: torch.Tensor,
+                          *, rot_dim: int | None = None, interleaved: bool = False, window: int = 0,
+                          scratch: torch.Tensor | None = None, num_splits: int | None = None,
+                          error_word: torch.Tensor | None = None) -> torch.Tensor:
+    """A step of single tokens straight from the rows of the qkv product: the TMA decode kernel rotates the queries,
+    rotates each token's key and writes it and the value into the token's page, then attends
+    (:func:`rope_append` followed by :func:`decode_attention`, in one kernel and bit for bit).  Every entry must bring
+    one token; needs a shape the TMA kernel takes (``decode_attention_tma_supports``)."""
+    _need(qkv, "qkv", torch.bfloat16), _need(pool, "pool", torch.bfloat16), _need(out, "out", torch.bfloat16)
+    _need(inv_freq, "inv_freq", torch.float32)
+    for name, t in (("q_start", q_start), ("kv_start", kv_start), ("slots", slots), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    rot = head_dim if rot_dim is None else rot_dim
+    if pool.dim() != 5 or pool.shape[1] != 2 or pool.shape[2] != kv_heads or pool.shape[4] != head_dim:
+        raise KernelError(f"attention: pool shape {tuple(pool.shape)} does not fit")
+    if qkv.dim() != 2 or qkv.shape[1] != (heads + 2 * kv_heads) * head_dim or out.shape != (qkv.shape[0], heads * head_dim):
+        raise KernelError("decode_attention_rope: qkv / out do not fit the head counts")
+    if inv_freq.numel() != rot // 2:
+        raise KernelError("decode_attention_rope: inv_freq has the wrong length")
+    if q_start.numel() < n_entries + 1 or kv_start.numel() < n_entries or slots.numel() < n_entries:
+        raise KernelError("attention: entry arrays are shorter than n_entries")
+    packed = pool.stride(0) == 2 * kv_heads * pool.shape[3] * head_dim
+    if not (packed and decode_attention_tma_supports(head_dim, heads // kv_heads, pool.shape[3])):
+        raise KernelError("decode_attention_rope: the TMA kernel does not take this shape")
+    if num_splits is None:
+        num_splits = decode_num_splits(n_entries, heads, kv_heads, max_kv_len)
+    scratch_o = scratch_ml = None
+    if num_splits > 1:
+        need = n_entries * heads * num_splits * (head_dim + 2)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=qkv.device)
+        _need(scratch, "scratch", torch.float32)
+        if scratch.numel() < need:
+            raise KernelError("decode_attention: scratch is too small")
+        scratch_o, scratch_ml = scratch, scratch[n_entries * heads * num_splits * head_dim:]
+    _check("decode_attention_tma_rope", lib().tib_decode_attention_tma_rope(
+        _ptr(qkv), _ptr(pool), _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), _ptr(q_start), _ptr(kv_start), _ptr(slots),
+        _ptr(block_table), c_int(block_table.stride(0)), c_int(n_entries), c_int(heads), c_int(kv_heads), c_int(head_dim),
+        c_int(pool.shape[3]), c_int64(pool.stride(0)), c_int(pool.shape[0]), c_int(window), c_float(scale),
+        c_int(num_splits), c_int(0), _ptr(_split_counters(qkv.device, n_entries * kv_heads) if num_splits > 1 else None),
+        _ptr(error_word), _ptr(inv_freq), c_int(rot), c_int(int(interleaved)), _stream()))
     return out
 
 

@@ -63,6 +63,13 @@ class GQAAttention(Mixer):
             raise RuntimeError("attention needs a cache binding")
         h, k, d = self.heads, self.kv_heads, self.head_dim
         n = x.shape[0]
+        window = self.window if self.window is not None else ctx.kv.window
+        if ctx.kv.writes and attention_kernels.decode_takes_unrotated(x, ctx, h, k, d, self.position):
+            # a step of single tokens: the decode kernel rotates and stores the newest token itself
+            qkv = linear(x, self.qkv_weight)
+            out = torch.empty((n, h * d), dtype=x.dtype, device=x.device)
+            attention_kernels.decode_attention_unrotated(qkv, out, ctx, h, k, d, self.scale, window, self.position)
+            return linear(out, self.o_weight)
         q = torch.empty((n, h * d), dtype=x.dtype, device=x.device)
         if ctx.kv.writes:
             qkv = linear(x, self.qkv_weight)
@@ -71,8 +78,7 @@ class GQAAttention(Mixer):
             q_only = linear(x, self.qkv_weight.rows(0, h * d))
             self.position.encode_and_store(q_only, q, ctx, h, 0, d)
         out = torch.empty_like(q)
-        attention_kernels.paged_attention(q, out, ctx, h, k, d, self.scale,
-                                          self.window if self.window is not None else ctx.kv.window)
+        attention_kernels.paged_attention(q, out, ctx, h, k, d, self.scale, window)
         return linear(out, self.o_weight)
 
 

@@ -53,6 +53,10 @@ class RotaryEncoding(PositionEncoding):
         self.interleaved = bool(interleaved)
         self.inv_freq = rotary_frequencies(self.rot_dim, float(theta), scaling).to(device)
 
+    def rotary_table(self):
+        """(inv_freq, rot_dim, interleaved): what a kernel needs to apply this encoding itself."""
+        return self.inv_freq, self.rot_dim, self.interleaved
+
     def encode_and_store(self, qkv, q_out, ctx: LayerContext, heads, kv_heads, head_dim):
         kv = ctx.kv
         write = kv is not None and kv.writes
@@ -69,6 +73,9 @@ class NoPositionEncoding(PositionEncoding):
     def __init__(self, *, head_dim: int, dtype: torch.dtype, device: torch.device) -> None:
         super().__init__(dtype=dtype, device=device)
         self.inv_freq = torch.zeros(0, dtype=torch.float32, device=device)
+
+    def rotary_table(self):
+        return self.inv_freq, 0, False
 
     def encode_and_store(self, qkv, q_out, ctx: LayerContext, heads, kv_heads, head_dim):
         kv = ctx.kv
