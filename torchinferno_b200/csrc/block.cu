@@ -39,7 +39,7 @@ int tib_gemm_tcgen05_swapab_supports(int, int, int);
 int tib_gemm_tcgen05_swapab(const void*, const void*, void*, int, int, int, int64_t, int64_t, int64_t, int, int, int, int*, cudaStream_t);
 int tib_blas_gemm(const void*, const void*, void*, int, int, int, int64_t, int64_t, int64_t, int, int, cudaStream_t);
 int tib_gemm_decode_supports(int, int, int, int, int, int);
-int tib_gemm_decode(const void*, const void*, void*, int, int, int, int64_t, int64_t, int64_t, int, int, int, int, int*, cudaStream_t);
+int tib_gemm_decode(const void*, const void*, void*, int, int, int, int64_t, int64_t, int64_t, int, int, int, int, int, int*, cudaStream_t);
 }
 
 // What a block is made of: sizes, constants and weights.  Filled once when the weights are bound.
@@ -49,7 +49,8 @@ struct TibPrenormBlockWeights {
   int qkv_kn, o_kn, gate_up_kn, down_kn; // 1: the matrix is stored [in, out]
   int qkv_few_rows, o_few_rows, gate_up_few_rows, down_few_rows;   // rows up to which a projection goes to a few-rows kernel (0: never)
   int qkv_features, o_features, gate_up_features, down_features;   // the few-rows kernel's tile width (128 or 256) ...
-  int qkv_splits, o_splits, gate_up_splits, down_splits;           // ... and K split (0: the older swap-AB kernel)
+  int qkv_splits, o_splits, gate_up_splits, down_splits;           // ... K split (0: the older swap-AB kernel) ...
+  int qkv_stages, o_stages, gate_up_stages, down_stages;           // ... and ring depth (0: the kernel's default)
   float eps_mixer, eps_feed_forward, scale;
   const float* norm_mixer;               // [hidden]
   const float* norm_feed_forward;        // [hidden]
@@ -179,10 +180,10 @@ TIB_API int tib_kernel_timers_read(double* ms, long long* count, int n, int rese
 // out[n, N] = x[n, K] . w^T, w stored [N, K] or (kn) [K, N]: a hand-written few-rows kernel up to few_rows rows (the
 // one of gemm_decode.cu with its tile width and K split when splits > 0, else the swap-AB kernel), else the library.
 static int project(const void* x, const void* w, void* out, int n, int N, int K, int kn, int few_rows, int features, int splits,
-                   int* error_word, cudaStream_t stream) {
+                   int stages, int* error_word, cudaStream_t stream) {
   if (few_rows > 0 && n <= few_rows) {
     if (kn && splits > 0 && tib_gemm_decode_supports(n, N, K, features, splits, 0))
-      return tib_gemm_decode(x, w, out, n, N, K, K, N, N, TIB_BF16, features, splits, 0, error_word, stream);
+      return tib_gemm_decode(x, w, out, n, N, K, K, N, N, TIB_BF16, features, splits, 0, stages, error_word, stream);
     if (tib_gemm_tcgen05_swapab_supports(n, N, K))
       return tib_gemm_tcgen05_swapab(x, w, out, n, N, K, K, kn ? N : K, N, kn, TIB_BF16, 0, error_word, stream);
   }
@@ -202,7 +203,7 @@ TIB_API int tib_prenorm_gqa_glu_block(const TibPrenormBlockWeights* w, const Tib
   const bool packed = page_stride == (int64_t)2 * k * page_size * d;
 
   TIB_TIMED(KC_NORM, tib_add_rmsnorm(pending, s->residual, nullptr, w->norm_mixer, s->normed, n, w->hidden, w->eps_mixer, TIB_BF16, stream));
-  TIB_TIMED(KC_QKV, project(s->normed, w->qkv, s->qkv, n, qkv_width, w->hidden, w->qkv_kn, w->qkv_few_rows, w->qkv_features, w->qkv_splits, s->error_word, stream));
+  TIB_TIMED(KC_QKV, project(s->normed, w->qkv, s->qkv, n, qkv_width, w->hidden, w->qkv_kn, w->qkv_few_rows, w->qkv_features, w->qkv_splits, w->qkv_stages, s->error_word, stream));
   // a step of single tokens only: the decode kernel rotates and stores the newest token itself (no rotary kernel)
   const bool fused_rope = s->decode_rotates && !s->n_multi && s->n_single == s->n_entries && packed &&
                           tib_decode_attention_tma_supports(d, group, page_size);
@@ -238,7 +239,7 @@ TIB_API int tib_prenorm_gqa_glu_block(const TibPrenormBlockWeights* w, const Tib
                                    table_stride, s->n_entries, h, k, d, page_size, page_stride, num_pages, window, w->scale,
                                    splits, 0, stream));
   }
-  TIB_TIMED(KC_O, project(s->attn, w->o, s->o_out, n, w->hidden, q_width, w->o_kn, w->o_few_rows, w->o_features, w->o_splits, s->error_word, stream));
+  TIB_TIMED(KC_O, project(s->attn, w->o, s->o_out, n, w->hidden, q_width, w->o_kn, w->o_few_rows, w->o_features, w->o_splits, w->o_stages, s->error_word, stream));
   TIB_TIMED(KC_NORM, tib_add_rmsnorm(s->o_out, s->residual, nullptr, w->norm_feed_forward, s->normed, n, w->hidden, w->eps_feed_forward,
                           TIB_BF16, stream));
   const int inter = w->intermediate;
@@ -246,12 +247,12 @@ TIB_API int tib_prenorm_gqa_glu_block(const TibPrenormBlockWeights* w, const Tib
   if (w->gate_up_kn && w->gate_up_few_rows > 0 && n <= w->gate_up_few_rows && w->gate_up_splits == 1 &&
       tib_gemm_decode_supports(n, 2 * inter, w->hidden, w->gate_up_features, 1, 1)) {
     TIB_TIMED(KC_GATE_UP, tib_gemm_decode(s->normed, w->gate_up, s->act, n, 2 * inter, w->hidden, w->hidden, 2 * inter, inter, TIB_BF16,
-                                          w->gate_up_features, 1, 1, s->error_word, stream));
+                                          w->gate_up_features, 1, 1, w->gate_up_stages, s->error_word, stream));
   } else {
     TIB_TIMED(KC_GATE_UP, project(s->normed, w->gate_up, s->gate_up, n, 2 * inter, w->hidden, w->gate_up_kn, w->gate_up_few_rows,
-                                  w->gate_up_features, w->gate_up_splits, s->error_word, stream));
+                                  w->gate_up_features, w->gate_up_splits, w->gate_up_stages, s->error_word, stream));
     TIB_TIMED(KC_SWIGLU, tib_swiglu(s->gate_up, s->act, n, inter, TIB_BF16, 1, stream));
   }
-  TIB_TIMED(KC_DOWN, project(s->act, w->down, s->out, n, w->hidden, inter, w->down_kn, w->down_few_rows, w->down_features, w->down_splits, s->error_word, stream));
+  TIB_TIMED(KC_DOWN, project(s->act, w->down, s->out, n, w->hidden, inter, w->down_kn, w->down_few_rows, w->down_features, w->down_splits, w->down_stages, s->error_word, stream));
   return TIB_OK;
 }

@@ -37,12 +37,17 @@ __host__ __device__ constexpr int dg_stages(int npad, int ft) {
   return ft == 256 ? (npad <= 16 ? 6 : npad <= 48 ? 5 : 4) : (npad <= 16 ? 7 : npad <= 32 ? 8 : npad <= 48 ? 6 : 5);
 }
 
+constexpr int kDgMaxStages = 16;
+
+// kStages: the depth of the ring (1 .. kDgMaxStages), chosen by the host: the depth that streams fastest for a matrix
+// that is mostly stream, fewer where the kernel after this one should fit on the SM beside it and fetch ahead (the
+// decode attention after the qkv product), more where a block's whole share of a small matrix then fits the ring
+// and is on its way before the kernel before this one has ended.
 template <int NPAD, int FT, int EPI, typename TOut>
 __global__ void __launch_bounds__(kDgThreads, 1)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                   TOut* __restrict__ out, int M, int N, int K, int64_t ldo, int* __restrict__ error_word) {
+                   TOut* __restrict__ out, int M, int N, int K, int64_t ldo, int kStages, int* __restrict__ error_word) {
   constexpr int H = FT / 128;                                              // accumulators (and MMAs per k step) of a tile
-  constexpr int kStages = dg_stages(NPAD, FT);
   constexpr uint32_t kWBytes = (uint32_t)FT * kDgBK * 2;
   constexpr uint32_t kXBytes = NPAD * kDgBK * 2;
   constexpr uint32_t kStage = dg_stage_bytes(NPAD, FT);
@@ -55,12 +60,12 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const uint32_t red = base + kStages * kStage;                            // 2 x [splits][rows_per][kRedStride] floats
   const uint32_t bars = red + 2 * kRedBytes;
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (kStages + s); };
-  auto acc_full_bar = [&](int b) { return bars + 8u * (2 * kStages + b); };
-  auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * kStages + 2 + b); };
-  auto red_full_bar = [&](int b) { return bars + 8u * (2 * kStages + 4 + b); };   // peers' partial bands have arrived
-  auto red_free_bar = [&](int b) { return bars + 8u * (2 * kStages + 6 + b); };   // every block has summed its band
-  const uint32_t tmem_slot = bars + 8u * (2 * kStages + 8);
+  auto empty_bar = [&](int s) { return bars + 8u * (kDgMaxStages + s); };
+  auto acc_full_bar = [&](int b) { return bars + 8u * (2 * kDgMaxStages + b); };
+  auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * kDgMaxStages + 2 + b); };
+  auto red_full_bar = [&](int b) { return bars + 8u * (2 * kDgMaxStages + 4 + b); };   // peers' partial bands have arrived
+  auto red_free_bar = [&](int b) { return bars + 8u * (2 * kDgMaxStages + 6 + b); };   // every block has summed its band
+  const uint32_t tmem_slot = bars + 8u * (2 * kDgMaxStages + 8);
   unsigned char* smem_gen = smem_raw + (base - smem_u32(smem_raw));        // generic pointer to `base`
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - base));
 
@@ -112,10 +117,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           load_w(base + ahead * kStage, t, kb, full_bar(ahead));
         }
       pdl_wait();
+      int s = 0;                 // stage and phase of iteration `it`, counted along (no division in the loop)
+      uint32_t phase = 0;
       for (int t = cluster_id; t < n_tiles && ok; t += clusters) {
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t phase = (it / kStages) & 1;
+        for (int kb = kb0; kb < kb1; ++kb, ++it, phase ^= (s + 1 == kStages), s = (s + 1 == kStages ? 0 : s + 1)) {
           const uint32_t w_dst = base + s * kStage, x_dst = w_dst + kWBytes;
           if (it < ahead) {   // (its weights are on their way)
             tma_load_2d(x_dst, &map_x, kb * kDgBK, 0, full_bar(s));
@@ -137,9 +142,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       // D fp32, A and B bf16, A MN-major (bit 15), B K-major, N = NPAD, M = 128
       constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((uint32_t)(NPAD >> 3) << 17) |
                                  ((uint32_t)(128 >> 4) << 24);
-      uint32_t it = 0;
       bool ok = true;
-      int j = 0;
+      int j = 0, s = 0;
+      uint32_t phase = 0;
       for (int t = cluster_id; t < n_tiles && ok; t += clusters, ++j) {
         const int b = j & 1;
         if (!mbar_wait(acc_empty_bar(b), ((j >> 1) & 1) ^ 1)) {
@@ -147,9 +152,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t phase = (it / kStages) & 1;
+        for (int kb = kb0; kb < kb1; ++kb, phase ^= (s + 1 == kStages), s = (s + 1 == kStages ? 0 : s + 1)) {
           if (!mbar_wait(full_bar(s), phase)) {
             if (error_word) atomicExch(error_word, 0x7C0042);
             ok = false;
@@ -276,16 +279,29 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   }
 }
 
+// Bytes of shared memory a block with a ring of `stages` takes.
+template <int NPAD, int FT>
+static constexpr uint32_t dg_smem(int stages) {
+  return 1024u + (uint32_t)stages * dg_stage_bytes(NPAD, FT) + (FT == 128 ? 2u * kDgRedRows * (NPAD + 4) * 4 : 0u) + 8u * (2 * kDgMaxStages + 10);
+}
+template <int NPAD, int FT>
+static constexpr int dg_most_stages() {
+  int n = kDgMaxStages;
+  while (n > 1 && dg_smem<NPAD, FT>(n) > 232448u) --n;
+  return n;
+}
+
 template <int NPAD, int FT, int EPI, typename TOut>
 static int launch_decode_gemm(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int M, int N, int K, int64_t ldo,
-                              int splits, int* error_word, cudaStream_t stream) {
-  constexpr uint32_t red_bytes = FT == 128 ? 2u * kDgRedRows * (NPAD + 4) * 4 : 0u;
-  constexpr uint32_t smem = 1024 + dg_stages(NPAD, FT) * dg_stage_bytes(NPAD, FT) + red_bytes + 256;
-  static_assert(smem <= 232448, "the ring does not fit an SM's shared memory");
+                              int splits, int stages, int* error_word, cudaStream_t stream) {
+  constexpr int most = dg_most_stages<NPAD, FT>();
+  if (stages <= 0) stages = dg_stages(NPAD, FT);
+  if (stages > most) stages = most;
+  const uint32_t smem = dg_smem<NPAD, FT>(stages);
   auto kern = gemm_decode_kernel<NPAD, FT, EPI, TOut>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dg_smem<NPAD, FT>(most));
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -306,15 +322,17 @@ static int launch_decode_gemm(const CUtensorMap& map_w, const CUtensorMap& map_x
   static int resident[9] = {0};
   if (resident[splits] == 0) {
     cfg.numAttrs = 1;
+    cfg.dynamicSmemBytes = dg_smem<NPAD, FT>(most);
     cfg.gridDim = dim3((unsigned)splits);
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) n = 1;
     resident[splits] = n;
   }
   const int clusters = tiles < resident[splits] ? tiles : resident[splits];
+  cfg.dynamicSmemBytes = smem;
   cfg.gridDim = dim3((unsigned)(clusters * splits));
   cfg.numAttrs = dependent_launch_flag() ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, (TOut*)out, M, N, K, ldo, error_word);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, (TOut*)out, M, N, K, ldo, stages, error_word);
   if (e != cudaSuccess) return (int)e;
   TIB_LAUNCH_CHECK();
   return TIB_OK;
@@ -336,15 +354,17 @@ TIB_API int tib_gemm_decode_supports(int M, int N, int K, int features, int spli
 }
 
 // x: [M <= 64, K] bf16 (row stride ldx); w: [K, N] bf16 (row stride ldw); out: [M, N] bf16 or fp32, or with the
-// SwiGLU epilogue [M, N / 2] (row stride ldo).  features: 128 or 256 per tile; splits: blocks that share K.
+// SwiGLU epilogue [M, N / 2] (row stride ldo).  features: 128 or 256 per tile; splits: blocks that share K;
+// stages: depth of the ring (0: the default for the tile; more than fits is cut to what fits).
 TIB_API int tib_gemm_decode(const void* x, const void* w, void* out, int M, int N, int K, int64_t ldx, int64_t ldw,
-                            int64_t ldo, int out_dtype, int features, int splits, int epilogue, int* error_word,
+                            int64_t ldo, int out_dtype, int features, int splits, int epilogue, int stages, int* error_word,
                             cudaStream_t stream) {
   if (M == 0 || N == 0) return TIB_OK;
   if (!x || !w || !out) return TIB_E_ARG;
   if (!tib_gemm_decode_supports(M, N, K, features, splits, epilogue)) return TIB_E_SIZE;
   if ((((uintptr_t)x | (uintptr_t)w) & 15) || ldx % 8 || ldw % 8) return TIB_E_ALIGN;
   if (out_dtype != TIB_BF16 && out_dtype != TIB_F32) return TIB_E_DTYPE;
+  if (stages < 0 || stages > kDgMaxStages) return TIB_E_SIZE;
   const int npad = (M + 15) / 16 * 16;
   CUtensorMap map_w, map_x;
   int rc = make_map(&map_w, w, K, N, ldw, 64);
@@ -352,8 +372,8 @@ TIB_API int tib_gemm_decode(const void* x, const void* w, void* out, int M, int 
   rc = make_map(&map_x, x, M, K, ldx, npad);
   if (rc != TIB_OK) return rc;
 #define TIB_DG_E(NP, FT, T) \
-  (epilogue == DG_SWIGLU ? launch_decode_gemm<NP, FT, DG_SWIGLU, T>(map_w, map_x, out, M, N, K, ldo, splits, error_word, stream) \
-                         : launch_decode_gemm<NP, FT, DG_PLAIN, T>(map_w, map_x, out, M, N, K, ldo, splits, error_word, stream))
+  (epilogue == DG_SWIGLU ? launch_decode_gemm<NP, FT, DG_SWIGLU, T>(map_w, map_x, out, M, N, K, ldo, splits, stages, error_word, stream) \
+                         : launch_decode_gemm<NP, FT, DG_PLAIN, T>(map_w, map_x, out, M, N, K, ldo, splits, stages, error_word, stream))
 #define TIB_DG_F(NP, T) (features == 256 ? TIB_DG_E(NP, 256, T) : TIB_DG_E(NP, 128, T))
 #define TIB_DG(NP) (out_dtype == TIB_BF16 ? TIB_DG_F(NP, __nv_bfloat16) : TIB_DG_F(NP, float))
   switch (npad) {

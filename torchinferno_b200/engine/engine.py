@@ -177,6 +177,12 @@ class InferenceEngine:
             plan = self.scheduler.plan()
             if not plan.entries:
                 return []
+            if len(plan.entries) > 1 and all(e.kind == "decode" for e in plan.entries):
+                # Longest context first: the decode attention kernel gives every (request, kv head) a block, the
+                # hardware hands blocks out in order, and a long context that starts last is the step's tail.
+                # (The steps planned ahead of this one keep the order, so the captured step's slots stay as they are.)
+                ordered = tuple(sorted(plan.entries, key=lambda e: -e.start))
+                plan = StepPlan(plan.step, ordered, plan.preempted, plan.admitted)
             current = self._launch(plan, False)
         if self.config.async_scheduling and current.device_tokens is not None and self.runner.use_cuda_graphs:
             ahead = self.scheduler.plan_ahead(current.plan)

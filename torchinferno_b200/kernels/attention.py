@@ -48,15 +48,21 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, ctx, heads: int, kv_head
 
 
 # Single tokens go to the decode kernel unrotated where it can rotate and store them itself (set False to compare
-# with the rotary kernel followed by the attention kernel).
+# with the rotary kernel followed by the attention kernel), in steps of up to DECODE_ROTATES_MAX_ENTRIES requests.
+# With few requests the step is a chain of short kernels and one link less is a gain (8 requests at 2,100 tokens,
+# 8B sizes: 3.54 -> 3.51 ms a step); with many the attention kernel streams long enough that the head start it had
+# under the rotary kernel (older keys are fetched while that runs) is worth more than the link (32 requests:
+# 4.47 -> 4.52 ms, 64: 5.92 -> 6.01; 4 and 16: no difference).
 DECODE_ROTATES = True
+DECODE_ROTATES_MAX_ENTRIES = 8
 
 
 def decode_takes_unrotated(x: torch.Tensor, ctx, heads: int, kv_heads: int, head_dim: int, position) -> bool:
     """Whether this step's attention can run as one kernel from the rows of the qkv product: a step of single tokens
     only, in bfloat16, a shape the TMA decode kernel takes, and a position encoding that is a rotary table."""
     batch, kv = ctx.batch, ctx.kv
-    return (DECODE_ROTATES and x.dtype == torch.bfloat16 and batch.n_multi == 0 and batch.n_single == batch.n_entries > 0
+    return (DECODE_ROTATES and x.dtype == torch.bfloat16 and batch.n_multi == 0
+            and 0 < batch.n_single == batch.n_entries <= DECODE_ROTATES_MAX_ENTRIES
             and hasattr(position, "rotary_table") and kv.pool.dim() == 5
             and kv.pool.stride(0) == 2 * kv_heads * kv.page_size * head_dim
             and ops.decode_attention_tma_supports(head_dim, heads // kv_heads, kv.page_size))

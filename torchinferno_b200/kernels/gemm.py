@@ -109,7 +109,7 @@ class LinearWeight:
         self.transposed = bool(allow_transpose and on_gpu and _backend != "tcgen05")
         self.tensor = weight.t().contiguous() if self.transposed else weight.contiguous()
         self.epilogue = epilogue
-        self.features, self.splits = 128, 0
+        self.features, self.splits, self.stages = 128, 0, 0
         if few_rows_tcgen05 is None and on_gpu and _backend == "auto":
             _undecided.add(self)
         _changed()
@@ -122,7 +122,7 @@ class LinearWeight:
         """The projection onto output features start .. stop-1 (a view, nothing is copied)."""
         view = object.__new__(LinearWeight)
         view.out_features, view.in_features, view.transposed = stop - start, self.in_features, self.transposed
-        view.few_rows, view.epilogue, view.features, view.splits = self.few_rows, "none", 128, 0
+        view.few_rows, view.epilogue, view.features, view.splits, view.stages = self.few_rows, "none", 128, 0, 0
         view.tensor = self.tensor[:, start:stop] if self.transposed else self.tensor[start:stop]
         return view
 
@@ -136,7 +136,7 @@ def linear(x: torch.Tensor, weight: "torch.Tensor | LinearWeight", *, out_dtype:
     few_rows = 0
     if isinstance(weight, LinearWeight):
         if weight.transposed:
-            return _linear_kn(x, weight.tensor, out_dtype or x.dtype, out, weight.few_rows, weight.features, weight.splits)
+            return _linear_kn(x, weight.tensor, out_dtype or x.dtype, out, weight.few_rows, weight.features, weight.splits, weight.stages)
         few_rows = weight.few_rows
         weight = weight.tensor
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
@@ -174,7 +174,8 @@ def linear_swiglu(x: torch.Tensor, weight: LinearWeight) -> torch.Tensor:
     if (weight.transposed and _backend == "auto" and 0 < m <= weight.few_rows and weight.splits == 1 and x.dtype == torch.bfloat16
             and _decode_takes(x, w, weight.features, 1, ops.DG_SWIGLU)):
         act = torch.empty((m, inter), dtype=x.dtype, device=x.device)
-        return ops.gemm_decode(x, w, act, features=weight.features, splits=1, epilogue=ops.DG_SWIGLU, error_word=_error_word)
+        return ops.gemm_decode(x, w, act, features=weight.features, splits=1, epilogue=ops.DG_SWIGLU, stages=weight.stages,
+                               error_word=_error_word)
     gate_up = linear(x, weight)
     act = torch.empty((m, inter), dtype=gate_up.dtype, device=x.device)
     return ops.swiglu(gate_up, act, interleaved=True)
@@ -188,7 +189,7 @@ def _decode_takes(x: torch.Tensor, weight_kn: torch.Tensor, features: int, split
 
 
 def _linear_kn(x: torch.Tensor, weight_kn: torch.Tensor, out_dtype: torch.dtype, out: torch.Tensor | None,
-               few_rows: int = 0, features: int = 128, splits: int = 0) -> torch.Tensor:
+               few_rows: int = 0, features: int = 128, splits: int = 0, stages: int = 0) -> torch.Tensor:
     """A matrix stored [in, out]: a few-rows kernel up to ``few_rows`` rows, else cuBLAS."""
     if x.dim() != 2 or x.shape[1] != weight_kn.shape[0]:
         raise ops.KernelError(f"linear: shapes {tuple(x.shape)} and [in, out] = {tuple(weight_kn.shape)} do not fit")
@@ -201,7 +202,7 @@ def _linear_kn(x: torch.Tensor, weight_kn: torch.Tensor, out_dtype: torch.dtype,
         out = torch.empty((x.shape[0], weight_kn.shape[1]), dtype=out_dtype, device=x.device)
     if _backend == "auto" and 0 < x.shape[0] <= few_rows:
         if splits > 0 and _decode_takes(x, weight_kn, features, splits):
-            return ops.gemm_decode(x, weight_kn, out, features=features, splits=splits, error_word=_error_word)
+            return ops.gemm_decode(x, weight_kn, out, features=features, splits=splits, stages=stages, error_word=_error_word)
         if _swapab_takes_kn(x, weight_kn):
             return ops.gemm_tcgen05_swapab(x, weight_kn, out, _error_word, w_kn=True)
     return ops.library_gemm(x, weight_kn, out, w_kn=True)

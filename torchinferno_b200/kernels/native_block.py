@@ -23,7 +23,8 @@ class BlockWeights(Structure):
                                            "qkv_kn", "o_kn", "gate_up_kn", "down_kn",
                                            "qkv_few_rows", "o_few_rows", "gate_up_few_rows", "down_few_rows",
                                            "qkv_features", "o_features", "gate_up_features", "down_features",
-                                           "qkv_splits", "o_splits", "gate_up_splits", "down_splits")] + \
+                                           "qkv_splits", "o_splits", "gate_up_splits", "down_splits",
+                                           "qkv_stages", "o_stages", "gate_up_stages", "down_stages")] + \
                [(name, c_float) for name in ("eps_mixer", "eps_feed_forward", "scale")] + \
                [(name, c_void_p) for name in ("norm_mixer", "norm_feed_forward", "inv_freq", "qkv", "o", "gate_up", "down")]
 
@@ -86,6 +87,7 @@ def block_weights(block) -> BlockWeights | None:
     for name, m in (("qkv", mixer.qkv_weight), ("o", mixer.o_weight), ("gate_up", ffn.gate_up_weight), ("down", ffn.down_weight)):
         setattr(w, name + "_features", m.features)
         setattr(w, name + "_splits", m.splits)
+        setattr(w, name + "_stages", m.stages)
     if ffn.gate_up_weight.epilogue != "swiglu":
         return None
     w.eps_mixer, w.eps_feed_forward, w.scale = n1.eps, n2.eps, mixer.scale
@@ -113,7 +115,7 @@ class StepWorkspace:
         s.n_tokens, s.n_entries, s.max_q_len, s.n_single, s.n_multi = n, batch.n_entries, batch.max_q_len, batch.n_single, batch.n_multi
         s.decode_splits = splits
         from torchinferno_b200.kernels import attention
-        s.decode_rotates = int(attention.DECODE_ROTATES)
+        s.decode_rotates = int(attention.DECODE_ROTATES and batch.n_entries <= attention.DECODE_ROTATES_MAX_ENTRIES)
         for name in ("positions", "token_slot", "q_start", "kv_start", "slots"):
             setattr(s, name, getattr(batch, name).data_ptr())
         s.residual = residual.data_ptr()

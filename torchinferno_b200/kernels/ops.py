@@ -620,9 +620,10 @@ def gemm_decode_supports(m: int, n: int, k: int, features: int = 128, splits: in
 
 
 def gemm_decode(x: torch.Tensor, w_kn: torch.Tensor, out: torch.Tensor, *, features: int = 128, splits: int = 1,
-                epilogue: int = DG_PLAIN, error_word: torch.Tensor | None = None) -> torch.Tensor:
+                epilogue: int = DG_PLAIN, stages: int = 0, error_word: torch.Tensor | None = None) -> torch.Tensor:
     """The product of a decode step, out[M, N] = x[M, K] . w for M <= 64 with ``w_kn`` stored [K, N]: tiles of
-    ``features`` (128 or 256) features streamed by TMA, K shared by ``splits`` blocks of a cluster.  With the SwiGLU
+    ``features`` (128 or 256) features streamed by TMA through a ring of ``stages`` stages (0: the kernel's default),
+    K shared by ``splits`` blocks of a cluster.  With the SwiGLU
     epilogue ``w_kn`` holds gate and up columns interleaved and ``out`` is the activation [M, N / 2]."""
     for name, t in (("x", x), ("w_kn", w_kn)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
@@ -633,8 +634,8 @@ def gemm_decode(x: torch.Tensor, w_kn: torch.Tensor, out: torch.Tensor, *, featu
         raise KernelError(f"gemm_decode: shapes {tuple(x.shape)} x {tuple(w_kn.shape)} -> {tuple(out.shape)} do not fit")
     _check("gemm_decode", lib().tib_gemm_decode(
         _ptr(x), _ptr(w_kn), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)), c_int64(w_kn.stride(0)),
-        c_int64(out.stride(0)), c_int(_code(out.dtype)), c_int(features), c_int(splits), c_int(epilogue), _ptr(error_word),
-        _stream()))
+        c_int64(out.stride(0)), c_int(_code(out.dtype)), c_int(features), c_int(splits), c_int(epilogue), c_int(stages),
+        _ptr(error_word), _stream()))
     return out
 
 
