@@ -302,10 +302,10 @@ def timed_workload(name: str, peaks: dict, gemm_backend: str) -> dict:
     engine = InferenceEngine(model, EngineConfig(
         model="<in memory>", dtype="bfloat16", page_size=PAGE_SIZE, max_batch_size=w["requests"], gemm_backend=gemm_backend,
         max_model_len=longest + PAGE_SIZE, kv_cache_tokens=w["requests"] * (longest + PAGE_SIZE)))
-    g = torch.Generator().manual_seed(17)
     weight_bytes, kv_bytes = model.weight_bytes(), engine.runner.cache.kv_bytes_per_token()
     result = {}
-    for it in range(2):                                   # (the first pass warms up: graphs are captured, kernels chosen)
+    for it in range(2):                                   # (the first pass warms up: the same requests, so that every
+        g = torch.Generator().manual_seed(17)             # batch size the run meets has its decode step captured)
         lengths = torch.randint(w["prompt_min"], w["prompt_max"] + 1, (w["requests"],), generator=g).tolist()
         for i, n in enumerate(lengths):
             engine.submit(GenerateRequest(f"{name}-{it}-{i}", prompt_token_ids=torch.randint(0, model.spec.vocab_size, (n,), generator=g).tolist(),

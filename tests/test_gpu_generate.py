@@ -200,6 +200,30 @@ def test_schedules_in_bfloat16_on_the_default_path_give_the_same_tokens(model_fo
     assert preempted > 0 and ahead > 20
 
 
+def test_warm_up_captures_the_decode_steps_ahead_of_serving_and_changes_no_token(model_folders):
+    """warm_up() captures the decode step for every batch size it is given with throw-away requests; afterwards the
+    cache is empty, serving replays those captures from its first decode step on, and the tokens are those of an
+    engine that was not warmed up."""
+    need_gpu()
+    config, seed = TINY["D"]
+    prompts = list(requests_for(config, seed, [30, 5, 17]).values())
+    with engine_for(model_folders["D"], "bfloat16", page_size=16, max_batch_size=4, gemm_backend="library") as engine:
+        cold = engine.generate_many(requests(prompts, 12, 0.7, [1, 2, 3]))
+    with engine_for(model_folders["D"], "bfloat16", page_size=16, max_batch_size=4, gemm_backend="library") as engine:
+        assert engine.warm_up() == [4, 3, 2, 1]
+        cache = engine.runner.cache
+        assert sorted(engine.runner._graphs) == [1, 2, 3, 4] and all(g.graph is not None for g in engine.runner._graphs.values())
+        assert cache.free_pages() == [cache.num_pages] and not cache.live_requests
+        cache.audit()
+        replays = engine.runner.graph_replays
+        warm = engine.generate_many(requests(prompts, 12, 0.7, [1, 2, 3]))
+        assert engine.runner.graph_replays - replays >= 11          # (every decode step of the run was a replay)
+        with pytest.raises(RuntimeError, match="idle"):
+            engine.submit(requests(prompts[:1], 4)[0])
+            engine.warm_up([2])
+    assert [o.token_ids for o in warm] == [o.token_ids for o in cold]
+
+
 def test_the_engine_sees_an_error_word_that_a_kernel_set_and_goes_on_without_the_failed_requests(model_folders):
     """The kernels report a page id outside its pool or a bounded wait that ran out in one device word; the
     engine reads it with the step's tokens.  Here the word is set from the host (no kernel is made to fail).

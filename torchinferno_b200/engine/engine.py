@@ -106,6 +106,34 @@ class InferenceEngine:
     def __exit__(self, *exc) -> None:
         self.close()
 
+    def warm_up(self, batch_sizes: Iterable[int] | None = None) -> list[int]:
+        """Capture the decode step for these numbers of running requests (default: every number up to
+        ``max_batch_size``) now instead of at the first step that meets them: a decode step is captured per exact
+        batch size (no padded rows), and a capture in the middle of serving costs that step several times its
+        usual time.  Runs throw-away requests of two tokens each; needs the cache empty.  Returns the sizes captured."""
+        runner, cache = self.runner, self.runner.cache
+        if cache.live_requests or self.scheduler.has_work():
+            raise RuntimeError("warm_up needs an idle engine")
+        if not (runner.use_cuda_graphs and runner._graph_ok and cache.device.type == "cuda"):
+            return []
+        sizes = sorted({int(n) for n in (batch_sizes if batch_sizes is not None else range(1, self.config.max_batch_size + 1))
+                        if 1 <= int(n) <= min(self.config.max_batch_size, cache.max_requests)}, reverse=True)
+        done = []
+        with torch.inference_mode():
+            for n in sizes:
+                if any(n > free for free in cache.free_pages()):      # (a page per request is the least it takes)
+                    continue
+                ids = [("warm-up", i) for i in range(n)]
+                runner.step([StepEntry(r, (0,), ()) for r in ids])           # one token each, then a decode step of n
+                runner.step([StepEntry(r, (0,), (0,)) for r in ids])
+                runner.step([StepEntry(r, (0,), (0,)) for r in ids])         # (the second one replays the captured step)
+                runner.end(ids)
+                done.append(n)
+            torch.cuda.synchronize(cache.device)
+        if cache.error_word is not None:
+            cache.error_word.zero_()
+        return done
+
     def kernel_times(self, reset: bool = False) -> dict[str, dict[str, float]]:
         """With ``profile_kernels``: milliseconds and launches per kernel class of the layers run so far (norm, qkv,
         rope_append, attention_prefill, attention_decode, o, gate_up, swiglu, down); and the step counters."""
@@ -177,17 +205,11 @@ class InferenceEngine:
             plan = self.scheduler.plan()
             if not plan.entries:
                 return []
-            if len(plan.entries) > 1 and all(e.kind == "decode" for e in plan.entries):
-                # Longest context first: the decode attention kernel gives every (request, kv head) a block, the
-                # hardware hands blocks out in order, and a long context that starts last is the step's tail.
-                # (The steps planned ahead of this one keep the order, so the captured step's slots stay as they are.)
-                ordered = tuple(sorted(plan.entries, key=lambda e: -e.start))
-                plan = StepPlan(plan.step, ordered, plan.preempted, plan.admitted)
-            current = self._launch(plan, False)
+            current = self._launch(_longest_first(plan), False)
         if self.config.async_scheduling and current.device_tokens is not None and self.runner.use_cuda_graphs:
             ahead = self.scheduler.plan_ahead(current.plan)
             if ahead is not None and len(current.drawing) == len(ahead.entries):
-                self._ahead = self._launch(ahead, True)
+                self._ahead = self._launch(_longest_first(ahead), True)
                 self.stats["steps_ahead"] += 1
         try:
             tokens = current.tokens()
@@ -305,6 +327,16 @@ class InferenceEngine:
             outputs.append(GenerateOutput(r.request_id, tuple(ids), self._decode(ids),
                                           reasons.get(r.request_id, "cancelled"), Usage(prompts[r.request_id], len(ids))))
         return outputs
+
+
+def _longest_first(plan: StepPlan) -> StepPlan:
+    """A step of decoded tokens only, longest context first: the decode attention kernel gives every (request, kv
+    head) a block, the hardware hands blocks out in order, and a long context that starts last is the step's tail.
+    (The order is stable from step to step, so the captured step's slots stay as they are.)"""
+    if len(plan.entries) < 2 or any(e.kind != "decode" for e in plan.entries):
+        return plan
+    ordered = tuple(sorted(plan.entries, key=lambda e: -e.start))
+    return plan if ordered == plan.entries else StepPlan(plan.step, ordered, plan.preempted, plan.admitted)
 
 
 def _default_cache_tokens(model, config: EngineConfig, limit: int) -> int:
