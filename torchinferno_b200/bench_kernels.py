@@ -97,6 +97,13 @@ def run_decode_attention(args) -> None:
                                               args.context, scratch=scratch, num_splits=splits, chunk=chunk, kernel=kernel)
             report(f"decode_attention[{kernel}]+merge", timer(fn), bytes_moved=kv_bytes, batch=n, context=args.context,
                    splits=splits, heads=h, kv_heads=k, head_dim=d)
+        if "tma" in kernels:      # the same from the unrotated rows of the qkv product: rotary and the cache write inside
+            qkv = torch.randn(n, (h + 2 * k) * d, device="cuda").to(torch.bfloat16)
+            inv_freq = (1.0 / (500000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).cuda()
+            fn = lambda: ops.decode_attention_rope(qkv, pool, out, q_start, kv_start, slots, table, n, h, k, d, 1 / math.sqrt(d),
+                                                   args.context, inv_freq, scratch=scratch, num_splits=splits)
+            report("decode_attention[tma, rotates and stores the newest token]+merge", timer(fn), bytes_moved=kv_bytes, batch=n,
+                   context=args.context, splits=splits, heads=h, kv_heads=k, head_dim=d)
 
 
 def run_prefill_attention(args) -> None:
@@ -131,6 +138,19 @@ def run_gemm(args) -> None:
         if ops.gemm_tcgen05_swapab_supports(args.rows, n, k):
             report(f"gemm_tcgen05_swapab[{name}]", timer(lambda: ops.gemm_tcgen05_swapab(x, w, out)), **common)
             w_kn = w.t().contiguous()
+            for features, splits in ((256, 1), (128, 1), (128, 2), (128, 4), (128, 5)):      # the few-rows kernel's tiles
+                if args.decode_config and (features, splits) != tuple(args.decode_config):
+                    continue
+                if ops.gemm_decode_supports(args.rows, n, k, features, splits):
+                    report(f"gemm_decode[{name}, {features} features, K over {splits}]",
+                           timer(lambda: ops.gemm_decode(x, w_kn, out, features=features, splits=splits)), **common)
+            if name == "gate_up":      # (the columns stand for interleaved gate / up pairs: the activation in the epilogue)
+                act = torch.empty(args.rows, n // 2, dtype=torch.bfloat16, device="cuda")
+                for features in (256, 128):
+                    if args.decode_config and features != args.decode_config[0]:
+                        continue
+                    report(f"gemm_decode[{name}, {features} features, SwiGLU epilogue]",
+                           timer(lambda: ops.gemm_decode(x, w_kn, act, features=features, splits=1, epilogue=ops.DG_SWIGLU)), **common)
             report(f"gemm_tcgen05_swapab_kn[{name}]", timer(lambda: ops.gemm_tcgen05_swapab(x, w_kn, out, w_kn=True)), **common)
             report(f"library_gemm_kn[{name}]", timer(lambda: torch.mm(x, w_kn, out=out)), **common)
             del w_kn
@@ -260,6 +280,8 @@ def main(argv=None) -> int:
     p.add_argument("--rows", type=int, default=8)
     p.add_argument("--only", nargs="*", default=None)
     p.add_argument("--iters", type=int, default=20)
+    p.add_argument("--decode-config", type=int, nargs=2, default=None, metavar=("FEATURES", "SPLITS"),
+                   help="of the few-rows kernel's configurations only this one")
     p.set_defaults(func=run_gemm)
     p = sub.add_parser("elementwise")
     p.add_argument("--rows", type=int, default=2048)

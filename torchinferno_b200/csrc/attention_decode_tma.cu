@@ -166,21 +166,26 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
       const uint32_t round = it / STAGES;
       const int key0 = kb + it * kDtBN;
       if (!waited && key0 + kDtBN > pos) {   // the tile that holds the newest token
+        // (what does not depend on the kernel before: the page of the newest position, cos and sin of its angles)
+        int page_new = -1;
+        if constexpr (ROPE) {
+          page_new = __ldg(table + (pos >> a.page_shift));
+          const int half = a.rot_dim >> 1;
+          for (int i = lane; i < half; i += 32) {
+            float sn, cn;
+            sincosf((float)pos * a.inv_freq[i], &sn, &cn);
+            cs_p[i] = cn;
+            cs_p[half + i] = sn;
+          }
+        }
         pdl_wait();
         waited = true;
         if constexpr (ROPE) {
           // this part holds the newest position: its key (rotated) and value go into their page first
-          const int page_new = __ldg(table + (pos >> a.page_shift));
           if (page_new < 0 || page_new >= a.num_pages) {
             if (a.error_word && lane == 0) atomicExch(a.error_word, 1 + entry);
           } else {
             const int half = a.rot_dim >> 1;
-            for (int i = lane; i < half; i += 32) {
-              float sn, cn;
-              sincosf((float)pos * a.inv_freq[i], &sn, &cn);
-              cs_p[i] = cn;
-              cs_p[half + i] = sn;
-            }
             __syncwarp();
             const __nv_bfloat16* ksrc = q + (size_t)row0 * a.q_stride + (size_t)(a.heads + kvh) * D;
             const __nv_bfloat16* vsrc = ksrc + (size_t)a.kv_heads * D;
@@ -238,9 +243,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
     // ----------------------------------------------------------------- consumers
     const int cw = warp - 1;                    // which 16 keys of every tile
     const int g_row = lane >> 2, tig = lane & 3;
-    pdl_wait();
-    if constexpr (ROPE) {
-      // the group's queries, rotated, into shared memory: 128 threads, a pair of dims each per pass
+    if constexpr (ROPE) {   // (cos and sin of the position's angles do not depend on the kernel before)
       const int ct = threadIdx.x - 32, half = a.rot_dim >> 1;
       for (int i = ct; i < half; i += 32 * kDtConsumers) {
         float sn, cn;
@@ -248,6 +251,11 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
         cs_s[i] = cn;
         cs_s[half + i] = sn;
       }
+    }
+    pdl_wait();
+    if constexpr (ROPE) {
+      // the group's queries, rotated, into shared memory: 128 threads, a pair of dims each per pass
+      const int ct = threadIdx.x - 32, half = a.rot_dim >> 1;
       asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kDtConsumers) : "memory");
       for (int w = ct; w < nrows * (D / 2); w += 32 * kDtConsumers) {
         const int r = w / (D / 2), i = w - r * (D / 2);
