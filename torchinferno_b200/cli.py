@@ -182,6 +182,8 @@ def run_llama_bench(args) -> int:
     if args.kv_cache_tokens is None:
         args.kv_cache_tokens = running * (args.input_len + args.output_len + args.page_size)
     with _bench_engine(args) as engine:
+        if args.warm_up:
+            engine.warm_up()          # (every batch size's decode step is captured before anything is timed)
         vocab = engine.model.spec.vocab_size
         g = torch.Generator().manual_seed(args.seed)
         count = args.num_prompts if throughput else args.batch_size
@@ -283,6 +285,7 @@ def build_parser() -> argparse.ArgumentParser:
     bench.add_argument("--seed", type=int, default=0)
     bench.add_argument("--benchmark", choices=["latency", "throughput"], default="latency")
     bench.add_argument("--num-prompts", type=int, default=64, help="throughput: requests submitted at once")
+    bench.add_argument("--warm-up", action="store_true", help="capture the decode step for every batch size before timing")
     bench.add_argument("--input-len-min", type=int, default=None,
                        help="prompt lengths are uniform in this .. --input-len (default: all --input-len)")
     bench.add_argument("--random-weights", action="store_true",
