@@ -469,6 +469,7 @@ def run_reference(args) -> dict:
             return b.elapsed_time(e), ids.numel() * ids.element_size()
         for _ in range(max(1, min(args.warmup, 3))):
             timed(2)
+        timed(1 + args.steps)      # (the first call at a length sets up what that length needs: not part of a step's time)
         mark = sampler.mark()
         short = timed(1)
         long = timed(1 + args.steps)
