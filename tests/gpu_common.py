@@ -14,10 +14,11 @@ F32_ATOL, F32_RTOL = 2e-5, 1e-4
 # (the measure of scripts/cmp_paged_dense_logits.py in the reference project, which expects
 # about 1 % in bf16 on a deep model).  Seen on the B200 with the tiny configurations: at most 0.0064 (twice
 # that is the bound); at the 8B layer sizes (two layers, width 4096, vocabulary 128256: the largest of far
-# more logits, each summed over far more terms): 0.0136 to 0.0143 for short prompts and for a 2,048-token
-# prompt followed by 64 decoded tokens alike.
+# more logits, each summed over far more terms): 0.0133 to 0.0143 for short prompts and for a 2,048-token
+# prompt followed by 64 decoded tokens alike, moving by a few per cent of itself with the kernels the measured
+# choice picks on a box (they sum in different orders); the bound there is 1.4 times the worst seen.
 BF16_REL = 0.0125
-BF16_REL_LARGE = 0.015
+BF16_REL_LARGE = 0.02
 
 
 # The largest error a test saw, as a share of its bound (printed at the end of the run, so that it shows how much

@@ -749,3 +749,31 @@ def test_temperature_sampling_draws_from_the_softmax():
     freq = torch.bincount(out.long(), minlength=5).double() / 20000
     want = torch.softmax(logits[0].double() / temp, dim=0)
     assert (freq - want).abs().max() < 0.012
+
+
+def test_the_library_plans_attention_and_products_for_both_ways_of_running_a_block():
+    """`tib_plan_attention` and `tib_plan_product` are where the kernels of a step are chosen, for the parts and for
+    the native block call: their answers on the shapes the engine meets."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    every = ops.ALLOW_PREFILL_TCGEN05 | ops.ALLOW_DECODE_ROTATES | ops.ALLOW_DECODE_TMA
+    plan = ops.plan_attention
+    # heads of 128 in groups of 4, pages of 16 back to back
+    assert plan(128, 4, 16, True, 8, 8, 0, every) == (ops.ATTENTION_NONE, ops.ATTENTION_DECODE_TMA_ROTATES)
+    assert plan(128, 4, 16, True, 9, 9, 0, every) == (ops.ATTENTION_NONE, ops.ATTENTION_DECODE_TMA)           # many requests
+    assert plan(128, 4, 16, True, 8, 7, 1, every) == (ops.ATTENTION_PREFILL_TCGEN05, ops.ATTENTION_DECODE_TMA)  # a portion among them
+    assert plan(128, 4, 16, True, 8, 8, 0, every & ~ops.ALLOW_DECODE_ROTATES)[1] == ops.ATTENTION_DECODE_TMA
+    assert plan(128, 4, 16, False, 8, 7, 1, every) == (ops.ATTENTION_PREFILL_MMA, ops.ATTENTION_DECODE_CP_ASYNC)  # pages not back to back
+    assert plan(128, 4, 16, True, 2, 0, 2, every & ~ops.ALLOW_PREFILL_TCGEN05) == (ops.ATTENTION_PREFILL_MMA, ops.ATTENTION_NONE)
+    assert plan(128, 4, 3, True, 2, 1, 1, every) == (ops.ATTENTION_PREFILL_MMA, ops.ATTENTION_DECODE_CP_ASYNC)   # pages of 3 tokens
+    assert plan(80, 4, 16, True, 2, 1, 1, every) == (ops.ATTENTION_PREFILL_MMA, ops.ATTENTION_DECODE_CP_ASYNC)   # heads of 80
+    assert plan(72, 4, 16, True, 2, 1, 1, every) == (ops.ATTENTION_SIMT, ops.ATTENTION_SIMT)                     # heads of 72
+    product = ops.plan_product
+    assert product(8, 4096, 4096, True, 64, 128, 4, False, True) == ops.PRODUCT_DECODE
+    assert product(8, 4096, 4096, True, 4, 128, 4, False, True) == ops.PRODUCT_LIBRARY      # more rows than the weight's bound
+    assert product(8, 4096, 4096, True, 64, 128, 4, False, False) == ops.PRODUCT_LIBRARY    # operands not aligned
+    assert product(8, 4096, 4096, True, 64, 128, 0, False, True) == ops.PRODUCT_SWAPAB      # no K split chosen: the older kernel
+    assert product(8, 4096, 4096, False, 64, 128, 4, False, True) == ops.PRODUCT_SWAPAB     # [out, in] weights
+    assert product(8, 28672, 4096, True, 64, 256, 1, True, True) == ops.PRODUCT_DECODE
+    assert product(8, 28672, 4096, True, 64, 128, 2, True, True) != ops.PRODUCT_DECODE      # the activation only unsplit
+    assert product(0, 4096, 4096, True, 64, 128, 4, False, True) == ops.PRODUCT_LIBRARY

@@ -27,6 +27,7 @@ int tib_prefill_attention_tcgen05(const void*, const void*, void*, const int*, c
                                   int, int, int, int, int, int64_t, int, int, float, int, int*, cudaStream_t);
 int tib_prefill_attention(const void*, const void*, void*, const int*, const int*, const int*, const int*, int, int, int, int,
                           int, int, int, int64_t, int, int, float, int, cudaStream_t);
+int tib_attention_mma_supports(int, int);
 int tib_decode_attention_tma_supports(int, int, int);
 int tib_decode_attention_tma(const void*, const void*, void*, float*, float*, const int*, const int*, const int*, const int*,
                              int, int, int, int, int, int, int64_t, int, int, float, int, int, int*, int*, cudaStream_t);
@@ -65,7 +66,8 @@ struct TibPrenormBlockWeights {
 struct TibPrenormBlockStep {
   int n_tokens, n_entries, max_q_len, n_single, n_multi;
   int decode_splits;
-  int decode_rotates;                    // 1: a step of single tokens goes to the decode kernel unrotated
+  int decode_rotates;                    // 1: a step of single tokens may go to the decode kernel unrotated
+  int own_launches;                      // (out) kernels of this library the call launched (library products not counted)
   const int* positions;
   const int* token_slot;
   const int* q_start;
@@ -144,6 +146,13 @@ struct TimedScope {
     TIB_TRY(call);                       \
   } while (0)
 
+// A launch of one of this library's own kernels (counted for the caller; the library products are not).
+#define TIB_OWN(kind, call)   \
+  do {                        \
+    TIB_TIMED(kind, call);    \
+    ++s->own_launches;        \
+  } while (0)
+
 // Switch the per-class timers on (1) or off (0); returns the setting before.
 TIB_API int tib_kernel_timers(int on) {
   KernelTimers& t = timers();
@@ -177,82 +186,145 @@ TIB_API int tib_kernel_timers_read(double* ms, long long* count, int n, int rese
   return KC_COUNT;
 }
 
-// out[n, N] = x[n, K] . w^T, w stored [N, K] or (kn) [K, N]: a hand-written few-rows kernel up to few_rows rows (the
-// one of gemm_decode.cu with its tile width and K split when splits > 0, else the swap-AB kernel), else the library.
-static int project(const void* x, const void* w, void* out, int n, int N, int K, int kn, int few_rows, int features, int splits,
-                   int stages, int* error_word, cudaStream_t stream) {
-  if (few_rows > 0 && n <= few_rows) {
-    if (kn && splits > 0 && tib_gemm_decode_supports(n, N, K, features, splits, 0))
-      return tib_gemm_decode(x, w, out, n, N, K, K, N, N, TIB_BF16, features, splits, 0, stages, error_word, stream);
-    if (tib_gemm_tcgen05_swapab_supports(n, N, K))
-      return tib_gemm_tcgen05_swapab(x, w, out, n, N, K, K, kn ? N : K, N, kn, TIB_BF16, 0, error_word, stream);
+// --- which kernel takes what ------------------------------------------------------------------------------------
+// Asked by this file and by the Python parts alike (kernels/attention.py, kernels/gemm.py), so that the two ways of
+// running a block cannot come to choose differently.
+
+// Attention of a step in bfloat16.  group: query heads per kv head; packed: the layer's pages lie back to back as
+// [2][kv_heads][page_size][head_dim]; allow: TIB_ALLOW_* bits (what the caller lets the plan use; rotary_table in
+// TIB_ALLOW_DECODE_ROTATES means the position encoding is a rotary table the decode kernel can apply itself).
+// *prefill, *decode: a TIB_ATTENTION_* kernel each, TIB_ATTENTION_NONE where the step has no such entries; where the
+// tensor-core kernels do not take the shape both are TIB_ATTENTION_SIMT (one kernel for the whole step).
+enum { TIB_ATTENTION_NONE = 0, TIB_ATTENTION_PREFILL_TCGEN05 = 1, TIB_ATTENTION_PREFILL_MMA = 2, TIB_ATTENTION_DECODE_TMA_ROTATES = 3,
+       TIB_ATTENTION_DECODE_TMA = 4, TIB_ATTENTION_DECODE_CP_ASYNC = 5, TIB_ATTENTION_SIMT = 6 };
+enum { TIB_ALLOW_PREFILL_TCGEN05 = 1, TIB_ALLOW_DECODE_ROTATES = 2, TIB_ALLOW_DECODE_TMA = 4 };
+// Single tokens go to the decode kernel unrotated in steps of up to this many requests.  With few requests the step
+// is a chain of short kernels and one link less is a gain (8 requests at 2,100 tokens, 8B sizes: 3.54 -> 3.51 ms a
+// step); with many the attention kernel streams long enough that the head start it has under the rotary kernel (older
+// keys are fetched while that runs) is worth more than the link (32 requests: 4.47 -> 4.52 ms, 64: 5.92 -> 6.01; 4 and
+// 16: no difference).
+constexpr int kDecodeRotatesMaxEntries = 8;
+
+TIB_API int tib_plan_attention(int head_dim, int group, int page_size, int packed, int n_entries, int n_single, int n_multi,
+                               int allow, int* prefill, int* decode) {
+  if (!prefill || !decode || group < 1 || n_entries < 0 || n_single < 0 || n_multi < 0) return TIB_E_ARG;
+  *prefill = *decode = TIB_ATTENTION_NONE;
+  if (!tib_attention_mma_supports(head_dim, group)) {
+    *prefill = *decode = TIB_ATTENTION_SIMT;
+    return TIB_OK;
   }
-  return tib_blas_gemm(x, w, out, n, N, K, K, kn ? N : K, N, kn, TIB_BF16, stream);
+  if (n_multi)
+    *prefill = (allow & TIB_ALLOW_PREFILL_TCGEN05) && packed && tib_prefill_attention_tcgen05_supports(head_dim, group, page_size)
+                   ? TIB_ATTENTION_PREFILL_TCGEN05 : TIB_ATTENTION_PREFILL_MMA;
+  if (n_single) {
+    const bool tma = (allow & TIB_ALLOW_DECODE_TMA) && packed && tib_decode_attention_tma_supports(head_dim, group, page_size);
+    if (tma && (allow & TIB_ALLOW_DECODE_ROTATES) && !n_multi && n_single == n_entries && n_entries <= kDecodeRotatesMaxEntries)
+      *decode = TIB_ATTENTION_DECODE_TMA_ROTATES;
+    else
+      *decode = tma ? TIB_ATTENTION_DECODE_TMA : TIB_ATTENTION_DECODE_CP_ASYNC;
+  }
+  return TIB_OK;
+}
+
+// A bf16 product of `rows` rows with a weight [N, K] or (kn) [K, N] that goes to a few-rows kernel up to few_rows rows
+// (0: never) with tiles of `features` and K over `splits` blocks (splits 0: the older swap-AB kernel); epilogue 1: the
+// weight holds gate and up columns interleaved and the activation is wanted; aligned: 16-byte pointers, row strides
+// that are multiples of 8.  Returns the kernel: TIB_PRODUCT_DECODE (gemm_decode.cu, with the activation in its
+// epilogue when asked), TIB_PRODUCT_SWAPAB (gemm_tcgen05.cu) or TIB_PRODUCT_LIBRARY (followed by the SwiGLU kernel when
+// the activation is wanted, as after TIB_PRODUCT_SWAPAB).
+enum { TIB_PRODUCT_LIBRARY = 0, TIB_PRODUCT_DECODE = 1, TIB_PRODUCT_SWAPAB = 2 };
+
+TIB_API int tib_plan_product(int rows, int N, int K, int kn, int few_rows, int features, int splits, int epilogue, int aligned) {
+  if (!(few_rows > 0 && rows > 0 && rows <= few_rows && aligned)) return TIB_PRODUCT_LIBRARY;
+  if (epilogue) {
+    if (kn && splits == 1 && tib_gemm_decode_supports(rows, N, K, features, 1, 1)) return TIB_PRODUCT_DECODE;
+  } else if (kn && splits > 0 && tib_gemm_decode_supports(rows, N, K, features, splits, 0)) {
+    return TIB_PRODUCT_DECODE;
+  }
+  return tib_gemm_tcgen05_swapab_supports(rows, N, K) ? TIB_PRODUCT_SWAPAB : TIB_PRODUCT_LIBRARY;
+}
+
+// out[n, N] = x[n, K] . w^T, w stored [N, K] or (kn) [K, N], by the kernel tib_plan_product names.
+static int project(const void* x, const void* w, void* out, int n, int N, int K, int kn, int few_rows, int features, int splits,
+                   int stages, int* error_word, int* own_launches, cudaStream_t stream) {
+  const int kernel = tib_plan_product(n, N, K, kn, few_rows, features, splits, 0, 1);
+  *own_launches += kernel != TIB_PRODUCT_LIBRARY;
+  switch (kernel) {
+    case TIB_PRODUCT_DECODE:
+      return tib_gemm_decode(x, w, out, n, N, K, K, N, N, TIB_BF16, features, splits, 0, stages, error_word, stream);
+    case TIB_PRODUCT_SWAPAB:
+      return tib_gemm_tcgen05_swapab(x, w, out, n, N, K, K, kn ? N : K, N, kn, TIB_BF16, 0, error_word, stream);
+    default:
+      return tib_blas_gemm(x, w, out, n, N, K, K, kn ? N : K, N, kn, TIB_BF16, stream);
+  }
 }
 
 // pending: the result of the block before (bf16 [n_tokens, hidden]) or null for the first.  pool: this layer's
 // pages [pages, 2, kv_heads, page_size, head_dim] (page_stride elements apart); window 0: every key.
-TIB_API int tib_prenorm_gqa_glu_block(const TibPrenormBlockWeights* w, const TibPrenormBlockStep* s, const void* pending, void* pool,
+TIB_API int tib_prenorm_gqa_glu_block(const TibPrenormBlockWeights* w, TibPrenormBlockStep* s, const void* pending, void* pool,
                             const int* block_table, int table_stride, int page_size, int64_t page_stride, int num_pages,
                             int window, cudaStream_t stream) {
   if (!w || !s || !pool || !block_table) return TIB_E_ARG;
   const int n = s->n_tokens;
+  s->own_launches = 0;
   if (n == 0) return TIB_OK;
   const int h = w->heads, k = w->kv_heads, d = w->head_dim, group = h / k;
   const int qkv_width = (h + 2 * k) * d, q_width = h * d;
   const bool packed = page_stride == (int64_t)2 * k * page_size * d;
 
-  TIB_TIMED(KC_NORM, tib_add_rmsnorm(pending, s->residual, nullptr, w->norm_mixer, s->normed, n, w->hidden, w->eps_mixer, TIB_BF16, stream));
-  TIB_TIMED(KC_QKV, project(s->normed, w->qkv, s->qkv, n, qkv_width, w->hidden, w->qkv_kn, w->qkv_few_rows, w->qkv_features, w->qkv_splits, w->qkv_stages, s->error_word, stream));
+  TIB_OWN(KC_NORM, tib_add_rmsnorm(pending, s->residual, nullptr, w->norm_mixer, s->normed, n, w->hidden, w->eps_mixer, TIB_BF16, stream));
+  TIB_TIMED(KC_QKV, project(s->normed, w->qkv, s->qkv, n, qkv_width, w->hidden, w->qkv_kn, w->qkv_few_rows, w->qkv_features, w->qkv_splits, w->qkv_stages, s->error_word, &s->own_launches, stream));
+  int prefill_kernel = 0, decode_kernel = 0;
+  TIB_TRY(tib_plan_attention(d, group, page_size, packed, s->n_entries, s->n_single, s->n_multi,
+                             TIB_ALLOW_PREFILL_TCGEN05 | TIB_ALLOW_DECODE_TMA | (s->decode_rotates ? TIB_ALLOW_DECODE_ROTATES : 0),
+                             &prefill_kernel, &decode_kernel));
+  if (prefill_kernel == TIB_ATTENTION_SIMT) return TIB_E_SIZE;      // (the caller keeps such shapes to the part-by-part sequence)
   // a step of single tokens only: the decode kernel rotates and stores the newest token itself (no rotary kernel)
-  const bool fused_rope = s->decode_rotates && !s->n_multi && s->n_single == s->n_entries && packed &&
-                          tib_decode_attention_tma_supports(d, group, page_size);
+  const bool fused_rope = decode_kernel == TIB_ATTENTION_DECODE_TMA_ROTATES;
   if (!fused_rope)
-    TIB_TIMED(KC_ROPE_APPEND, tib_rope_append(s->qkv, s->q, pool, s->positions, s->token_slot, block_table, table_stride, w->inv_freq, n, h, k, d,
+    TIB_OWN(KC_ROPE_APPEND, tib_rope_append(s->qkv, s->q, pool, s->positions, s->token_slot, block_table, table_stride, w->inv_freq, n, h, k, d,
                             w->rot_dim, w->interleaved, page_size, page_stride, num_pages, 1, s->error_word, TIB_BF16, stream));
-  if (s->n_multi) {
-    if (packed && tib_prefill_attention_tcgen05_supports(d, group, page_size))
-      TIB_TIMED(KC_ATTENTION_PREFILL, tib_prefill_attention_tcgen05(s->q, pool, s->attn, s->q_start, s->kv_start, s->slots, block_table, table_stride,
-                                            s->n_entries, s->max_q_len, n, h, k, d, page_size, page_stride, num_pages, window,
-                                            w->scale, s->n_single > 0, s->error_word, stream));
-    else
-      TIB_TIMED(KC_ATTENTION_PREFILL, tib_prefill_attention(s->q, pool, s->attn, s->q_start, s->kv_start, s->slots, block_table, table_stride,
-                                    s->n_entries, s->max_q_len, h, k, d, page_size, page_stride, num_pages, window, w->scale,
-                                    s->n_single > 0, stream));
-  }
-  if (s->n_single) {
+  if (prefill_kernel == TIB_ATTENTION_PREFILL_TCGEN05)
+    TIB_OWN(KC_ATTENTION_PREFILL, tib_prefill_attention_tcgen05(s->q, pool, s->attn, s->q_start, s->kv_start, s->slots, block_table, table_stride,
+                                          s->n_entries, s->max_q_len, n, h, k, d, page_size, page_stride, num_pages, window,
+                                          w->scale, s->n_single > 0, s->error_word, stream));
+  else if (prefill_kernel == TIB_ATTENTION_PREFILL_MMA)
+    TIB_OWN(KC_ATTENTION_PREFILL, tib_prefill_attention(s->q, pool, s->attn, s->q_start, s->kv_start, s->slots, block_table, table_stride,
+                                  s->n_entries, s->max_q_len, h, k, d, page_size, page_stride, num_pages, window, w->scale,
+                                  s->n_single > 0, stream));
+  if (decode_kernel != TIB_ATTENTION_NONE) {
     const int splits = s->decode_splits < 1 ? 1 : s->decode_splits;
     float* scratch_o = splits > 1 ? s->split_scratch : nullptr;
     float* scratch_ml = splits > 1 ? s->split_scratch + (size_t)s->n_entries * h * splits * d : nullptr;
     if (splits > 1 && !scratch_o) return TIB_E_ARG;
-    if (fused_rope)
-      TIB_TIMED(KC_ATTENTION_DECODE, tib_decode_attention_tma_rope(s->qkv, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots,
+    if (decode_kernel == TIB_ATTENTION_DECODE_TMA_ROTATES)
+      TIB_OWN(KC_ATTENTION_DECODE, tib_decode_attention_tma_rope(s->qkv, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots,
                                               block_table, table_stride, s->n_entries, h, k, d, page_size, page_stride, num_pages,
                                               window, w->scale, splits, 0, splits > 1 ? s->split_counters : nullptr, s->error_word,
                                               w->inv_freq, w->rot_dim, w->interleaved, stream));
-    else if (packed && tib_decode_attention_tma_supports(d, group, page_size))
-      TIB_TIMED(KC_ATTENTION_DECODE, tib_decode_attention_tma(s->q, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots, block_table,
+    else if (decode_kernel == TIB_ATTENTION_DECODE_TMA)
+      TIB_OWN(KC_ATTENTION_DECODE, tib_decode_attention_tma(s->q, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots, block_table,
                                        table_stride, s->n_entries, h, k, d, page_size, page_stride, num_pages, window, w->scale,
                                        splits, 0, splits > 1 ? s->split_counters : nullptr, s->error_word, stream));
     else
-      TIB_TIMED(KC_ATTENTION_DECODE, tib_decode_attention(s->q, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots, block_table,
+      TIB_OWN(KC_ATTENTION_DECODE, tib_decode_attention(s->q, pool, s->attn, scratch_o, scratch_ml, s->q_start, s->kv_start, s->slots, block_table,
                                    table_stride, s->n_entries, h, k, d, page_size, page_stride, num_pages, window, w->scale,
                                    splits, 0, stream));
   }
-  TIB_TIMED(KC_O, project(s->attn, w->o, s->o_out, n, w->hidden, q_width, w->o_kn, w->o_few_rows, w->o_features, w->o_splits, w->o_stages, s->error_word, stream));
-  TIB_TIMED(KC_NORM, tib_add_rmsnorm(s->o_out, s->residual, nullptr, w->norm_feed_forward, s->normed, n, w->hidden, w->eps_feed_forward,
+  TIB_TIMED(KC_O, project(s->attn, w->o, s->o_out, n, w->hidden, q_width, w->o_kn, w->o_few_rows, w->o_features, w->o_splits, w->o_stages, s->error_word, &s->own_launches, stream));
+  TIB_OWN(KC_NORM, tib_add_rmsnorm(s->o_out, s->residual, nullptr, w->norm_feed_forward, s->normed, n, w->hidden, w->eps_feed_forward,
                           TIB_BF16, stream));
   const int inter = w->intermediate;
   // gate and up rows are interleaved in the weight; at few rows the few-rows kernel writes silu(gate) * up itself
-  if (w->gate_up_kn && w->gate_up_few_rows > 0 && n <= w->gate_up_few_rows && w->gate_up_splits == 1 &&
-      tib_gemm_decode_supports(n, 2 * inter, w->hidden, w->gate_up_features, 1, 1)) {
-    TIB_TIMED(KC_GATE_UP, tib_gemm_decode(s->normed, w->gate_up, s->act, n, 2 * inter, w->hidden, w->hidden, 2 * inter, inter, TIB_BF16,
+  if (tib_plan_product(n, 2 * inter, w->hidden, w->gate_up_kn, w->gate_up_few_rows, w->gate_up_features, w->gate_up_splits, 1, 1) ==
+      TIB_PRODUCT_DECODE) {
+    TIB_OWN(KC_GATE_UP, tib_gemm_decode(s->normed, w->gate_up, s->act, n, 2 * inter, w->hidden, w->hidden, 2 * inter, inter, TIB_BF16,
                                           w->gate_up_features, 1, 1, w->gate_up_stages, s->error_word, stream));
   } else {
     TIB_TIMED(KC_GATE_UP, project(s->normed, w->gate_up, s->gate_up, n, 2 * inter, w->hidden, w->gate_up_kn, w->gate_up_few_rows,
-                                  w->gate_up_features, w->gate_up_splits, w->gate_up_stages, s->error_word, stream));
-    TIB_TIMED(KC_SWIGLU, tib_swiglu(s->gate_up, s->act, n, inter, TIB_BF16, 1, stream));
+                                  w->gate_up_features, w->gate_up_splits, w->gate_up_stages, s->error_word, &s->own_launches, stream));
+    TIB_OWN(KC_SWIGLU, tib_swiglu(s->gate_up, s->act, n, inter, TIB_BF16, 1, stream));
   }
-  TIB_TIMED(KC_DOWN, project(s->act, w->down, s->out, n, w->hidden, inter, w->down_kn, w->down_few_rows, w->down_features, w->down_splits, w->down_stages, s->error_word, stream));
+  TIB_TIMED(KC_DOWN, project(s->act, w->down, s->out, n, w->hidden, inter, w->down_kn, w->down_few_rows, w->down_features, w->down_splits, w->down_stages, s->error_word, &s->own_launches, stream));
   return TIB_OK;
 }

@@ -158,12 +158,6 @@ def linear(x: torch.Tensor, weight: "torch.Tensor | LinearWeight", *, out_dtype:
     return _linear_bf16(x, weight, out_dtype, out, few_rows)
 
 
-def _swapab_takes_kn(x: torch.Tensor, weight_kn: torch.Tensor) -> bool:
-    k, n = weight_kn.shape
-    return (x.stride(1) == 1 and weight_kn.stride(1) == 1 and x.stride(0) % 8 == 0 and weight_kn.stride(0) % 8 == 0
-            and weight_kn.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0 and ops.gemm_tcgen05_swapab_supports(x.shape[0], n, k))
-
-
 def linear_swiglu(x: torch.Tensor, weight: LinearWeight) -> torch.Tensor:
     """silu(gate) * up of the product with a weight whose rows are (gate i, up i) pairs: [tokens, out / 2].
     At few rows the few-rows kernel applies it in its epilogue; else the product is followed by the SwiGLU kernel."""
@@ -171,8 +165,9 @@ def linear_swiglu(x: torch.Tensor, weight: LinearWeight) -> torch.Tensor:
         raise ops.KernelError("linear_swiglu: the weight was not bound with epilogue='swiglu'")
     m, inter = x.shape[0], weight.out_features // 2
     w = weight.tensor
-    if (weight.transposed and _backend == "auto" and 0 < m <= weight.few_rows and weight.splits == 1 and x.dtype == torch.bfloat16
-            and _decode_takes(x, w, weight.features, 1, ops.DG_SWIGLU)):
+    if (weight.transposed and _backend == "auto" and x.dtype == torch.bfloat16
+            and ops.plan_product(m, weight.out_features, weight.in_features, True, weight.few_rows, weight.features, weight.splits,
+                                 True, _aligned(x, w)) == ops.PRODUCT_DECODE):
         act = torch.empty((m, inter), dtype=x.dtype, device=x.device)
         return ops.gemm_decode(x, w, act, features=weight.features, splits=1, epilogue=ops.DG_SWIGLU, stages=weight.stages,
                                error_word=_error_word)
@@ -181,11 +176,10 @@ def linear_swiglu(x: torch.Tensor, weight: LinearWeight) -> torch.Tensor:
     return ops.swiglu(gate_up, act, interleaved=True)
 
 
-def _decode_takes(x: torch.Tensor, weight_kn: torch.Tensor, features: int, splits: int, epilogue: int = 0) -> bool:
-    k, n = weight_kn.shape
-    return (x.stride(1) == 1 and weight_kn.stride(1) == 1 and x.stride(0) % 8 == 0 and weight_kn.stride(0) % 8 == 0
-            and weight_kn.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0
-            and ops.gemm_decode_supports(x.shape[0], n, k, features, splits, epilogue))
+def _aligned(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """What the TMA copies of the few-rows kernels ask of their operands."""
+    return (x.stride(1) == 1 and weight.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+            and weight.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0)
 
 
 def _linear_kn(x: torch.Tensor, weight_kn: torch.Tensor, out_dtype: torch.dtype, out: torch.Tensor | None,
@@ -200,10 +194,12 @@ def _linear_kn(x: torch.Tensor, weight_kn: torch.Tensor, out_dtype: torch.dtype,
         raise ops.KernelError(f"linear: unsupported output dtype {out_dtype}")
     if out is None or out.dtype != out_dtype:
         out = torch.empty((x.shape[0], weight_kn.shape[1]), dtype=out_dtype, device=x.device)
-    if _backend == "auto" and 0 < x.shape[0] <= few_rows:
-        if splits > 0 and _decode_takes(x, weight_kn, features, splits):
+    if _backend == "auto":      # (which kernel: decided where the native block call decides it too)
+        k, n = weight_kn.shape
+        kernel = ops.plan_product(x.shape[0], n, k, True, few_rows, features, splits, False, _aligned(x, weight_kn))
+        if kernel == ops.PRODUCT_DECODE:
             return ops.gemm_decode(x, weight_kn, out, features=features, splits=splits, stages=stages, error_word=_error_word)
-        if _swapab_takes_kn(x, weight_kn):
+        if kernel == ops.PRODUCT_SWAPAB:
             return ops.gemm_tcgen05_swapab(x, weight_kn, out, _error_word, w_kn=True)
     return ops.library_gemm(x, weight_kn, out, w_kn=True)
 
@@ -416,8 +412,8 @@ def _linear_bf16(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
     k = x.shape[1]
     if _backend != "library" and out_dtype in (torch.bfloat16, torch.float32):
         rows = few_rows if _backend == "auto" else 64
-        aligned = x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
-        if aligned and m <= rows and ops.gemm_tcgen05_swapab_supports(m, n, k):
+        aligned = _aligned(x, weight)
+        if ops.plan_product(m, n, k, False, rows, 128, 0, False, aligned) == ops.PRODUCT_SWAPAB:
             if out is None or out.dtype != out_dtype:
                 out = torch.empty((m, n), dtype=out_dtype, device=x.device)
             return ops.gemm_tcgen05_swapab(x, weight, out, _error_word)

@@ -30,7 +30,7 @@ class BlockWeights(Structure):
 
 
 class BlockStep(Structure):
-    _fields_ = [(name, c_int) for name in ("n_tokens", "n_entries", "max_q_len", "n_single", "n_multi", "decode_splits", "decode_rotates")] + \
+    _fields_ = [(name, c_int) for name in ("n_tokens", "n_entries", "max_q_len", "n_single", "n_multi", "decode_splits", "decode_rotates", "own_launches")] + \
                [(name, c_void_p) for name in ("positions", "token_slot", "q_start", "kv_start", "slots", "residual", "normed",
                                               "qkv", "q", "attn", "o_out", "gate_up", "act", "out", "split_scratch",
                                               "split_counters", "error_word")]
@@ -115,7 +115,7 @@ class StepWorkspace:
         s.n_tokens, s.n_entries, s.max_q_len, s.n_single, s.n_multi = n, batch.n_entries, batch.max_q_len, batch.n_single, batch.n_multi
         s.decode_splits = splits
         from torchinferno_b200.kernels import attention
-        s.decode_rotates = int(attention.DECODE_ROTATES and batch.n_entries <= attention.DECODE_ROTATES_MAX_ENTRIES)
+        s.decode_rotates = int(attention.DECODE_ROTATES)
         for name in ("positions", "token_slot", "q_start", "kv_start", "slots"):
             setattr(s, name, getattr(batch, name).data_ptr())
         s.residual = residual.data_ptr()
@@ -144,12 +144,5 @@ def run_block(w: BlockWeights, stream_state, ctx, window: int | None) -> None:
     if status:
         raise ops.KernelError(f"native block: status {status} (negative: refused arguments; 20000 + n: cuBLAS status n; "
                               f"else a CUDA error at launch)")
-    # this library's own kernels among them: two norms, rotary, SwiGLU, one or two attention kernels, and the
-    # projections that the swap-AB kernel takes (the library products are not counted)
-    own_products = sum(1 for rows in (w.qkv_few_rows, w.o_few_rows, w.gate_up_few_rows, w.down_few_rows) if 0 < batch.n_tokens <= rows)
-    fused_swiglu = 0 < batch.n_tokens <= w.gate_up_few_rows and w.gate_up_splits == 1 and w.gate_up_kn
-    fused_rope = (ws.step.decode_rotates and not batch.n_multi and batch.n_single == batch.n_entries
-                  and kv.pool.stride(0) == 2 * w.kv_heads * kv.page_size * w.head_dim
-                  and ops.decode_attention_tma_supports(w.head_dim, w.heads // w.kv_heads, kv.page_size))
-    ops.count_launches(5 - int(fused_swiglu) - int(fused_rope) + (1 if batch.n_single and batch.n_multi else 0) + own_products)
+    ops.count_launches(ws.step.own_launches)      # this library's own kernels among them (the library products are not counted)
     stream_state.pending = ws.buffers["out"]

@@ -118,7 +118,8 @@ def lib() -> ctypes.CDLL:
                    "tib_kernel_timers", "tib_kernel_timers_read",
                    "tib_blas_init", "tib_blas_gemm", "tib_gemm_tcgen05_2cta", "tib_gemm_tcgen05_2cta_supports",
                    "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
-                   "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports", "tib_gemm_decode", "tib_gemm_decode_supports"):
+                   "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports", "tib_gemm_decode", "tib_gemm_decode_supports",
+                   "tib_plan_attention", "tib_plan_product"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
     return library
@@ -380,6 +381,32 @@ def decode_split(n_entries: int, heads: int, kv_heads: int, max_kv_len: int, tar
     return -(-tiles // per), per * 64
 
 
+# What tib_plan_attention answers (csrc/block.cu), and what it may be allowed to use.
+ATTENTION_NONE, ATTENTION_PREFILL_TCGEN05, ATTENTION_PREFILL_MMA, ATTENTION_DECODE_TMA_ROTATES, ATTENTION_DECODE_TMA, \
+    ATTENTION_DECODE_CP_ASYNC, ATTENTION_SIMT = range(7)
+ALLOW_PREFILL_TCGEN05, ALLOW_DECODE_ROTATES, ALLOW_DECODE_TMA = 1, 2, 4
+PRODUCT_LIBRARY, PRODUCT_DECODE, PRODUCT_SWAPAB = 0, 1, 2
+
+
+def plan_attention(head_dim: int, group: int, page_size: int, packed: bool, n_entries: int, n_single: int, n_multi: int,
+                   allow: int) -> tuple[int, int]:
+    """(kernel for the portions of prompts, kernel for the single tokens) of a bfloat16 step, as the CUDA library
+    chooses them: the one place where that is decided, for the part-by-part sequence and the native block alike."""
+    prefill, decode = c_int(0), c_int(0)
+    _check("plan_attention", lib().tib_plan_attention(c_int(head_dim), c_int(group), c_int(page_size), c_int(int(packed)),
+                                                      c_int(n_entries), c_int(n_single), c_int(n_multi), c_int(allow),
+                                                      ctypes.byref(prefill), ctypes.byref(decode)))
+    return prefill.value, decode.value
+
+
+def plan_product(rows: int, n: int, k: int, kn: bool, few_rows: int, features: int, splits: int, swiglu: bool,
+                 aligned: bool) -> int:
+    """The kernel a bf16 product of ``rows`` rows goes to (PRODUCT_*), chosen in the same place for both ways of
+    running a block."""
+    return int(lib().tib_plan_product(c_int(rows), c_int(n), c_int(k), c_int(int(kn)), c_int(few_rows), c_int(features),
+                                      c_int(splits), c_int(int(swiglu)), c_int(int(aligned))))
+
+
 def decode_num_splits(n_entries: int, heads: int, kv_heads: int, max_kv_len: int | None = None,
                       target_blocks: int = 256) -> int:
     """How many parts the grid provides for each request's context when the kernel sizes the parts itself.
@@ -431,7 +458,8 @@ def decode_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, q_s
     if kernel not in ("auto", "tma", "cp_async"):
         raise KernelError(f"decode_attention: no kernel {kernel!r}")
     packed = pool.stride(0) == 2 * kv_heads * pool.shape[3] * head_dim
-    tma = kernel != "cp_async" and packed and decode_attention_tma_supports(head_dim, heads // kv_heads, pool.shape[3])
+    tma = plan_attention(head_dim, heads // kv_heads, pool.shape[3], packed, n_entries, n_entries, 0,
+                         0 if kernel == "cp_async" else ALLOW_DECODE_TMA)[1] == ATTENTION_DECODE_TMA
     if kernel == "tma" and not tma:
         raise KernelError("decode_attention: the TMA kernel does not take this shape "
                           f"(head_dim {head_dim}, group {heads // kv_heads}, pages of {pool.shape[3]}, packed={packed})")
