@@ -55,6 +55,13 @@ enum TibRequestRecord : int {
 
 namespace tib {
 
+// The two halves of a bf16 pair as floats, by shift and mask (a bf16 is the upper half of the float it stands for).
+// `__bfloat1622float2` compiles to two conversion instructions here, which run on the special-function unit at an
+// eighth of the rate: in a kernel that only unpacks, computes a little and packs, that unit was 61 % busy.
+__device__ __forceinline__ float2 bf16x2_floats(const __nv_bfloat162 v) {
+  const uint32_t u = *reinterpret_cast<const uint32_t*>(&v);
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -90,7 +90,7 @@ add_rmsnorm_bf16x8_kernel(const __nv_bfloat16* __restrict__ delta, float* __rest
       const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(d2[i]);
+        const float2 f = bf16x2_floats(d2[i]);
         h[2 * i] += f.x;
         h[2 * i + 1] += f.y;
       }
@@ -178,15 +178,15 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, 
     if (interleaved) {
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        const float2 p0 = __bfloat1622float2(a2[2 * k]), p1 = __bfloat1622float2(a2[2 * k + 1]);
-        const float2 q0 = __bfloat1622float2(b2[2 * k]), q1 = __bfloat1622float2(b2[2 * k + 1]);
+        const float2 p0 = bf16x2_floats(a2[2 * k]), p1 = bf16x2_floats(a2[2 * k + 1]);
+        const float2 q0 = bf16x2_floats(b2[2 * k]), q1 = bf16x2_floats(b2[2 * k + 1]);
         o2[k] = __floats2bfloat162_rn(silu_fast(p0.x) * p0.y, silu_fast(p1.x) * p1.y);
         o2[2 + k] = __floats2bfloat162_rn(silu_fast(q0.x) * q0.y, silu_fast(q1.x) * q1.y);
       }
     } else {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const float2 g = __bfloat1622float2(a2[k]), u = __bfloat1622float2(b2[k]);
+        const float2 g = bf16x2_floats(a2[k]), u = bf16x2_floats(b2[k]);
         o2[k] = __floats2bfloat162_rn(silu_fast(g.x) * u.x, silu_fast(g.y) * u.y);
       }
     }

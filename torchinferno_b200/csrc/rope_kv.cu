@@ -177,7 +177,7 @@ rope_append_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
         *reinterpret_cast<float4*>(sv + 4) = *reinterpret_cast<const float4*>(cs + half + c + 4);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const float2 lo = __bfloat1622float2(l2[k]), hi = __bfloat1622float2(h2[k]);
+          const float2 lo = bf16x2_floats(l2[k]), hi = bf16x2_floats(h2[k]);
           const float c0 = cv[2 * k], c1 = cv[2 * k + 1], s0 = sv[2 * k], s1 = sv[2 * k + 1];
           lo2[k] = __floats2bfloat162_rn(rope_lo(lo.x, hi.x, c0, s0), rope_lo(lo.y, hi.y, c1, s1));
           hi2[k] = __floats2bfloat162_rn(rope_hi(lo.x, hi.x, c0, s0), rope_hi(lo.y, hi.y, c1, s1));
