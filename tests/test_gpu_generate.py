@@ -151,6 +151,70 @@ def test_many_requests_on_a_tight_pool_do_not_depend_on_how_they_are_scheduled(m
     assert preempted > 0                                   # the tight pools really ran out
 
 
+def _random_round(model_folders, draw):
+    """Draw number ``draw`` of a random search over schedules, in float32: a tiny configuration, 8 to 30 requests
+    of random lengths, budgets, temperatures and (for some) a stop token that occurs, run once with room and once
+    under a random schedule on a pool that may be tight.  Returns (tokens and reasons with room, the same under the
+    schedule, the schedule, preemptions)."""
+    import random
+    from torchinferno_b200.engine.types import GenerateRequest, SamplingConfig
+    rng = random.Random(1000 + draw)
+    name = rng.choice("ABCDE")
+    config, seed = TINY[name]
+    top = min(120, config["max_position_embeddings"] // 2)
+    n = rng.randint(8, 30)
+    lengths = [rng.randint(1, top) for _ in range(n)]
+    prompts = list(requests_for(config, seed + draw, lengths).values())
+    budgets = [rng.randint(1, min(40, config["max_position_embeddings"] - l - 1)) for l in lengths]
+    temps = [0.0 if rng.random() < 0.5 else rng.choice([0.5, 0.9, 1.3]) for _ in prompts]
+    page = rng.choice([4, 8, 16, 32])
+
+    def make(stops):
+        return [GenerateRequest(f"s{i}", prompt_token_ids=p, sampling=SamplingConfig(budgets[i], temps[i], stops[i], 7000 + 13 * i + draw))
+                for i, p in enumerate(prompts)]
+
+    with engine_for(model_folders[name], "float32", page_size=page, max_batch_size=4, kv_cache_tokens=4096) as engine:
+        roomy = engine.generate_many(make([()] * n))
+        stops = [(o.token_ids[len(o.token_ids) // 2],) if rng.random() < 0.3 and len(o.token_ids) > 2 else () for o in roomy]
+        want = engine.generate_many(make(stops))
+    longest = max(l + b for l, b in zip(lengths, budgets))
+    need = -(-longest // page) * page
+    way = dict(async_scheduling=rng.random() < 0.7, max_batch_size=rng.randint(1, 12),
+               kv_cache_tokens=max(need + page, rng.randint(need, 6 * need)), max_num_batched_tokens=rng.randint(8, 200),
+               prefill_chunk_size=rng.randint(2, 64), page_size=page)
+    with engine_for(model_folders[name], "float32", **way) as engine:
+        got = engine.generate_many(make(stops))
+        preemptions = engine.scheduler.stats["preemptions"]
+        engine.runner.cache.audit()
+        assert engine.runner.cache.free_pages() == [engine.runner.cache.num_pages]
+    return [(o.token_ids, o.finish_reason) for o in want], [(o.token_ids, o.finish_reason) for o in got], way, preemptions
+
+
+@pytest.mark.parametrize("draw", [395, 95, 70, 285])
+def test_a_recomputation_that_ends_one_token_short_feeds_that_token_from_the_host(model_folders, draw):
+    """Draws of the random search below that found this: a preempted request whose recomputation, cut into portions,
+    ends exactly one token short of its sequence goes on with a decode step for the token it had last generated.
+    That token is known to the host and was never drawn on the device since the request was opened again, so the
+    step must take it from the host, not from the request's record (which then held no token: the embedding of "no
+    token" is NaN, and the request went on with token 0)."""
+    need_gpu()
+    want, got, way, preemptions = _random_round(model_folders, draw)
+    assert preemptions > 0
+    assert got == want, way
+
+
+def test_random_schedules_give_every_request_the_tokens_it_gets_with_room(model_folders):
+    """Thirty draws of the random search (other than the ones above): whatever the schedule, in float32 every request
+    gets exactly the tokens and the finish reason it gets with room; no page is lost on the way."""
+    need_gpu()
+    preempted = 0
+    for draw in range(30):
+        want, got, way, preemptions = _random_round(model_folders, draw)
+        preempted += preemptions
+        assert got == want, (draw, way)
+    assert preempted > 20
+
+
 def test_schedules_in_bfloat16_on_the_default_path_give_the_same_tokens(model_folders):
     """Config D (head size 64: tcgen05 prompt attention, TMA decode attention, the native block call, captured
     decode steps, steps launched ahead) in bfloat16 with the library's products, which makes the kernels of a row

@@ -224,9 +224,13 @@ class InferenceEngine:
         runner, cache = self.runner, self.runner.cache
         with torch.inference_mode():
             # a step of decoded tokens only takes its inputs from the requests' records on the device, where the
-            # sampler left them: nothing but new block-table entries is copied
+            # sampler left them: nothing but new block-table entries is copied.  (Not every decoded token is there: a
+            # recomputation after a preemption may end one token short of the sequence, and that last token, which
+            # the host knows, was never drawn on the device since.)
+            requests = [self.scheduler.request(e.request_id) for e in plan.entries]
             fed_by_device = ahead or (runner.use_cuda_graphs and runner._graph_ok
-                                      and all(e.kind == "decode" and e.request_id in cache for e in plan.entries))
+                                      and all(e.kind == "decode" and e.request_id in cache and r is not None and r.token_on_device
+                                              for e, r in zip(plan.entries, requests)))
             try:
                 if fed_by_device:
                     logits = runner.decode_ahead([e.request_id for e in plan.entries])
@@ -251,7 +255,9 @@ class InferenceEngine:
             self.stats["h2d_bytes"] += batch.h2d_bytes
             self.stats["tokens"] += batch.n_tokens
             drawing = [e for e in plan.entries if e.samples]
-            requests = [self.scheduler.request(e.request_id) for e in plan.entries]
+            for e, r in zip(plan.entries, requests):
+                if r is not None:
+                    r.token_on_device = e.samples      # (the sampler below leaves the token it draws in the record)
             if not drawing:
                 return _Launched(plan, requests, [], None, cache.error_word)
             tokens = self.sampler.sample_records(logits, cache.request_records, batch.logit_slots)

@@ -51,6 +51,10 @@ class SchedulerRequest:
     admitted_at: int = -1        # admission counter; larger is younger
     preemptions: int = 0
     finish_reason: str | None = None
+    # The request's record on the device holds its last token: the sampler drew it in the last step that ran the
+    # request.  Kept by whoever runs the steps; false again after a preemption, and after a recomputation that ends
+    # one token short of the sequence (that token is known, so nothing is drawn for it).
+    token_on_device: bool = False
 
     @property
     def tokens(self) -> list[int]:
@@ -196,6 +200,7 @@ class Scheduler:
                     room[g] += after - before
             victim.computed = 0
             victim.preemptions += 1
+            victim.token_on_device = False
             self.waiting.appendleft(victim)
             preempted.append(victim.request_id)
             self.stats["preemptions"] += 1
