@@ -777,3 +777,109 @@ def test_the_library_plans_attention_and_products_for_both_ways_of_running_a_blo
     assert product(8, 28672, 4096, True, 64, 256, 1, True, True) == ops.PRODUCT_DECODE
     assert product(8, 28672, 4096, True, 64, 128, 2, True, True) != ops.PRODUCT_DECODE      # the activation only unsplit
     assert product(0, 4096, 4096, True, 64, 128, 4, False, True) == ops.PRODUCT_LIBRARY
+
+
+def test_attention_kernels_on_random_shapes_and_batches():
+    """Eighty draws of a random search over the attention kernels: head sizes, numbers of heads and groups, page
+    sizes, windows, forced splits and ragged batches that no list in this file names, each against the float64
+    plain attention; a shape a kernel does not take is passed over."""
+    need_gpu()
+    import random
+    from torchinferno_b200.kernels import ops
+    ran = {}
+    for draw in range(80):
+        rng = random.Random(77000 + draw)
+        kernel = rng.choice(["simt32", "simt16", "mma", "mma_prefill", "tcgen05_prefill", "tma"])
+        kv = rng.randint(1, 4)
+        if kernel.startswith("simt"):
+            d, group, page = rng.choice([8, 16, 24, 40, 64, 72, 96, 128, 160, 256]), rng.randint(1, 9), rng.choice([1, 2, 3, 4, 5, 8, 16, 32, 64])
+        elif kernel in ("mma", "mma_prefill"):
+            d, group = rng.choice([16, 32, 48, 64, 80, 96, 112, 128]), rng.choice([1, 2, 3, 4, 5, 7, 8, 12, 16, 20, 33, 64])
+            page = rng.choice([1, 2, 3, 4, 5, 8, 16, 32, 64])
+            if not ops.attention_mma_supports(d, group):
+                continue
+        else:
+            d, group = rng.choice([64, 128]), rng.choice([1, 2, 3, 4, 5, 7, 8, 12, 16])
+            page = rng.choice([8, 16, 32, 64, 128] if kernel == "tcgen05_prefill" else [8, 16, 32, 64])
+            takes = ops.prefill_attention_tcgen05_supports if kernel == "tcgen05_prefill" else ops.decode_attention_tma_supports
+            if not takes(d, group, page):
+                continue
+        heads = kv * group
+        if heads * d > 8192:
+            continue
+        entries = []
+        for _ in range(rng.randint(1, 6)):
+            r = rng.random()
+            entries.append((rng.randint(0, 900), 1) if r < 0.35 else (0, rng.randint(1, 300)) if r < 0.5 else
+                           (rng.randint(0, 500), rng.randint(2, 200)))
+        window = rng.choice([0, 0, 0, 1, 7, 64, 65, 130, 400])
+        splits = (rng.choice([1, 2, 3, 5, 8, 16, 32]), 0) if kernel in ("mma", "tma") and rng.random() < 0.5 else None
+        dtype = torch.float32 if kernel == "simt32" else torch.bfloat16
+        out, ref = attention_case(dtype, heads, kv, d, page, entries, window=window, seed=draw,
+                                  kernel="simt" if kernel.startswith("simt") else kernel, splits=splits)
+        what = (draw, kernel, heads, kv, d, page, window, splits, entries)
+        assert torch.isfinite(out).all(), what
+        assert torch.allclose(out.double(), ref, **(dict(atol=3e-6, rtol=1e-5) if dtype == torch.float32 else BF16_ATTN)), what
+        ran[kernel] = ran.get(kernel, 0) + 1
+    assert len(ran) == 6 and min(ran.values()) >= 5, ran
+
+
+def test_product_kernels_on_random_shapes():
+    """Two hundred draws of a random search over the product kernels (the two tcgen05 kernels for many rows, the two
+    for few rows with either weight layout, tile width, K split, ring depth and the SwiGLU epilogue, the library in
+    both layouts, the 32-bit kernel), each against float64; NaN in the output beforehand shows what was not written."""
+    need_gpu()
+    import random
+    from torchinferno_b200.kernels import ops
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ran = {}
+    for draw in range(200):
+        rng = random.Random(31000 + draw)
+        kind = rng.choice(["tcgen05", "2cta", "swapab", "swapab_kn", "decode", "decode_swiglu", "library", "library_kn", "f32"])
+        g = torch.Generator().manual_seed(draw)
+        few = kind in ("swapab", "swapab_kn", "decode", "decode_swiglu")
+        m = rng.randint(1, 64) if few else rng.choice([1, 2, 7, 64, 100, 129, 256, 300, 513, 1000])
+        n = rng.choice([8, 16, 24, 64, 72, 128, 136, 200, 256, 264, 512, 1000, 1024, 3072, 4104])
+        k = rng.choice([64, 128, 192, 256, 320, 1024, 2048, 4096])
+        out_dtype = rng.choice([torch.bfloat16, torch.float32])
+        blank = lambda width, dtype: torch.full((m, width), float("nan"), dtype=dtype, device="cuda")
+        if kind == "f32":
+            n, k = rng.choice([1, 3, 64, 67, 129, 500]), rng.choice([1, 7, 64, 100, 257, 1000])
+            x, w = torch.randn(m, k, generator=g).cuda(), torch.randn(n, k, generator=g).cuda()
+            out, want, rel = ops.gemm_f32(x, w, blank(n, torch.float32)), as_ref(x) @ as_ref(w).T, 1e-5
+        else:
+            x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+            kn = kind in ("swapab_kn", "decode", "decode_swiglu", "library_kn")
+            w = (torch.randn((k, n) if kn else (n, k), generator=g) * 0.05).to(torch.bfloat16).cuda()
+            want = as_ref(x) @ (as_ref(w) if kn else as_ref(w).T)
+            if kind in ("decode", "decode_swiglu"):
+                features = rng.choice([128, 256])
+                splits = rng.randint(1, 8) if features == 128 and kind == "decode" else 1
+                epilogue = ops.DG_SWIGLU if kind == "decode_swiglu" else ops.DG_PLAIN
+                if not ops.gemm_decode_supports(m, n, k, features, splits, epilogue):
+                    continue
+                if epilogue == ops.DG_SWIGLU:
+                    want, out_dtype = want[:, 0::2] / (1 + torch.exp(-want[:, 0::2])) * want[:, 1::2], torch.bfloat16
+                out = ops.gemm_decode(x, w, blank(want.shape[1], out_dtype), features=features, splits=splits, epilogue=epilogue,
+                                      stages=rng.choice([0, 0, 1, 2, 3, 5, 9, 16]), error_word=err)
+            elif kind in ("swapab", "swapab_kn"):
+                if not ops.gemm_tcgen05_swapab_supports(m, n, k):
+                    continue
+                out = ops.gemm_tcgen05_swapab(x, w, blank(n, out_dtype), err, w_kn=kn)
+            elif kind in ("library", "library_kn"):
+                out = ops.library_gemm(x, w, blank(n, out_dtype), w_kn=kn)
+            elif kind == "tcgen05":
+                if not ops.gemm_tcgen05_supports(m, n, k):
+                    continue
+                out = ops.gemm_tcgen05(x, w, blank(n, out_dtype), err)
+            else:
+                if not ops.gemm_tcgen05_2cta_supports(m, n, k):
+                    continue
+                out = ops.gemm_tcgen05_2cta(x, w, blank(n, out_dtype), err)
+            rel = 1.2e-2 if out.dtype == torch.bfloat16 else 2e-4
+        what = (draw, kind, m, n, k, out.dtype)
+        assert torch.isfinite(out).all(), what
+        assert (as_ref(out) - want).abs().max() <= rel * want.abs().max() + 1e-6, what
+        assert int(err) == 0, what
+        ran[kind] = ran.get(kind, 0) + 1
+    assert len(ran) == 9 and min(ran.values()) >= 5, ran
