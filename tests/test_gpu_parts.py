@@ -564,6 +564,135 @@ def test_a_toy_mixer_with_keys_narrower_than_values_and_a_stage_after_the_embedd
         unregister_architecture("Toy3ForCausalLM")
 
 
+def test_a_toy_norm_and_a_toy_arrangement_of_a_block_are_registered_and_stepped(tmp_path):
+    """The two kinds of part the other toy tests leave alone, defined here and unknown to the framework: a norm with
+    a mean and a bias (y = (x - mean) / sqrt(var + eps) * w + b, its own way of folding the pending delta in), and a
+    block that arranges its parts differently: one norm, whose rows go to the mixer and to the feed-forward side by
+    side, and one add (h = h + mixer(n(h)) + feed_forward(n(h))).  The first layer is such a block, the second the
+    framework's pre-norm block with the toy norm in both places.  Stepped whole, in portions and mixed, against plain
+    arithmetic."""
+    need_gpu()
+    from torchinferno_b200.config.registry import ArchitectureEntry, register_architecture, unregister_architecture
+    from torchinferno_b200.engine.batch import StepEntry
+    from torchinferno_b200.engine.factory import load_model, make_runner
+    from torchinferno_b200.models.spec import BlockSpec, LayerCall, ModelSpec
+    from torchinferno_b200.parts.base import Block, Norm, PartSpec, WeightSpec, build_part, register_part, unregister_part
+    from torchinferno_b200.weights.random_init import write_random_model
+    WIDTH, INTER, HEADS, KV, D, EPS = 40, 24, 4, 2, 16, 1e-4
+
+    class CenteredNorm(Norm):
+        def __init__(self, *, width, eps, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            self.width, self.eps = width, eps
+
+        def weight_specs(self):
+            return [WeightSpec("weight", (self.width,), init="normal", std=0.5, role="vector"),
+                    WeightSpec("bias", (self.width,), init="normal", std=0.3, role="vector")]
+
+        def bind(self, weights):
+            self.weight, self.bias = weights["weight"].float(), weights["bias"].float()
+
+        def forward(self, residual, out, rows=None):
+            x = residual if rows is None else residual[rows.long()]
+            centred = x - x.mean(-1, keepdim=True)
+            out.copy_((centred * torch.rsqrt(centred.square().mean(-1, keepdim=True) + self.eps) * self.weight + self.bias).to(out.dtype))
+            return out
+
+        def add_forward(self, delta, residual, out, rows=None):
+            if rows is None:
+                residual += delta.float()                       # the stream takes the delta for good
+                return self.forward(residual, out)
+            chosen = rows.long()                                # only looked at: the stream keeps the delta pending
+            return self.forward((residual[chosen] + delta[chosen].float()).contiguous(), out)
+
+    class SideBySideBlock(Block):
+        def __init__(self, *, mixer, feed_forward, norm, dtype, device):
+            super().__init__(dtype=dtype, device=device)
+            as_spec = lambda v: v if isinstance(v, PartSpec) else PartSpec(**v)
+            self.specs = {"mixer": as_spec(mixer), "feed_forward": as_spec(feed_forward), "norm": as_spec(norm)}
+            self.mixer = build_part("mixer", self.specs["mixer"], dtype=dtype, device=device)
+            self.feed_forward = build_part("feed_forward", self.specs["feed_forward"], dtype=dtype, device=device)
+            self.norm = build_part("norm", self.specs["norm"], dtype=dtype, device=device)
+
+        def named_parts(self):
+            return [(self.specs[k].prefix, getattr(self, k)) for k in ("norm", "mixer", "feed_forward")]
+
+        def forward(self, stream, ctx):
+            rows = stream.normed(self.norm)
+            stream.add(self.mixer.forward(rows, ctx) + self.feed_forward.forward(rows, ctx))
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyConfig:
+        vocab_size: int
+
+        @classmethod
+        def from_dict(cls, data):
+            return cls(data["vocab_size"])
+
+    def build_toy(cfg):
+        norm = PartSpec("centred", {"width": WIDTH, "eps": EPS})
+        attention = PartSpec("gqa_attention", {"hidden_size": WIDTH, "heads": HEADS, "kv_heads": KV, "head_dim": D,
+                                               "position": PartSpec("rotary", {"head_dim": D, "theta": 100.0})}, prefix="attn.")
+        ffn = PartSpec("swiglu", {"hidden_size": WIDTH, "intermediate_size": INTER}, prefix="ffn.")
+        side = PartSpec("side_by_side", {"mixer": attention, "feed_forward": ffn, "norm": dataclasses.replace(norm, prefix="n.")})
+        pre = PartSpec("prenorm", {"mixer": attention, "feed_forward": ffn, "mixer_norm": dataclasses.replace(norm, prefix="n1."),
+                                   "feed_forward_norm": dataclasses.replace(norm, prefix="n2.")})
+        return ModelSpec(architecture="Toy4ForCausalLM", hidden_size=WIDTH, vocab_size=cfg.vocab_size, max_positions=128,
+                         embedding_name="emb.weight", layers=(BlockSpec(side, "l0."), BlockSpec(pre, "l1.")),
+                         schedule=(LayerCall(0, 0), LayerCall(1, 1)),
+                         final_norm=dataclasses.replace(norm, prefix="final."), head_name="head.weight")
+
+    register_part("norm", "centred", CenteredNorm)
+    register_part("block", "side_by_side", SideBySideBlock)
+    register_architecture(ArchitectureEntry("Toy4ForCausalLM", ToyConfig, build_toy, model_types=("toy4",)))
+    try:
+        write_random_model({"architectures": ["Toy4ForCausalLM"], "model_type": "toy4", "vocab_size": 50}, tmp_path, seed=8)
+        model = load_model(tmp_path, dtype="float32")
+        runner = make_runner(model, page_size=4, max_tokens=96, max_requests=3)
+        reqs = {"a": torch.randint(0, 50, (27,)).tolist(), "b": torch.randint(0, 50, (11,)).tolist()}
+        with torch.inference_mode():
+            whole = {k: runner.step([StepEntry(k + "w", v, list(range(len(v))))]).cpu() for k, v in reqs.items()}
+            runner.end(["aw", "bw"])
+            got = {"a": [], "b": []}
+            got["a"].append(runner.step([StepEntry("a", reqs["a"][:5], list(range(5)))]).cpu())
+            mixed = runner.step([StepEntry("b", reqs["b"][:10], list(range(10))), StepEntry("a", reqs["a"][5:6], [0])]).cpu()
+            got["b"].append(mixed[:10]), got["a"].append(mixed[10:])
+            mixed = runner.step([StepEntry("a", reqs["a"][6:], [0, 20]), StepEntry("b", reqs["b"][10:], [0])]).cpu()   # wanted rows only
+            runner.end(["a", "b"])
+        assert torch.allclose(torch.cat(got["a"]), whole["a"][:6], atol=2e-5, rtol=1e-4)
+        assert torch.allclose(mixed[:2], whole["a"][[6, 26]], atol=2e-5, rtol=1e-4)
+        assert torch.allclose(torch.cat([got["b"][0], mixed[2:]]), whole["b"], atol=2e-5, rtol=1e-4)
+        _, w = plain_llama.read_model_folder(tmp_path)
+
+        def norm(x, p):
+            centred = x - x.mean(-1, keepdim=True)
+            return centred * torch.rsqrt(centred.square().mean(-1, keepdim=True) + EPS) * w[p + "weight"] + w[p + "bias"]
+
+        def attention(n, p):
+            T = n.shape[0]
+            inv_freq = 1.0 / (100.0 ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
+            q = (n @ w[p + "attn.q_proj.weight"].T).view(T, HEADS, D).transpose(0, 1)
+            k = (n @ w[p + "attn.k_proj.weight"].T).view(T, KV, D).transpose(0, 1)
+            v = (n @ w[p + "attn.v_proj.weight"].T).view(T, KV, D).transpose(0, 1)
+            q, k = plain_llama.rotary(q, torch.arange(T), inv_freq), plain_llama.rotary(k, torch.arange(T), inv_freq)
+            return plain_llama.causal_attention(q, k, v, HEADS // KV).transpose(0, 1).reshape(T, HEADS * D) @ w[p + "attn.o_proj.weight"].T
+
+        def ffn(n, p):
+            return plain_llama.swiglu_mlp(n, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
+
+        x = w["emb.weight"][torch.tensor(reqs["a"])]
+        n = norm(x, "l0.n.")
+        x = x + attention(n, "l0.") + ffn(n, "l0.")
+        x = x + attention(norm(x, "l1.n1."), "l1.")
+        x = x + ffn(norm(x, "l1.n2."), "l1.")
+        want = norm(x, "final.") @ w["head.weight"].T
+        assert torch.allclose(whole["a"].double(), want, atol=5e-5, rtol=2e-4), (whole["a"].double() - want).abs().max()
+    finally:
+        unregister_part("norm", "centred")
+        unregister_part("block", "side_by_side")
+        unregister_architecture("Toy4ForCausalLM")
+
+
 @pytest.mark.parametrize("name", ["D", "E"])
 def test_the_native_block_call_gives_the_bits_of_the_part_by_part_sequence(model_folders, name, monkeypatch):
     """A block of the built-in parts in bfloat16 is issued as one call into the CUDA library; it must launch the
