@@ -12,7 +12,9 @@
 //     meet in distributed shared memory, as in gemm_tcgen05.cu.
 //   * warp 0 / one lane: TMA producer into a ring of stages; it requests its first ring of weights before
 //     `griddepcontrol.wait`, while the kernel before this one is still running (the weights do not depend on it).
-//     warp 1 / one lane: MMA issue and TMEM ownership.  warps 2..5: epilogue.
+//     warp 1 / one lane: MMA issue and TMEM ownership.  warps 2..5: epilogue; with tiles of 256 features four such
+//     sets of four warps (a warp reaches only its quarter of the lanes of tensor memory, so the sets share the work
+//     by accumulator and by odd and even rows): the epilogue is not overlapped with anything when a block has one tile.
 //   * Epilogues: plain (bf16 or fp32 rows), or SwiGLU: the matrix holds gate and up columns interleaved
 //     (feature 2i = gate i, 2i + 1 = up i), adjacent lanes exchange by shuffle and row i of the activation
 //     silu(gate) * up is written directly (src/torchinferno/kernels/triton_ops.py:16-68 is the reference's
@@ -25,7 +27,8 @@
 namespace tib {
 
 constexpr int kDgBK = 64;
-constexpr int kDgThreads = 192;
+__host__ __device__ constexpr int dg_epilogue_sets(int ft) { return ft == 256 ? 4 : 1; }
+__host__ __device__ constexpr int dg_threads(int ft) { return 64 + 128 * dg_epilogue_sets(ft); }
 constexpr int kDgRedRows = 136;                   // splits * ceil(128 / splits) <= 135 for up to 8 splits
 enum DecodeEpilogue : int { DG_PLAIN = 0, DG_SWIGLU = 1 };
 
@@ -44,7 +47,7 @@ constexpr int kDgMaxStages = 16;
 // decode attention after the qkv product), more where a block's whole share of a small matrix then fits the ring
 // and is on its way before the kernel before this one has ended.
 template <int NPAD, int FT, int EPI, typename TOut>
-__global__ void __launch_bounds__(kDgThreads, 1)
+__global__ void __launch_bounds__(dg_threads(FT), 1)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    TOut* __restrict__ out, int M, int N, int K, int64_t ldo, int kStages, int* __restrict__ error_word) {
   constexpr int H = FT / 128;                                              // accumulators (and MMAs per k step) of a tile
@@ -85,7 +88,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full_bar(b), 1);
-      mbar_init(acc_empty_bar(b), 4);           // one arrival per epilogue warp
+      mbar_init(acc_empty_bar(b), 4 * dg_epilogue_sets(FT));   // one arrival per epilogue warp
       mbar_init(red_full_bar(b), 4 * splits);   // one arrival per epilogue warp of every block of the cluster
       mbar_init(red_free_bar(b), 4 * splits);   // likewise, once they have summed their share of the band
     }
@@ -176,14 +179,21 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   } else {
     pdl_wait();                                        // `out` may be memory the kernel before still reads
     const int quarter = warp & 3;
-    const int et = threadIdx.x - 64;                   // 0 .. 127 among the epilogue threads
+    const int et = threadIdx.x - 64;                   // 0 .. 127 among the epilogue threads (of the one set of FT = 128)
+    // this warp's share of a tile: its quarter of the lanes of one accumulator; with four sets (FT = 256), set s takes
+    // accumulator s & 1 and the rows of x of parity s >> 1
+    constexpr int kSets = dg_epilogue_sets(FT);
+    const int set = (warp - 2) >> 2;
+    const int h = kSets > 1 ? (set & (H - 1)) : 0;
+    const int m_first = kSets > 1 ? set / H : 0;
+    constexpr int kRowStep = kSets / H;
     const int first = rank * rows_per;
     const int mine = max(0, min(rows_per, 128 - first));
     int j = 0;
     for (int t = cluster_id; t < n_tiles; t += clusters, ++j) {
       const int b = j & 1;
       const uint32_t par = (j >> 1) & 1;
-      float acc[H][NPAD];
+      float acc[NPAD];
       if (kb1 > kb0) {
         if (!mbar_wait(acc_full_bar(b), par)) {
           if (error_word && lane == 0) atomicExch(error_word, 0x7C0043);
@@ -191,45 +201,40 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
-        for (int h = 0; h < H; ++h)
+        for (int c = 0; c < NPAD / 16; ++c) {
+          uint32_t v[16];
+          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (b * H + h) * NPAD + c * 16, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-          for (int c = 0; c < NPAD / 16; ++c) {
-            uint32_t v[16];
-            tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (b * H + h) * NPAD + c * 16, v);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-            for (int q = 0; q < 16; ++q) acc[h][c * 16 + q] = __uint_as_float(v[q]);
-          }
+          for (int q = 0; q < 16; ++q) acc[c * 16 + q] = __uint_as_float(v[q]);
+        }
         asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty_bar(b));   // the MMA warp may reuse this accumulator
       } else {
 #pragma unroll
-        for (int h = 0; h < H; ++h)
-#pragma unroll
-          for (int q = 0; q < NPAD; ++q) acc[h][q] = 0.f;    // a block without k blocks adds nothing
+        for (int q = 0; q < NPAD; ++q) acc[q] = 0.f;      // a block without k blocks adds nothing
       }
       if (splits == 1) {
+        const int f = t * FT + h * 128 + quarter * 32 + lane;     // feature (column of w)
+        if constexpr (EPI == DG_SWIGLU) {
+          // even lanes hold gate i, odd lanes up i (i = f / 2): the pair meets by shuffle
 #pragma unroll
-        for (int h = 0; h < H; ++h) {
-          const int f = t * FT + h * 128 + quarter * 32 + lane;     // feature (column of w)
-          if constexpr (EPI == DG_SWIGLU) {
-            // even lanes hold gate i, odd lanes up i (i = f / 2): the pair meets by shuffle
+          for (int mm = 0; mm < NPAD; mm += kRowStep) {
+            const int m = mm + m_first;
+            if (m >= M) break;                                     // (the same for every lane)
+            const float g = kRowStep == 2 && m_first ? acc[mm + kRowStep - 1] : acc[mm];   // (row m, by constant indices)
+            const float other = __shfl_xor_sync(0xffffffffu, g, 1);
+            const float act = __fdividef(g, 1.0f + __expf(-g)) * other;
+            if (!(lane & 1) && f < N) out[(size_t)m * ldo + (f >> 1)] = from_f32<TOut>(act);
+          }
+        } else {
+          if (f < N) {
 #pragma unroll
-            for (int m = 0; m < NPAD; ++m) {
-              if (m >= M) break;                                     // (the same for every lane)
-              const float other = __shfl_xor_sync(0xffffffffu, acc[h][m], 1);
-              const float g = acc[h][m];
-              const float act = __fdividef(g, 1.0f + __expf(-g)) * other;
-              if (!(lane & 1) && f < N) out[(size_t)m * ldo + (f >> 1)] = from_f32<TOut>(act);
-            }
-          } else {
-            if (f < N) {
-#pragma unroll
-              for (int m = 0; m < NPAD; ++m) {
-                if (m >= M) break;
-                out[(size_t)m * ldo + f] = from_f32<TOut>(acc[h][m]);   // lanes = consecutive features
-              }
+            for (int mm = 0; mm < NPAD; mm += kRowStep) {
+              const int m = mm + m_first;
+              if (m >= M) break;
+              out[(size_t)m * ldo + f] = from_f32<TOut>(kRowStep == 2 && m_first ? acc[mm + kRowStep - 1] : acc[mm]);   // lanes = consecutive features
             }
           }
         }
@@ -248,7 +253,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           const uint32_t owner = f / rows_per, local = f - owner * rows_per;
           const uint32_t dst = map_to_cta(red_b + ((rank * rows_per + local) * kRedStride) * 4, owner);
 #pragma unroll
-          for (int q = 0; q < NPAD; q += 4) st_cluster_f32x4(dst + q * 4, acc[0][q], acc[0][q + 1], acc[0][q + 2], acc[0][q + 3]);
+          for (int q = 0; q < NPAD; q += 4) st_cluster_f32x4(dst + q * 4, acc[q], acc[q + 1], acc[q + 2], acc[q + 3]);
         }
         __syncwarp();
         if (lane < splits) mbar_arrive_remote(map_to_cta(red_full_bar(b), lane));   // this warp's rows are written, everywhere
@@ -307,7 +312,7 @@ static int launch_decode_gemm(const CUtensorMap& map_w, const CUtensorMap& map_x
   }
   const int tiles = ceil_div(N, FT);
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kDgThreads);
+  cfg.blockDim = dim3(dg_threads(FT));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
