@@ -71,3 +71,5 @@ def test_parts_provided_for_split_decode_attention():
     assert decode_num_splits(1, 32, 8, max_kv_len=8192) == 16 and decode_num_splits(1, 32, 8, max_kv_len=8193) == 32
     assert decode_num_splits(2, 32, 8, max_kv_len=100000) == 16          # 16 blocks of kv heads x 16 parts are 256
     assert decode_num_splits(1, 64, 2) == 16 and decode_num_splits(3, 40, 40) == 2   # groups above 16 take more row tiles
+    # a batch a little over one round of blocks (296 at once) is cut so that its last round is not nearly empty
+    assert {b: decode_num_splits(b, 32, 8) for b in (37, 38, 44, 45, 53, 54, 74, 80)} == {37: 1, 38: 3, 44: 3, 45: 2, 53: 2, 54: 1, 74: 1, 80: 1}

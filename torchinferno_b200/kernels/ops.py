@@ -408,7 +408,7 @@ def plan_product(rows: int, n: int, k: int, kn: bool, few_rows: int, features: i
 
 
 def decode_num_splits(n_entries: int, heads: int, kv_heads: int, max_kv_len: int | None = None,
-                      target_blocks: int = 256) -> int:
+                      target_blocks: int = 256, slots: int = 296) -> int:
     """How many parts the grid provides for each request's context when the kernel sizes the parts itself.
 
     Measured on the B200 at 3,072 tokens of context (32 heads, 8 kv heads of 128): the kernel is fastest
@@ -416,9 +416,20 @@ def decode_num_splits(n_entries: int, heads: int, kv_heads: int, max_kv_len: int
     8: 4, 16: 2, 32 and up: 1); more than 16 parts cost more in the merge than they gain, except where the
     context may be long (``max_kv_len`` above 8,192: one request at 32,768 tokens streams at 3.1 TB/s in 16
     parts, 128 blocks), where up to 32 are provided.  The TMA kernel uses only as many of them as the
-    request's own context has stretches of 192 keys."""
+    request's own context has stretches of 192 keys.
+
+    ``slots``: the blocks that run at once (two on each of 148 SMs).  A batch a little larger than that would run
+    one full round and a nearly empty second one; cut in two or three parts its blocks are more and shorter rounds
+    (2,100 tokens of context, 38 / 44 / 48 / 52 requests: 95 / 99 / 101 / 103 us in one part, 85 / 91 / 95 / 105 in
+    three, 89 / 94 / 95 / 99 in two; from 56 requests on, and past two rounds, one part is fastest again)."""
     group = heads // kv_heads
     blocks = max(1, n_entries * kv_heads * ((group + 15) // 16))
+    if slots < blocks < 2 * slots:
+        last_round = blocks / slots - 1            # how full the second round would be
+        if last_round <= 0.2:
+            return 3
+        if last_round <= 0.45:
+            return 2
     most = 32 if max_kv_len is not None and max_kv_len > 8192 else 16
     return max(1, min(most, target_blocks // blocks))
 
